@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-inference hot path on B200.
+
+  python bench.py --gpus N --steps K --warmup W            (this build's CUDA path)
+  python bench.py --impl reference --gpus N --steps K ...  (the reference's CPU algorithm)
+
+Headline workload: the int4 decode GEMV configuration — QuantizedLinear forward over
+resident int4 codes `[4096, 4096]` (packed, low nibble = even k) with a 1x128 f32 scale
+grid, X bf16 `[M=1, 4096]`, f32 out.  One "step" is one pass over LAYERS distinct weight
+matrices (one forward launch each); the matrices together exceed L2, so every launch
+streams its codes from HBM.  Inputs are seeded synthetic data of the stated shapes.
+
+Metric: weight GB/s = algorithmic bytes (codes + scales + X + Y) of all launches / time.
+With N > 1 every rank holds its own `[4096, 4096]` column shard of a `[4096*N, 4096]` layer
+(weak scaling) and the shards' outputs are all-gathered after every layer.
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_OUT, K_IN, GROUP = 4096, 4096, 128
+LAYERS = 32  # 32 x 8.9 MB = 286 MB of codes + scales, larger than the 126 MB L2
+METRIC = "QuantizedLinear weight GB/s (int4 decode GEMV)"
+
+
+def layer_bytes(m: int) -> int:
+    """Algorithmic bytes of one forward launch: codes N*K/2 + scales N*(K/128)*4 + X m*K*2 + Y m*N*4."""
+    return N_OUT * K_IN // 2 + N_OUT * (K_IN // GROUP) * 4 + m * K_IN * 2 + m * N_OUT * 4
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.stop, self.thread = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) >= 6:
+                    self.samples.append(f)
+            except Exception:
+                pass
+            self.stop.wait(0.1)
+
+    def __enter__(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        mhz = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": float(self.samples[0][1]),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def make_inputs(m: int, layers: int, seed: int):
+    """Seeded synthetic weights ~ N(0, 0.02) and X ~ N(0, 1) (bf16 by round-to-nearest-even)."""
+    rng = np.random.default_rng(seed)
+    w = [rng.standard_normal((N_OUT, K_IN), dtype=np.float32) * np.float32(0.02) for _ in range(layers)]
+    x = rng.standard_normal((16, K_IN), dtype=np.float32)[:m]
+    return w, x
+
+
+# ---------------------------------------------------------------------------------------
+# reference arm: the reference's CPU algorithm (dequantize the whole weight, then the
+# sequential-k f32 GEMM) on the host cores, timed on a bounded sample of the same workload
+# ---------------------------------------------------------------------------------------
+
+def cpu_forward_gbs(m: int, threads: int, layers: int, reps: int):
+    import oracle as o
+    w, x = make_inputs(m, layers, seed=1)
+    xq = o.bf16_to_f32(o.f32_to_bf16(x))
+    quant = [o.quantize_host(wi, N_OUT, K_IN, 4, 1, GROUP) for wi in w]
+    scratch = np.empty(N_OUT * K_IN, dtype=np.float32)
+    o.qlinear_apply(quant[0][0], quant[0][1], N_OUT, K_IN, 4, 1, GROUP, o.OUT_IN, xq, None, threads, scratch)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for c, s in quant:
+            o.qlinear_apply(c, s, N_OUT, K_IN, 4, 1, GROUP, o.OUT_IN, xq, None, threads, scratch)
+    dt = time.perf_counter() - t0
+    return layer_bytes(m) * layers * reps / dt / 1e9, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle as o
+    threads = o.max_threads()
+    layers = 2
+    for _ in range(max(args.warmup, 1)):
+        cpu_forward_gbs(args.m, threads, 1, 1)
+    vals, t_total = [], 0.0
+    for _ in range(args.steps):
+        v, dt = cpu_forward_gbs(args.m, threads, layers, 1)
+        vals.append(v)
+        t_total += dt
+    value = float(np.mean(vals))
+    sample = f"{layers} of {LAYERS} layers per step, dequantize + sequential-k f32 GEMM, {threads} OpenMP threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(args.steps, 1), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{args.m},{K_IN}]",
+                   "layers_per_step": layers},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+# this build's arm
+# ---------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import quanta_b200 as qb
+    from quanta_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device — this build has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    m = args.m
+    lib = _lib.load()
+    # device-side quantize-on-load of this rank's shards (seeded per rank)
+    gen = torch.Generator(device=dev).manual_seed(1 + rank)
+    layers = []
+    for _ in range(LAYERS):
+        w = torch.randn(N_OUT, K_IN, device=dev, generator=gen) * 0.02
+        qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, GROUP))
+        layers.append(qb.QuantizedLinear.new(qm, None, qb.OUT_IN))
+        del w
+    x = torch.randn(m, K_IN, device=dev, generator=gen).to(torch.bfloat16)
+    y = torch.empty(m, N_OUT, device=dev, dtype=torch.float32)
+    y_all = torch.empty(world, m, N_OUT, device=dev, dtype=torch.float32) if world > 1 else None
+    stream = torch.cuda.current_stream(dev)
+
+    def step():
+        for ql in layers:
+            st = lib.qb200_qlinear_forward(ql._h, x.data_ptr(), _lib.BF16, m, y.data_ptr(), _lib.F32, stream.cuda_stream)
+            if st:
+                raise RuntimeError(_lib.last_error())
+            if world > 1:
+                dist.all_gather_into_tensor(y_all, y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        tmax = torch.tensor([ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms = float(tmax.item())
+    launches = LAYERS * args.steps
+    total_bytes = layer_bytes(m) * launches * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+
+    # end to end through the host-buffer entry point: pinned host X in, host Y out, every launch
+    xh = torch.empty(m, K_IN, dtype=torch.bfloat16).pin_memory()
+    xh.copy_(x.cpu())
+    yh = torch.empty(m, N_OUT, dtype=torch.float32).pin_memory()
+
+    def step_host():
+        for ql in layers:
+            st = lib.qb200_qlinear_forward_host(ql._h, xh.data_ptr(), _lib.BF16, m, yh.data_ptr(), _lib.F32)
+            if st:
+                raise RuntimeError(_lib.last_error())
+
+    for _ in range(3):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = max(1, min(args.steps, 20))
+    for _ in range(e2e_steps):
+        step_host()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        tmax = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_s = float(tmax.item())
+    e2e = layer_bytes(m) * LAYERS * e2e_steps * world / e2e_s / 1e9
+
+    if rank == 0:
+        peak, which = measured_peak_gbs()
+        per_launch_s = ms * 1e-3 / launches
+        achieved = layer_bytes(m) / per_launch_s / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 x int4 -> f32", "data": "synthetic",
+            "config": {"workload": f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{m},{K_IN}], f32 out",
+                       "layers_per_step": LAYERS, "l2": "inputs larger than L2 (32 distinct weight matrices, 286 MB)",
+                       "kernel": layers[0].last_kernel(),
+                       "parallelism": "single GPU" if world == 1 else f"column-sharded x{world} + all-gather per layer"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * m * K_IN * 2,
+                    "d2h_bytes_per_step": LAYERS * m * N_OUT * 4},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": which, "launch_us": per_launch_s * 1e6},
+        }
+        if world == 1 and not args.no_cpu:
+            import oracle as o
+            threads = o.max_threads()
+            v, dt = cpu_forward_gbs(m, threads, 2, 2)
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": f"2 of {LAYERS} layers x 2 passes ({dt:.1f} s), dequantize + sequential-k "
+                                              f"f32 GEMM, {threads} OpenMP threads"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="activation rows (1, 4 or 16 for the decode configuration)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,242 @@
+/*
+ * qb200.h — C ABI of the B200-native quantized-inference path.
+ *
+ * The drop-in boundary for quanta's weight-only int8/int4 path
+ * (`quanta::sci::quant` / `quanta::nn::quant`): QuantizedMatrix quantize /
+ * dequantize, QuantizedLinear forward over resident codes with a 2-D scale
+ * grid, and the quantized-safetensors byte layout.  Each entry point names the
+ * reference interface it replaces (path within the reference project : line).
+ *
+ * Conventions
+ *   - Every function returns a qb200_status (0 = OK).  On failure a
+ *     self-contained message naming the offender is kept per host thread and
+ *     read back with qb200_last_error(); its wording carries the reference's
+ *     message substrings (crates/sci/quanta-array/src/quant.rs:235-265).
+ *   - `*_dev` pointers are device pointers on the current CUDA device.  Device
+ *     work is asynchronous on the caller's stream (a cudaStream_t passed as
+ *     void*; NULL = the legacy default stream) unless the name ends in `_host`
+ *     or `_sync`.
+ *   - No entry point falls back to the CPU: without a usable CUDA device the
+ *     device entry points return QB200_ERR_CUDA.
+ *   - Matrices are rank-2 `[rows, cols]`, row-major.  Scale grid: tile
+ *     `(gr, gc)`, scales `[ceil(rows/gr), ceil(cols/gc)]` f32 row-major, the
+ *     scale of element (r, c) is scales[(r/gr)*ceil(cols/gc) + c/gc]
+ *     (crates/sci/quanta-array/src/quant.rs:4-8).
+ *   - Codes: bits = 8 -> int8, one byte per element `[rows, cols]`;
+ *     bits = 4 -> uint32 words `[rows, ceil(cols/8)]`, 8 nibbles per word, low
+ *     nibble first, every row starts a fresh word, pad nibbles zero
+ *     (crates/sci/quanta-array/src/quant.rs:27-30).
+ *   - Handles are not thread-safe; distinct handles are independent.
+ */
+#ifndef QB200_H
+#define QB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define QB200_API __attribute__((visibility("default")))
+#else
+#define QB200_API
+#endif
+
+typedef int32_t qb200_status;
+
+/* Status codes.  1..6 mirror the arms of QuantError
+ * (crates/sci/quanta-array/src/quant.rs:210-233); 7 is
+ * ArrayError::LengthMismatch; 8 is QuantaError::invalid_param. */
+enum {
+    QB200_OK = 0,
+    QB200_ERR_RANK = 1,
+    QB200_ERR_GRANULARITY = 2,
+    QB200_ERR_GRID = 3,
+    QB200_ERR_FORMAT = 4,
+    QB200_ERR_NOT_SUPPORTED = 5,
+    QB200_ERR_SCALE = 6,
+    QB200_ERR_LENGTH = 7,
+    QB200_ERR_INVALID_PARAM = 8,
+    QB200_ERR_CUDA = 9,
+    QB200_ERR_NCCL = 10,
+    QB200_ERR_TIMEOUT = 11
+};
+
+/* Granularity spellings (crates/sci/quanta-array/src/quant.rs:94-104).
+ * BLOCK{rows, cols} is an additive arm: the reference's arithmetic takes any
+ * (gr, gc) but its enum cannot spell a 2-D block such as 32x32. */
+enum { QB200_PER_TENSOR = 0, QB200_PER_CHANNEL = 1, QB200_GROUP = 2, QB200_BLOCK = 3 };
+
+/* Weight orientation of a QuantizedLinear.
+ * IN_OUT: the matrix is `[in, out]`, y = x @ deq(w)  (the reference's Linear,
+ *         crates/ml/quanta-nn/src/quant.rs:820-835).
+ * OUT_IN: the matrix is `[out, in]`, y = x @ deq(w)^T (K-contiguous rows). */
+enum { QB200_IN_OUT = 0, QB200_OUT_IN = 1 };
+
+/* Activation / output element types. */
+enum { QB200_F32 = 0, QB200_BF16 = 1, QB200_F16 = 2 };
+
+/* ---- library ------------------------------------------------------------ */
+
+/* "major.minor.patch" of this library. */
+QB200_API const char* qb200_version(void);
+
+/* Copies the calling thread's last error message (NUL-terminated, truncated to
+ * cap) and returns its full length.  Replaces Display for QuantError /
+ * ArrayError (crates/sci/quanta-array/src/quant.rs:235-265). */
+QB200_API size_t qb200_last_error(char* buf, size_t cap);
+
+/* Number of CUDA devices visible (0 when none / no driver). */
+QB200_API int32_t qb200_device_count(void);
+
+/* ---- grid vocabulary (host only) --------------------------------------- */
+
+/* Granularity::tile — spelling -> (gr, gc)
+ * (crates/sci/quanta-array/src/quant.rs:109-144).  size is Group's size or
+ * Block's rows; size2 is Block's cols. */
+QB200_API qb200_status qb200_tile(int32_t kind, uint64_t axis, uint64_t size, uint64_t size2, uint64_t rows,
+                        uint64_t cols, uint64_t* gr, uint64_t* gc);
+
+/* granularity_from_grid — canonical spelling of a stored grid, precedence
+ * PerTensor > PerChannel > Group (crates/ml/quanta-nn/src/quant.rs:119-145).
+ * Returns QB200_ERR_FORMAT for a grid no v1 writer produces unless
+ * allow_block is non-zero (then kind = QB200_BLOCK). */
+QB200_API qb200_status qb200_granularity_from_grid(uint64_t rows, uint64_t cols, uint64_t gr, uint64_t gc,
+                                         int32_t allow_block, int32_t* kind, uint64_t* axis,
+                                         uint64_t* size, uint64_t* size2);
+
+/* Byte size of the codes payload and element count of the scale grid. */
+QB200_API qb200_status qb200_codes_bytes(uint64_t rows, uint64_t cols, uint32_t bits, uint64_t* bytes);
+QB200_API qb200_status qb200_scales_count(uint64_t rows, uint64_t cols, uint64_t gr, uint64_t gc,
+                                uint64_t* tile_rows, uint64_t* tile_cols);
+
+/* QuantizedMatrix::from_parts validation: codes / scales element counts
+ * against the logical shape and grid
+ * (crates/sci/quanta-array/src/quant.rs:521-568). */
+QB200_API qb200_status qb200_check_parts(uint64_t codes_rows, uint64_t codes_cols, uint64_t scales_rows,
+                               uint64_t scales_cols, uint64_t rows, uint64_t cols, uint32_t bits,
+                               uint64_t gr, uint64_t gc);
+
+/* ---- quantize / dequantize on the device ------------------------------- */
+
+/* QuantizedMatrix::quantize + quantize_host: per-tile max-abs -> s = m/hi ->
+ * clamp(round_ties_even(w/s)) -> pack
+ * (crates/sci/quanta-array/src/quant.rs:293-367, 480-513).  The reference runs
+ * this loop on one host thread over a device read-back; here it is one pass
+ * over HBM.  src_dtype is the element type of w_dev (F32 exact; BF16 / F16
+ * are widened exactly first, crates/ml/quanta-nn/src/safetensors.rs:497-551).
+ * Bit-exact codes and scales. */
+QB200_API qb200_status qb200_quantize(const void* w_dev, int32_t src_dtype, uint64_t rows, uint64_t cols,
+                            uint32_t bits, uint64_t gr, uint64_t gc, void* codes_dev,
+                            float* scales_dev, void* stream);
+
+/* QuantizedMatrix::dequantize / dequantize_host: out[r,c] = s * f32(q)
+ * (crates/sci/quanta-array/src/quant.rs:373-413, 605-752).  Bit-exact. */
+QB200_API qb200_status qb200_dequantize(const void* codes_dev, const float* scales_dev, uint64_t rows,
+                              uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc,
+                              float* out_dev, void* stream);
+
+/* ---- QuantizedLinear ---------------------------------------------------- */
+
+typedef struct qb200_qlinear qb200_qlinear;
+
+/* QuantizedLinear::new (Mode B, resident codes)
+ * (crates/ml/quanta-nn/src/quant.rs:853-862).  Borrows the caller's device
+ * buffers (codes, scales, optional f32 bias of out_dim elements): they must
+ * outlive the handle.  bias_len is the bias element count (checked against
+ * out_dim like check_bias, quant.rs:838-848); pass bias_dev = NULL for none. */
+QB200_API qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev, uint64_t rows,
+                                  uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc,
+                                  int32_t layout, const float* bias_dev, uint64_t bias_len,
+                                  qb200_qlinear** out);
+QB200_API void qb200_qlinear_destroy(qb200_qlinear* ql);
+
+/* Layer::in_dim / Layer::out_dim (crates/ml/quanta-nn/src/quant.rs:882-887). */
+QB200_API uint64_t qb200_qlinear_in_dim(const qb200_qlinear* ql);
+QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
+
+/* Layer::apply without the tape — y = x @ deq(w) (+ b), fused: the f32 weight
+ * is never materialised (crates/ml/quanta-nn/src/quant.rs:892-918, the
+ * "INTEGRATOR SEAM").  x is `[m, in_dim]` of x_dtype, y is `[m, out_dim]` of
+ * y_dtype, both device, row-major.  f32 accumulation. */
+QB200_API qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype,
+                                   uint64_t m, void* y_dev, int32_t y_dtype, void* stream);
+
+/* The same call over HOST buffers: copies x to the device, runs the forward,
+ * copies y back and synchronises.  Staging buffers are owned by the handle
+ * and grow on demand. */
+QB200_API qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, int32_t x_dtype,
+                                        uint64_t m, void* y_host, int32_t y_dtype);
+
+/* Name of the kernel family the last forward on this handle dispatched to
+ * ("gemv_mma", "gemm_tcgen05", "generic_rows", "generic_cols"). */
+QB200_API const char* qb200_qlinear_last_kernel(const qb200_qlinear* ql);
+
+/* ---- quantized-safetensors (host bytes in, host bytes out) -------------- */
+
+typedef struct qb200_st_file qb200_st_file;
+typedef struct qb200_st_writer qb200_st_writer;
+
+/* One validated leaf in header order. */
+typedef struct {
+    const char* name;      /* leaf name (quantized: without the .q / .qs suffix) */
+    int32_t quantized;     /* 0 = plain tensor, 1 = quantized leaf                */
+    const char* dtype;     /* plain: "F32" / "F16" / "BF16"; quantized: "I8"/"U32" */
+    uint32_t ndim;         /* plain: rank; quantized: 2                            */
+    const uint64_t* shape; /* plain: tensor shape; quantized: logical [rows, cols] */
+    uint64_t data_offset;  /* byte offset of the tensor / codes in the input bytes */
+    uint64_t data_len;
+    uint32_t bits;         /* quantized only: 8 / 4                                */
+    uint64_t gr, gc;       /* quantized only                                       */
+    uint64_t scales_offset; /* quantized only: F32 scale grid in the input bytes   */
+    uint64_t scales_len;
+    int32_t gran_kind;     /* canonical granularity spelling of the grid           */
+    uint64_t gran_axis, gran_size, gran_size2;
+} qb200_st_item;
+
+/* validate(): container parse, version gate and total per-leaf validation
+ * before anything is interpreted (crates/ml/quanta-nn/src/quant.rs:420-635,
+ * crates/ml/quanta-nn/src/safetensors.rs:398-492).  bytes must stay alive
+ * while the handle is used.  allow_block admits 2-D block grids. */
+QB200_API qb200_status qb200_st_validate(const uint8_t* bytes, uint64_t len, int32_t allow_block,
+                               qb200_st_file** out);
+QB200_API void qb200_st_free(qb200_st_file* f);
+QB200_API uint64_t qb200_st_num_items(const qb200_st_file* f);
+QB200_API qb200_status qb200_st_item_at(const qb200_st_file* f, uint64_t i, qb200_st_item* out);
+/* User metadata (the quant:* entries and the version key are stripped). */
+QB200_API uint64_t qb200_st_num_metadata(const qb200_st_file* f);
+QB200_API qb200_status qb200_st_metadata_at(const qb200_st_file* f, uint64_t i, const char** key,
+                                  const char** value);
+
+/* entry_to_f32 on the host: widen a plain F32 / F16 / BF16 tensor to f32
+ * (crates/ml/quanta-nn/src/safetensors.rs:497-551).  out holds count f32. */
+QB200_API qb200_status qb200_st_plain_to_f32(const qb200_st_file* f, uint64_t i, float* out, uint64_t count);
+
+/* save_named(): leaves in the given order, metadata keys sorted, the version
+ * key and quant:<leaf> entries synthesised
+ * (crates/ml/quanta-nn/src/quant.rs:279-390,
+ * crates/ml/quanta-nn/src/safetensors.rs:72-125). */
+QB200_API qb200_status qb200_st_writer_create(qb200_st_writer** out);
+QB200_API void qb200_st_writer_free(qb200_st_writer* w);
+/* has_metadata: the caller passed Some(map) even when it is empty. */
+QB200_API qb200_status qb200_st_writer_set_has_metadata(qb200_st_writer* w, int32_t has_metadata);
+QB200_API qb200_status qb200_st_writer_add_metadata(qb200_st_writer* w, const char* key, const char* value);
+QB200_API qb200_status qb200_st_writer_add_f32(qb200_st_writer* w, const char* name, const uint64_t* shape,
+                                     uint32_t ndim, const float* data);
+QB200_API qb200_status qb200_st_writer_add_quantized(qb200_st_writer* w, const char* name, uint32_t bits,
+                                           uint64_t rows, uint64_t cols, uint64_t gr, uint64_t gc,
+                                           const void* codes, const float* scales);
+/* Serialises; the returned bytes belong to the writer until it is freed. */
+QB200_API qb200_status qb200_st_writer_finish(qb200_st_writer* w, const uint8_t** bytes, uint64_t* len);
+
+/* parse_quant_meta(): the `quant:<leaf>` value grammar
+ * (crates/ml/quanta-nn/src/quant.rs:211-271). */
+QB200_API qb200_status qb200_st_parse_quant_meta(const char* leaf, const char* value, uint32_t* bits,
+                                       uint64_t* gr, uint64_t* gc, uint64_t* rows, uint64_t* cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QB200_H */

@@ -1,0 +1,252 @@
+// QuantizedLinear forward, generic kernels: every dtype, every scale grid, both
+// weight orientations, f32 or bf16 activations.  The f32 weight is never
+// materialised: codes are unpacked and scaled in registers and accumulated in
+// f32 (the reference dequantizes the whole matrix to f32 and then runs an f32
+// GEMM, crates/ml/quanta-nn/src/quant.rs:903-918).
+//
+//   rows kernel  (OUT_IN, W `[out, in]`): one warp per output feature, lanes
+//                stride over 8-code chunks of K, shuffle reduction.
+//   cols kernel  (IN_OUT, W `[in, out]`, the reference's Linear orientation):
+//                each thread owns 8 adjacent output features and streams down
+//                K (coalesced along N); K is split across warps and, for small
+//                N, across CTAs — partial sums go to a scratch buffer and a
+//                second kernel folds them, adds the bias and casts.
+#include <cstdint>
+
+#include "forward.hpp"
+#include "quant_math.cuh"
+
+namespace qb {
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<uint16_t>(uint16_t v) { return bf16_bits_to_f32(v); }
+
+template <typename T>
+__device__ __forceinline__ void store_out(T* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<uint16_t>(uint16_t* p, float v) { *p = f32_to_bf16_bits(v); }
+
+template <int BITS>
+__device__ __forceinline__ int code_at(const void* codes, uint64_t row, uint64_t col, uint64_t cols, uint64_t wpr) {
+    if constexpr (BITS == 4)
+        return int4_unpack(static_cast<const uint32_t*>(codes)[row * wpr + (col >> 3)], (uint32_t)(col & 7));
+    else
+        return (int)static_cast<const int8_t*>(codes)[row * cols + col];
+}
+
+// ---- OUT_IN: warp per output feature ---------------------------------------
+
+template <int BITS, typename XT, typename YT, int MT>
+__global__ void __launch_bounds__(256) k_forward_rows(FwdArgs a) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t n = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= a.out_dim) return;  // whole warp exits together
+    const uint64_t K = a.in_dim, wpr = (K + 7) >> 3, tc = a.tc;
+    const XT* x = static_cast<const XT*>(a.x);
+    const uint64_t srow = (n / a.gr) * tc;
+    const bool chunk_scale = (a.gc & 7u) == 0;
+    for (uint64_t m0 = (uint64_t)blockIdx.y * MT; m0 < a.m; m0 += (uint64_t)gridDim.y * MT) {
+        float acc[MT];
+#pragma unroll
+        for (int i = 0; i < MT; i++) acc[i] = 0.0f;
+        for (uint64_t ch = lane; ch < wpr; ch += 32) {
+            const uint64_t k0 = ch << 3;
+            int q[8];
+            if constexpr (BITS == 4) {
+                uint32_t word = __ldg(static_cast<const uint32_t*>(a.codes) + n * wpr + ch);
+#pragma unroll
+                for (int j = 0; j < 8; j++) q[j] = int4_unpack(word, j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    q[j] = (k0 + j < K) ? (int)__ldg(static_cast<const int8_t*>(a.codes) + n * K + k0 + j) : 0;
+            }
+            float wv[8];
+            if (chunk_scale) {
+                float s = __ldg(a.scales + srow + k0 / a.gc);
+#pragma unroll
+                for (int j = 0; j < 8; j++) wv[j] = s * (float)q[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    uint64_t k = k0 + j;
+                    wv[j] = k < K ? __ldg(a.scales + srow + k / a.gc) * (float)q[j] : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+                if (m0 + i < a.m) {
+                    const XT* xr = x + (m0 + i) * K + k0;
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        if (k0 + j < K) acc[i] = fmaf(to_f32<XT>(xr[j]), wv[j], acc[i]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MT; i++) {
+            float v = acc[i];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+            if (lane == 0 && m0 + i < a.m) {
+                if (a.bias) v += a.bias[n];
+                store_out<YT>(static_cast<YT*>(a.y) + (m0 + i) * a.out_dim + n, v);
+            }
+        }
+    }
+}
+
+// ---- IN_OUT: thread per 8 output features, streaming down K ------------------
+
+constexpr int COLS_WARPS = 8;
+constexpr int COLS_MT = 4;
+
+// grid: x = column blocks of 256, y = K slices, z = m tiles of COLS_MT.
+// Writes y directly when gridDim.y == 1, else f32 partials `[slice, m, out]`.
+template <int BITS, typename XT, typename YT>
+__global__ void __launch_bounds__(32 * COLS_WARPS) k_forward_cols(FwdArgs a, float* __restrict__ partial) {
+    __shared__ float red[COLS_WARPS][COLS_MT][256 + 8];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint64_t N = a.out_dim, K = a.in_dim, wpr = (N + 7) >> 3, tc = a.tc;
+    const uint64_t n0 = ((uint64_t)blockIdx.x * 32 + lane) << 3;
+    const uint64_t m0 = (uint64_t)blockIdx.z * COLS_MT;
+    const uint64_t kper = (K + gridDim.y - 1) / gridDim.y;
+    const uint64_t kbeg = (uint64_t)blockIdx.y * kper, kend = min(K, kbeg + kper);
+    const XT* x = static_cast<const XT*>(a.x);
+    const bool chunk_scale = (a.gc & 7u) == 0;
+
+    float acc[COLS_MT][8];
+#pragma unroll
+    for (int i = 0; i < COLS_MT; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+    if (n0 < N) {
+        for (uint64_t k = kbeg + warp; k < kend; k += COLS_WARPS) {
+            int q[8];
+            if constexpr (BITS == 4) {
+                uint32_t word = __ldg(static_cast<const uint32_t*>(a.codes) + k * wpr + (n0 >> 3));
+#pragma unroll
+                for (int j = 0; j < 8; j++) q[j] = int4_unpack(word, j);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    q[j] = (n0 + j < N) ? (int)__ldg(static_cast<const int8_t*>(a.codes) + k * N + n0 + j) : 0;
+            }
+            const uint64_t srow = (k / a.gr) * tc;
+            float wv[8];
+            if (chunk_scale) {
+                float s = __ldg(a.scales + srow + n0 / a.gc);
+#pragma unroll
+                for (int j = 0; j < 8; j++) wv[j] = s * (float)q[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    wv[j] = (n0 + j < N) ? __ldg(a.scales + srow + (n0 + j) / a.gc) * (float)q[j] : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < COLS_MT; i++) {
+                if (m0 + i < a.m) {
+                    float xv = to_f32<XT>(__ldg(x + (m0 + i) * K + k));
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[i][j] = fmaf(xv, wv[j], acc[i][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < COLS_MT; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) red[warp][i][lane * 8 + j] = acc[i][j];
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < COLS_MT * 256; e += blockDim.x) {
+        const uint32_t i = e >> 8, c = e & 255u;
+        const uint64_t n = (uint64_t)blockIdx.x * 256 + c;
+        if (n >= N || m0 + i >= a.m) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < COLS_WARPS; w++) v += red[w][i][c];
+        if (gridDim.y == 1) {
+            if (a.bias) v += a.bias[n];
+            store_out<YT>(static_cast<YT*>(a.y) + (m0 + i) * N + n, v);
+        } else {
+            partial[((uint64_t)blockIdx.y * a.m + (m0 + i)) * N + n] = v;
+        }
+    }
+}
+
+template <typename YT>
+__global__ void k_fold_partials(const float* __restrict__ partial, uint32_t slices, uint64_t m, uint64_t N,
+                                const float* __restrict__ bias, YT* __restrict__ y) {
+    const uint64_t total = m * N;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        float v = 0.0f;
+        for (uint32_t s = 0; s < slices; s++) v += partial[(uint64_t)s * total + i];
+        if (bias) v += bias[i % N];
+        store_out<YT>(y + i, v);
+    }
+}
+
+// ---- launchers ----------------------------------------------------------------
+
+template <int BITS, typename XT, typename YT>
+static qb200_status launch_rows(const FwdArgs& a, cudaStream_t st) {
+    const uint32_t warps = 8;
+    dim3 grid((uint32_t)div_ceil(a.out_dim, warps), 1);
+    if (a.m <= 1) k_forward_rows<BITS, XT, YT, 1><<<grid, warps * 32, 0, st>>>(a);
+    else if (a.m <= 2) k_forward_rows<BITS, XT, YT, 2><<<grid, warps * 32, 0, st>>>(a);
+    else if (a.m <= 4) k_forward_rows<BITS, XT, YT, 4><<<grid, warps * 32, 0, st>>>(a);
+    else {
+        grid.y = (uint32_t)(div_ceil(a.m, 8) > 64 ? 64 : div_ceil(a.m, 8));
+        k_forward_rows<BITS, XT, YT, 8><<<grid, warps * 32, 0, st>>>(a);
+    }
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+uint32_t forward_cols_slices(uint64_t in_dim, uint64_t out_dim, uint64_t m) {
+    const uint64_t ctas = div_ceil(out_dim, 256) * div_ceil(m, COLS_MT);
+    uint64_t s = 1;
+    while (ctas * s < 296 && in_dim / (s * 2) >= 64 && s < 64) s *= 2;
+    return (uint32_t)s;
+}
+
+template <int BITS, typename XT, typename YT>
+static qb200_status launch_cols(const FwdArgs& a, float* scratch, uint32_t slices, cudaStream_t st) {
+    dim3 grid((uint32_t)div_ceil(a.out_dim, 256), slices, (uint32_t)div_ceil(a.m, COLS_MT));
+    if (grid.z > 65535) return fail(QB200_ERR_INVALID_PARAM, "forward: m too large for the column kernel");
+    k_forward_cols<BITS, XT, YT><<<grid, 32 * COLS_WARPS, 0, st>>>(a, scratch);
+    QB_CUDA_TRY(cudaGetLastError());
+    if (slices > 1) {
+        uint64_t total = a.m * a.out_dim;
+        uint32_t blocks = (uint32_t)(div_ceil(total, 256) > 148 * 16 ? 148 * 16 : div_ceil(total, 256));
+        k_fold_partials<YT><<<blocks, 256, 0, st>>>(scratch, slices, a.m, a.out_dim, a.bias, static_cast<YT*>(a.y));
+        QB_CUDA_TRY(cudaGetLastError());
+    }
+    return QB200_OK;
+}
+
+template <int BITS, typename XT>
+static qb200_status by_out(const FwdArgs& a, int y_dtype, bool rows, float* scratch, uint32_t slices, cudaStream_t st) {
+    if (y_dtype == QB200_F32)
+        return rows ? launch_rows<BITS, XT, float>(a, st) : launch_cols<BITS, XT, float>(a, scratch, slices, st);
+    return rows ? launch_rows<BITS, XT, uint16_t>(a, st) : launch_cols<BITS, XT, uint16_t>(a, scratch, slices, st);
+}
+
+qb200_status forward_generic(const FwdArgs& a, uint32_t bits, int x_dtype, int y_dtype, bool rows_kernel,
+                             float* scratch, uint32_t slices, cudaStream_t st) {
+    if (bits == 4) {
+        return x_dtype == QB200_F32 ? by_out<4, float>(a, y_dtype, rows_kernel, scratch, slices, st)
+                                    : by_out<4, uint16_t>(a, y_dtype, rows_kernel, scratch, slices, st);
+    }
+    return x_dtype == QB200_F32 ? by_out<8, float>(a, y_dtype, rows_kernel, scratch, slices, st)
+                                : by_out<8, uint16_t>(a, y_dtype, rows_kernel, scratch, slices, st);
+}
+
+}  // namespace qb

@@ -1,0 +1,152 @@
+// The QuantizedLinear handle: validation at construction (the reference's
+// QuantizedLinear::new, crates/ml/quanta-nn/src/quant.rs:853-862) and kernel
+// selection per forward (the body of Layer::apply, quant.rs:903-918).
+#include <cstring>
+#include <string>
+
+#include "forward.hpp"
+
+struct qb200_qlinear {
+    const void* codes = nullptr;
+    const float* scales = nullptr;
+    const float* bias = nullptr;
+    uint64_t rows = 0, cols = 0, gr = 0, gc = 0, tc = 0;
+    uint32_t bits = 0;
+    int32_t layout = QB200_IN_OUT;
+    uint64_t in_dim = 0, out_dim = 0;
+    // split-K partial sums of the column kernel (grow-only)
+    float* scratch = nullptr;
+    uint64_t scratch_bytes = 0;
+    // device staging for the host-buffer entry point (grow-only)
+    void* x_stage = nullptr;
+    void* y_stage = nullptr;
+    uint64_t x_stage_bytes = 0, y_stage_bytes = 0;
+    cudaStream_t host_stream = nullptr;
+    const char* last_kernel = "";
+};
+
+using qb::fail;
+
+namespace {
+
+uint64_t dtype_size(int32_t dt) { return dt == QB200_F32 ? 4 : 2; }
+
+qb200_status grow(void** p, uint64_t* have, uint64_t need) {
+    if (*have >= need) return QB200_OK;
+    if (*p) QB_CUDA_TRY(cudaFree(*p));
+    *p = nullptr;
+    *have = 0;
+    QB_CUDA_TRY(cudaMalloc(p, need));
+    *have = need;
+    return QB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev, uint64_t rows, uint64_t cols,
+                                  uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, const float* bias_dev,
+                                  uint64_t bias_len, qb200_qlinear** out) {
+    if (!out) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_create: null output pointer");
+    *out = nullptr;
+    uint64_t tr, tc, cbytes;
+    if (qb200_status s = qb200_codes_bytes(rows, cols, bits, &cbytes)) return s;
+    if (qb200_status s = qb200_scales_count(rows, cols, gr, gc, &tr, &tc)) return s;
+    if (layout != QB200_IN_OUT && layout != QB200_OUT_IN)
+        return fail(QB200_ERR_INVALID_PARAM, "QuantizedLinear: unknown weight layout " + std::to_string(layout));
+    if (!codes_dev || !scales_dev) return fail(QB200_ERR_INVALID_PARAM, "QuantizedLinear: null codes or scales pointer");
+    const uint64_t in_dim = layout == QB200_IN_OUT ? rows : cols;
+    const uint64_t out_dim = layout == QB200_IN_OUT ? cols : rows;
+    if (bias_dev && bias_len != out_dim)
+        return fail(QB200_ERR_INVALID_PARAM, "QuantizedLinear: bias shape [" + std::to_string(bias_len) +
+                                                 "], weight [in, " + std::to_string(out_dim) + "] wants [" +
+                                                 std::to_string(out_dim) + "]");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        return fail(QB200_ERR_CUDA, "QuantizedLinear: no CUDA device is available (this library has no CPU path)");
+    }
+    auto* ql = new qb200_qlinear();
+    ql->codes = codes_dev;
+    ql->scales = scales_dev;
+    ql->bias = bias_dev;
+    ql->rows = rows;
+    ql->cols = cols;
+    ql->gr = gr;
+    ql->gc = gc;
+    ql->tc = tc;
+    ql->bits = bits;
+    ql->layout = layout;
+    ql->in_dim = in_dim;
+    ql->out_dim = out_dim;
+    *out = ql;
+    return QB200_OK;
+}
+
+void qb200_qlinear_destroy(qb200_qlinear* ql) {
+    if (!ql) return;
+    if (ql->scratch) cudaFree(ql->scratch);
+    if (ql->x_stage) cudaFree(ql->x_stage);
+    if (ql->y_stage) cudaFree(ql->y_stage);
+    if (ql->host_stream) cudaStreamDestroy(ql->host_stream);
+    delete ql;
+}
+
+uint64_t qb200_qlinear_in_dim(const qb200_qlinear* ql) { return ql ? ql->in_dim : 0; }
+uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql) { return ql ? ql->out_dim : 0; }
+const char* qb200_qlinear_last_kernel(const qb200_qlinear* ql) { return ql ? ql->last_kernel : ""; }
+
+qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype, uint64_t m, void* y_dev,
+                                   int32_t y_dtype, void* stream) {
+    if (!ql) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward: null handle");
+    if (!x_dev || !y_dev) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward: null device pointer");
+    if ((x_dtype != QB200_F32 && x_dtype != QB200_BF16) || (y_dtype != QB200_F32 && y_dtype != QB200_BF16))
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward: activations are f32 or bf16");
+    if (m == 0) return QB200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    qb::FwdArgs a;
+    a.codes = ql->codes;
+    a.scales = ql->scales;
+    a.bias = ql->bias;
+    a.x = x_dev;
+    a.y = y_dev;
+    a.m = m;
+    a.in_dim = ql->in_dim;
+    a.out_dim = ql->out_dim;
+    a.gr = ql->gr;
+    a.gc = ql->gc;
+    a.tc = ql->tc;
+    if (ql->layout == QB200_OUT_IN) {
+        ql->last_kernel = "generic_rows";
+        return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, true, nullptr, 1, st);
+    }
+    const uint32_t slices = qb::forward_cols_slices(ql->in_dim, ql->out_dim, m);
+    if (slices > 1) {
+        void* p = ql->scratch;
+        qb200_status s = grow(&p, &ql->scratch_bytes, (uint64_t)slices * m * ql->out_dim * sizeof(float));
+        ql->scratch = static_cast<float*>(p);
+        if (s) return s;
+    }
+    ql->last_kernel = "generic_cols";
+    return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, false, ql->scratch, slices, st);
+}
+
+qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, int32_t x_dtype, uint64_t m,
+                                        void* y_host, int32_t y_dtype) {
+    if (!ql) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_host: null handle");
+    if (!x_host || !y_host) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_host: null host pointer");
+    if (m == 0) return QB200_OK;
+    const uint64_t xb = m * ql->in_dim * dtype_size(x_dtype), yb = m * ql->out_dim * dtype_size(y_dtype);
+    if (qb200_status s = grow(&ql->x_stage, &ql->x_stage_bytes, xb)) return s;
+    if (qb200_status s = grow(&ql->y_stage, &ql->y_stage_bytes, yb)) return s;
+    if (!ql->host_stream) QB_CUDA_TRY(cudaStreamCreateWithFlags(&ql->host_stream, cudaStreamNonBlocking));
+    QB_CUDA_TRY(cudaMemcpyAsync(ql->x_stage, x_host, xb, cudaMemcpyHostToDevice, ql->host_stream));
+    if (qb200_status s = qb200_qlinear_forward(ql, ql->x_stage, x_dtype, m, ql->y_stage, y_dtype, ql->host_stream))
+        return s;
+    QB_CUDA_TRY(cudaMemcpyAsync(y_host, ql->y_stage, yb, cudaMemcpyDeviceToHost, ql->host_stream));
+    QB_CUDA_TRY(cudaStreamSynchronize(ql->host_stream));
+    return QB200_OK;
+}
+
+}  // extern "C"

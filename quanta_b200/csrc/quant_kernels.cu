@@ -1,0 +1,365 @@
+// Quantize-on-load and dequantize: the two bandwidth kernels of the path.
+//
+// quantize  : per-tile max-abs -> s = m / hi -> clamp(rte(w / s)) -> pack
+//             (reference: crates/sci/quanta-array/src/quant.rs:293-367, a
+//             single-threaded host loop over a device read-back).
+// dequantize: out[r, c] = s * f32(q)
+//             (reference: crates/sci/quanta-array/src/quant.rs:373-413, 639-752).
+//
+// Data layout in HBM: W `[rows, cols]` row-major (f32 / bf16 / f16); codes int8
+// `[rows, cols]` or packed int4 `[rows, ceil(cols/8)]` u32 words; scales f32
+// `[ceil(rows/gr), ceil(cols/gc)]`.
+//
+// The tile kernel reads every weight exactly once: a sub-warp group of G lanes
+// owns one tile, keeps its 8-element chunks in registers, reduces the max with
+// shuffles and writes codes as whole words.  Tiles that do not fit the register
+// budget, or matrices whose rows are not 8-element aligned, take the three-pass
+// generic path (bit-pattern atomicMax into the scale grid, finalize, encode).
+#include <cstdint>
+#include <string>
+
+#include "common.hpp"
+#include "quant_math.cuh"
+
+namespace qb {
+
+enum SrcType { SRC_F32 = 0, SRC_BF16 = 1, SRC_F16 = 2 };
+
+// ---- 8-element chunk loads --------------------------------------------------
+
+template <int SRC>
+__device__ __forceinline__ void load_chunk8(const void* base, uint64_t elem, float (&v)[8]) {
+    if constexpr (SRC == SRC_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
+        float4 a = __ldcs(p), b = __ldcs(p + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem);
+        uint4 a = __ldcs(p);
+        uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if constexpr (SRC == SRC_BF16) {
+                v[2 * i] = bf16_bits_to_f32(w[i] & 0xFFFFu);
+                v[2 * i + 1] = bf16_bits_to_f32(w[i] >> 16);
+            } else {
+                v[2 * i] = half_bits_to_f32((uint16_t)(w[i] & 0xFFFFu));
+                v[2 * i + 1] = half_bits_to_f32((uint16_t)(w[i] >> 16));
+            }
+        }
+    }
+}
+
+template <int SRC>
+__device__ __forceinline__ float load_elem(const void* base, uint64_t i) {
+    if constexpr (SRC == SRC_F32) return static_cast<const float*>(base)[i];
+    uint16_t h = static_cast<const uint16_t*>(base)[i];
+    if constexpr (SRC == SRC_BF16) return bf16_bits_to_f32(h);
+    return half_bits_to_f32(h);
+}
+
+// ---- the single-pass tile kernel ------------------------------------------
+
+struct TileGeom {
+    uint64_t rows, cols;      // matrix
+    uint32_t gr, gc;          // tile
+    uint64_t tr, tc;          // scale grid
+    uint32_t chunks_per_row;  // gc / 8
+    uint32_t chunks;          // gr * gc / 8 chunks per tile
+    uint32_t lanes;           // G: lanes per tile (power of two <= 32)
+};
+
+// CPL: chunks per lane (ceil(chunks / lanes)).  One group of `lanes` lanes
+// quantizes one tile; a warp holds 32 / lanes groups.
+template <int SRC, int BITS, int CPL>
+__global__ void __launch_bounds__(256) k_quantize_tiles(const void* __restrict__ w, TileGeom g,
+                                                        void* __restrict__ codes,
+                                                        float* __restrict__ scales) {
+    constexpr int HI = BITS == 8 ? 127 : 7;
+    constexpr int LO = -HI - 1;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t sub = lane & (g.lanes - 1u);
+    const uint64_t groups_per_block = blockDim.x / g.lanes;
+    const uint64_t tile = (uint64_t)blockIdx.x * groups_per_block + threadIdx.x / g.lanes;
+    const bool tile_ok = tile < g.tr * g.tc;
+    const uint64_t t_r = tile_ok ? tile / g.tc : 0, t_c = tile_ok ? tile % g.tc : 0;
+    const uint64_t r0 = t_r * g.gr, c0 = t_c * g.gc;
+
+    float v[CPL][8];
+    bool ok[CPL];
+    uint64_t pos[CPL];
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < CPL; i++) {
+        uint32_t ch = sub + (uint32_t)i * g.lanes;
+        uint64_t r = r0 + ch / g.chunks_per_row;
+        uint64_t c = c0 + (uint64_t)(ch % g.chunks_per_row) * 8u;
+        ok[i] = tile_ok && ch < g.chunks && r < g.rows && c < g.cols;
+        pos[i] = r * g.cols + c;
+        if (ok[i]) {
+            load_chunk8<SRC>(w, pos[i], v[i]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[i][j] = 0.0f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < CPL; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) m = fmaxf(m, abs_or_zero(v[i][j]));
+    for (uint32_t o = g.lanes >> 1; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    const float s = scale_from_maxabs(m, HI);
+    if (tile_ok && sub == 0) scales[tile] = s;
+
+#pragma unroll
+    for (int i = 0; i < CPL; i++) {
+        if (!ok[i]) continue;
+        int q[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) q[j] = quantize_code(v[i][j], s, LO, HI);
+        if constexpr (BITS == 4) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) word |= ((uint32_t)q[j] & 0xFu) << (4 * j);
+            static_cast<uint32_t*>(codes)[pos[i] >> 3] = word;  // cols % 8 == 0: word index = elem / 8
+        } else {
+            uint2 out;
+            out.x = ((uint32_t)q[0] & 0xFFu) | (((uint32_t)q[1] & 0xFFu) << 8) | (((uint32_t)q[2] & 0xFFu) << 16) |
+                    (((uint32_t)q[3] & 0xFFu) << 24);
+            out.y = ((uint32_t)q[4] & 0xFFu) | (((uint32_t)q[5] & 0xFFu) << 8) | (((uint32_t)q[6] & 0xFFu) << 16) |
+                    (((uint32_t)q[7] & 0xFFu) << 24);
+            *reinterpret_cast<uint2*>(static_cast<int8_t*>(codes) + pos[i]) = out;
+        }
+    }
+}
+
+// ---- the generic three-pass path ------------------------------------------
+
+// Pass 1: scales[tile] holds the bit pattern of max|w| (non-negative floats
+// order like unsigned integers; NaN is mapped to 0 first).
+template <int SRC>
+__global__ void k_absmax_generic(const void* __restrict__ w, uint64_t rows, uint64_t cols, uint64_t gr,
+                                 uint64_t gc, uint64_t tc, uint32_t* __restrict__ maxbits) {
+    const uint64_t n = rows * cols;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t r = i / cols, c = i % cols;
+        float a = abs_or_zero(load_elem<SRC>(w, i));
+        if (a != 0.0f) atomicMax(&maxbits[(r / gr) * tc + c / gc], __float_as_uint(a));
+    }
+}
+
+__global__ void k_scales_finalize(float* scales, uint64_t n, int hi) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) scales[i] = scale_from_maxabs(scales[i], hi);
+}
+
+// Pass 3: one thread per output word (int4: 8 codes) or per 4 codes (int8).
+template <int SRC, int BITS>
+__global__ void k_encode_generic(const void* __restrict__ w, uint64_t rows, uint64_t cols, uint64_t gr,
+                                 uint64_t gc, uint64_t tc, const float* __restrict__ scales,
+                                 void* __restrict__ codes) {
+    constexpr int HI = BITS == 8 ? 127 : 7;
+    constexpr int LO = -HI - 1;
+    constexpr uint64_t PER = BITS == 4 ? 8 : 1;
+    const uint64_t upr = (cols + PER - 1) / PER;  // units per row
+    const uint64_t n = rows * upr;
+    for (uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; u < n; u += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t r = u / upr, c0 = (u % upr) * PER;
+        if constexpr (BITS == 4) {
+            uint32_t word = 0;
+            for (uint64_t j = 0; j < 8 && c0 + j < cols; j++) {
+                uint64_t c = c0 + j;
+                float s = scales[(r / gr) * tc + c / gc];
+                int q = quantize_code(load_elem<SRC>(w, r * cols + c), s, LO, HI);
+                word |= ((uint32_t)q & 0xFu) << (4 * j);
+            }
+            static_cast<uint32_t*>(codes)[u] = word;
+        } else {
+            float s = scales[(r / gr) * tc + c0 / gc];
+            static_cast<int8_t*>(codes)[u] = (int8_t)quantize_code(load_elem<SRC>(w, u), s, LO, HI);
+        }
+    }
+}
+
+// ---- dequantize -------------------------------------------------------------
+
+// Fast path: cols % 8 == 0 and gc % 8 == 0, so one scale covers a chunk of 8.
+template <int BITS>
+__global__ void __launch_bounds__(256) k_dequant_chunks(const void* __restrict__ codes,
+                                                        const float* __restrict__ scales, uint64_t rows,
+                                                        uint64_t cols, uint64_t gr, uint64_t gc, uint64_t tc,
+                                                        float* __restrict__ out) {
+    const uint64_t cpr = cols >> 3;
+    const uint64_t n = rows * cpr;
+    uint64_t ch = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= n) return;
+    uint64_t r = ch / cpr, c = (ch % cpr) << 3;
+    float s = __ldg(&scales[(r / gr) * tc + c / gc]);
+    int q[8];
+    if constexpr (BITS == 4) {
+        uint32_t word = __ldcs(static_cast<const uint32_t*>(codes) + ch);
+#pragma unroll
+        for (int j = 0; j < 8; j++) q[j] = int4_unpack(word, j);
+    } else {
+        uint2 b = __ldcs(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(codes) + (ch << 3)));
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            q[j] = (int)(int8_t)((b.x >> (8 * j)) & 0xFFu);
+            q[4 + j] = (int)(int8_t)((b.y >> (8 * j)) & 0xFFu);
+        }
+    }
+    float4 a = make_float4(dequantize_code(q[0], s), dequantize_code(q[1], s), dequantize_code(q[2], s),
+                           dequantize_code(q[3], s));
+    float4 b4 = make_float4(dequantize_code(q[4], s), dequantize_code(q[5], s), dequantize_code(q[6], s),
+                            dequantize_code(q[7], s));
+    float4* o = reinterpret_cast<float4*>(out + (ch << 3));
+    __stcs(o, a);
+    __stcs(o + 1, b4);
+}
+
+template <int BITS>
+__global__ void k_dequant_generic(const void* __restrict__ codes, const float* __restrict__ scales,
+                                  uint64_t rows, uint64_t cols, uint64_t gr, uint64_t gc, uint64_t tc,
+                                  float* __restrict__ out) {
+    const uint64_t n = rows * cols, wpr = (cols + 7) / 8;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t r = i / cols, c = i % cols;
+        float s = scales[(r / gr) * tc + c / gc];
+        int q;
+        if constexpr (BITS == 4)
+            q = int4_unpack(static_cast<const uint32_t*>(codes)[r * wpr + c / 8], (uint32_t)(c % 8));
+        else
+            q = (int)static_cast<const int8_t*>(codes)[i];
+        out[i] = dequantize_code(q, s);
+    }
+}
+
+// ---- dispatch -----------------------------------------------------------------
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static qb200_status check_grid(uint64_t rows, uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc) {
+    uint64_t tr, tc;
+    if (qb200_status s = qb200_scales_count(rows, cols, gr, gc, &tr, &tc)) return s;
+    if (bits != 8 && bits != 4)
+        return fail(QB200_ERR_INVALID_PARAM, "code width must be 8 or 4 bits, got " + std::to_string(bits));
+    return QB200_OK;
+}
+
+static uint32_t grid_for(uint64_t n, uint32_t block, uint64_t cap) {
+    uint64_t b = (n + block - 1) / block;
+    if (b < 1) b = 1;
+    return (uint32_t)(b > cap ? cap : b);
+}
+
+template <int SRC, int BITS>
+static qb200_status launch_tiles(const void* w, const TileGeom& g, void* codes, float* scales, cudaStream_t st) {
+    const uint32_t cpl = (g.chunks + g.lanes - 1) / g.lanes;
+    const uint32_t block = 256;
+    const uint64_t tiles = g.tr * g.tc, per_block = block / g.lanes;
+    const uint64_t blocks = (tiles + per_block - 1) / per_block;
+    if (blocks > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "quantize: matrix too large for one launch");
+    dim3 grid((uint32_t)blocks);
+    switch (cpl) {
+        case 1: k_quantize_tiles<SRC, BITS, 1><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        case 2: k_quantize_tiles<SRC, BITS, 2><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        case 3:
+        case 4: k_quantize_tiles<SRC, BITS, 4><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        default: k_quantize_tiles<SRC, BITS, 8><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+    }
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+template <int SRC, int BITS>
+static qb200_status quantize_typed(const void* w, uint64_t rows, uint64_t cols, uint64_t gr, uint64_t gc,
+                                   void* codes, float* scales, cudaStream_t st) {
+    const uint64_t tr = div_ceil(rows, gr), tc = div_ceil(cols, gc);
+    const uint64_t chunks = (gr * gc) / 8;
+    const bool src_ok = aligned16(w) && (SRC == SRC_F32 || cols % 8 == 0);
+    const bool dst_ok = BITS == 4 ? (reinterpret_cast<uintptr_t>(codes) & 3u) == 0
+                                  : (reinterpret_cast<uintptr_t>(codes) & 7u) == 0;
+    if (cols % 8 == 0 && gc % 8 == 0 && chunks <= 256 && gr <= 0xFFFFFFFFull && src_ok && dst_ok) {
+        TileGeom g;
+        g.rows = rows; g.cols = cols; g.gr = (uint32_t)gr; g.gc = (uint32_t)gc; g.tr = tr; g.tc = tc;
+        g.chunks_per_row = (uint32_t)(gc / 8);
+        g.chunks = (uint32_t)chunks;
+        uint32_t lanes = 1;
+        while (lanes < 32 && lanes < g.chunks) lanes <<= 1;
+        g.lanes = lanes;
+        return launch_tiles<SRC, BITS>(w, g, codes, scales, st);
+    }
+    // generic: any grid, any alignment
+    const int hi = BITS == 8 ? 127 : 7;
+    QB_CUDA_TRY(cudaMemsetAsync(scales, 0, tr * tc * sizeof(float), st));
+    k_absmax_generic<SRC><<<grid_for(rows * cols, 256, 148 * 32), 256, 0, st>>>(
+        w, rows, cols, gr, gc, tc, reinterpret_cast<uint32_t*>(scales));
+    QB_CUDA_TRY(cudaGetLastError());
+    k_scales_finalize<<<grid_for(tr * tc, 256, 0x7FFFFFFF), 256, 0, st>>>(scales, tr * tc, hi);
+    QB_CUDA_TRY(cudaGetLastError());
+    const uint64_t units = BITS == 4 ? rows * div_ceil(cols, 8) : rows * cols;
+    k_encode_generic<SRC, BITS><<<grid_for(units, 256, 148 * 32), 256, 0, st>>>(w, rows, cols, gr, gc, tc, scales, codes);
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+}  // namespace qb
+
+using qb::fail;
+
+extern "C" {
+
+int32_t qb200_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+qb200_status qb200_quantize(const void* w_dev, int32_t src_dtype, uint64_t rows, uint64_t cols, uint32_t bits,
+                            uint64_t gr, uint64_t gc, void* codes_dev, float* scales_dev, void* stream) {
+    if (qb200_status s = qb::check_grid(rows, cols, bits, gr, gc)) return s;
+    if (!w_dev || !codes_dev || !scales_dev) return fail(QB200_ERR_INVALID_PARAM, "qb200_quantize: null device pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define QB_Q(SRC)                                                                                              \
+    (bits == 8 ? qb::quantize_typed<SRC, 8>(w_dev, rows, cols, gr, gc, codes_dev, scales_dev, st)              \
+               : qb::quantize_typed<SRC, 4>(w_dev, rows, cols, gr, gc, codes_dev, scales_dev, st))
+    switch (src_dtype) {
+        case QB200_F32: return QB_Q(qb::SRC_F32);
+        case QB200_BF16: return QB_Q(qb::SRC_BF16);
+        case QB200_F16: return QB_Q(qb::SRC_F16);
+        default: return fail(QB200_ERR_INVALID_PARAM, "qb200_quantize: unknown source dtype " + std::to_string(src_dtype));
+    }
+#undef QB_Q
+}
+
+qb200_status qb200_dequantize(const void* codes_dev, const float* scales_dev, uint64_t rows, uint64_t cols,
+                              uint32_t bits, uint64_t gr, uint64_t gc, float* out_dev, void* stream) {
+    if (qb200_status s = qb::check_grid(rows, cols, bits, gr, gc)) return s;
+    if (!codes_dev || !scales_dev || !out_dev) return fail(QB200_ERR_INVALID_PARAM, "qb200_dequantize: null device pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint64_t tc = qb::div_ceil(cols, gc);
+    const bool fast = cols % 8 == 0 && gc % 8 == 0 && qb::aligned16(out_dev) &&
+                      (reinterpret_cast<uintptr_t>(codes_dev) & (bits == 4 ? 3u : 7u)) == 0;
+    if (fast) {
+        const uint64_t n = rows * (cols / 8), blocks = (n + 255) / 256;
+        if (blocks > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "dequantize: matrix too large for one launch");
+        if (bits == 4)
+            qb::k_dequant_chunks<4><<<(uint32_t)blocks, 256, 0, st>>>(codes_dev, scales_dev, rows, cols, gr, gc, tc, out_dev);
+        else
+            qb::k_dequant_chunks<8><<<(uint32_t)blocks, 256, 0, st>>>(codes_dev, scales_dev, rows, cols, gr, gc, tc, out_dev);
+    } else {
+        uint32_t grid = qb::grid_for(rows * cols, 256, 148 * 32);
+        if (bits == 4)
+            qb::k_dequant_generic<4><<<grid, 256, 0, st>>>(codes_dev, scales_dev, rows, cols, gr, gc, tc, out_dev);
+        else
+            qb::k_dequant_generic<8><<<grid, 256, 0, st>>>(codes_dev, scales_dev, rows, cols, gr, gc, tc, out_dev);
+    }
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,66 @@
+// Device twins of the reference's quantization arithmetic
+// (crates/gpu/quanta-ir/src/dtype.rs:8-21, 232-268).  Every function here is
+// bit-exact against the host definition: IEEE f32 divide, round-to-nearest-even,
+// saturating conversion, one f32 multiply for dequantize.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace qb {
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+// Round-to-nearest-even; a NaN keeps its top half and is quieted (dtype.rs:14-21).
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
+    uint32_t bits = __float_as_uint(v);
+    if (v != v) return (uint16_t)((bits >> 16) | 0x0040u);
+    uint32_t bias = 0x7fffu + ((bits >> 16) & 1u);
+    return (uint16_t)((bits + bias) >> 16);
+}
+
+// |w| for the tile max: Rust's f32::max ignores a NaN operand, so a NaN weight
+// contributes nothing (quanta-array/src/quant.rs:302-306).
+__device__ __forceinline__ float abs_or_zero(float w) { return (w != w) ? 0.0f : fabsf(w); }
+
+// s = max|w| / hi as one IEEE divide (quanta-array/src/quant.rs:308).
+__device__ __forceinline__ float scale_from_maxabs(float m, int hi) { return __fdiv_rn(m, (float)hi); }
+
+// clamp(round_ties_even(x / s) as i32, lo, hi) with s == 0 -> 0
+// (dtype.rs:238-242, quanta-array/src/quant.rs:336-343).  __float2int_rn rounds
+// to nearest even, saturates and maps NaN to 0 — Rust's `as i32`.
+__device__ __forceinline__ int quantize_code(float x, float s, int lo, int hi) {
+    if (s == 0.0f) return 0;
+    int r = __float2int_rn(__fdiv_rn(x, s));
+    return min(max(r, lo), hi);
+}
+
+// scale * f32(q): one multiply, never fused with anything (dtype.rs:245-247).
+__device__ __forceinline__ float dequantize_code(int q, float s) { return __fmul_rn(s, (float)q); }
+
+// Nibble i (0..8) of a packed word, sign-extended (dtype.rs:256-260).
+__device__ __forceinline__ int int4_unpack(uint32_t word, uint32_t i) {
+    uint32_t n = (word >> (i * 4u)) & 0xFu;
+    return (int)((n ^ 0x8u) - 0x8u);
+}
+
+__device__ __forceinline__ float load_as_f32(const float* p, uint64_t i) { return p[i]; }
+
+// IEEE half -> f32 is exact for every class (safetensors.rs:354-373).
+__device__ __forceinline__ float half_bits_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)(h >> 15)) << 31, e = (h >> 10) & 0x1Fu, m = h & 0x3FFu, bits;
+    if (e == 0) {
+        if (m == 0) {
+            bits = sign;
+        } else {
+            int top = 31 - __clz((int)m);
+            bits = sign | ((uint32_t)(127 + top - 24) << 23) | ((m << (23 - top)) & 0x7FFFFFu);
+        }
+    } else if (e == 0x1F) {
+        bits = sign | 0x7F800000u | (m << 13);
+    } else {
+        bits = sign | ((e + 112u) << 23) | (m << 13);
+    }
+    return __uint_as_float(bits);
+}
+
+}  // namespace qb

@@ -1,0 +1,320 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle.
+
+Bit-exact for codes, scales and dequantized weights; the reference's own tolerance form
+|got - want| <= tol * (1 + |want|) (crates/sci/quanta-blas/tests/gemm_quant.rs:74-79) for
+the forward: 1e-4 for f32 activations, 1e-3 where bf16 staging is involved."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+import quanta_b200 as qb
+from tests.golden import kats
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def codes_np(m):
+    c = m.codes().cpu().numpy()
+    return c if c.dtype == np.int8 else c.view(np.uint32)
+
+
+def gran_of(kind, axis, size):
+    return qb.Granularity(kind, axis, size)
+
+
+def quantize_both(w, rows, cols, dtype, gran):
+    """(device QuantizedMatrix, oracle codes, oracle scales) on the same input."""
+    gr, gc = gran.tile(rows, cols)
+    m = qb.QuantizedMatrix.quantize(t(np.asarray(w, np.float32).reshape(rows, cols)), dtype, gran)
+    oc, os_ = o.quantize_host(w, rows, cols, dtype.bits(), gr, gc)
+    return m, oc, os_
+
+
+def assert_quant_equal(m, oc, os_, ctx=""):
+    assert (codes_np(m) == oc).all(), f"{ctx}: codes differ"
+    assert (bits(m.scales().cpu().numpy()) == bits(os_)).all(), f"{ctx}: scales differ"
+
+
+def close(got, want, tol):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    err = np.abs(got - want) - tol * (1 + np.abs(want))
+    assert (err <= 0).all(), f"max excess {err.max():.3e} at {np.unravel_index(err.argmax(), err.shape)}"
+
+
+# ---- quantize / dequantize: the reference's own shape grid -------------------
+
+@pytest.mark.parametrize("r,c,g", kats.DEVICE_HOST_SHAPES)
+def test_device_matches_host_shape_grid(r, c, g):
+    # quanta-array/tests/quant.rs:75-115 — 2 dtypes x 5 spellings
+    w = kats.weights(r * c)
+    for dtype in (qb.QuantDtype.Int8, qb.QuantDtype.Int4):
+        for kind, axis, size in kats.spellings(g):
+            gran = gran_of(kind, axis, size)
+            m, oc, os_ = quantize_both(w, r, c, dtype, gran)
+            ctx = f"[{r},{c}] {dtype.name} {gran!r}"
+            assert_quant_equal(m, oc, os_, ctx)
+            gr, gc = gran.tile(r, c)
+            host = o.dequantize_host(oc, os_, r, c, dtype.bits(), gr, gc)
+            dev = m.dequantize().cpu().numpy()
+            assert dev.shape == (r, c)
+            assert (bits(dev) == bits(host)).all(), ctx
+
+
+@pytest.mark.parametrize("case,dtype", [(kats.RTE_INT8, qb.QuantDtype.Int8), (kats.RTE_INT4, qb.QuantDtype.Int4)])
+def test_ties_to_even_pinned(case, dtype):
+    m = qb.QuantizedMatrix.quantize(t(np.array(case["w"], np.float32).reshape(2, 4)), dtype, qb.PerTensor())
+    assert m.scales().cpu().tolist() == [[case["scale"]]]
+    assert (bits(m.dequantize().cpu().numpy().reshape(-1)) == bits(case["deq"])).all()
+
+
+@pytest.mark.parametrize("case", [kats.NIBBLE_ORDER, kats.ROW_PACKING])
+def test_int4_nibble_contract(case):
+    r, c = case["rows"], case["cols"]
+    m = qb.QuantizedMatrix.quantize(t(np.array(case["w"], np.float32).reshape(r, c)), qb.QuantDtype.Int4, qb.PerTensor())
+    assert codes_np(m).reshape(-1).tolist() == case["words"]
+    assert (bits(m.dequantize().cpu().numpy().reshape(-1)) == bits(case["w"])).all()
+
+
+def test_exact_multiples_and_op_matrix():
+    for ints, dtype in [(kats.EXACT_INT8, qb.QuantDtype.Int8), (kats.EXACT_INT4, qb.QuantDtype.Int4)]:
+        m = qb.QuantizedMatrix.quantize(t(np.array(ints, np.float32).reshape(2, 4)), dtype, qb.PerTensor())
+        assert m.scales().cpu().reshape(-1).tolist() == [1.0]
+        assert (bits(m.dequantize().cpu().numpy().reshape(-1)) == bits(ints)).all()
+    # op-matrix: every representable code dequantizes exactly at scale 0.5
+    for b, dt in [(8, torch.int8), (4, torch.int32)]:
+        lo, hi = kats.QUANT_RANGES[b]
+        vals = list(range(lo, hi + 1))
+        n = len(vals)
+        if b == 8:
+            codes = torch.tensor(vals, dtype=torch.int8).reshape(1, n)
+        else:
+            words = []
+            for i in range(0, n, 8):
+                w = 0
+                for j, v in enumerate(vals[i:i + 8]):
+                    w |= (v & 0xF) << (4 * j)
+                words.append(w)
+            codes = torch.from_numpy(np.array(words, np.uint32).view(np.int32)).reshape(1, -1)
+        m = qb.QuantizedMatrix.from_parts(codes.to(DEV), [1, n], torch.tensor([[0.5]], device=DEV), qb.PerTensor())
+        want = np.float32(0.5) * np.array(vals, np.float32)
+        assert (bits(m.dequantize().cpu().numpy().reshape(-1)) == bits(want)).all()
+
+
+def test_from_parts_dequantizes():
+    c8 = torch.tensor(kats.FROM_PARTS_INT8["codes"], dtype=torch.int8).reshape(2, 2).to(DEV)
+    s = torch.tensor(kats.FROM_PARTS_INT8["scales"]).reshape(2, 1).to(DEV)
+    assert qb.QuantizedMatrix.from_parts(c8, [2, 2], s, qb.PerChannel(0)).dequantize().cpu().reshape(-1).tolist() == \
+        kats.FROM_PARTS_INT8["deq"]
+    c4 = torch.tensor(kats.FROM_PARTS_INT4["words"], dtype=torch.int32).reshape(2, 1).to(DEV)
+    assert qb.QuantizedMatrix.from_parts(c4, [2, 2], s, qb.PerChannel(0)).dequantize().cpu().reshape(-1).tolist() == \
+        kats.FROM_PARTS_INT4["deq"]
+
+
+def test_all_zero_tile_and_specials():
+    w = kats.weights(16)
+    w[8] = w[9] = 0.0
+    m, oc, os_ = quantize_both(w, 4, 4, qb.QuantDtype.Int8, qb.Group(1, 2))
+    assert_quant_equal(m, oc, os_)
+    assert m.scales().cpu()[2, 0] == 0.0
+    d = m.dequantize().cpu().numpy()
+    assert bits(d)[2, 0] == 0 and bits(d)[2, 1] == 0
+    # NaN contributes nothing to the scale and quantizes to 0; inf gives s = inf, codes 0
+    for special in (np.nan, np.inf, -np.inf):
+        for shape, gran in [((4, 64), qb.Group(1, 16)), ((5, 7), qb.PerChannel(0)), ((64, 64), qb.Block(32, 32))]:
+            w = np.random.default_rng(3).standard_normal(shape).astype(np.float32)
+            w[1, 3] = special
+            w[shape[0] - 1, shape[1] - 1] = -0.0
+            for dtype in (qb.QuantDtype.Int8, qb.QuantDtype.Int4):
+                m, oc, os_ = quantize_both(w, *shape, dtype, gran)
+                assert_quant_equal(m, oc, os_, f"{special} {shape} {gran!r}")
+    # denormal scales survive (no flush-to-zero)
+    w = (np.random.default_rng(4).standard_normal((8, 128)) * 1e-39).astype(np.float32)
+    m, oc, os_ = quantize_both(w, 8, 128, qb.QuantDtype.Int4, qb.Group(1, 128))
+    assert_quant_equal(m, oc, os_, "denormal")
+
+
+@pytest.mark.parametrize("shape,gran", [
+    ((256, 512), qb.Group(1, 128)), ((256, 512), qb.Block(32, 32)), ((96, 200), qb.Block(32, 32)),
+    ((64, 1024), qb.Group(1, 256)), ((64, 1024), qb.PerChannel(0)), ((300, 72), qb.Group(0, 128)),
+    ((128, 136), qb.Group(1, 64)), ((33, 130), qb.Group(1, 128)), ((1, 8), qb.PerTensor()), ((130, 9), qb.Block(64, 4)),
+    ((512, 64), qb.Block(256, 8)), ((77, 4096), qb.Group(1, 2048)),
+])
+def test_quantize_paths_bit_exact(shape, gran):
+    rng = np.random.default_rng(hash(shape) & 0xFFFF)
+    w = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    for dtype in (qb.QuantDtype.Int8, qb.QuantDtype.Int4):
+        m, oc, os_ = quantize_both(w, *shape, dtype, gran)
+        assert_quant_equal(m, oc, os_, f"{shape} {gran!r} {dtype.name}")
+        gr, gc = gran.tile(*shape)
+        assert (bits(m.dequantize().cpu().numpy()) == bits(o.dequantize_host(oc, os_, *shape, dtype.bits(), gr, gc))).all()
+
+
+def test_quantize_from_half_sources():
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((64, 256)) * 0.02).astype(np.float32)
+    for tdt in (torch.bfloat16, torch.float16):
+        src = torch.from_numpy(w).to(tdt)
+        exact = src.to(torch.float32).numpy()
+        for dtype, gran in [(qb.QuantDtype.Int4, qb.Group(1, 128)), (qb.QuantDtype.Int8, qb.PerTensor())]:
+            m = qb.QuantizedMatrix.quantize(src.to(DEV), dtype, gran)
+            gr, gc = gran.tile(64, 256)
+            oc, os_ = o.quantize_host(exact, 64, 256, dtype.bits(), gr, gc)
+            assert_quant_equal(m, oc, os_, f"{tdt}")
+
+
+# ---- BASELINE configs at oracle-sized inputs -----------------------------------
+
+def test_config1_int8_block32_cpu_runnable():
+    g = np.random.default_rng(0)
+    w = (g.standard_normal((1024, 1024), dtype=np.float32) * np.float32(0.02))
+    x = g.standard_normal((8, 1024), dtype=np.float32)
+    m, oc, os_ = quantize_both(w, 1024, 1024, qb.QuantDtype.Int8, qb.Block(32, 32))
+    assert_quant_equal(m, oc, os_)
+    assert codes_np(m).min() >= -127 and codes_np(m).max() <= 127
+    wd = o.dequantize_host(oc, os_, 1024, 1024, 8, 32, 32)
+    assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()
+    ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    y = ql.forward(t(x)).cpu().numpy()
+    close(y, o.linear_forward(x, wd, None, o.OUT_IN, threads=8), 1e-4)
+    yh = ql.forward_host(x)
+    assert (bits(yh) == bits(y)).all()
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_config2_int4_decode_shapes(M):
+    g = np.random.default_rng(1)
+    w = g.standard_normal((4096, 4096), dtype=np.float32) * np.float32(0.02)
+    x = g.standard_normal((16, 4096), dtype=np.float32)
+    xb = o.f32_to_bf16(x)[:M]
+    m, oc, os_ = quantize_both(w, 4096, 4096, qb.QuantDtype.Int4, qb.Group(1, 128))
+    assert_quant_equal(m, oc, os_)
+    assert m.scales().shape == (4096, 32)
+    wd = o.dequantize_host(oc, os_, 4096, 4096, 4, 1, 128)
+    ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    y = ql.forward(xt, out_dtype=torch.float32).cpu().numpy()
+    want = o.linear_forward(o.bf16_to_f32(xb), wd, None, o.OUT_IN, threads=8)
+    close(y, want, 1e-3)
+
+
+# ---- QuantizedLinear == Linear(deq w), every orientation / dtype / grid ---------
+
+@pytest.mark.parametrize("layout", [qb.IN_OUT, qb.OUT_IN])
+@pytest.mark.parametrize("dtype,gran,shape", [
+    (qb.QuantDtype.Int8, qb.PerChannel(1), (6, 4)), (qb.QuantDtype.Int4, qb.Group(0, 3), (6, 4)),
+    (qb.QuantDtype.Int4, qb.Group(0, 8), (64, 40)), (qb.QuantDtype.Int8, qb.PerTensor(), (33, 17)),
+    (qb.QuantDtype.Int4, qb.Group(1, 128), (96, 256)), (qb.QuantDtype.Int8, qb.Block(32, 32), (128, 96)),
+    (qb.QuantDtype.Int4, qb.Group(0, 128), (1024, 520)), (qb.QuantDtype.Int8, qb.Group(1, 64), (40, 1024)),
+])
+def test_quantized_linear_matches_linear_of_dequantized(layout, dtype, gran, shape):
+    # quanta-nn/tests/quant.rs:467-524 (the reference claims bitwise for its f32 chain; the fused
+    # kernels accumulate in a different order, so the stated 1e-4 bound applies)
+    r, c = shape
+    w = kats.fill(r * c, 21).reshape(r, c)
+    in_dim, out_dim = (r, c) if layout == qb.IN_OUT else (c, r)
+    b = kats.fill(out_dim, 22)
+    m, oc, os_ = quantize_both(w, r, c, dtype, gran)
+    gr, gc = gran.tile(r, c)
+    wd = o.dequantize_host(oc, os_, r, c, dtype.bits(), gr, gc)
+    for M in (1, 3, 9):
+        x = kats.fill(M * in_dim, 9 + M).reshape(M, in_dim)
+        want = o.linear_forward(x, wd, b, layout)
+        ql = qb.QuantizedLinear.new(m, t(b), layout)
+        assert ql.in_dim() == in_dim and ql.out_dim(in_dim) == out_dim and ql.init() == ()
+        y = ql.apply(None, (), t(x)).cpu().numpy()
+        close(y, want, 1e-4)
+        # Mode A (dequantized once) agrees with Mode B
+        ya = qb.QuantizedLinear.dequantized(m, t(b), layout).forward(t(x)).cpu().numpy()
+        close(ya, want, 1e-4)
+        # bf16 activations in / out
+        xb = o.f32_to_bf16(x)
+        yb = ql.forward(torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV))
+        wantb = o.linear_forward(o.bf16_to_f32(xb), wd, b, layout)
+        close(yb.to(torch.float32).cpu().numpy(), wantb, 1e-2)  # bf16 output rounding: 2^-9 relative
+        assert yb.dtype == torch.bfloat16
+
+
+def test_trained_linear_round_trip_bound():
+    # quanta-nn/tests/quant.rs:543-663, with the trained weight replaced by a seeded one:
+    # |dy| <= sum_k |x_k| s/2 * 1.001 + 1e-6
+    n, k, mo = 8, 4, 3
+    x = kats.fill(n * k, 11).reshape(n, k)
+    w = kats.fill(k * mo, 12).reshape(k, mo)
+    b = kats.fill(mo, 13)
+    y_f = o.linear_forward(x, w, b, o.IN_OUT)
+    for dtype, gran in [(qb.QuantDtype.Int8, qb.PerChannel(1)), (qb.QuantDtype.Int4, qb.Group(0, 2))]:
+        entries = qb.quantize_named([("w", t(w)), ("b", t(b))], lambda name, a: (dtype, gran) if name == "w" else None)
+        data = qb.save_named(entries, None)
+        restored = qb.load(DEV, {"w": torch.zeros(k, mo), "b": torch.zeros(mo)}, data)
+        y_a = (t(x) @ restored["w"] + restored["b"]).cpu().numpy()
+        loaded = qb.load_named(DEV, data)
+        leaves = dict(loaded.leaves)
+        mq = leaves["w"].value
+        ql = qb.QuantizedLinear.new(mq, leaves["b"].value)
+        y_b = ql.forward(t(x)).cpu().numpy()
+        close(y_b, y_a, 1e-5)
+        gr, gc = mq.tile()
+        s = mq.scales().cpu().numpy()
+        for i in range(n):
+            for j in range(mo):
+                bound = sum(abs(float(x[i, kk])) * float(s[kk // gr, j // gc]) / 2 for kk in range(k))
+                assert abs(float(y_b[i, j]) - float(y_f[i, j])) <= bound * 1.001 + 1e-6
+
+
+def test_mode_a_load_equals_device_dequantize_bitwise():
+    # quanta-nn/tests/quant.rs:239-276
+    entries = []
+    for name, kind, shape, vals in kats.REFERENCE_ENTRIES:
+        a = t(np.array(vals, np.float32).reshape(shape))
+        if kind == "f32":
+            entries.append((name, qb.QuantLeaf.F32(a)))
+        else:
+            dt = qb.QuantDtype.Int8 if kind == "q8" else qb.QuantDtype.Int4
+            entries.append((name, qb.QuantLeaf.Quantized(qb.QuantizedMatrix.quantize(a, dt, qb.PerTensor()))))
+    data = qb.save_named(entries, None)
+    assert data == kats.reference_quantized_bytes()
+    loaded = qb.load_named_f32(DEV, data)
+    for (name, leaf), (lname, arr) in zip(entries, loaded.tensors):
+        assert name == lname
+        want = leaf.value.dequantize() if leaf.is_quantized else leaf.value
+        assert list(arr.shape) == list(want.shape)
+        assert torch.equal(arr.view(torch.int32), want.view(torch.int32))
+
+
+# ---- size-independent properties at full BASELINE sizes -------------------------
+
+def test_full_size_properties_config3_shape():
+    """int4 1x128 over [11008, 4096]: the s/2 round-trip bound, clamp-freeness, idempotence of
+    re-quantizing the dequantized weight, and linearity of the forward in x."""
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    w = torch.randn(11008, 4096, device=DEV, generator=gen) * 0.02
+    m = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
+    d = m.dequantize()
+    s = m.scales().repeat_interleave(128, dim=1)
+    assert bool(((d - w).abs() <= s * (0.5 + 1e-4)).all())
+    words = m.codes()
+    nib = torch.stack([(words >> (4 * j)) & 0xF for j in range(8)], dim=-1)
+    assert int((nib == 8).sum()) == 0  # code -8 is never produced
+    m2 = qb.QuantizedMatrix.quantize(d, qb.QuantDtype.Int4, qb.Group(1, 128))
+    assert torch.equal(m2.codes(), m.codes())  # codes are a fixed point (the scale may move one ulp)
+    assert bool(((m2.dequantize() - d).abs() <= d.abs() * 2.0 ** -22).all())
+    ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    x1 = torch.randn(4, 4096, device=DEV, generator=gen)
+    x2 = torch.randn(4, 4096, device=DEV, generator=gen)
+    y12 = ql.forward(x1 + x2)
+    ysum = ql.forward(x1) + ql.forward(x2)
+    assert bool(((y12 - ysum).abs() <= 1e-4 * (1 + ysum.abs())).all())
+    ref = x1 @ d.t()
+    y1 = ql.forward(x1)
+    assert bool(((y1 - ref).abs() <= 1e-3 * (1 + ref.abs())).all())
