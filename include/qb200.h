@@ -164,6 +164,12 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
 QB200_API qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype,
                                    uint64_t m, void* y_dev, int32_t y_dtype, void* stream);
 
+/* Synchronises `stream` and reads the handle's device status word: kernels whose
+ * bounded waits (on an async copy) ran out of polls record QB200_ERR_TIMEOUT there
+ * and return early instead of spinning.  No counterpart in the reference (its
+ * error taxonomy names Timeout, crates/gpu/quanta-core/src/api/error.rs:29-60). */
+QB200_API qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream);
+
 /* The same call over HOST buffers: copies x to the device, runs the forward,
  * copies y back and synchronises.  Staging buffers are owned by the handle
  * and grow on demand. */

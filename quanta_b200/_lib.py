@@ -48,6 +48,7 @@ SIGNATURES = {
     "qb200_qlinear_in_dim": (u64, [vp]),
     "qb200_qlinear_out_dim": (u64, [vp]),
     "qb200_qlinear_forward": (i32, [vp, vp, i32, u64, vp, i32, vp]),
+    "qb200_qlinear_check": (i32, [vp, vp]),
     "qb200_qlinear_forward_host": (i32, [vp, vp, i32, u64, vp, i32]),
     "qb200_qlinear_last_kernel": (cp, [vp]),
     "qb200_st_validate": (i32, [vp, u64, i32, P(vp)]),

@@ -22,6 +22,13 @@ struct FwdArgs {
 qb200_status forward_generic(const FwdArgs& a, uint32_t bits, int x_dtype, int y_dtype, bool rows_kernel,
                              float* scratch, uint32_t slices, cudaStream_t st);
 #endif
+// Decode GEMV on the tensor pipe (gemv_decode.cu): int4, 1x128 grid, OUT_IN, bf16 x, m <= 16.
+bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
+                      uint64_t m, int x_dtype, const void* codes, const void* scales, const void* x);
+#ifdef __CUDACC__
+// QB200_ERR_NOT_SUPPORTED (no message) when no launch plan fits the shape.
+qb200_status gemv_i4_forward(const FwdArgs& a, int y_dtype, int32_t* status, cudaStream_t st);
+#endif
 // K slices the column kernel splits into (1 = no scratch needed).
 uint32_t forward_cols_slices(uint64_t in_dim, uint64_t out_dim, uint64_t m);
 

@@ -22,6 +22,7 @@ struct qb200_qlinear {
     void* y_stage = nullptr;
     uint64_t x_stage_bytes = 0, y_stage_bytes = 0;
     cudaStream_t host_stream = nullptr;
+    int32_t* status = nullptr;  // device word written by kernels whose bounded waits ran out
     const char* last_kernel = "";
 };
 
@@ -80,12 +81,18 @@ qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev
     ql->layout = layout;
     ql->in_dim = in_dim;
     ql->out_dim = out_dim;
+    if (cudaMalloc(&ql->status, sizeof(int32_t)) != cudaSuccess || cudaMemset(ql->status, 0, sizeof(int32_t)) != cudaSuccess) {
+        cudaGetLastError();
+        delete ql;
+        return fail(QB200_ERR_CUDA, "QuantizedLinear: could not allocate the device status word");
+    }
     *out = ql;
     return QB200_OK;
 }
 
 void qb200_qlinear_destroy(qb200_qlinear* ql) {
     if (!ql) return;
+    if (ql->status) cudaFree(ql->status);
     if (ql->scratch) cudaFree(ql->scratch);
     if (ql->x_stage) cudaFree(ql->x_stage);
     if (ql->y_stage) cudaFree(ql->y_stage);
@@ -117,6 +124,14 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     a.gr = ql->gr;
     a.gc = ql->gc;
     a.tc = ql->tc;
+    if (qb::gemv_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes,
+                             ql->scales, x_dev)) {
+        qb200_status s = qb::gemv_i4_forward(a, y_dtype, ql->status, st);
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            ql->last_kernel = "gemv_mma";
+            return s;
+        }
+    }
     if (ql->layout == QB200_OUT_IN) {
         ql->last_kernel = "generic_rows";
         return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, true, nullptr, 1, st);
@@ -130,6 +145,17 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     }
     ql->last_kernel = "generic_cols";
     return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, false, ql->scratch, slices, st);
+}
+
+qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream) {
+    if (!ql) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_check: null handle");
+    int32_t st = 0;
+    QB_CUDA_TRY(cudaMemcpyAsync(&st, ql->status, sizeof st, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    QB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    if (st == QB200_ERR_TIMEOUT)
+        return fail(QB200_ERR_TIMEOUT, "QuantizedLinear: a device-side wait ran out of polls (an async copy never completed)");
+    if (st != 0) return fail(QB200_ERR_CUDA, "QuantizedLinear: device status " + std::to_string(st));
+    return QB200_OK;
 }
 
 qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, int32_t x_dtype, uint64_t m,

@@ -318,3 +318,48 @@ def test_full_size_properties_config3_shape():
     ref = x1 @ d.t()
     y1 = ql.forward(x1)
     assert bool(((y1 - ref).abs() <= 1e-3 * (1 + ref.abs())).all())
+
+
+# ---- the decode GEMV on the tensor pipe ---------------------------------------
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1000, 1024), (37, 128), (4096, 11008), (11008, 4096), (16, 256), (300, 2560)])
+def test_decode_gemv_shapes(N, K):
+    rng = np.random.default_rng(N * 7 + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int4, qb.Group(1, 128))
+    wd = o.dequantize_host(oc, os_, N, K, 4, 1, 128)
+    ql = qb.QuantizedLinear.new(m, t(bias), qb.OUT_IN)
+    for M in (1, 2, 5, 8, 9, 16):
+        xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+        y = ql.forward(xt, out_dtype=torch.float32)
+        assert ql.last_kernel() == "gemv_mma"
+        want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
+        close(y.cpu().numpy(), want, 1e-4)   # exact codes, f32 accumulate: far inside the stated 1e-3
+        yb = ql.forward(xt)                  # bf16 out
+        close(yb.to(torch.float32).cpu().numpy(), want, 1e-2)
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
+def test_decode_gemv_under_graph_replay_matches_eager():
+    rng = np.random.default_rng(77)
+    qls, outs = [], []
+    for i in range(4):
+        w = torch.randn(1024, 2048, device=DEV) * 0.02
+        qls.append(qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128)), None, qb.OUT_IN))
+    x = torch.randn(4, 2048, device=DEV).to(torch.bfloat16)
+    eager = [ql.forward(x, out_dtype=torch.float32) for ql in qls]
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        outs = [torch.empty(4, 1024, device=DEV) for _ in qls]
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            cap = [ql.forward(x, out_dtype=torch.float32) for ql in qls]
+        for _ in range(3):
+            g.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(eager, cap):
+        assert torch.equal(a, b)
