@@ -168,6 +168,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    global LAYERS
+    LAYERS = args.layers
     m = args.m
     lib = _lib.load()
     # device-side quantize-on-load of this rank's shards (seeded per rank)
@@ -183,13 +185,28 @@ def run_ours(args):
     y_all = torch.empty(world, m, N_OUT, device=dev, dtype=torch.float32) if world > 1 else None
     stream = torch.cuda.current_stream(dev)
 
+    ys = [torch.empty(m, N_OUT, device=dev, dtype=torch.float32) for _ in layers]
+    hs = (_lib.vp * LAYERS)(*[ql._h for ql in layers])
+    xp = (_lib.vp * LAYERS)(*[x.data_ptr()] * LAYERS)
+    yp = (_lib.vp * LAYERS)(*[t.data_ptr() for t in ys])
+    grouped = args.launch == "grouped"
+
     def step():
-        for ql in layers:
-            st = lib.qb200_qlinear_forward(ql._h, x.data_ptr(), _lib.BF16, m, y.data_ptr(), _lib.F32, stream.cuda_stream)
+        cur = torch.cuda.current_stream(dev).cuda_stream  # the capture stream while a graph is recorded
+        if grouped:  # the 32 layers read the same x: one persistent launch streams all their codes
+            st = lib.qb200_qlinear_forward_many(hs, LAYERS, xp, _lib.BF16, m, yp, _lib.F32, cur)
             if st:
                 raise RuntimeError(_lib.last_error())
             if world > 1:
-                dist.all_gather_into_tensor(y_all, y)
+                for t in ys:
+                    dist.all_gather_into_tensor(y_all, t)
+            return
+        for ql, t in zip(layers, ys):
+            st = lib.qb200_qlinear_forward(ql._h, x.data_ptr(), _lib.BF16, m, t.data_ptr(), _lib.F32, cur)
+            if st:
+                raise RuntimeError(_lib.last_error())
+            if world > 1:
+                dist.all_gather_into_tensor(y_all, t)
 
     def barrier():
         if world > 1:
@@ -211,7 +228,7 @@ def run_ours(args):
     # spin the clocks up and keep the sampler busy for at least half a second before timing
     t_spin = time.perf_counter()
     n_warm = 0
-    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_spin < 0.5:
+    while n_warm < max(args.warmup, 3) or (not args.profile and time.perf_counter() - t_spin < 0.5):
         step()
         n_warm += 1
         if n_warm % 64 == 0:
@@ -230,8 +247,8 @@ def run_ours(args):
         tmax = torch.tensor([ms], device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms = float(tmax.item())
-    launches = LAYERS * args.steps
-    total_bytes = layer_bytes(m) * launches * world
+    launches = (1 if grouped else LAYERS) * args.steps
+    total_bytes = layer_bytes(m) * LAYERS * args.steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
 
     # end to end through the host-buffer entry point: pinned host X in, host Y out, every launch
@@ -245,11 +262,11 @@ def run_ours(args):
             if st:
                 raise RuntimeError(_lib.last_error())
 
-    for _ in range(3):
+    for _ in range(0 if args.profile else 3):
         step_host()
     barrier()
     t0 = time.perf_counter()
-    e2e_steps = max(1, min(args.steps, 20))
+    e2e_steps = 1 if args.profile else max(1, min(args.steps, 20))
     for _ in range(e2e_steps):
         step_host()
     barrier()
@@ -263,14 +280,15 @@ def run_ours(args):
     if rank == 0:
         peak, which = measured_peak_gbs()
         per_launch_s = ms * 1e-3 / launches
-        achieved = layer_bytes(m) / per_launch_s / 1e9
+        achieved = layer_bytes(m) * (LAYERS if grouped else 1) / per_launch_s / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 x int4 -> f32", "data": "synthetic",
             "config": {"workload": f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{m},{K_IN}], f32 out",
                        "layers_per_step": LAYERS, "l2": "inputs larger than L2 (32 distinct weight matrices, 286 MB)",
-                       "kernel": layers[0].last_kernel(), "launch": "eager" if args.no_graph else "cuda graph replay",
+                       "kernel": layers[0].last_kernel(), "launch": ("one persistent launch per step" if grouped else "one launch per layer") +
+                                 (", eager" if args.no_graph else ", cuda graph replay"),
                        "parallelism": "single GPU" if world == 1 else f"column-sharded x{world} + all-gather per layer"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * m * K_IN * 2,
@@ -279,7 +297,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": which, "launch_us": per_launch_s * 1e6},
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.profile:
             import oracle as o
             threads = o.max_threads()
             v, dt = cpu_forward_gbs(m, threads, 2, 2)
@@ -299,6 +317,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows (1, 4 or 16 for the decode configuration)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--profile", action="store_true", help="short run for a profiler: no clock spin-up, no CPU leg")
+    ap.add_argument("--launch", default="grouped", choices=["grouped", "per-layer"],
+                    help="grouped: the step's layers go through qb200_qlinear_forward_many (one persistent launch); "
+                         "per-layer: one qb200_qlinear_forward launch per layer")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

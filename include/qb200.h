@@ -164,6 +164,17 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
 QB200_API qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype,
                                    uint64_t m, void* y_dev, int32_t y_dtype, void* stream);
 
+/* `count` forwards in one call: entry i computes y_dev[i] = layers[i](x_dev[i]), the
+ * result of calling qb200_qlinear_forward once per layer in order (the reference
+ * stacks layers and loops over Layer::apply,
+ * crates/ml/quanta-nn/tests/quant.rs:507-523).  Layers that share the input width
+ * and take the decode path run as ONE persistent launch that streams all their
+ * codes back to back (fused QKV / gate+up projections); any other mix falls back
+ * to the per-layer loop.  The outputs must not alias each other's inputs. */
+QB200_API qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t count,
+                                        const void* const* x_dev, int32_t x_dtype, uint64_t m,
+                                        void* const* y_dev, int32_t y_dtype, void* stream);
+
 /* Synchronises `stream` and reads the handle's device status word: kernels whose
  * bounded waits (on an async copy) ran out of polls record QB200_ERR_TIMEOUT there
  * and return early instead of spinning.  No counterpart in the reference (its
@@ -177,7 +188,7 @@ QB200_API qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void*
                                         uint64_t m, void* y_host, int32_t y_dtype);
 
 /* Name of the kernel family the last forward on this handle dispatched to
- * ("gemv_mma", "gemm_tcgen05", "generic_rows", "generic_cols"). */
+ * ("gemv_mma", "gemv_mma_grouped", "gemm_tcgen05", "generic_rows", "generic_cols"). */
 QB200_API const char* qb200_qlinear_last_kernel(const qb200_qlinear* ql);
 
 /* ---- quantized-safetensors (host bytes in, host bytes out) -------------- */

@@ -28,6 +28,8 @@ bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
 #ifdef __CUDACC__
 // QB200_ERR_NOT_SUPPORTED (no message) when no launch plan fits the shape.
 qb200_status gemv_i4_forward(const FwdArgs& a, int y_dtype, int32_t* status, cudaStream_t st);
+// One persistent launch over several layers that share K and m (x and y per layer).
+qb200_status gemv_i4_forward_many(const FwdArgs* a, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st);
 #endif
 // K slices the column kernel splits into (1 = no scratch needed).
 uint32_t forward_cols_slices(uint64_t in_dim, uint64_t out_dim, uint64_t m);

@@ -1,20 +1,33 @@
 // Decode GEMV (M <= 16): y[m, n] = sum_k x[m, k] * s[n, k/128] * q[n, k] over resident
 // packed-int4 codes `[N, K/8]` (u32, low nibble first) with a 1x128 f32 scale grid and bf16
-// activations.  HBM-bound: the kernel's job is to keep the codes streaming.
+// activations.  HBM-bound: the kernel's job is to keep the codes streaming and to spend as
+// few issue slots per weight as possible.
 //
 // Layout and flow, one CTA per contiguous slab of output rows:
 //   1. one warp issues bulk async copies (cp.async.bulk, completion on an mbarrier per
 //      16-row block) for the slab's codes — every row a contiguous K/2-byte burst — and all
-//      threads fetch its scales; nothing here depends on the previous kernel, so with programmatic dependent
-//      launch this prefetch overlaps the previous layer's tail;
-//   2. griddepcontrol.wait, then each warp takes a slice of the scale groups: it loads its
-//      x fragment from L2, unpacks nibbles to exact bf16 integers in registers
-//      (lop3 with the 136.0 magic constant, one bf16x2 subtract), multiplies on the tensor
-//      pipe (mma.sync m16n8k16, f32 accumulate: W rows are the M side, the batch is the N
-//      side) and applies the f32 scale once per 128-k group to the group's partial sum;
+//      threads fetch its scales; nothing here depends on the previous kernel, so with
+//      programmatic dependent launch this prefetch overlaps the previous layer's tail;
+//   2. griddepcontrol.wait, then each warp takes a slice of the scale groups, loads its x
+//      fragment from L2 and multiplies on the tensor pipe (mma.sync m16n8k16, f32
+//      accumulate; W rows are the M side, the batch is the N side);
 //   3. warps fold their K slices through shared memory and write y (+ bias).
-// Codes are exact in bf16 and products accumulate in f32, so the only rounding is the f32
-// accumulation order.
+//
+// Unpacking costs five integer instructions per packed word.  A bf16 whose exponent field is
+// 0 or 1 is linear in its bit pattern (value = bits * 2^-133), and the tensor pipe honours
+// such inputs exactly, so a masked nibble IS a bf16 operand: `(w & 0x000F000F) ^ 0x00080008`
+// holds (q + 8) for nibbles 0 and 4, `(w & 0x00F000F0) ^ 0x00800080` holds 16 (q + 8) for
+// nibbles 1 and 5, and one shift by 8 exposes nibbles 2, 3, 6, 7 the same way.  x is scaled by
+// 2^40 (2^36 against the 16x positions) so products stay normal f32; the "+ 8" is removed by
+// subtracting 8 * sum_k x_k per group (summed once per CTA), and the group's f32 scale and
+// 2^93 are applied once per 128-k group.  Every product (integer code times bf16 activation)
+// is exact in f32; the only rounding is f32 accumulation.  Activations must satisfy
+// |x| < 2^87.
+//
+// The kernel is persistent: a CTA walks work items (a slab of <= 16*RB rows of one layer)
+// through a ring of shared-memory stages, so the copies of later items are in flight while
+// the current one is multiplied.  One launch can serve several layers (grouped forward);
+// a single layer is the same kernel with one descriptor.
 #include <cuda_bf16.h>
 #include <cstdint>
 
@@ -23,19 +36,22 @@
 
 namespace qb {
 
-constexpr int GEMV_WARPS = 8;
-constexpr int GEMV_THREADS = GEMV_WARPS * 32;
-constexpr uint32_t GEMV_ROW_PAD = 64;        // bytes added to each smem row: shifts banks by 16
 constexpr uint32_t GEMV_SPIN_LIMIT = 1u << 22;  // mbarrier polls before giving up (~ seconds)
+constexpr int GEMV_MAX_LAYERS = 48;             // descriptors travel by value in the kernel parameters
 
-struct GemvArgs {
+struct GemvLayer {
     const uint32_t* codes;  // [N, K/8]
     const float* scales;    // [N, K/128]
     const float* bias;      // [N] or null
     const uint16_t* x;      // bf16 [M, K]
     void* y;                // [M, N] f32 or bf16
-    int32_t* status;        // device status word (0 = ok, QB200_ERR_TIMEOUT on a wait that ran out)
-    uint32_t M, N, K, rows_per_cta;
+    uint32_t N, rows_per_item, item0;  // this layer owns items [item0, item0 + ceil(N / rows_per_item))
+};
+
+struct GemvBatch {
+    GemvLayer layer[GEMV_MAX_LAYERS];
+    int32_t* status;  // device status word (0 = ok, QB200_ERR_TIMEOUT on a wait that ran out)
+    uint32_t count, total_items, M, K, stages;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -77,20 +93,14 @@ __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_
     return d;
 }
 
-// One packed word -> four bf16x2 registers of exact integer codes:
-// r[i] = (q_i, q_{i+4}).  0x4308 is bf16 136.0 = 128 + 8: xor-ing it onto a masked nibble n
-// sets the exponent and flips bit 3, giving 128 + (n ^ 8) = 136 + q; one subtract leaves q.
-__device__ __forceinline__ void unpack_word(uint32_t w, uint32_t (&r)[4]) {
-    constexpr uint32_t MASK = 0x000F000Fu, MAGIC = 0x43084308u;
-    const __nv_bfloat162 bias = *reinterpret_cast<const __nv_bfloat162*>(&MAGIC);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t v = lop3_and_xor(w >> (4 * i), MASK, MAGIC);
-        __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
-        r[i] = *reinterpret_cast<uint32_t*>(&q);
-    }
+// d = a * b (+ 0): the first MMA of a chain takes a zero accumulator without spending moves.
+__device__ __forceinline__ void mma_bf16_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
-
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
     asm volatile(
@@ -106,177 +116,270 @@ __device__ __forceinline__ void store_y<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_y<uint16_t>(uint16_t* p, float v) { *p = f32_to_bf16_bits(v); }
 
-// RB: 16-row blocks per CTA; NT: 8-wide batch tiles (M <= 8 * NT).
-template <int RB, int NT, typename YT>
-__global__ void __launch_bounds__(GEMV_THREADS) k_gemv_i4(GemvArgs a) {
+// Masks and xor constants of the four nibble pairs of a word (see the header comment).
+constexpr uint32_t NIB_LO = 0x000F000Fu, NIB_HI = 0x00F000F0u, EIGHT_LO = 0x00080008u, EIGHT_HI = 0x00800080u;
+constexpr uint32_t X_SCALE_LO = 0x53805380u;  // bf16x2 2^40
+constexpr uint32_t X_SCALE_HI = 0x51805180u;  // bf16x2 2^36: pairs with the 16x nibble positions
+#define GEMV_UNSCALE 9903520314283042199192993792.0f  // 2^93 = 2^133 / 2^40
+#define GEMV_EIGHT_X 8.077935669463161e-28f           // 8 * 2^-93: the "+ 8" in units of the MMA partial sums
+
+// Shared-memory carve-up, identical on host and device.
+struct GemvSmem {
+    uint32_t corr, xtab, red, scales, codes, total;  // byte offsets; barriers sit at 0
+    uint32_t stride, stage_scales, stage_codes;
+};
+__host__ __device__ inline GemvSmem gemv_smem_layout(uint32_t K, uint32_t M, uint32_t rb, uint32_t nt, uint32_t warps,
+                                                     uint32_t stages) {
+    GemvSmem L;
+    const uint32_t groups = K / 128, rows = rb * 16, batch = nt * 8;
+    auto up = [](uint32_t v) { return (v + 127u) & ~127u; };
+    L.stride = K / 2;  // rows stay contiguous so an item is ONE bulk copy (small copies cap the copy engine)
+    L.corr = 128;
+    L.xtab = L.corr + up(groups * batch * 4);
+    L.red = L.xtab + up(M * K * 2);
+    L.scales = L.red + up(2 * warps * rows * batch * 4);
+    L.stage_scales = up(rows * groups * 4);
+    L.codes = L.scales + stages * L.stage_scales;
+    L.stage_codes = up(rows * L.stride);
+    L.total = L.codes + stages * L.stage_codes;
+    return L;
+}
+
+// Offset (bytes) of the 16-byte piece i of the x fragment of (batch row b, group G, lane t).
+// Pieces of odd batch rows are swapped in pairs so the two rows served in one shared-memory
+// phase fall in different banks.
+__device__ __forceinline__ uint32_t xtab_offset(uint32_t b, uint32_t G, uint32_t groups, uint32_t i, uint32_t t) {
+    return ((b * groups + G) * 4 + (i ^ (b & 1))) * 64 + t * 16;
+}
+
+// Builds the activation table of one layer: per (batch row, group, lane) the 32 activations a
+// thread feeds to its eight MMAs, permuted to the nibble order and scaled (2^40 against nibble
+// pairs (2h, 2h+4), 2^36 against the 16x pairs (2h+1, 2h+5)), plus corr[G][b] = 8 * 2^-93 * sum, the value the "+ 8" adds to an MMA partial sum.
+template <int NT>
+__device__ __forceinline__ void build_xtab(const uint16_t* __restrict__ x, uint32_t M, uint32_t K, uint8_t* xtab,
+                                           float* corr, uint32_t tid, uint32_t threads) {
+    const uint32_t groups = K >> 7, chunks = M * groups * 4;
+    uint32_t klo = X_SCALE_LO, khi = X_SCALE_HI;
+    const __nv_bfloat162 slo = *reinterpret_cast<const __nv_bfloat162*>(&klo);
+    const __nv_bfloat162 shi = *reinterpret_cast<const __nv_bfloat162*>(&khi);
+    for (uint32_t c0 = 0; c0 < chunks; c0 += threads) {
+        const uint32_t c = c0 + tid;  // chunk = 32 consecutive activations; 4 chunks per (b, G)
+        const bool ok = c < chunks;
+        const uint32_t t = c & 3, G = (c >> 2) % groups, b = (c >> 2) / groups;
+        float sum = 0.0f;
+        if (ok) {
+            const uint4* xp = reinterpret_cast<const uint4*>(x + (uint64_t)b * K + G * 128 + t * 32);
+            uint32_t xr[16];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint4 v = __ldg(xp + i);
+                xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) sum += bf16_bits_to_f32(xr[i] & 0xFFFFu) + bf16_bits_to_f32(xr[i] >> 16);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t o[4];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t lo = __byte_perm(xr[4 * j + h], xr[4 * j + h + 2], 0x5410);
+                    uint32_t hi = __byte_perm(xr[4 * j + h], xr[4 * j + h + 2], 0x7632);
+                    __nv_bfloat162 l2 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&lo), slo);
+                    __nv_bfloat162 h2 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&hi), shi);
+                    o[2 * h] = *reinterpret_cast<uint32_t*>(&l2);
+                    o[2 * h + 1] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(xtab + xtab_offset(b, G, groups, j, t)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if (ok && t == 0) corr[G * (NT * 8) + b] = sum * GEMV_EIGHT_X;
+    }
+}
+
+// RB: 16-row blocks per work item; NT: 8-wide batch tiles (M <= 8 * NT); WARPS: warps per CTA.
+template <int RB, int NT, int WARPS, typename YT>
+__global__ void __launch_bounds__(WARPS * 32) k_gemv_i4(const __grid_constant__ GemvBatch a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t groups = a.K >> 7;               // scale groups per row
-    const uint32_t row_bytes = a.K >> 1;            // packed codes per row
-    const uint32_t stride = row_bytes + GEMV_ROW_PAD;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                     // RB barriers
-    float* s_scales = reinterpret_cast<float*>(smem + 64);                  // [RB*16][groups]
-    uint8_t* s_codes = smem + 64 + (((uint32_t)RB * 16 * groups * 4 + 127) & ~127u);  // [RB*16][stride]
+    constexpr uint32_t THREADS = WARPS * 32, ROWS = RB * 16, BATCH = NT * 8;
+    const uint32_t groups = a.K >> 7, row_bytes = a.K >> 1, S = a.stages;
+    const GemvSmem L = gemv_smem_layout(a.K, a.M, RB, NT, WARPS, S);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    float* s_corr = reinterpret_cast<float*>(smem + L.corr);
+    uint8_t* s_xtab = smem + L.xtab;
+    float* s_red = reinterpret_cast<float*>(smem + L.red);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t row0 = blockIdx.x * a.rows_per_cta;
-    const uint32_t nrows = min(a.rows_per_cta, a.N - row0);
+    const uint32_t n_my = blockIdx.x < a.total_items ? (a.total_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+    // which layer an item belongs to (items are numbered layer by layer)
+    auto layer_of = [&](uint32_t item, uint32_t from) {
+        uint32_t l = from;
+        while (l + 1 < a.count && item >= a.layer[l + 1].item0) l++;
+        return l;
+    };
+    // One thread arms the stage barrier and issues ONE bulk copy for the item's codes (its rows are
+    // contiguous in HBM) and, when 16-byte aligned, one for its scales; unaligned scales travel as
+    // 4-byte async copies.  Every thread's copies are counted on the same barrier.
+    auto issue = [&](uint32_t j, uint32_t l) {
+        const GemvLayer& ly = a.layer[l];
+        const uint32_t item = blockIdx.x + j * gridDim.x, st = j % S;
+        const uint32_t row0 = (item - ly.item0) * ly.rows_per_item, nrows = min(ly.rows_per_item, ly.N - row0);
+        const float* src = ly.scales + (uint64_t)row0 * groups;
+        const uint32_t sbytes = nrows * groups * 4;
+        const bool bulk_scales = ((reinterpret_cast<uintptr_t>(src) | sbytes) & 15u) == 0;
+        if (tid == 0) {
+            mbar_expect_tx(&bars[st], nrows * row_bytes + (bulk_scales ? sbytes : 0));
+            bulk_g2s(smem + L.codes + st * L.stage_codes,
+                     reinterpret_cast<const uint8_t*>(ly.codes) + (uint64_t)row0 * row_bytes, nrows * row_bytes, &bars[st]);
+            if (bulk_scales) bulk_g2s(smem + L.scales + st * L.stage_scales, src, sbytes, &bars[st]);
+        }
+        if (!bulk_scales) {
+            const uint32_t sc = smem_u32(smem + L.scales + st * L.stage_scales);
+            for (uint32_t i = tid; i < nrows * groups; i += THREADS)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sc + i * 4), "l"(src + i) : "memory");
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars[st])) : "memory");
+    };
 
     if (tid == 0) {
-#pragma unroll
-        for (int rb = 0; rb < RB; rb++) mbar_init(&bars[rb], 1);
+        for (uint32_t s = 0; s < S; s++) mbar_init(&bars[s], 1 + THREADS);  // the expect_tx arrival + one per thread
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 0) {
-        // lane rb arms barrier rb with the byte count of its rows, then lanes share the row copies
-#pragma unroll
-        for (int rb = 0; rb < RB; rb++) {
-            const uint32_t lo = rb * 16, hi = min(nrows, lo + 16u);
-            if (lane == 0 && hi > lo) {
-                mbar_expect_tx(&bars[rb], (hi - lo) * row_bytes);
-            }
-        }
-        __syncwarp();
-        for (uint32_t r = lane; r < nrows; r += 32)
-            bulk_g2s(s_codes + r * stride, reinterpret_cast<const uint8_t*>(a.codes) + (uint64_t)(row0 + r) * row_bytes,
-                     row_bytes, &bars[r >> 4]);
+    uint32_t l_issue = 0;
+    for (uint32_t j = 0; j < n_my && j < S; j++) {
+        l_issue = layer_of(blockIdx.x + j * gridDim.x, l_issue);
+        issue(j, l_issue);
     }
-    // The slab's scales are a few KB at any alignment: plain loads, also ahead of the wait.
-    for (uint32_t i = tid; i < nrows * groups; i += GEMV_THREADS) s_scales[i] = __ldg(a.scales + (uint64_t)row0 * groups + i);
-    // Let the next kernel in the stream start its own prefetch; then wait for the previous
-    // one to finish before touching x or y (both no-ops without programmatic launch).
+    // The codes and scales do not depend on the previous kernel; everything below may.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __syncthreads();
 
-    float acc[RB][NT][4];
-#pragma unroll
-    for (int rb = 0; rb < RB; rb++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
-
-    bool ready[RB];
-#pragma unroll
-    for (int rb = 0; rb < RB; rb++) ready[rb] = false;
+    const uint16_t* cur_x = nullptr;
+    uint32_t l_cur = 0;
     bool failed = false;
-
-    for (uint32_t G = warp; G < groups && !failed; G += GEMV_WARPS) {
-        // x fragments of this group, permuted to the nibble order of unpack_word
-        uint32_t bx[NT][8][2];
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            const uint32_t b = g + 8 * nt;
-            uint32_t xr[16];
-            if (b < a.M) {
-                const uint4* xp = reinterpret_cast<const uint4*>(a.x + (uint64_t)b * a.K + G * 128 + t * 32);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    uint4 v = __ldg(xp + i);
-                    xr[4 * i] = v.x; xr[4 * i + 1] = v.y; xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) xr[i] = 0;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    bx[nt][2 * j + h][0] = __byte_perm(xr[4 * j + h], xr[4 * j + h + 2], 0x5410);
-                    bx[nt][2 * j + h][1] = __byte_perm(xr[4 * j + h], xr[4 * j + h + 2], 0x7632);
-                }
+    for (uint32_t j = 0; j < n_my; j++) {
+        const uint32_t item = blockIdx.x + j * gridDim.x, st = j % S;
+        l_cur = layer_of(item, l_cur);
+        const GemvLayer& ly = a.layer[l_cur];
+        if (ly.x != cur_x) {  // uniform: rebuild the activation table (the barrier below also orders the reuse)
+            cur_x = ly.x;
+            build_xtab<NT>(cur_x, a.M, a.K, s_xtab, s_corr, tid, THREADS);
+            __syncthreads();
+        } else if (j == 0) {
+            __syncthreads();
         }
+        const uint32_t row0 = (item - ly.item0) * ly.rows_per_item, nrows = min(ly.rows_per_item, ly.N - row0);
+        if (!mbar_wait_bounded(&bars[st], (j / S) & 1)) failed = true;
+
+        const uint8_t* s_codes = smem + L.codes + st * L.stage_codes;
+        const float* s_scales = reinterpret_cast<const float*>(smem + L.scales + st * L.stage_scales);
+        float acc[RB][NT][4];
 #pragma unroll
-        for (int rb = 0; rb < RB; rb++) {
-            if (rb * 16u >= nrows) break;
-            if (!ready[rb]) {
-                if (!mbar_wait_bounded(&bars[rb], 0)) {
-                    failed = true;
-                    break;
-                }
-                ready[rb] = true;
-            }
-            const uint32_t ra = rb * 16 + g, rc = ra + 8;
-            const uint4 c0 = *reinterpret_cast<const uint4*>(s_codes + ra * stride + G * 64 + t * 16);
-            const uint4 c1 = *reinterpret_cast<const uint4*>(s_codes + rc * stride + G * 64 + t * 16);
-            const uint32_t w0[4] = {c0.x, c0.y, c0.z, c0.w}, w1[4] = {c1.x, c1.y, c1.z, c1.w};
-            float part[NT][4];
+        for (int rb = 0; rb < RB; rb++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) part[nt][i] = 0.0f;
+                for (int i = 0; i < 4; i++) acc[rb][nt][i] = 0.0f;
+
+        for (uint32_t G = warp; G < groups && !failed; G += WARPS) {
+            // codes of this group: rows g and g + 8 of every row block
+            uint4 c0[RB], c1[RB];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint32_t r0[4], r1[4];
-                unpack_word(w0[j], r0);
-                unpack_word(w1[j], r1);
-#pragma unroll
-                for (int h = 0; h < 2; h++)
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++)
-                        mma_bf16(part[nt], r0[2 * h], r1[2 * h], r0[2 * h + 1], r1[2 * h + 1], bx[nt][2 * j + h][0],
-                                 bx[nt][2 * j + h][1]);
+            for (int rb = 0; rb < RB; rb++) {
+                c0[rb] = *reinterpret_cast<const uint4*>(s_codes + (rb * 16 + g) * L.stride + G * 64 + t * 16);
+                c1[rb] = *reinterpret_cast<const uint4*>(s_codes + (rb * 16 + g + 8) * L.stride + G * 64 + t * 16);
             }
-            const float s0 = s_scales[ra * groups + G], s1 = s_scales[rc * groups + G];
+            float p[RB][NT][2][4];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; j4++) {
+                uint4 bx[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint32_t b = g + 8 * nt;
+                    bx[nt] = b < a.M ? *reinterpret_cast<const uint4*>(s_xtab + xtab_offset(b, G, groups, j4, t))
+                                     : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int rb = 0; rb < RB; rb++) {
+                    const uint32_t w0 = j4 == 0 ? c0[rb].x : j4 == 1 ? c0[rb].y : j4 == 2 ? c0[rb].z : c0[rb].w;
+                    const uint32_t w1 = j4 == 0 ? c1[rb].x : j4 == 1 ? c1[rb].y : j4 == 2 ? c1[rb].z : c1[rb].w;
+                    const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
+                    const uint32_t a0 = lop3_and_xor(w0, NIB_LO, EIGHT_LO), a2 = lop3_and_xor(w0, NIB_HI, EIGHT_HI);
+                    const uint32_t a1 = lop3_and_xor(w1, NIB_LO, EIGHT_LO), a3 = lop3_and_xor(w1, NIB_HI, EIGHT_HI);
+                    const uint32_t d0 = lop3_and_xor(w0s, NIB_LO, EIGHT_LO), d2 = lop3_and_xor(w0s, NIB_HI, EIGHT_HI);
+                    const uint32_t d1 = lop3_and_xor(w1s, NIB_LO, EIGHT_LO), d3 = lop3_and_xor(w1s, NIB_HI, EIGHT_HI);
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        if (j4 == 0) {
+                            mma_bf16_first(p[rb][nt][0], a0, a1, a2, a3, bx[nt].x, bx[nt].y);
+                            mma_bf16_first(p[rb][nt][1], d0, d1, d2, d3, bx[nt].z, bx[nt].w);
+                        } else {
+                            mma_bf16(p[rb][nt][0], a0, a1, a2, a3, bx[nt].x, bx[nt].y);
+                            mma_bf16(p[rb][nt][1], d0, d1, d2, d3, bx[nt].z, bx[nt].w);
+                        }
+                    }
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                acc[rb][nt][0] = fmaf(s0, part[nt][0], acc[rb][nt][0]);
-                acc[rb][nt][1] = fmaf(s0, part[nt][1], acc[rb][nt][1]);
-                acc[rb][nt][2] = fmaf(s1, part[nt][2], acc[rb][nt][2]);
-                acc[rb][nt][3] = fmaf(s1, part[nt][3], acc[rb][nt][3]);
+                const float2 kc = *reinterpret_cast<const float2*>(s_corr + G * BATCH + nt * 8 + 2 * t);
+#pragma unroll
+                for (int rb = 0; rb < RB; rb++) {
+                    const float s0 = s_scales[(rb * 16 + g) * groups + G] * GEMV_UNSCALE;
+                    const float s1 = s_scales[(rb * 16 + g + 8) * groups + G] * GEMV_UNSCALE;
+                    acc[rb][nt][0] = fmaf(s0, (p[rb][nt][0][0] + p[rb][nt][1][0]) - kc.x, acc[rb][nt][0]);
+                    acc[rb][nt][1] = fmaf(s0, (p[rb][nt][0][1] + p[rb][nt][1][1]) - kc.y, acc[rb][nt][1]);
+                    acc[rb][nt][2] = fmaf(s1, (p[rb][nt][0][2] + p[rb][nt][1][2]) - kc.x, acc[rb][nt][2]);
+                    acc[rb][nt][3] = fmaf(s1, (p[rb][nt][0][3] + p[rb][nt][1][3]) - kc.y, acc[rb][nt][3]);
+                }
             }
         }
-    }
-    if (failed) atomicExch(a.status, QB200_ERR_TIMEOUT);
-    // Every thread must have seen the copies land before the buffer is reused below.
-    if (__syncthreads_or(failed ? 1 : 0)) {
-        // A copy never completed: wait (bounded) for whatever is still in flight, then leave.
+
+        // fold the K slices of the warps through red[j & 1][warp][row][batch]
+        float* red = s_red + (j & 1) * (WARPS * ROWS * BATCH);
 #pragma unroll
         for (int rb = 0; rb < RB; rb++)
-            if (rb * 16u < nrows) mbar_wait_bounded(&bars[rb], 0);
-        return;
-    }
-
-    // fold the K slices of the 8 warps: red[warp][row][batch] aliases the codes buffer
-    constexpr int BATCH = NT * 8;
-    float* red = reinterpret_cast<float*>(s_codes);
 #pragma unroll
-    for (int rb = 0; rb < RB; rb++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            float* base = red + ((warp * RB * 16 + rb * 16) * BATCH) + nt * 8;
-            base[(g)*BATCH + 2 * t] = acc[rb][nt][0];
-            base[(g)*BATCH + 2 * t + 1] = acc[rb][nt][1];
-            base[(g + 8) * BATCH + 2 * t] = acc[rb][nt][2];
-            base[(g + 8) * BATCH + 2 * t + 1] = acc[rb][nt][3];
+            for (int nt = 0; nt < NT; nt++) {
+                float* base = red + (warp * ROWS + rb * 16) * BATCH + nt * 8;
+                *reinterpret_cast<float2*>(base + g * BATCH + 2 * t) = make_float2(acc[rb][nt][0], acc[rb][nt][1]);
+                *reinterpret_cast<float2*>(base + (g + 8) * BATCH + 2 * t) = make_float2(acc[rb][nt][2], acc[rb][nt][3]);
+            }
+        if (__syncthreads_or(failed ? 1 : 0)) {
+            failed = true;
+            break;
         }
-    __syncthreads();
-    for (uint32_t e = tid; e < nrows * a.M; e += GEMV_THREADS) {
-        const uint32_t r = e % nrows, b = e / nrows;
-        float v = 0.0f;
+        // the stage is free: refill it with the item S steps ahead
+        if (j + S < n_my) {
+            l_issue = layer_of(blockIdx.x + (j + S) * gridDim.x, l_issue);
+            issue(j + S, l_issue);
+        }
+        for (uint32_t e = tid; e < nrows * a.M; e += THREADS) {
+            const uint32_t r = e % nrows, b = e / nrows;
+            float v = 0.0f;
 #pragma unroll
-        for (int w = 0; w < GEMV_WARPS; w++) v += red[(w * RB * 16 + r) * BATCH + b];
-        const uint32_t n = row0 + r;
-        if (a.bias) v += a.bias[n];
-        store_y<YT>(static_cast<YT*>(a.y) + (uint64_t)b * a.N + n, v);
+            for (int w = 0; w < WARPS; w++) v += red[(w * ROWS + r) * BATCH + b];
+            const uint32_t n = row0 + r;
+            if (ly.bias) v += ly.bias[n];
+            store_y<YT>(static_cast<YT*>(ly.y) + (uint64_t)b * ly.N + n, v);
+        }
+    }
+    if (failed) {
+        // A copy never completed: record it, give copies still in flight a bounded chance to land, leave.
+        if (tid == 0) atomicExch(a.status, QB200_ERR_TIMEOUT);
+        for (uint32_t s = 0; s < S; s++) mbar_wait_bounded(&bars[s], 0);
     }
 }
 
 // ---- host side ------------------------------------------------------------------
 
-struct GemvPlan {
-    uint32_t ctas, rows_per_cta, rb, smem;
+struct GemvShape {
+    uint32_t rb, nt, warps, stages, smem, rows_per_item;
 };
-
-static uint32_t gemv_smem(uint32_t rb, uint32_t K, uint32_t nt) {
-    const uint32_t groups = K / 128;
-    uint32_t codes = rb * 16 * (K / 2 + GEMV_ROW_PAD);
-    uint32_t red = GEMV_WARPS * rb * 16 * nt * 8 * 4;
-    return 64 + ((rb * 16 * groups * 4 + 127) & ~127u) + (codes > red ? codes : red);
-}
 
 bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* scales, const void* x) {
@@ -286,79 +389,99 @@ bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
     return al(codes) && al(scales) && al(x);
 }
 
-static bool gemv_plan(uint32_t N, uint32_t K, uint32_t nt, GemvPlan& p) {
-    for (uint32_t c = 1; c <= 64; c++) {
-        uint32_t ctas = 148 * c;
-        if (ctas > N) ctas = N;
-        uint32_t rows = (N + ctas - 1) / ctas;
-        uint32_t rb = (rows + 15) / 16;
-        if (rb <= 4) {
-            uint32_t smem = gemv_smem(rb, K, nt);
-            if (smem <= 100 * 1024 || (ctas == N && smem <= 200 * 1024)) {
-                p.ctas = (N + rows - 1) / rows;
-                p.rows_per_cta = rows;
-                p.rb = rb;
-                p.smem = smem;
-                return true;
-            }
+// Rows per work item: the layer is cut into a multiple of 148 items of at most 16 * rb rows,
+// so the last wave of items is as full as the others.
+static uint32_t gemv_rows_per_item(uint32_t N, uint32_t rb) {
+    const uint32_t tiles = (N + 16 * rb - 1) / (16 * rb), k = (tiles + 147) / 148;
+    uint32_t rows = (N + 148 * k - 1) / (148 * k);
+    return rows < 1 ? 1 : rows;
+}
+
+// Picks the stage count that fits shared memory; false when the activation table does not fit.
+static bool gemv_shape(uint32_t K, uint32_t M, uint32_t max_items_per_cta, bool chained, GemvShape& s) {
+    s.nt = M <= 8 ? 1 : 2;
+    s.rb = 1;
+    s.warps = s.nt == 1 ? 16 : 8;
+    const uint32_t cap = 227 * 1024, want = max_items_per_cta < 2 ? 2 : (max_items_per_cta > 4 ? 4 : max_items_per_cta);
+    for (uint32_t st = want; st >= 2; st--) {
+        GemvSmem L = gemv_smem_layout(K, M, s.rb, s.nt, s.warps, st);
+        if (L.total <= cap) {
+            s.stages = st;
+            s.smem = L.total;
+            (void)chained;
+            return true;
         }
-        if (ctas == N) break;
     }
     return false;
 }
 
-template <int RB, int NT, typename YT>
-static qb200_status launch_gemv(const GemvArgs& a, const GemvPlan& p, cudaStream_t st) {
-    auto kern = k_gemv_i4<RB, NT, YT>;
+template <int NT, typename YT>
+static qb200_status launch_gemv(const GemvBatch& b, const GemvShape& s, uint32_t ctas, cudaStream_t st) {
+    auto kern = k_gemv_i4<1, NT, (NT == 1 ? 16 : 8), YT>;
     static bool attr_set[64] = {};  // per instantiation and device
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        QB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        QB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set[dev & 63] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.ctas);
-    cfg.blockDim = dim3(GEMV_THREADS);
-    cfg.dynamicSmemBytes = p.smem;
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(s.warps * 32);
+    cfg.dynamicSmemBytes = s.smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    QB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a));
+    QB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, b));
     return QB200_OK;
 }
 
-template <int NT, typename YT>
-static qb200_status by_rb(const GemvArgs& a, const GemvPlan& p, cudaStream_t st) {
-    switch (p.rb) {
-        case 1: return launch_gemv<1, NT, YT>(a, p, st);
-        case 2: return launch_gemv<2, NT, YT>(a, p, st);
-        case 3: return launch_gemv<3, NT, YT>(a, p, st);
-        default: return launch_gemv<4, NT, YT>(a, p, st);
+// Grouped forward over `count` layers that share K and M.  Returns QB200_ERR_NOT_SUPPORTED
+// (without setting an error) when the shape does not fit the kernel.
+qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st) {
+    if (count == 0) return QB200_OK;
+    const uint32_t K = (uint32_t)f[0].in_dim, M = (uint32_t)f[0].m;
+    for (uint32_t base = 0; base < count; base += GEMV_MAX_LAYERS) {
+        const uint32_t n = count - base < (uint32_t)GEMV_MAX_LAYERS ? count - base : GEMV_MAX_LAYERS;
+        GemvBatch b = {};
+        uint32_t items = 0;
+        for (uint32_t i = 0; i < n; i++) {
+            const FwdArgs& a = f[base + i];
+            GemvLayer& ly = b.layer[i];
+            ly.codes = static_cast<const uint32_t*>(a.codes);
+            ly.scales = a.scales;
+            ly.bias = a.bias;
+            ly.x = static_cast<const uint16_t*>(a.x);
+            ly.y = a.y;
+            ly.N = (uint32_t)a.out_dim;
+            ly.rows_per_item = gemv_rows_per_item(ly.N, 1);
+            ly.item0 = items;
+            items += (ly.N + ly.rows_per_item - 1) / ly.rows_per_item;
+        }
+        b.status = status;
+        b.count = n;
+        b.total_items = items;
+        b.M = M;
+        b.K = K;
+        const uint32_t ctas = items < 148 ? items : 148;
+        GemvShape s;
+        if (!gemv_shape(K, M, (items + ctas - 1) / ctas, n == 1, s)) return QB200_ERR_NOT_SUPPORTED;
+        b.stages = s.stages;
+        qb200_status r;
+        if (y_dtype == QB200_F32)
+            r = s.nt == 1 ? launch_gemv<1, float>(b, s, ctas, st) : launch_gemv<2, float>(b, s, ctas, st);
+        else
+            r = s.nt == 1 ? launch_gemv<1, uint16_t>(b, s, ctas, st) : launch_gemv<2, uint16_t>(b, s, ctas, st);
+        if (r) return r;
     }
+    return QB200_OK;
 }
 
-// Returns QB200_ERR_NOT_SUPPORTED (without setting an error) when no launch plan fits.
 qb200_status gemv_i4_forward(const FwdArgs& f, int y_dtype, int32_t* status, cudaStream_t st) {
-    GemvArgs a;
-    a.codes = static_cast<const uint32_t*>(f.codes);
-    a.scales = f.scales;
-    a.bias = f.bias;
-    a.x = static_cast<const uint16_t*>(f.x);
-    a.y = f.y;
-    a.status = status;
-    a.M = (uint32_t)f.m;
-    a.N = (uint32_t)f.out_dim;
-    a.K = (uint32_t)f.in_dim;
-    const uint32_t nt = f.m <= 8 ? 1 : 2;
-    GemvPlan p;
-    if (!gemv_plan(a.N, a.K, nt, p)) return QB200_ERR_NOT_SUPPORTED;
-    a.rows_per_cta = p.rows_per_cta;
-    if (y_dtype == QB200_F32) return nt == 1 ? by_rb<1, float>(a, p, st) : by_rb<2, float>(a, p, st);
-    return nt == 1 ? by_rb<1, uint16_t>(a, p, st) : by_rb<2, uint16_t>(a, p, st);
+    return gemv_i4_forward_many(&f, 1, y_dtype, status, st);
 }
 
 }  // namespace qb

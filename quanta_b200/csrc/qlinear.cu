@@ -3,6 +3,7 @@
 // selection per forward (the body of Layer::apply, quant.rs:903-918).
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "forward.hpp"
 
@@ -145,6 +146,51 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     }
     ql->last_kernel = "generic_cols";
     return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, false, ql->scratch, slices, st);
+}
+
+qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev,
+                                        int32_t x_dtype, uint64_t m, void* const* y_dev, int32_t y_dtype,
+                                        void* stream) {
+    if (count == 0 || m == 0) return QB200_OK;
+    if (!layers || !x_dev || !y_dev) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many: null argument");
+    for (uint32_t i = 0; i < count; i++)
+        if (!layers[i] || !x_dev[i] || !y_dev[i])
+            return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many: null entry " + std::to_string(i));
+    // One persistent launch when every layer takes the decode GEMV and they share the input width.
+    bool grouped = count > 1 && (y_dtype == QB200_F32 || y_dtype == QB200_BF16);
+    for (uint32_t i = 0; i < count && grouped; i++) {
+        const qb200_qlinear* q = layers[i];
+        grouped = q->in_dim == layers[0]->in_dim &&
+                  qb::gemv_i4_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes,
+                                       q->scales, x_dev[i]);
+    }
+    if (grouped) {
+        std::vector<qb::FwdArgs> args(count);
+        for (uint32_t i = 0; i < count; i++) {
+            const qb200_qlinear* q = layers[i];
+            qb::FwdArgs& a = args[i];
+            a.codes = q->codes;
+            a.scales = q->scales;
+            a.bias = q->bias;
+            a.x = x_dev[i];
+            a.y = y_dev[i];
+            a.m = m;
+            a.in_dim = q->in_dim;
+            a.out_dim = q->out_dim;
+            a.gr = q->gr;
+            a.gc = q->gc;
+            a.tc = q->tc;
+        }
+        qb200_status s = qb::gemv_i4_forward_many(args.data(), count, y_dtype, layers[0]->status,
+                                                  static_cast<cudaStream_t>(stream));
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_grouped";
+            return s;
+        }
+    }
+    for (uint32_t i = 0; i < count; i++)
+        if (qb200_status s = qb200_qlinear_forward(layers[i], x_dev[i], x_dtype, m, y_dev[i], y_dtype, stream)) return s;
+    return QB200_OK;
 }
 
 qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream) {

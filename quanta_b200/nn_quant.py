@@ -310,6 +310,34 @@ class QuantizedLinear:
                                                  _ACT[out_dtype], _stream(x)))
         return y
 
+    @staticmethod
+    def forward_many(layers: List["QuantizedLinear"], xs: List[torch.Tensor], out_dtype: Optional[torch.dtype] = None,
+                     outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
+        """``[layer.forward(x) for layer, x in zip(layers, xs)]`` in one call: layers that share the input
+        width and take the decode path run as one persistent launch (fused QKV / gate+up projections)."""
+        if len(layers) != len(xs):
+            raise QuantError(L.ERR_INVALID_PARAM, "forward_many: one input per layer")
+        if not layers:
+            return []
+        m, dt = xs[0].shape[0], xs[0].dtype
+        out_dtype = out_dtype or dt
+        for ql, x in zip(layers, xs):
+            if ql._h is None:
+                raise QuantError(L.ERR_INVALID_PARAM, "forward_many needs Mode B layers")
+            if x.dim() != 2 or x.shape[1] != ql._in or x.shape[0] != m or x.dtype != dt or dt not in _ACT:
+                raise QuantError(L.ERR_INVALID_PARAM, "forward_many: inputs must be [m, in] of one f32 / bf16 dtype")
+            _require_cuda(x, "the input")
+        xs = [x.contiguous() for x in xs]
+        if outs is None:
+            outs = [torch.empty((m, ql._out), dtype=out_dtype, device=xs[0].device) for ql in layers]
+        n = len(layers)
+        hs = (L.vp * n)(*[ql._h for ql in layers])
+        xp = (L.vp * n)(*[x.data_ptr() for x in xs])
+        yp = (L.vp * n)(*[y.data_ptr() for y in outs])
+        with torch.cuda.device(xs[0].device):
+            check(L.load().qb200_qlinear_forward_many(hs, n, xp, _ACT[dt], m, yp, _ACT[out_dtype], _stream(xs[0])))
+        return outs
+
     def apply(self, _tape, _params, x: torch.Tensor) -> torch.Tensor:
         """``Layer::apply(tape, &(), x)`` — the params slot is the empty tree, the tape is unused."""
         return self.forward(x)

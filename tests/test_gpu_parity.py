@@ -363,3 +363,28 @@ def test_decode_gemv_under_graph_replay_matches_eager():
     torch.cuda.synchronize()
     for a, b in zip(eager, cap):
         assert torch.equal(a, b)
+
+
+def test_forward_many_matches_per_layer_forward():
+    rng = np.random.default_rng(5)
+    shapes = [(1024, 1024), (3000, 1024), (37, 1024), (4096, 1024)]
+    qls = []
+    for N, K in shapes:
+        w = torch.from_numpy((rng.standard_normal((N, K)) * 0.02).astype(np.float32)).to(DEV)
+        b = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).to(DEV)
+        qls.append(qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128)), b, qb.OUT_IN))
+    for M in (1, 3, 8, 16):
+        x_shared = torch.randn(M, 1024, device=DEV).to(torch.bfloat16)
+        x_other = torch.randn(M, 1024, device=DEV).to(torch.bfloat16)
+        xs = [x_shared, x_shared, x_other, x_shared]
+        want = [ql.forward(x, out_dtype=torch.float32) for ql, x in zip(qls, xs)]
+        got = qb.QuantizedLinear.forward_many(qls, xs, out_dtype=torch.float32)
+        assert qls[0].last_kernel() == "gemv_mma_grouped"
+        for a, b_ in zip(got, want):
+            assert torch.equal(a, b_)
+    # a mix the grouped kernel cannot take falls back to the per-layer loop
+    w8 = torch.randn(64, 1024, device=DEV) * 0.02
+    q8 = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w8, qb.QuantDtype.Int8, qb.PerChannel(0)), None, qb.OUT_IN)
+    x = torch.randn(2, 1024, device=DEV).to(torch.bfloat16)
+    got = qb.QuantizedLinear.forward_many([qls[0], q8], [x, x], out_dtype=torch.float32)
+    assert torch.equal(got[1], q8.forward(x, out_dtype=torch.float32)) and q8.last_kernel() == "generic_rows"
