@@ -52,6 +52,7 @@ struct GemvBatch {
     GemvLayer layer[GEMV_MAX_LAYERS];
     int32_t* status;  // device status word (0 = ok, QB200_ERR_TIMEOUT on a wait that ran out)
     uint32_t count, total_items, M, K, stages;
+    uint32_t async_scales;  // scales are not 16-byte aligned slabs: copy them element-wise
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -375,7 +376,38 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv_i4(const __grid_constant__ 
     }
 }
 
+}  // namespace qb
+
+#include "gemv_reg.cuh"
+#include "gemv_reg_kernel.cuh"
+
+namespace qb {
+
 // ---- host side ------------------------------------------------------------------
+
+template <int NT, int RB, int OCC, typename YT>
+static qb200_status launch_gemv_reg(const GemvBatch& b, uint32_t smem, uint32_t ctas, cudaStream_t st) {
+    auto kern = k_gemv_i4_reg<NT, RB, OCC, YT>;
+    static bool attr_set[64] = {};  // per instantiation and device
+    int dev = 0;
+    QB_CUDA_TRY(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        QB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev & 63] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(REG_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, b));
+    return QB200_OK;
+}
 
 struct GemvShape {
     uint32_t rb, nt, warps, stages, smem, rows_per_item;
@@ -444,8 +476,19 @@ static qb200_status launch_gemv(const GemvBatch& b, const GemvShape& s, uint32_t
 qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st) {
     if (count == 0) return QB200_OK;
     const uint32_t K = (uint32_t)f[0].in_dim, M = (uint32_t)f[0].m;
-    for (uint32_t base = 0; base < count; base += GEMV_MAX_LAYERS) {
-        const uint32_t n = count - base < (uint32_t)GEMV_MAX_LAYERS ? count - base : GEMV_MAX_LAYERS;
+    const bool reg_path = K / 128 <= 2 * REG_WARPS;
+    // Row blocks per item: a lone small layer keeps 16-row items (more items to pipeline and to
+    // overlap with the neighbouring launches); grouped launches take 32-row items.
+    uint32_t rb = count > 1 ? 2 : 1;
+    if (!reg_path) rb = 1;
+    for (uint32_t base = 0, n = 0; base < count; base += n) {
+        // as many layers as fit the descriptor table and, on the register path, the per-CTA item table
+        n = 0;
+        for (uint32_t items = 0; base + n < count && n < (uint32_t)GEMV_MAX_LAYERS; n++) {
+            const uint32_t N = (uint32_t)f[base + n].out_dim, rpi = gemv_rows_per_item(N, rb);
+            items += (N + rpi - 1) / rpi;
+            if (reg_path && n > 0 && items > REG_MAX_ITEMS * 148) break;
+        }
         GemvBatch b = {};
         uint32_t items = 0;
         for (uint32_t i = 0; i < n; i++) {
@@ -457,16 +500,38 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             ly.x = static_cast<const uint16_t*>(a.x);
             ly.y = a.y;
             ly.N = (uint32_t)a.out_dim;
-            ly.rows_per_item = gemv_rows_per_item(ly.N, 1);
+            ly.rows_per_item = gemv_rows_per_item(ly.N, rb);
             ly.item0 = items;
             items += (ly.N + ly.rows_per_item - 1) / ly.rows_per_item;
         }
+        b.async_scales = (K % 512 != 0) ? 1 : 0;  // a row of scales is K / 32 bytes
+        for (uint32_t i = 0; i < n; i++)
+            if (reinterpret_cast<uintptr_t>(b.layer[i].scales) & 15u) b.async_scales = 1;
         b.status = status;
         b.count = n;
         b.total_items = items;
         b.M = M;
         b.K = K;
-        const uint32_t ctas = items < 148 ? items : 148;
+        uint32_t ctas = items < 148 ? items : 148;
+        if (reg_path && (items + 147) / 148 <= REG_MAX_ITEMS) {  // activation fragments stay in registers
+            const uint32_t nt = M <= 8 ? 1 : 2;
+            uint32_t occ = (nt == 1 && rb == 1) ? 2 : 1;
+            ctas = items < 148 * occ ? items : 148 * occ;
+            const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : 200u) * 1024;
+            uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
+            while (stages > 2 && reg_smem_layout(K, nt, rb, stages).total > budget) stages--;
+            b.stages = stages;
+            const uint32_t smem = reg_smem_layout(K, nt, rb, stages).total;
+            qb200_status r;
+#define QB_LAUNCH(YT)                                                                                          \
+    (nt == 2 ? (rb == 2 ? launch_gemv_reg<2, 2, 1, YT>(b, smem, ctas, st) : launch_gemv_reg<2, 1, 1, YT>(b, smem, ctas, st)) \
+             : rb == 2 ? launch_gemv_reg<1, 2, 1, YT>(b, smem, ctas, st)                                       \
+                       : (occ == 2 ? launch_gemv_reg<1, 1, 2, YT>(b, smem, ctas, st) : launch_gemv_reg<1, 1, 1, YT>(b, smem, ctas, st)))
+            r = y_dtype == QB200_F32 ? QB_LAUNCH(float) : QB_LAUNCH(uint16_t);
+#undef QB_LAUNCH
+            if (r) return r;
+            continue;
+        }
         GemvShape s;
         if (!gemv_shape(K, M, (items + ctas - 1) / ctas, n == 1, s)) return QB200_ERR_NOT_SUPPORTED;
         b.stages = s.stages;
