@@ -1,0 +1,395 @@
+// Prefill GEMM (M >= 64): Y[m, n] = sum_k X[m, k] * s[n, k/128] * q[n, k] over resident
+// packed-int4 codes `[N, K/8]` with a 1x128 f32 scale grid, bf16 activations, f32 accumulation.
+// Tensor-core bound: tcgen05.mma with the accumulator in TMEM.
+//
+// Staging (stated, and mirrored by the checker): the codes enter the tensor core as EXACT
+// integers and the activations as exact bf16, so every product is exact in f32; a group's
+// f32 scale is applied to the group's partial sum, never to a weight.  Concretely
+//   * a pre-pass writes X' = X * 2^40 (exact in bf16) and corr[m, g] = 8 * sum_{k in g} X[m, k];
+//   * the B operand holds (q + 8) as a bf16 whose exponent field is zero — such a value is
+//     its bit pattern times 2^-133, and the tensor core honours it exactly — so unpacking a
+//     word costs one shift, two LOP3 and four PRMT and no floating-point work;
+//   * per 128-k group the MMA leaves D_g = 2^-93 * sum (q + 8) x in TMEM; the epilogue warps
+//     fold total += s[n, g] * (D_g * 2^93 - corr[m, g]) in registers (f32).
+// X' and corr live in a scratch buffer owned by the QuantizedLinear handle.
+//
+// One CTA computes a 128 (m) x 128 (n) tile: warp 0 feeds X' tiles by TMA (128B-swizzled),
+// warp 1 issues the MMAs, warps 2-5 unpack codes straight from global memory into the swizzled
+// B tile, warps 6-9 are the TMEM epilogue.  A ring of shared-memory stages and a pair of TMEM
+// accumulators keep the four roles overlapped.  Every wait is bounded and reports through the
+// handle's status word.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <string>
+
+#include "forward.hpp"
+#include "quant_math.cuh"
+
+namespace qb {
+
+constexpr uint32_t PF_BM = 128, PF_BN = 128, PF_BK = 64;  // tile; BK bf16 = one 128-byte swizzle row
+constexpr uint32_t PF_STAGES = 4;
+constexpr uint32_t PF_THREADS = 320;
+constexpr uint32_t PF_SPIN = 1u << 22;
+#define PF_UNSCALE 9903520314283042199192993792.0f  // 2^93
+
+// ---- pre-pass: X' = X * 2^40, corr[m, g] = 8 * sum_{k in g} X[m, k] -----------------------
+// One warp per (row, group of 128): lanes read 8 bytes each.
+__global__ void __launch_bounds__(256) k_prefill_prep(const uint16_t* __restrict__ x, uint32_t M, uint32_t K,
+                                                      uint16_t* __restrict__ xs, float* __restrict__ corr) {
+    const uint32_t groups = K >> 7, lane = threadIdx.x & 31;
+    const uint64_t unit = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (uint64_t)M * groups) return;
+    const uint32_t m = (uint32_t)(unit / groups), g = (uint32_t)(unit % groups);
+    const uint64_t off = (uint64_t)m * K + g * 128 + lane * 4;
+    const uint2 v = *reinterpret_cast<const uint2*>(x + off);
+    const uint32_t k40 = 0x53805380u;  // bf16x2 2^40
+    const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(&k40);
+    uint32_t w[2] = {v.x, v.y};
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        sum += bf16_bits_to_f32(w[i] & 0xFFFFu) + bf16_bits_to_f32(w[i] >> 16);
+        __nv_bfloat162 p = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&w[i]), sc);
+        w[i] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    *reinterpret_cast<uint2*>(xs + off) = make_uint2(w[0], w[1]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane == 0) corr[(uint64_t)m * groups + g] = 8.0f * sum;
+}
+
+// ---- PTX helpers ------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t pf_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void pf_mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(pf_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void pf_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pf_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void pf_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(pf_smem(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false when the poll limit ran out.
+__device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < PF_SPIN; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(pf_smem(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void pf_tma_load_2d(void* dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            pf_smem(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(pf_smem(bar))
+        : "memory");
+}
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t pf_desc(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;               // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;     // stride byte offset
+    d |= (uint64_t)1 << 46;               // descriptor version
+    d |= (uint64_t)2 << 61;               // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void pf_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void pf_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pf_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+
+struct PrefillArgs {
+    const uint32_t* codes;  // [N, K/8]
+    const float* scales;    // [N, K/128]
+    const float* bias;      // [N] or null
+    const float* corr;      // [M, K/128]: 8 * group sums of X
+    void* y;                // [M, N] bf16 or f32
+    int32_t* status;
+    uint32_t M, N, K;
+};
+
+// One packed word -> eight bf16 values (q + 8) * 2^-133 in natural k order (four registers).
+__device__ __forceinline__ void pf_unpack(uint32_t w, uint32_t (&r)[4]) {
+    uint32_t t0, t1;
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(t0) : "r"(w), "r"(0x0F0F0F0Fu), "r"(0x08080808u));       // nibbles 0,2,4,6
+    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(t1) : "r"(w >> 4), "r"(0x0F0F0F0Fu), "r"(0x08080808u));  // nibbles 1,3,5,7
+    // selector 8 replicates the (clear) sign bit of a byte: a zero byte for the bf16 high halves
+    // (prmt.b32 in PTX: the __byte_perm intrinsic ignores the replicate bit)
+    asm("prmt.b32 %0, %1, %2, 0x8480;" : "=r"(r[0]) : "r"(t0), "r"(t1));
+    asm("prmt.b32 %0, %1, %2, 0x8581;" : "=r"(r[1]) : "r"(t0), "r"(t1));
+    asm("prmt.b32 %0, %1, %2, 0x8682;" : "=r"(r[2]) : "r"(t0), "r"(t1));
+    asm("prmt.b32 %0, %1, %2, 0x8783;" : "=r"(r[3]) : "r"(t0), "r"(t1));
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, PrefillArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK;
+    uint8_t* sA = smem;                                   // [S][128 rows][128 B]
+    uint8_t* sB = smem + PF_STAGES * 16384;               // [S][128 rows][128 B]
+    float* s_scales = reinterpret_cast<float*>(smem + 2 * PF_STAGES * 16384);  // [groups][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * PF_STAGES * 16384 + groups * 512);
+    uint64_t* full_a = bars;
+    uint64_t* full_b = bars + PF_STAGES;
+    uint64_t* empty = bars + 2 * PF_STAGES;
+    uint64_t* dfull = bars + 3 * PF_STAGES;
+    uint64_t* dempty = dfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t n0 = blockIdx.x * PF_BN, m0 = blockIdx.y * PF_BM;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < PF_STAGES; s++) {
+            pf_mbar_init(&full_a[s], 1);
+            pf_mbar_init(&full_b[s], 4);
+            pf_mbar_init(&empty[s], 1);
+        }
+        for (uint32_t b = 0; b < 2; b++) {
+            pf_mbar_init(&dfull[b], 1);
+            pf_mbar_init(&dempty[b], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // 256 TMEM columns: two 128-column f32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(pf_smem(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---- TMA producer: X' tiles ----
+        if (lane == 0) {
+            uint32_t st = 0, par = 0;
+            for (uint32_t s = 0; s < num_k; s++) {
+                if (s >= PF_STAGES && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
+                pf_mbar_expect_tx(&full_a[st], 16384);
+                pf_tma_load_2d(sA + st * 16384, &xmap, (int32_t)(s * PF_BK), (int32_t)m0, &full_a[st]);
+                if (++st == PF_STAGES) { st = 0; par ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            // f32 accumulate, bf16 x bf16, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_BN >> 3) << 17) | ((PF_BM >> 4) << 24);
+            uint32_t st = 0, par = 0;
+            for (uint32_t s = 0; s < num_k; s++) {
+                const uint32_t g = s >> 1, buf = g & 1;
+                if ((s & 1) == 0 && g >= 2 && !pf_wait(&dempty[buf], ((g >> 1) & 1) ^ 1)) { failed = true; break; }
+                if (!pf_wait(&full_a[st], par) || !pf_wait(&full_b[st], par)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = pf_desc(pf_smem(sA + st * 16384)), db = pf_desc(pf_smem(sB + st * 16384));
+                const uint32_t d = tmem_base + buf * PF_BN;
+#pragma unroll
+                for (uint32_t kk = 0; kk < PF_BK / 16; kk++)
+                    pf_mma(d, da + 2 * kk, db + 2 * kk, idesc, ((s & 1) | kk) ? 1u : 0u);  // +32 bytes per k16 step
+                pf_commit(&empty[st]);
+                if (s & 1) pf_commit(&dfull[buf]);
+                if (++st == PF_STAGES) { st = 0; par ^= 1; }
+            }
+        }
+    } else if (warp < 6) {
+        // ---- unpack warps: thread r owns row n0 + r of the B tile ----
+        const uint32_t r = tid - 64, n = n0 + r;
+        const bool valid = n < a.N;
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.codes) + (uint64_t)(valid ? n : 0) * (a.K >> 1));
+        const uint32_t row_off = r * 128 + ((r & 7) << 4);  // chunk c lands at (row_off ^ (c << 4))
+        uint4 c0 = valid ? __ldg(src) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+        uint4 c1 = valid ? __ldg(src + 1) : c0;
+        uint32_t st = 0, par = 0;
+        for (uint32_t s = 0; s < num_k; s++) {
+            uint4 n0v = c0, n1v = c1;
+            if (valid && s + 1 < num_k) {
+                n0v = __ldg(src + 2 * (s + 1));
+                n1v = __ldg(src + 2 * (s + 1) + 1);
+            }
+            if (s >= PF_STAGES && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
+            uint8_t* dst = sB + st * 16384;
+            const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (uint32_t c = 0; c < 8; c++) {
+                uint32_t o[4];
+                pf_unpack(w[c], o);
+                *reinterpret_cast<uint4*>(dst + (row_off ^ (c << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) pf_mbar_arrive(&full_b[st]);
+            c0 = n0v;
+            c1 = n1v;
+            if (++st == PF_STAGES) { st = 0; par ^= 1; }
+        }
+    } else {
+        // ---- epilogue warps: thread = accumulator row (TMEM lane) ----
+        const uint32_t e = tid - 192;  // 0..127
+        {   // scales of the tile, transposed to [group][row] so a thread reads consecutive rows
+            const uint32_t n = n0 + e;
+            for (uint32_t g = 0; g < groups; g++) s_scales[g * 128 + e] = n < a.N ? __ldg(a.scales + (uint64_t)n * groups + g) : 0.0f;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        const uint32_t quad = warp & 3, ml = quad * 32 + lane, m = m0 + ml;
+        const float* corr = a.corr + (uint64_t)(m < a.M ? m : 0) * groups;
+        float total[PF_BN];
+#pragma unroll
+        for (uint32_t i = 0; i < PF_BN; i++) total[i] = 0.0f;
+        for (uint32_t g = 0; g < groups; g++) {
+            const uint32_t buf = g & 1;
+            if (!pf_wait(&dfull[buf], (g >> 1) & 1)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float c = __ldg(corr + g);
+            const float* sg = s_scales + g * 128;
+#pragma unroll
+            for (uint32_t ch = 0; ch < 4; ch++) {
+                float v[32];
+                pf_tmem_ld32(tmem_base + ((quad * 32) << 16) + buf * PF_BN + ch * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (uint32_t i = 0; i < 32; i++)
+                    total[ch * 32 + i] = fmaf(sg[ch * 32 + i], fmaf(v[i], PF_UNSCALE, -c), total[ch * 32 + i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) pf_mbar_arrive(&dempty[buf]);
+        }
+        if (!failed && m < a.M) {
+            YT* yrow = static_cast<YT*>(a.y) + (uint64_t)m * a.N + n0;
+#pragma unroll
+            for (uint32_t i = 0; i < PF_BN; i++) {
+                if (n0 + i < a.N) {
+                    float v = total[i];
+                    if (a.bias) v += __ldg(a.bias + n0 + i);
+                    if constexpr (sizeof(YT) == 4) yrow[i] = v;
+                    else yrow[i] = f32_to_bf16_bits(v);
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(a.status, QB200_ERR_TIMEOUT);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+}
+
+
+// ---- host side ------------------------------------------------------------------------------------
+
+bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
+                      uint64_t m, int x_dtype, const void* codes, const void* x) {
+    if (bits != 4 || gr != 1 || gc != 128 || layout != QB200_OUT_IN || x_dtype != QB200_BF16) return false;
+    if (m < 64 || m > 0x7FFFFFFF || in_dim % 128 != 0 || in_dim > 16384 || out_dim > 0x7FFFFFFF) return false;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    return al(codes) && al(x);
+}
+
+// Scratch the prefill path needs for m rows: X' (m * K bf16) followed by corr (m * K/128 f32).
+uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim) {
+    const uint64_t xs = (m * in_dim * 2 + 255) & ~uint64_t(255);
+    return xs + m * (in_dim / 128) * 4;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
+    const uint32_t M = (uint32_t)f.m, N = (uint32_t)f.out_dim, K = (uint32_t)f.in_dim, groups = K / 128;
+    uint16_t* xs = static_cast<uint16_t*>(scratch);
+    float* corr = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + (((uint64_t)M * K * 2 + 255) & ~uint64_t(255)));
+    {
+        const uint64_t units = (uint64_t)M * groups;
+        k_prefill_prep<<<(uint32_t)((units + 7) / 8), 256, 0, st>>>(static_cast<const uint16_t*>(f.x), M, K, xs, corr);
+        QB_CUDA_TRY(cudaGetLastError());
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {K, M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {PF_BK, PF_BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled failed with code " + std::to_string((int)cr));
+
+    PrefillArgs a;
+    a.codes = static_cast<const uint32_t*>(f.codes);
+    a.scales = f.scales;
+    a.bias = f.bias;
+    a.corr = corr;
+    a.y = f.y;
+    a.status = status;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    const uint32_t smem = 1024 + 2 * PF_STAGES * 16384 + groups * 512 + 256;
+    dim3 grid((N + PF_BN - 1) / PF_BN, (M + PF_BM - 1) / PF_BM);
+    static bool attr_set[2][64] = {};
+    int dev = 0;
+    QB_CUDA_TRY(cudaGetDevice(&dev));
+    if (y_dtype == QB200_F32) {
+        if (!attr_set[0][dev & 63]) {
+            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            attr_set[0][dev & 63] = true;
+        }
+        k_gemm_i4_tc<float><<<grid, PF_THREADS, smem, st>>>(map, a);
+    } else {
+        if (!attr_set[1][dev & 63]) {
+            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            attr_set[1][dev & 63] = true;
+        }
+        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, smem, st>>>(map, a);
+    }
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+}  // namespace qb

@@ -389,3 +389,47 @@ def test_forward_many_matches_per_layer_forward():
     x = torch.randn(2, 1024, device=DEV).to(torch.bfloat16)
     got = qb.QuantizedLinear.forward_many([qls[0], q8], [x, x], out_dtype=torch.float32)
     assert torch.equal(got[1], q8.forward(x, out_dtype=torch.float32)) and q8.last_kernel() == "generic_rows"
+
+
+# ---- the prefill GEMM on tcgen05 -------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 256, 256), (256, 384, 1024), (200, 300, 512), (64, 130, 2048), (333, 128, 4096)])
+def test_prefill_gemm_against_oracle(M, N, K):
+    """Stated staging: codes enter the tensor core as exact integers, activations as exact bf16, f32
+    accumulation per 128-k group, the f32 scale applied to the group sum.  Checker: f64 accumulation of
+    bf16(x) * (s * q) — no rounding of the weights — at the 1e-3 bound."""
+    rng = np.random.default_rng(M * 31 + N * 7 + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int4, qb.Group(1, 128))
+    wd = o.dequantize_host(oc, os_, N, K, 4, 1, 128)
+    xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
+    ql = qb.QuantizedLinear.new(m, t(bias), qb.OUT_IN)
+    y = ql.forward(xt, out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemm_tcgen05"
+    close(y.cpu().numpy(), want, 1e-3)
+    yb = ql.forward(xt)
+    assert yb.dtype == torch.bfloat16
+    close(yb.to(torch.float32).cpu().numpy(), want, 1e-2)
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
+def test_prefill_gemm_config3_full_size_properties():
+    """int4 prefill at the BASELINE size (X [2048, 4096], W [11008, 4096]): against an f32 matmul over the
+    bit-exact dequantized weight, and linearity in x."""
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    w = torch.randn(11008, 4096, device=DEV, generator=gen) * 0.02
+    x = torch.randn(2048, 4096, device=DEV, generator=gen).to(torch.bfloat16)
+    m = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
+    ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    y = ql.forward(x, out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemm_tcgen05"
+    ref = x.to(torch.float32) @ m.dequantize().t()
+    assert bool(((y - ref).abs() <= 1e-3 * (1 + ref.abs())).all())
+    y2 = ql.forward((x.to(torch.float32) * 2).to(torch.bfloat16), out_dtype=torch.float32)  # exact doubling in bf16
+    assert bool(((y2 - 2 * y).abs() <= 1e-5 * (1 + y.abs())).all())
+    yb = ql.forward(x)
+    assert bool(((yb.to(torch.float32) - ref).abs() <= 1e-2 * (1 + ref.abs())).all())
