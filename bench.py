@@ -7,8 +7,10 @@
 Headline workload: the int4 decode GEMV configuration — QuantizedLinear forward over
 resident int4 codes `[4096, 4096]` (packed, low nibble = even k) with a 1x128 f32 scale
 grid, X bf16 `[M=1, 4096]`, f32 out.  One "step" is one pass over LAYERS distinct weight
-matrices (one forward launch each); the matrices together exceed L2, so every launch
-streams its codes from HBM.  Inputs are seeded synthetic data of the stated shapes.
+matrices that read the same X (independent projections, as fused QKV / gate+up are): by
+default one grouped call (qb200_qlinear_forward_many, one persistent launch), with
+--launch per-layer one qb200_qlinear_forward launch per matrix.  The matrices together
+exceed L2, so their codes stream from HBM.  Inputs are seeded synthetic data of the stated shapes.
 
 Metric: weight GB/s = algorithmic bytes (codes + scales + X + Y) of all launches / time.
 With N > 1 every rank holds its own `[4096, 4096]` column shard of a `[4096*N, 4096]` layer
@@ -129,15 +131,18 @@ def run_reference(args):
     for _ in range(max(args.warmup, 1)):
         cpu_forward_gbs(args.m, threads, 1, 1)
     vals, t_total = [], 0.0
-    for _ in range(args.steps):
-        v, dt = cpu_forward_gbs(args.m, threads, layers, 1)
+    _, probe = cpu_forward_gbs(args.m, threads, layers, 1)
+    reps = max(1, int(1.0 / max(probe, 1e-3)))   # about one second of CPU work per step
+    steps = min(args.steps, 60)                  # bounded: the whole run stays within minutes
+    for _ in range(steps):
+        v, dt = cpu_forward_gbs(args.m, threads, layers, reps)
         vals.append(v)
         t_total += dt
     value = float(np.mean(vals))
-    sample = f"{layers} of {LAYERS} layers per step, dequantize + sequential-k f32 GEMM, {threads} OpenMP threads"
+    sample = f"{layers} of {LAYERS} layers x {reps} passes per step, dequantize + sequential-k f32 GEMM, {threads} OpenMP threads"
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(args.steps, 1), "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(steps, 1), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{args.m},{K_IN}]",
                    "layers_per_step": layers},
@@ -150,6 +155,50 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------
 # this build's arm
 # ---------------------------------------------------------------------------------------
+
+def measure_extras(torch, qb, dev):
+    """Secondary numbers of the same path on one GPU (device-resident inputs, CUDA events):
+    the int4 prefill GEMM configuration and quantize-on-load, each with its roofline fraction."""
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / iters
+
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(2)
+    M, N, K = 2048, 11008, 4096
+    w = torch.randn(N, K, device=dev, generator=gen) * 0.02
+    x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+    # quantize-on-load: f32 [11008, 4096] (180 MB, larger than L2) -> int4 1x128 and int8 32x32
+    for name, dt, gran, wbytes in [("quantize_int4_1x128", qb.QuantDtype.Int4, qb.Group(1, 128), N * K // 2 + N * (K // 128) * 4),
+                                   ("quantize_int8_32x32", qb.QuantDtype.Int8, qb.Block(32, 32), N * K + (N // 32) * (K // 32) * 4)]:
+        ms = timed(lambda: qb.QuantizedMatrix.quantize(w, dt, gran), 10)
+        out[name] = {"read_GB/s": N * K * 4 / ms / 1e6, "ms": ms, "roofline_frac": (N * K * 4 + wbytes) / ms / 1e6 / hbm,
+                     "shape": [N, K]}
+    qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
+    ms = timed(lambda: qm.dequantize(), 10)
+    out["dequantize_int4_1x128"] = {"write_GB/s": N * K * 4 / ms / 1e6, "ms": ms,
+                                    "roofline_frac": (N * K * 4.5 + N * (K // 128) * 4) / ms / 1e6 / hbm, "shape": [N, K]}
+    ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
+    ms = timed(lambda: ql.forward(x), 10)
+    out["prefill_int4_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
+                                "peak_TFLOP/s": tf, "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}
+    return out
+
 
 def run_ours(args):
     import torch
@@ -225,7 +274,10 @@ def run_ours(args):
             eager_step()
         step = graph.replay
         stream = torch.cuda.current_stream(dev)
-    # spin the clocks up and keep the sampler busy for at least half a second before timing
+    # spin the clocks up for at least half a second before timing; the clock sampler runs from here
+    # to the end of the timed region (same kernel, same load)
+    clocks = ClockSampler(local)
+    clocks.__enter__()
     t_spin = time.perf_counter()
     n_warm = 0
     while n_warm < max(args.warmup, 3) or (not args.profile and time.perf_counter() - t_spin < 0.5):
@@ -235,13 +287,13 @@ def run_ours(args):
             torch.cuda.synchronize(dev)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        barrier()
-        e0.record(stream)
-        for _ in range(args.steps):
-            step()
-        e1.record(stream)
-        barrier()
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    clocks.__exit__()
     ms = e0.elapsed_time(e1)
     if world > 1:
         tmax = torch.tensor([ms], device=dev)
@@ -254,11 +306,18 @@ def run_ours(args):
     # end to end through the host-buffer entry point: pinned host X in, host Y out, every launch
     xh = torch.empty(m, K_IN, dtype=torch.bfloat16).pin_memory()
     xh.copy_(x.cpu())
-    yh = torch.empty(m, N_OUT, dtype=torch.float32).pin_memory()
+    yh = torch.empty(LAYERS, m, N_OUT, dtype=torch.float32).pin_memory()
+    xhp = (_lib.vp * LAYERS)(*[xh.data_ptr()] * LAYERS)
+    yhp = (_lib.vp * LAYERS)(*[yh[i].data_ptr() for i in range(LAYERS)])
 
     def step_host():
-        for ql in layers:
-            st = lib.qb200_qlinear_forward_host(ql._h, xh.data_ptr(), _lib.BF16, m, yh.data_ptr(), _lib.F32)
+        if grouped:  # one call: x copied once, one persistent launch, every layer's y copied back
+            st = lib.qb200_qlinear_forward_many_host(hs, LAYERS, xhp, _lib.BF16, m, yhp, _lib.F32)
+            if st:
+                raise RuntimeError(_lib.last_error())
+            return
+        for i, ql in enumerate(layers):
+            st = lib.qb200_qlinear_forward_host(ql._h, xh.data_ptr(), _lib.BF16, m, yh[i].data_ptr(), _lib.F32)
             if st:
                 raise RuntimeError(_lib.last_error())
 
@@ -291,18 +350,23 @@ def run_ours(args):
                                  (", eager" if args.no_graph else ", cuda graph replay"),
                        "parallelism": "single GPU" if world == 1 else f"column-sharded x{world} + all-gather per layer"},
             "clocks": clocks.summary(),
-            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": LAYERS * m * K_IN * 2,
-                    "d2h_bytes_per_step": LAYERS * m * N_OUT * 4},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": (1 if grouped else LAYERS) * m * K_IN * 2,
+                    "d2h_bytes_per_step": LAYERS * m * N_OUT * 4,
+                    "call": "qb200_qlinear_forward_many_host" if grouped else "qb200_qlinear_forward_host"},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": which, "launch_us": per_launch_s * 1e6},
         }
+        if world == 1 and not args.profile and not args.no_extras:
+            line["extras"] = measure_extras(torch, qb, dev)
         if world == 1 and not args.no_cpu and not args.profile:
             import oracle as o
             threads = o.max_threads()
             v, dt = cpu_forward_gbs(m, threads, 2, 2)
+            reps = max(2, int(10.0 / max(dt / 2, 1e-3)))  # about ten seconds of CPU work
+            v, dt = cpu_forward_gbs(m, threads, 2, reps)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
-                                    "sample": f"2 of {LAYERS} layers x 2 passes ({dt:.1f} s), dequantize + sequential-k "
+                                    "sample": f"2 of {LAYERS} layers x {reps} passes ({dt:.1f} s), dequantize + sequential-k "
                                               f"f32 GEMM, {threads} OpenMP threads"}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -312,7 +376,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows (1, 4 or 16 for the decode configuration)")
@@ -322,6 +386,7 @@ def main():
                     help="grouped: the step's layers go through qb200_qlinear_forward_many (one persistent launch); "
                          "per-layer: one qb200_qlinear_forward launch per layer")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

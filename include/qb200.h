@@ -175,6 +175,13 @@ QB200_API qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, 
                                         const void* const* x_dev, int32_t x_dtype, uint64_t m,
                                         void* const* y_dev, int32_t y_dtype, void* stream);
 
+/* qb200_qlinear_forward_many over HOST buffers: every distinct input pointer is
+ * copied to the device once, the forwards run, all outputs are copied back and
+ * the call synchronises.  Staging buffers belong to layers[0] and grow on demand. */
+QB200_API qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint32_t count,
+                                             const void* const* x_host, int32_t x_dtype, uint64_t m,
+                                             void* const* y_host, int32_t y_dtype);
+
 /* Synchronises `stream` and reads the handle's device status word: kernels whose
  * bounded waits (on an async copy) ran out of polls record QB200_ERR_TIMEOUT there
  * and return early instead of spinning.  No counterpart in the reference (its

@@ -203,6 +203,55 @@ qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t c
     return QB200_OK;
 }
 
+qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint32_t count, const void* const* x_host,
+                                             int32_t x_dtype, uint64_t m, void* const* y_host, int32_t y_dtype) {
+    if (count == 0 || m == 0) return QB200_OK;
+    if (!layers || !x_host || !y_host) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_host: null argument");
+    qb200_qlinear* lead = layers[0];
+    if (!lead) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_host: null entry 0");
+    // every distinct input is copied once; outputs are packed back to back in one staging buffer
+    std::vector<uint64_t> x_off(count), y_off(count);
+    std::vector<const void*> uniq;
+    std::vector<uint64_t> uniq_off;
+    uint64_t xb = 0, yb = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        if (!layers[i] || !x_host[i] || !y_host[i])
+            return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_host: null entry " + std::to_string(i));
+        size_t k = 0;
+        while (k < uniq.size() && uniq[k] != x_host[i]) k++;
+        if (k == uniq.size()) {
+            uniq.push_back(x_host[i]);
+            uniq_off.push_back(xb);
+            xb += (m * layers[i]->in_dim * dtype_size(x_dtype) + 255) & ~uint64_t(255);
+        }
+        x_off[i] = uniq_off[k];
+        y_off[i] = yb;
+        yb += (m * layers[i]->out_dim * dtype_size(y_dtype) + 255) & ~uint64_t(255);
+    }
+    if (qb200_status s = grow(&lead->x_stage, &lead->x_stage_bytes, xb)) return s;
+    if (qb200_status s = grow(&lead->y_stage, &lead->y_stage_bytes, yb)) return s;
+    if (!lead->host_stream) QB_CUDA_TRY(cudaStreamCreateWithFlags(&lead->host_stream, cudaStreamNonBlocking));
+    cudaStream_t st = lead->host_stream;
+    for (size_t k = 0; k < uniq.size(); k++) {
+        uint64_t in_dim = 0;
+        for (uint32_t i = 0; i < count; i++)
+            if (x_host[i] == uniq[k]) in_dim = layers[i]->in_dim;
+        QB_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(lead->x_stage) + uniq_off[k], uniq[k],
+                                    m * in_dim * dtype_size(x_dtype), cudaMemcpyHostToDevice, st));
+    }
+    std::vector<const void*> xd(count);
+    std::vector<void*> yd(count);
+    for (uint32_t i = 0; i < count; i++) {
+        xd[i] = static_cast<uint8_t*>(lead->x_stage) + x_off[i];
+        yd[i] = static_cast<uint8_t*>(lead->y_stage) + y_off[i];
+    }
+    if (qb200_status s = qb200_qlinear_forward_many(layers, count, xd.data(), x_dtype, m, yd.data(), y_dtype, st)) return s;
+    for (uint32_t i = 0; i < count; i++)
+        QB_CUDA_TRY(cudaMemcpyAsync(y_host[i], yd[i], m * layers[i]->out_dim * dtype_size(y_dtype), cudaMemcpyDeviceToHost, st));
+    QB_CUDA_TRY(cudaStreamSynchronize(st));
+    return QB200_OK;
+}
+
 qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream) {
     if (!ql) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_check: null handle");
     int32_t st = 0;
