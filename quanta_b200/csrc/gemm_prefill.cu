@@ -14,8 +14,8 @@
 // X' and corr live in a scratch buffer owned by the QuantizedLinear handle.
 //
 // One CTA computes a 128 (m) x 128 (n) tile: warp 0 feeds X' tiles by TMA (128B-swizzled),
-// warp 1 issues the MMAs, warps 2-5 unpack codes straight from global memory into the swizzled
-// B tile, warps 6-9 are the TMEM epilogue.  A ring of shared-memory stages and a pair of TMEM
+// warp 1 issues the MMAs, warps 4-7 unpack codes straight from global memory into the swizzled
+// B tile, warps 8-11 are the TMEM epilogue.  A ring of shared-memory stages and a pair of TMEM
 // accumulators keep the four roles overlapped.  Every wait is bounded and reports through the
 // handle's status word.
 #include <cuda.h>
@@ -29,10 +29,11 @@
 namespace qb {
 
 constexpr uint32_t PF_BM = 128, PF_BN = 128, PF_BK = 64;  // tile; BK bf16 = one 128-byte swizzle row
-constexpr uint32_t PF_STAGES = 4;
-constexpr uint32_t PF_THREADS = 320;
+constexpr uint32_t PF_MAX_STAGES = 6;  // ring depth is chosen per shape so the tile's scale / correction tables fit too
+constexpr uint32_t PF_THREADS = 384;  // three warpgroups: feeders (TMA, MMA), unpack, epilogue
 constexpr uint32_t PF_SPIN = 1u << 22;
 #define PF_UNSCALE 9903520314283042199192993792.0f  // 2^93
+#define PF_RESCALE 1.0097419586828951e-28f             // 2^-93
 
 // ---- pre-pass: X' = X * 2^40, corr[m, g] = 8 * sum_{k in g} X[m, k] -----------------------
 // One warp per (row, group of 128): lanes read 8 bytes each.
@@ -129,6 +130,21 @@ __device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, float (&v)[32]) {
 }
 
 
+__device__ __forceinline__ uint64_t pf_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+// (t0, t1) += (s0, s1) * ((v0, v1) + (c, c)) with the packed f32x2 add / fma of sm_100
+__device__ __forceinline__ void pf_fold2(float& t0, float& t1, float s0, float s1, float v0, float v1, uint64_t c2) {
+    asm("{\n\t.reg .b64 t, s, v, d;\n\t"
+        "mov.b64 t, {%0, %1};\n\tmov.b64 s, {%2, %3};\n\tmov.b64 v, {%4, %5};\n\t"
+        "add.rn.f32x2 d, v, %6;\n\tfma.rn.f32x2 t, s, d, t;\n\t"
+        "mov.b64 {%0, %1}, t;\n\t}"
+        : "+f"(t0), "+f"(t1)
+        : "f"(s0), "f"(s1), "f"(v0), "f"(v1), "l"(c2));
+}
+
 struct PrefillArgs {
     const uint32_t* codes;  // [N, K/8]
     const float* scales;    // [N, K/128]
@@ -136,7 +152,7 @@ struct PrefillArgs {
     const float* corr;      // [M, K/128]: 8 * group sums of X
     void* y;                // [M, N] bf16 or f32
     int32_t* status;
-    uint32_t M, N, K;
+    uint32_t M, N, K, stages;
 };
 
 // One packed word -> eight bf16 values (q + 8) * 2^-133 in natural k order (four registers).
@@ -156,15 +172,16 @@ template <typename YT>
 __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK;
+    const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK, PF_STAGES = a.stages;
     uint8_t* sA = smem;                                   // [S][128 rows][128 B]
     uint8_t* sB = smem + PF_STAGES * 16384;               // [S][128 rows][128 B]
     float* s_scales = reinterpret_cast<float*>(smem + 2 * PF_STAGES * 16384);  // [groups][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * PF_STAGES * 16384 + groups * 512);
+    float* s_corr = s_scales + groups * 128;                                   // [groups][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * PF_STAGES * 16384 + groups * 1024);
     uint64_t* full_a = bars;
-    uint64_t* full_b = bars + PF_STAGES;
-    uint64_t* empty = bars + 2 * PF_STAGES;
-    uint64_t* dfull = bars + 3 * PF_STAGES;
+    uint64_t* full_b = bars + PF_MAX_STAGES;
+    uint64_t* empty = bars + 2 * PF_MAX_STAGES;
+    uint64_t* dfull = bars + 3 * PF_MAX_STAGES;
     uint64_t* dempty = dfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
 
@@ -225,24 +242,29 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
                 if (++st == PF_STAGES) { st = 0; par ^= 1; }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 4) {
+        // idle warps of the feeder warpgroup
+    } else if (warp < 8) {
         // ---- unpack warps: thread r owns row n0 + r of the B tile ----
-        const uint32_t r = tid - 64, n = n0 + r;
+        const uint32_t r = tid - 128, n = n0 + r;
         const bool valid = n < a.N;
         const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.codes) + (uint64_t)(valid ? n : 0) * (a.K >> 1));
         const uint32_t row_off = r * 128 + ((r & 7) << 4);  // chunk c lands at (row_off ^ (c << 4))
-        uint4 c0 = valid ? __ldg(src) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-        uint4 c1 = valid ? __ldg(src + 1) : c0;
+        const uint4 zero8 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // nibble 8 -> q + 8 = 0
+        // codes of the next two k-steps are always in flight (registers), hiding the L2 / HBM latency
+        uint4 q0[3], q1[3];
+#pragma unroll
+        for (uint32_t d = 0; d < 2; d++) {
+            q0[d] = (valid && d < num_k) ? __ldg(src + 2 * d) : zero8;
+            q1[d] = (valid && d < num_k) ? __ldg(src + 2 * d + 1) : zero8;
+        }
         uint32_t st = 0, par = 0;
         for (uint32_t s = 0; s < num_k; s++) {
-            uint4 n0v = c0, n1v = c1;
-            if (valid && s + 1 < num_k) {
-                n0v = __ldg(src + 2 * (s + 1));
-                n1v = __ldg(src + 2 * (s + 1) + 1);
-            }
+            q0[2] = (valid && s + 2 < num_k) ? __ldg(src + 2 * (s + 2)) : zero8;
+            q1[2] = (valid && s + 2 < num_k) ? __ldg(src + 2 * (s + 2) + 1) : zero8;
             if (s >= PF_STAGES && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
             uint8_t* dst = sB + st * 16384;
-            const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const uint32_t w[8] = {q0[0].x, q0[0].y, q0[0].z, q0[0].w, q1[0].x, q1[0].y, q1[0].z, q1[0].w};
 #pragma unroll
             for (uint32_t c = 0; c < 8; c++) {
                 uint32_t o[4];
@@ -252,20 +274,23 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) pf_mbar_arrive(&full_b[st]);
-            c0 = n0v;
-            c1 = n1v;
+            q0[0] = q0[1]; q1[0] = q1[1];
+            q0[1] = q0[2]; q1[1] = q1[2];
             if (++st == PF_STAGES) { st = 0; par ^= 1; }
         }
     } else {
         // ---- epilogue warps: thread = accumulator row (TMEM lane) ----
-        const uint32_t e = tid - 192;  // 0..127
+        const uint32_t e = tid - 256;  // 0..127
         {   // scales of the tile, transposed to [group][row] so a thread reads consecutive rows
             const uint32_t n = n0 + e;
-            for (uint32_t g = 0; g < groups; g++) s_scales[g * 128 + e] = n < a.N ? __ldg(a.scales + (uint64_t)n * groups + g) : 0.0f;
+            const uint32_t mr = m0 + e;  // thread e also stages row e's corrections, already in MMA units (negated)
+            for (uint32_t g = 0; g < groups; g++) {
+                s_scales[g * 128 + e] = n < a.N ? __ldg(a.scales + (uint64_t)n * groups + g) : 0.0f;
+                s_corr[g * 128 + e] = mr < a.M ? -__ldg(a.corr + (uint64_t)mr * groups + g) * PF_RESCALE : 0.0f;
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         const uint32_t quad = warp & 3, ml = quad * 32 + lane, m = m0 + ml;
-        const float* corr = a.corr + (uint64_t)(m < a.M ? m : 0) * groups;
         float total[PF_BN];
 #pragma unroll
         for (uint32_t i = 0; i < PF_BN; i++) total[i] = 0.0f;
@@ -273,16 +298,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
             const uint32_t buf = g & 1;
             if (!pf_wait(&dfull[buf], (g >> 1) & 1)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float c = __ldg(corr + g);
-            const float* sg = s_scales + g * 128;
+            // totals are kept in MMA units (2^-93): total += s * (D - corr * 2^-93), two columns per instruction
+            const float c = s_corr[g * 128 + ml];
+            const uint64_t c2 = pf_pack2(c, c);
+            const float4* sg = reinterpret_cast<const float4*>(s_scales + g * 128);
 #pragma unroll
             for (uint32_t ch = 0; ch < 4; ch++) {
                 float v[32];
                 pf_tmem_ld32(tmem_base + ((quad * 32) << 16) + buf * PF_BN + ch * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (uint32_t i = 0; i < 32; i++)
-                    total[ch * 32 + i] = fmaf(sg[ch * 32 + i], fmaf(v[i], PF_UNSCALE, -c), total[ch * 32 + i]);
+                for (uint32_t i = 0; i < 8; i++) {
+                    const float4 s4 = sg[ch * 8 + i];
+                    const uint32_t o = ch * 32 + 4 * i;
+                    pf_fold2(total[o], total[o + 1], s4.x, s4.y, v[4 * i], v[4 * i + 1], c2);
+                    pf_fold2(total[o + 2], total[o + 3], s4.z, s4.w, v[4 * i + 2], v[4 * i + 3], c2);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -293,7 +324,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
 #pragma unroll
             for (uint32_t i = 0; i < PF_BN; i++) {
                 if (n0 + i < a.N) {
-                    float v = total[i];
+                    float v = total[i] * PF_UNSCALE;
                     if (a.bias) v += __ldg(a.bias + n0 + i);
                     if constexpr (sizeof(YT) == 4) yrow[i] = v;
                     else yrow[i] = f32_to_bf16_bits(v);
@@ -370,7 +401,10 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     a.M = M;
     a.N = N;
     a.K = K;
-    const uint32_t smem = 1024 + 2 * PF_STAGES * 16384 + groups * 512 + 256;
+    uint32_t stages = PF_MAX_STAGES;
+    while (stages > 2 && 1024 + 2 * stages * 16384 + groups * 1024 + 256 > 227 * 1024) stages--;
+    a.stages = stages;
+    const uint32_t smem = 1024 + 2 * stages * 16384 + groups * 1024 + 256;
     dim3 grid((N + PF_BN - 1) / PF_BN, (M + PF_BM - 1) / PF_BM);
     static bool attr_set[2][64] = {};
     int dev = 0;

@@ -135,7 +135,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     }
     if (qb::gemm_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev) &&
         qb::gemm_i4_scratch_bytes(m, ql->in_dim) + 1024 + 8 * 16384 + (ql->in_dim / 128) * 512 < (1ull << 40) &&
-        (ql->in_dim / 128) * 512 <= 90 * 1024) {
+        (ql->in_dim / 128) * 1024 <= 160 * 1024) {
         void* p = ql->scratch;
         qb200_status s = grow(&p, &ql->scratch_bytes, qb::gemm_i4_scratch_bytes(m, ql->in_dim));
         ql->scratch = static_cast<float*>(p);
