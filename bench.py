@@ -156,7 +156,7 @@ def run_reference(args):
 # this build's arm
 # ---------------------------------------------------------------------------------------
 
-def measure_extras(torch, qb, dev):
+def measure_extras(torch, qb, dev, only=None, small=False):
     """Secondary numbers of the same path on one GPU (device-resident inputs, CUDA events):
     the int4 prefill GEMM configuration and quantize-on-load, each with its roofline fraction."""
     peaks = {}
@@ -180,10 +180,16 @@ def measure_extras(torch, qb, dev):
 
     out = {}
     gen = torch.Generator(device=dev).manual_seed(2)
-    M, N, K = 2048, 11008, 4096
+    M, N, K = (512, 2048, 4096) if small else (2048, 11008, 4096)
     w = torch.randn(N, K, device=dev, generator=gen) * 0.02
     x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
     # quantize-on-load: f32 [11008, 4096] (180 MB, larger than L2) -> int4 1x128 and int8 32x32
+    if only == "prefill":
+        qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
+        ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
+        ms = timed(lambda: ql.forward(x), 3 if small else 10)
+        return {"prefill_int4_gemm": {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
+                                      "peak_TFLOP/s": tf, "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}}
     for name, dt, gran, wbytes in [("quantize_int4_1x128", qb.QuantDtype.Int4, qb.Group(1, 128), N * K // 2 + N * (K // 128) * 4),
                                    ("quantize_int8_32x32", qb.QuantDtype.Int8, qb.Block(32, 32), N * K + (N // 32) * (K // 32) * 4)]:
         ms = timed(lambda: qb.QuantizedMatrix.quantize(w, dt, gran), 10)
@@ -221,6 +227,11 @@ def run_ours(args):
     LAYERS = args.layers
     m = args.m
     lib = _lib.load()
+    if args.only:  # side workloads alone (used for profiling): prefill GEMM or quantize / dequantize
+        ex = measure_extras(torch, qb, dev, only=args.only, small=args.small)
+        if rank == 0:
+            print(json.dumps({"only": args.only, "extras": ex}), flush=True)
+        return
     # device-side quantize-on-load of this rank's shards (seeded per rank)
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
     layers = []
@@ -387,6 +398,8 @@ def main():
                          "per-layer: one qb200_qlinear_forward launch per layer")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
+    ap.add_argument("--only", default=None, choices=["prefill", "quantize"], help="run only a side workload and print its numbers")
+    ap.add_argument("--small", action="store_true", help="with --only: a reduced shape, for profiler captures")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
