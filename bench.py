@@ -245,7 +245,9 @@ def run_ours(args):
     y_all = torch.empty(world, m, N_OUT, device=dev, dtype=torch.float32) if world > 1 else None
     stream = torch.cuda.current_stream(dev)
 
-    ys = [torch.empty(m, N_OUT, device=dev, dtype=torch.float32) for _ in layers]
+    y_cat = torch.empty(LAYERS, m, N_OUT, device=dev, dtype=torch.float32)
+    ys = [y_cat[i] for i in range(LAYERS)]
+    y_cat_all = torch.empty(world * LAYERS, m, N_OUT, device=dev, dtype=torch.float32) if world > 1 else None
     hs = (_lib.vp * LAYERS)(*[ql._h for ql in layers])
     xp = (_lib.vp * LAYERS)(*[x.data_ptr()] * LAYERS)
     yp = (_lib.vp * LAYERS)(*[t.data_ptr() for t in ys])
@@ -257,9 +259,8 @@ def run_ours(args):
             st = lib.qb200_qlinear_forward_many(hs, LAYERS, xp, _lib.BF16, m, yp, _lib.F32, cur)
             if st:
                 raise RuntimeError(_lib.last_error())
-            if world > 1:
-                for t in ys:
-                    dist.all_gather_into_tensor(y_all, t)
+            if world > 1:  # the step's outputs are independent: one all-gather for all of them
+                dist.all_gather_into_tensor(y_cat_all, y_cat)
             return
         for ql, t in zip(layers, ys):
             st = lib.qb200_qlinear_forward(ql._h, x.data_ptr(), _lib.BF16, m, t.data_ptr(), _lib.F32, cur)
@@ -289,14 +290,25 @@ def run_ours(args):
     # to the end of the timed region (same kernel, same load)
     clocks = ClockSampler(local)
     clocks.__enter__()
-    t_spin = time.perf_counter()
-    n_warm = 0
-    while n_warm < max(args.warmup, 3) or (not args.profile and time.perf_counter() - t_spin < 0.5):
+    # every rank must run the same number of steps (they hold collectives): rank 0 sizes the
+    # spin-up from ten timed steps and broadcasts the count
+    for _ in range(max(args.warmup, 3)):
         step()
-        n_warm += 1
-        if n_warm % 64 == 0:
-            torch.cuda.synchronize(dev)
     barrier()
+    t_spin = time.perf_counter()
+    for _ in range(10):
+        step()
+    barrier()
+    per_step = (time.perf_counter() - t_spin) / 10
+    n_spin = 0 if args.profile else int(min(max(0.5 / max(per_step, 1e-6), 1), 20000))
+    if world > 1:
+        cnt = torch.tensor([n_spin], device=dev, dtype=torch.int64)
+        dist.broadcast(cnt, 0)
+        n_spin = int(cnt.item())
+    for i in range(n_spin):
+        step()
+        if i % 64 == 63:
+            torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(stream)
@@ -359,14 +371,18 @@ def run_ours(args):
                        "layers_per_step": LAYERS, "l2": "inputs larger than L2 (32 distinct weight matrices, 286 MB)",
                        "kernel": layers[0].last_kernel(), "launch": ("one persistent launch per step" if grouped else "one launch per layer") +
                                  (", eager" if args.no_graph else ", cuda graph replay"),
-                       "parallelism": "single GPU" if world == 1 else f"column-sharded x{world} + all-gather per layer"},
+                       "parallelism": "single GPU" if world == 1 else (f"column-sharded x{world}, one all-gather of the step's outputs" if grouped
+                                        else f"column-sharded x{world}, all-gather per layer")},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": (1 if grouped else LAYERS) * m * K_IN * 2,
                     "d2h_bytes_per_step": LAYERS * m * N_OUT * 4,
                     "call": "qb200_qlinear_forward_many_host" if grouped else "qb200_qlinear_forward_host"},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": which, "launch_us": per_launch_s * 1e6},
+                         # dram__bytes_read + write of one ncu capture of an 8-layer launch (72.28 MB),
+                         # scaled by the layers a launch processes (traffic grows in proportion)
+                         "traffic": 72.28e6 / 8 * (LAYERS if grouped else 1) if m == 1 else None,
+                         "peak_source": which, "launch_us": per_launch_s * 1e6},
         }
         if world == 1 and not args.profile and not args.no_extras:
             line["extras"] = measure_extras(torch, qb, dev)
@@ -381,7 +397,11 @@ def run_ours(args):
                                               f"f32 GEMM, {threads} OpenMP threads"}
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the process group down: destroying it while a captured graph that
+        # holds collectives is alive can block
+        barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def main():

@@ -225,4 +225,11 @@ def qlinear_apply(codes, scales, rows, cols, bits, gr, gc, layout, x, bias=None,
 
 
 def max_threads() -> int:
-    return lib().qo_max_threads()
+    """Host threads the timed baselines use: every core this process may run on (launchers such as
+    torchrun pin OMP_NUM_THREADS to 1; the thread count is passed to the library explicitly)."""
+    if lib().qo_max_threads() <= 0:
+        return 1
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
