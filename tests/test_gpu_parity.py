@@ -335,7 +335,7 @@ def test_decode_gemv_shapes(N, K):
         xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
         y = ql.forward(xt, out_dtype=torch.float32)
         # the tensor-pipe GEMV keeps the activations on chip; shapes whose activations do not fit use the generic kernel
-        assert ql.last_kernel() == "gemv_mma" or (K * M * 2 > 100 * 1024 and ql.last_kernel() == "generic_rows")
+        assert ql.last_kernel() == "gemv_mma" or (K > 4096 and ql.last_kernel() == "generic_rows")
         want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
         close(y.cpu().numpy(), want, 1e-4)   # exact codes, f32 accumulate: far inside the stated 1e-3
         yb = ql.forward(xt)                  # bf16 out
