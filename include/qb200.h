@@ -164,6 +164,25 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
 QB200_API qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype,
                                    uint64_t m, void* y_dev, int32_t y_dtype, void* stream);
 
+/* qb200_qlinear_forward for callers that may not allocate device memory (serving
+ * loops with a frozen memory budget, hosts that hand every device buffer to another
+ * runtime, latency-critical code where cudaMalloc's implicit synchronisation is not
+ * acceptable).  No counterpart in the reference.
+ * Serves `[in, out]` handles (QB200_IN_OUT), whose column kernel splits K and needs
+ * room for partial sums: here that room is a 2 MiB array built into the library
+ * image (held by every GPU that loads the library until the process exits) instead
+ * of the handle's grow-on-demand buffer.  The call performs no cudaMalloc / cudaFree.
+ *   - `K slices * m * out_dim` partial sums must fit 2^19 floats; larger calls are
+ *     refused with QB200_ERR_INVALID_PARAM and a message naming the sizes.
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress);
+ *     make that first call outside any stream capture.
+ *   - All calls share the one array: two calls that overlap on the GPU (different
+ *     streams, or different handles) race on it.  Calls ordered on one stream are safe.
+ *     The array keeps the last call's contents; nothing in it needs to start at zero.
+ * Results are identical to qb200_qlinear_forward. */
+QB200_API qb200_status qb200_qlinear_forward_static(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype,
+                                          uint64_t m, void* y_dev, int32_t y_dtype, void* stream);
+
 /* `count` forwards in one call: entry i computes y_dev[i] = layers[i](x_dev[i]), the
  * result of calling qb200_qlinear_forward once per layer in order (the reference
  * stacks layers and loops over Layer::apply,

@@ -48,6 +48,7 @@ SIGNATURES = {
     "qb200_qlinear_in_dim": (u64, [vp]),
     "qb200_qlinear_out_dim": (u64, [vp]),
     "qb200_qlinear_forward": (i32, [vp, vp, i32, u64, vp, i32, vp]),
+    "qb200_qlinear_forward_static": (i32, [vp, vp, i32, u64, vp, i32, vp]),
     "qb200_qlinear_forward_many": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32, vp]),
     "qb200_qlinear_forward_many_host": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32]),
     "qb200_qlinear_check": (i32, [vp, vp]),

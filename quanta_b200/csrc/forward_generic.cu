@@ -12,8 +12,10 @@
 //                N, across CTAs — partial sums go to a scratch buffer and a
 //                second kernel folds them, adds the bias and casts.
 #include <cstdint>
+#include <string>
 
 #include "forward.hpp"
+#include "qlinear_handle.hpp"
 #include "quant_math.cuh"
 
 namespace qb {
@@ -250,3 +252,63 @@ qb200_status forward_generic(const FwdArgs& a, uint32_t bits, int x_dtype, int y
 }
 
 }  // namespace qb
+
+// ---- forward without any allocation ------------------------------------------------------------
+// Some callers may not allocate device memory at all: latency-critical code where cudaMalloc's
+// implicit synchronisation is not acceptable, real-time serving loops with a fixed memory
+// budget, and hosts that pre-register every device buffer with another runtime.  For them the split-K partial sums of the column kernel live in a fixed
+// array inside the library image instead of a cudaMalloc'd buffer.  Every GPU that loads the
+// library holds these 2 MiB until the process exits.
+
+namespace qb {
+constexpr uint64_t STATIC_SCRATCH_FLOATS = 1ull << 19;  // 2 MiB: slices * m * out_dim must fit
+}
+static __device__ __align__(256) float g_static_partials[qb::STATIC_SCRATCH_FLOATS];
+
+extern "C" qb200_status qb200_qlinear_forward_static(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype, uint64_t m,
+                                                     void* y_dev, int32_t y_dtype, void* stream) {
+    using qb::fail;
+    if (!ql) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_static: null handle");
+    if (!x_dev || !y_dev) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_static: null device pointer");
+    if ((x_dtype != QB200_F32 && x_dtype != QB200_BF16) || (y_dtype != QB200_F32 && y_dtype != QB200_BF16))
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_static: activations are f32 or bf16");
+    if (ql->layout != QB200_IN_OUT)
+        return fail(QB200_ERR_NOT_SUPPORTED,
+                    "qb200_qlinear_forward_static serves [in, out] weights (the column kernel); an [out, in] "
+                    "handle needs no scratch: call qb200_qlinear_forward");
+    if (m == 0) return QB200_OK;
+    const uint32_t slices = qb::forward_cols_slices(ql->in_dim, ql->out_dim, m);
+    const uint64_t need = slices > 1 ? (uint64_t)slices * m * ql->out_dim : 0;
+    if (need > qb::STATIC_SCRATCH_FLOATS)
+        return fail(QB200_ERR_INVALID_PARAM,
+                    "qb200_qlinear_forward_static: " + std::to_string(slices) + " K slices x m = " + std::to_string(m) +
+                        " x out = " + std::to_string(ql->out_dim) + " needs " + std::to_string(need) +
+                        " partial sums, the built-in scratch holds " + std::to_string(qb::STATIC_SCRATCH_FLOATS) +
+                        " (2 MiB); lower m or call qb200_qlinear_forward");
+    // The array's name is a host-side stand-in here, not a device address: look the address up once
+    // per device, with that device current.
+    static float* scratch_of_device[64] = {};
+    int dev = 0;
+    QB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_static: device index out of range");
+    if (!scratch_of_device[dev]) {
+        float* p = nullptr;
+        QB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials));
+        scratch_of_device[dev] = p;
+    }
+    qb::FwdArgs a;
+    a.codes = ql->codes;
+    a.scales = ql->scales;
+    a.bias = ql->bias;
+    a.x = x_dev;
+    a.y = y_dev;
+    a.m = m;
+    a.in_dim = ql->in_dim;
+    a.out_dim = ql->out_dim;
+    a.gr = ql->gr;
+    a.gc = ql->gc;
+    a.tc = ql->tc;
+    // Nothing needs clearing: the column kernel writes every partial sum the fold kernel reads.
+    return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, false, scratch_of_device[dev], slices,
+                               static_cast<cudaStream_t>(stream));
+}
