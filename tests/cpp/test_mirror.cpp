@@ -1,0 +1,148 @@
+// Parity tests written against the C++ mirror (include/qb200.hpp), in the shape of the reference's
+// own suites: crates/sci/quanta-array/tests/quant.rs and crates/ml/quanta-nn/tests/quant.rs.
+// Expected values are the reference's source literals.  Exit code 0 = all passed.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "qb200.hpp"
+
+using namespace qb200;
+
+static int failures = 0;
+#define EXPECT(cond)                                                      \
+    do {                                                                  \
+        if (!(cond)) {                                                    \
+            std::printf("FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond);   \
+            failures++;                                                   \
+        }                                                                 \
+    } while (0)
+
+static bool bits_eq(const std::vector<float>& a, const std::vector<float>& b) {
+    return a.size() == b.size() && std::memcmp(a.data(), b.data(), a.size() * 4) == 0;
+}
+
+// quanta-array/tests/quant.rs:34-41
+static std::vector<float> weights(size_t n) {
+    std::vector<float> w(n);
+    for (size_t i = 0; i < n; i++) {
+        float x = (float)i * 0.7311f - (float)n * 0.317f;
+        w[i] = (i % 3 == 0) ? -x * 0.13f : x * 0.171f;
+    }
+    return w;
+}
+
+int main() {
+    // dequant_ties_to_even_pinned_int8 / int4 (tests/quant.rs:177-205)
+    {
+        auto a = DeviceArray<float>::from_slice({63.5f, -63.5f, 0.25f, 0.26f, 0.75f, -0.75f, 1.0f, 0.0f}, {2, 4});
+        auto qm = QuantizedMatrix::quantize(a, QuantDtype::Int8, Granularity::PerTensor());
+        EXPECT(qm.scales().to_vec() == std::vector<float>{0.5f});
+        EXPECT(bits_eq(qm.dequantize().to_vec(), {63.5f, -63.5f, 0.0f, 0.5f, 1.0f, -1.0f, 1.0f, 0.0f}));
+        auto b = DeviceArray<float>::from_slice({3.5f, -3.5f, 0.25f, 0.26f, 0.75f, -0.75f, 1.0f, 0.0f}, {2, 4});
+        auto q4 = QuantizedMatrix::quantize(b, QuantDtype::Int4, Granularity::PerTensor());
+        EXPECT(q4.scales().to_vec() == std::vector<float>{0.5f});
+        EXPECT(bits_eq(q4.dequantize().to_vec(), {3.5f, -3.5f, 0.0f, 0.5f, 1.0f, -1.0f, 1.0f, 0.0f}));
+    }
+    // int4_nibble_order_low_first_pinned / rows pack independently (tests/quant.rs:216-243)
+    {
+        auto a = DeviceArray<float>::from_slice({1, 2, -1, -7, 7, 0, 3, -3}, {1, 8});
+        auto qm = QuantizedMatrix::quantize(a, QuantDtype::Int4, Granularity::PerTensor());
+        EXPECT(qm.codes_u32().to_vec() == std::vector<uint32_t>{0xD3079F21u});
+        auto b = DeviceArray<float>::from_slice({1, -1, 2, 3, -2, 7}, {2, 3});
+        auto q2 = QuantizedMatrix::quantize(b, QuantDtype::Int4, Granularity::PerTensor());
+        EXPECT((q2.codes_u32().to_vec() == std::vector<uint32_t>{0x2F1u, 0x7E3u}));
+        EXPECT(bits_eq(q2.dequantize().to_vec(), {1, -1, 2, 3, -2, 7}));
+    }
+    // from_parts (tests/quant.rs:247-282) and its loud errors (:397-435)
+    {
+        auto qm = QuantizedMatrix::from_parts(DeviceArray<int8_t>::from_slice({2, -2, 4, -4}, {2, 2}), 2, 2,
+                                              DeviceArray<float>::from_slice({0.5f, 0.25f}, {2, 1}), Granularity::PerChannel(0));
+        EXPECT((qm.dequantize().to_vec() == std::vector<float>{1, -1, 1, -1}));
+        auto q4 = QuantizedMatrix::from_parts(DeviceArray<uint32_t>::from_slice({0xF1u, 0xE2u}, {2, 1}), 2, 2,
+                                              DeviceArray<float>::from_slice({0.5f, 0.25f}, {2, 1}), Granularity::PerChannel(0));
+        EXPECT((q4.dequantize().to_vec() == std::vector<float>{0.5f, -0.5f, 0.5f, -0.5f}));
+        try {
+            QuantizedMatrix::from_parts(DeviceArray<int8_t>::from_slice({1, 2, 3, 4}, {2, 2}), 4, 2,
+                                        DeviceArray<float>::from_slice({1.0f}, {1, 1}), Granularity::PerTensor());
+            EXPECT(false);
+        } catch (const Error& e) {
+            EXPECT(std::string(e.kind()) == "Grid" && std::string(e.what()).find("[4, 2]") != std::string::npos);
+        }
+        try {
+            Granularity::Group(1, 99).tile(4, 4);
+            EXPECT(false);
+        } catch (const Error& e) {
+            EXPECT(std::string(e.kind()) == "Granularity" && std::string(e.what()).find("99") != std::string::npos);
+        }
+    }
+    // record accessors (tests/quant.rs:322-338)
+    {
+        auto a = DeviceArray<float>::from_slice(weights(35), {5, 7});
+        auto qm = QuantizedMatrix::quantize(a, QuantDtype::Int4, Granularity::Group(0, 3));
+        EXPECT((qm.shape() == std::pair<uint64_t, uint64_t>{5, 7}) && qm.dtype() == QuantDtype::Int4);
+        EXPECT((qm.tile() == std::pair<uint64_t, uint64_t>{3, 1}) && qm.granularity() == Granularity::Group(0, 3));
+        EXPECT((qm.scales().shape() == std::vector<uint64_t>{2, 7}) && (qm.codes_u32().shape() == std::vector<uint64_t>{5, 1}));
+    }
+    // save matches the reference bytes (quanta-nn/tests/quant.rs:80-140), load round trip (:175-237)
+    {
+        auto b = DeviceArray<float>::from_slice({0.5f, -1.5f}, {2});
+        auto w = DeviceArray<float>::from_slice({1, -2, 3, -4, 5, -6, 7, 127}, {2, 4});
+        auto v = DeviceArray<float>::from_slice({7, -2, 3, -4}, {1, 4});
+        auto qw = QuantizedMatrix::quantize(w, QuantDtype::Int8, Granularity::PerTensor());
+        auto qv = QuantizedMatrix::quantize(v, QuantDtype::Int4, Granularity::PerTensor());
+        auto bytes = save_named({{"b", QuantLeaf::F32(b)}, {"w", QuantLeaf::Quantized(qw)}, {"v", QuantLeaf::Quantized(qv)}});
+        const std::string header =
+            "{\"__metadata__\":{\"quant:v\":\"q4s;gr=1;gc=4;rows=1;cols=4\",\"quant:w\":\"q8s;gr=2;gc=4;rows=2;cols=4\","
+            "\"quanta.quant\":\"1\"},\"b\":{\"dtype\":\"F32\",\"shape\":[2],\"data_offsets\":[0,8]},"
+            "\"w.q\":{\"dtype\":\"I8\",\"shape\":[2,4],\"data_offsets\":[8,16]},\"w.qs\":{\"dtype\":\"F32\",\"shape\":[1,1],\"data_offsets\":[16,20]},"
+            "\"v.q\":{\"dtype\":\"U32\",\"shape\":[1,1],\"data_offsets\":[20,24]},\"v.qs\":{\"dtype\":\"F32\",\"shape\":[1,1],\"data_offsets\":[24,28]}}";
+        std::string padded = header;
+        while ((padded.size() + 8) % 8) padded += ' ';
+        EXPECT(bytes.size() == 8 + padded.size() + 28 && std::memcmp(bytes.data() + 8, padded.data(), padded.size()) == 0);
+        const uint8_t want_codes[8] = {0x01, 0xFE, 0x03, 0xFC, 0x05, 0xFA, 0x07, 0x7F};
+        EXPECT(std::memcmp(bytes.data() + 8 + padded.size() + 8, want_codes, 8) == 0);
+        auto loaded = load_named(bytes);
+        EXPECT(loaded.leaves.size() == 3 && loaded.leaves[1].first == "w" && loaded.leaves[2].second.bits == 4);
+        EXPECT(save_named(loaded.leaves) == bytes);
+        bytes[bytes.size() - 1] = 0x7F;  // scale of v becomes non-finite? (0x7F80.. needs two bytes) -> corrupt the exponent
+        bytes[bytes.size() - 2] = 0x80;
+        try {
+            load_named(bytes);
+            EXPECT(false);
+        } catch (const Error& e) {
+            EXPECT(std::string(e.kind()) == "Scale" && std::string(e.what()).find("non-finite") != std::string::npos);
+        }
+    }
+    // QuantizedLinear == Linear(dequantized w) (quanta-nn/tests/quant.rs:467-524), both orientations
+    for (int layout : {QB200_IN_OUT, QB200_OUT_IN}) {
+        const uint64_t r = 64, c = 40, m = 3;
+        auto wv = weights(r * c);
+        for (auto& x : wv) x *= 0.01f;
+        auto qm = QuantizedMatrix::quantize(DeviceArray<float>::from_slice(wv, {r, c}), QuantDtype::Int4, Granularity::Group(0, 8));
+        auto wd = qm.dequantize().to_vec();
+        const uint64_t in = layout == QB200_IN_OUT ? r : c, out = layout == QB200_IN_OUT ? c : r;
+        std::vector<float> bias(out), xh(m * in);
+        for (size_t i = 0; i < bias.size(); i++) bias[i] = 0.01f * (float)i;
+        for (size_t i = 0; i < xh.size(); i++) xh[i] = std::sin((float)i);
+        auto ql = QuantizedLinear::new_(std::move(qm), DeviceArray<float>::from_slice(bias, {out}), layout);
+        EXPECT(ql.in_dim() == in && ql.out_dim() == out);
+        auto y = ql.forward(DeviceArray<float>::from_slice(xh, {m, in})).to_vec();
+        for (uint64_t i = 0; i < m; i++)
+            for (uint64_t j = 0; j < out; j++) {
+                float acc = 0.0f;
+                for (uint64_t k = 0; k < in; k++) acc = acc + xh[i * in + k] * (layout == QB200_IN_OUT ? wd[k * c + j] : wd[j * c + k]);
+                acc += bias[j];
+                EXPECT(std::fabs(y[i * out + j] - acc) <= 1e-4f * (1.0f + std::fabs(acc)));
+            }
+        try {
+            auto q2 = QuantizedMatrix::quantize(DeviceArray<float>::from_slice(wv, {r, c}), QuantDtype::Int8, Granularity::PerTensor());
+            QuantizedLinear::new_(std::move(q2), DeviceArray<float>::from_slice({0, 0, 0}, {3}), layout);
+            EXPECT(false);
+        } catch (const Error& e) {
+            EXPECT(std::string(e.what()).find("bias") != std::string::npos);
+        }
+    }
+    std::printf(failures ? "%d FAILED\n" : "all C++ mirror tests passed\n", failures);
+    return failures ? 1 : 0;
+}
