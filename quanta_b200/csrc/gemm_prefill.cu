@@ -13,11 +13,18 @@
 //     fold total += s[n, g] * (D_g * 2^93 - corr[m, g]) in registers (f32).
 // X' and corr live in a scratch buffer owned by the QuantizedLinear handle.
 //
-// One CTA computes a 128 (m) x 128 (n) tile: warp 0 feeds X' tiles by TMA (128B-swizzled),
-// warp 1 issues the MMAs, warps 4-7 unpack codes straight from global memory into the swizzled
-// B tile, warps 8-11 are the TMEM epilogue.  A ring of shared-memory stages and a pair of TMEM
-// accumulators keep the four roles overlapped.  Every wait is bounded and reports through the
-// handle's status word.
+// A persistent kernel, one CTA per SM, walks 128 (m) x 256 (n) output tiles (m fastest, so the
+// CTAs that run together share code rows in L2).  The tile is wide in n because the int4 side
+// is the cheap one to fetch: per 64-k step a CTA pulls 16 KB of activations and 8 KB of codes
+// for 512 tensor-core cycles of work.  Roles, by warp:
+//   warp 0        TMA producer of X' tiles (128B-swizzled, ring of PF_SA stages)
+//   warp 1        MMA issuer (128 x 256 x 16, two 256-column TMEM accumulators)
+//   warps 2-3     stage the tile's scales and corrections, four groups at a time, transposed
+//   warps 4-7     unpack codes (held PF_PD k-steps ahead in registers) into the swizzled B ring
+//   warps 8-15    TMEM epilogue: per-group promotion into 128 f32 totals per thread, final store
+// Registers are re-balanced between the roles with setmaxnreg (the epilogue keeps a 128 x 256
+// f32 tile).  All rings run across tile boundaries, so one tile's store overlaps the next
+// tile's K loop.  Every wait is bounded and reports through the handle's status word.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdint>
@@ -28,9 +35,14 @@
 
 namespace qb {
 
-constexpr uint32_t PF_BM = 128, PF_BN = 128, PF_BK = 64;  // tile; BK bf16 = one 128-byte swizzle row
-constexpr uint32_t PF_MAX_STAGES = 6;  // ring depth is chosen per shape so the tile's scale / correction tables fit too
-constexpr uint32_t PF_THREADS = 384;  // three warpgroups: feeders (TMA, MMA), unpack, epilogue
+constexpr uint32_t PF_BM = 128, PF_BN = 256, PF_BK = 64;  // tile; BK bf16 = one 128-byte swizzle row
+constexpr uint32_t PF_SA = 6, PF_SB = 3;                  // ring depths: X' stages (16 KB), B stages (32 KB)
+constexpr uint32_t PF_SC = 3, PF_CG = 4;                  // scale ring: slots, groups per slot
+constexpr uint32_t PF_SLOT_FLOATS = PF_CG * (PF_BN + PF_BM);
+constexpr uint32_t PF_PD = 4;                             // k-steps of codes an unpack thread keeps in flight
+constexpr uint32_t PF_THREADS = 512;
+constexpr uint32_t PF_A_BYTES = PF_BM * 128, PF_B_BYTES = PF_BN * 128;
+constexpr uint32_t PF_SMEM = 1024 + PF_SA * PF_A_BYTES + PF_SB * PF_B_BYTES + PF_SC * PF_SLOT_FLOATS * 4 + 256;
 constexpr uint32_t PF_SPIN = 1u << 22;
 #define PF_UNSCALE 9903520314283042199192993792.0f  // 2^93
 #define PF_RESCALE 1.0097419586828951e-28f             // 2^-93
@@ -152,7 +164,8 @@ struct PrefillArgs {
     const float* corr;      // [M, K/128]: 8 * group sums of X
     void* y;                // [M, N] bf16 or f32
     int32_t* status;
-    uint32_t M, N, K, stages;
+    uint32_t M, N, K;
+    uint32_t vec_store;     // 1 when every row of y and the bias take 16-byte accesses
 };
 
 // One packed word -> eight bf16 values (q + 8) * 2^-133 in natural k order (four registers).
@@ -168,40 +181,62 @@ __device__ __forceinline__ void pf_unpack(uint32_t w, uint32_t (&r)[4]) {
     asm("prmt.b32 %0, %1, %2, 0x8783;" : "=r"(r[3]) : "r"(t0), "r"(t1));
 }
 
+// Unpacks the 64 codes of one row and k-step (two 16-byte loads) into the row's 128-byte line of a
+// swizzled B stage: chunk c lands at (row_off ^ (c << 4)).
+__device__ __forceinline__ void pf_unpack_row(uint8_t* dst, uint32_t row_off, const uint4& lo, const uint4& hi) {
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (uint32_t c = 0; c < 8; c++) {
+        uint32_t o[4];
+        pf_unpack(w[c], o);
+        *reinterpret_cast<uint4*>(dst + (row_off ^ (c << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 template <typename YT>
 __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK, PF_STAGES = a.stages;
-    uint8_t* sA = smem;                                   // [S][128 rows][128 B]
-    uint8_t* sB = smem + PF_STAGES * 16384;               // [S][128 rows][128 B]
-    float* s_scales = reinterpret_cast<float*>(smem + 2 * PF_STAGES * 16384);  // [groups][128]
-    float* s_corr = s_scales + groups * 128;                                   // [groups][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * PF_STAGES * 16384 + groups * 1024);
+    const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK;
+    uint8_t* sA = smem;                                      // [SA][128 rows][128 B]
+    uint8_t* sB = sA + PF_SA * PF_A_BYTES;                   // [SB][256 rows][128 B]
+    float* sS = reinterpret_cast<float*>(sB + PF_SB * PF_B_BYTES);  // [SC]{ scales [CG][256], corr [CG][128] }
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sS + PF_SC * PF_SLOT_FLOATS);
     uint64_t* full_a = bars;
-    uint64_t* full_b = bars + PF_MAX_STAGES;
-    uint64_t* empty = bars + 2 * PF_MAX_STAGES;
-    uint64_t* dfull = bars + 3 * PF_MAX_STAGES;
+    uint64_t* empty_a = full_a + PF_SA;
+    uint64_t* full_b = empty_a + PF_SA;
+    uint64_t* empty_b = full_b + PF_SB;
+    uint64_t* sfull = empty_b + PF_SB;
+    uint64_t* sempty = sfull + PF_SC;
+    uint64_t* dfull = sempty + PF_SC;
     uint64_t* dempty = dfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t n0 = blockIdx.x * PF_BN, m0 = blockIdx.y * PF_BM;
+    const uint32_t m_tiles = (a.M + PF_BM - 1) / PF_BM, n_tiles = (a.N + PF_BN - 1) / PF_BN;
+    const uint32_t tiles = m_tiles * n_tiles;  // numbered m-fastest; this CTA takes blockIdx.x, + gridDim.x, ...
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < PF_STAGES; s++) {
+        for (uint32_t s = 0; s < PF_SA; s++) {
             pf_mbar_init(&full_a[s], 1);
+            pf_mbar_init(&empty_a[s], 1);
+        }
+        for (uint32_t s = 0; s < PF_SB; s++) {
             pf_mbar_init(&full_b[s], 4);
-            pf_mbar_init(&empty[s], 1);
+            pf_mbar_init(&empty_b[s], 1);
+        }
+        for (uint32_t s = 0; s < PF_SC; s++) {
+            pf_mbar_init(&sfull[s], 64);
+            pf_mbar_init(&sempty[s], 8);
         }
         for (uint32_t b = 0; b < 2; b++) {
             pf_mbar_init(&dfull[b], 1);
-            pf_mbar_init(&dempty[b], 4);
+            pf_mbar_init(&dempty[b], 8);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // 256 TMEM columns: two 128-column f32 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(pf_smem(tmem_slot)) : "memory");
+    if (warp == 1) {  // all 512 TMEM columns: two 256-column f32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(pf_smem(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -210,124 +245,209 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
 
-    if (warp == 0) {
-        // ---- TMA producer: X' tiles ----
-        if (lane == 0) {
-            uint32_t st = 0, par = 0;
-            for (uint32_t s = 0; s < num_k; s++) {
-                if (s >= PF_STAGES && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
-                pf_mbar_expect_tx(&full_a[st], 16384);
-                pf_tma_load_2d(sA + st * 16384, &xmap, (int32_t)(s * PF_BK), (int32_t)m0, &full_a[st]);
-                if (++st == PF_STAGES) { st = 0; par ^= 1; }
-            }
-        }
-    } else if (warp == 1) {
-        // ---- MMA issuer ----
-        if (lane == 0) {
-            // f32 accumulate, bf16 x bf16, both K-major, N = 128, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_BN >> 3) << 17) | ((PF_BM >> 4) << 24);
-            uint32_t st = 0, par = 0;
-            for (uint32_t s = 0; s < num_k; s++) {
-                const uint32_t g = s >> 1, buf = g & 1;
-                if ((s & 1) == 0 && g >= 2 && !pf_wait(&dempty[buf], ((g >> 1) & 1) ^ 1)) { failed = true; break; }
-                if (!pf_wait(&full_a[st], par) || !pf_wait(&full_b[st], par)) { failed = true; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = pf_desc(pf_smem(sA + st * 16384)), db = pf_desc(pf_smem(sB + st * 16384));
-                const uint32_t d = tmem_base + buf * PF_BN;
-#pragma unroll
-                for (uint32_t kk = 0; kk < PF_BK / 16; kk++)
-                    pf_mma(d, da + 2 * kk, db + 2 * kk, idesc, ((s & 1) | kk) ? 1u : 0u);  // +32 bytes per k16 step
-                pf_commit(&empty[st]);
-                if (s & 1) pf_commit(&dfull[buf]);
-                if (++st == PF_STAGES) { st = 0; par ^= 1; }
-            }
-        }
-    } else if (warp < 4) {
-        // idle warps of the feeder warpgroup
-    } else if (warp < 8) {
-        // ---- unpack warps: thread r owns row n0 + r of the B tile ----
-        const uint32_t r = tid - 128, n = n0 + r;
-        const bool valid = n < a.N;
-        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.codes) + (uint64_t)(valid ? n : 0) * (a.K >> 1));
-        const uint32_t row_off = r * 128 + ((r & 7) << 4);  // chunk c lands at (row_off ^ (c << 4))
-        const uint4 zero8 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // nibble 8 -> q + 8 = 0
-        // codes of the next two k-steps are always in flight (registers), hiding the L2 / HBM latency
-        uint4 q0[3], q1[3];
-#pragma unroll
-        for (uint32_t d = 0; d < 2; d++) {
-            q0[d] = (valid && d < num_k) ? __ldg(src + 2 * d) : zero8;
-            q1[d] = (valid && d < num_k) ? __ldg(src + 2 * d + 1) : zero8;
-        }
-        uint32_t st = 0, par = 0;
-        for (uint32_t s = 0; s < num_k; s++) {
-            q0[2] = (valid && s + 2 < num_k) ? __ldg(src + 2 * (s + 2)) : zero8;
-            q1[2] = (valid && s + 2 < num_k) ? __ldg(src + 2 * (s + 2) + 1) : zero8;
-            if (s >= PF_STAGES && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
-            uint8_t* dst = sB + st * 16384;
-            const uint32_t w[8] = {q0[0].x, q0[0].y, q0[0].z, q0[0].w, q1[0].x, q1[0].y, q1[0].z, q1[0].w};
-#pragma unroll
-            for (uint32_t c = 0; c < 8; c++) {
-                uint32_t o[4];
-                pf_unpack(w[c], o);
-                *reinterpret_cast<uint4*>(dst + (row_off ^ (c << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
-            __syncwarp();
-            if (lane == 0) pf_mbar_arrive(&full_b[st]);
-            q0[0] = q0[1]; q1[0] = q1[1];
-            q0[1] = q0[2]; q1[1] = q1[2];
-            if (++st == PF_STAGES) { st = 0; par ^= 1; }
-        }
-    } else {
-        // ---- epilogue warps: thread = accumulator row (TMEM lane) ----
-        const uint32_t e = tid - 256;  // 0..127
-        {   // scales of the tile, transposed to [group][row] so a thread reads consecutive rows
-            const uint32_t n = n0 + e;
-            const uint32_t mr = m0 + e;  // thread e also stages row e's corrections, already in MMA units (negated)
-            for (uint32_t g = 0; g < groups; g++) {
-                s_scales[g * 128 + e] = n < a.N ? __ldg(a.scales + (uint64_t)n * groups + g) : 0.0f;
-                s_corr[g * 128 + e] = mr < a.M ? -__ldg(a.corr + (uint64_t)mr * groups + g) * PF_RESCALE : 0.0f;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-        const uint32_t quad = warp & 3, ml = quad * 32 + lane, m = m0 + ml;
-        float total[PF_BN];
-#pragma unroll
-        for (uint32_t i = 0; i < PF_BN; i++) total[i] = 0.0f;
-        for (uint32_t g = 0; g < groups; g++) {
-            const uint32_t buf = g & 1;
-            if (!pf_wait(&dfull[buf], (g >> 1) & 1)) { failed = true; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // totals are kept in MMA units (2^-93): total += s * (D - corr * 2^-93), two columns per instruction
-            const float c = s_corr[g * 128 + ml];
-            const uint64_t c2 = pf_pack2(c, c);
-            const float4* sg = reinterpret_cast<const float4*>(s_scales + g * 128);
-#pragma unroll
-            for (uint32_t ch = 0; ch < 4; ch++) {
-                float v[32];
-                pf_tmem_ld32(tmem_base + ((quad * 32) << 16) + buf * PF_BN + ch * 32, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (uint32_t i = 0; i < 8; i++) {
-                    const float4 s4 = sg[ch * 8 + i];
-                    const uint32_t o = ch * 32 + 4 * i;
-                    pf_fold2(total[o], total[o + 1], s4.x, s4.y, v[4 * i], v[4 * i + 1], c2);
-                    pf_fold2(total[o + 2], total[o + 3], s4.z, s4.w, v[4 * i + 2], v[4 * i + 3], c2);
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0) {
+            // ---- TMA producer: X' tiles ----
+            if (lane == 0) {
+                uint32_t sa = 0, par = 0, it = 0;
+                for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
+                    const int32_t m0 = (int32_t)((t % m_tiles) * PF_BM);
+                    for (uint32_t s = 0; s < num_k; s++, it++) {
+                        if (it >= PF_SA && !pf_wait(&empty_a[sa], par ^ 1)) { failed = true; break; }
+                        pf_mbar_expect_tx(&full_a[sa], PF_A_BYTES);
+                        pf_tma_load_2d(sA + sa * PF_A_BYTES, &xmap, (int32_t)(s * PF_BK), m0, &full_a[sa]);
+                        if (++sa == PF_SA) { sa = 0; par ^= 1; }
+                    }
                 }
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) pf_mbar_arrive(&dempty[buf]);
-        }
-        if (!failed && m < a.M) {
-            YT* yrow = static_cast<YT*>(a.y) + (uint64_t)m * a.N + n0;
+        } else if (warp == 1) {
+            // ---- MMA issuer ----
+            if (lane == 0) {
+                // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 128
+                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_BN >> 3) << 17) | ((PF_BM >> 4) << 24);
+                uint32_t sa = 0, pa = 0, sb = 0, pb = 0, gcount = 0;  // gcount: k-groups issued, over all tiles
+                for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
+                    for (uint32_t s = 0; s < num_k; s++) {
+                        const uint32_t buf = gcount & 1;
+                        if ((s & 1) == 0 && gcount >= 2 && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
+                        if (!pf_wait(&full_a[sa], pa) || !pf_wait(&full_b[sb], pb)) { failed = true; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t da = pf_desc(pf_smem(sA + sa * PF_A_BYTES)), db = pf_desc(pf_smem(sB + sb * PF_B_BYTES));
+                        const uint32_t d = tmem_base + buf * PF_BN;
 #pragma unroll
-            for (uint32_t i = 0; i < PF_BN; i++) {
-                if (n0 + i < a.N) {
-                    float v = total[i] * PF_UNSCALE;
-                    if (a.bias) v += __ldg(a.bias + n0 + i);
-                    if constexpr (sizeof(YT) == 4) yrow[i] = v;
-                    else yrow[i] = f32_to_bf16_bits(v);
+                        for (uint32_t kk = 0; kk < PF_BK / 16; kk++)
+                            pf_mma(d, da + 2 * kk, db + 2 * kk, idesc, ((s & 1) | kk) ? 1u : 0u);  // +32 bytes per k16 step
+                        pf_commit(&empty_a[sa]);
+                        pf_commit(&empty_b[sb]);
+                        if (s & 1) { pf_commit(&dfull[buf]); gcount++; }
+                        if (++sa == PF_SA) { sa = 0; pa ^= 1; }
+                        if (++sb == PF_SB) { sb = 0; pb ^= 1; }
+                    }
+                }
+            }
+        } else {
+            // ---- scale stagers: thread j stages rows j, j + 64, ... of the tile, PF_CG groups per slot ----
+            const uint32_t j = tid - 64;
+            uint32_t slot = 0, par = 0, cit = 0;
+            for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
+                const uint32_t n0 = (t / m_tiles) * PF_BN, m0 = (t % m_tiles) * PF_BM;
+                for (uint32_t g0 = 0; g0 < groups; g0 += PF_CG, cit++) {
+                    float sv[4][PF_CG], cv[2][PF_CG];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; i++) {
+                        const uint32_t n = n0 + j + 64 * i;
+#pragma unroll
+                        for (uint32_t g = 0; g < PF_CG; g++)
+                            sv[i][g] = (n < a.N && g0 + g < groups) ? __ldg(a.scales + (uint64_t)n * groups + g0 + g) : 0.0f;
+                    }
+#pragma unroll
+                    for (uint32_t i = 0; i < 2; i++) {
+                        const uint32_t m = m0 + j + 64 * i;
+#pragma unroll
+                        for (uint32_t g = 0; g < PF_CG; g++)
+                            cv[i][g] = (m < a.M && g0 + g < groups) ? __ldg(a.corr + (uint64_t)m * groups + g0 + g) : 0.0f;
+                    }
+                    if (cit >= PF_SC && !pf_wait(&sempty[slot], par ^ 1)) { failed = true; break; }
+                    float* S = sS + slot * PF_SLOT_FLOATS;
+#pragma unroll
+                    for (uint32_t g = 0; g < PF_CG; g++) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; i++) S[g * PF_BN + j + 64 * i] = sv[i][g];
+#pragma unroll
+                        for (uint32_t i = 0; i < 2; i++)  // corrections in MMA units, negated
+                            S[PF_CG * PF_BN + g * PF_BM + j + 64 * i] = -cv[i][g] * PF_RESCALE;
+                    }
+                    pf_mbar_arrive(&sfull[slot]);
+                    if (++slot == PF_SC) { slot = 0; par ^= 1; }
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ---- unpack warps: thread r owns rows r and r + 128 of the B tile ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        const uint32_t r = tid - 128;
+        const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t total = my_tiles * num_k;
+        const uint32_t row_off = r * 128 + ((r & 7) << 4);
+        const uint4 zero8 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // nibble 8 -> q + 8 = 0
+        // load cursor: runs PF_PD k-steps ahead of the unpacking, across tile boundaries
+        uint32_t lt = blockIdx.x, ls = 0, loaded = 0;
+        const uint4 *p0 = nullptr, *p1 = nullptr;
+        auto set_tile = [&](uint32_t t) {
+            const uint32_t n = (t / m_tiles) * PF_BN + r;
+            const uint8_t* base = reinterpret_cast<const uint8_t*>(a.codes);
+            p0 = (t < tiles && n < a.N) ? reinterpret_cast<const uint4*>(base + (uint64_t)n * (a.K >> 1)) : nullptr;
+            p1 = (t < tiles && n + 128 < a.N) ? reinterpret_cast<const uint4*>(base + (uint64_t)(n + 128) * (a.K >> 1)) : nullptr;
+        };
+        auto load = [&](uint4 (&q)[4]) {
+            q[0] = p0 ? __ldg(p0 + 2 * ls) : zero8;
+            q[1] = p0 ? __ldg(p0 + 2 * ls + 1) : zero8;
+            q[2] = p1 ? __ldg(p1 + 2 * ls) : zero8;
+            q[3] = p1 ? __ldg(p1 + 2 * ls + 1) : zero8;
+            loaded++;
+            if (++ls == num_k) { ls = 0; lt += gridDim.x; set_tile(lt); }
+        };
+        set_tile(lt);
+        uint4 q[PF_PD][4];
+#pragma unroll
+        for (uint32_t d = 0; d < PF_PD; d++) {
+            if (loaded < total) load(q[d]);
+        }
+        uint32_t sb = 0, pb = 0, it = 0;
+        while (it < total && !failed) {
+#pragma unroll
+            for (uint32_t d = 0; d < PF_PD; d++) {
+                if (it >= total) break;
+                if (it >= PF_SB && !pf_wait(&empty_b[sb], pb ^ 1)) { failed = true; break; }
+                uint8_t* dst = sB + sb * PF_B_BYTES;
+                pf_unpack_row(dst, row_off, q[d][0], q[d][1]);
+                pf_unpack_row(dst + 128 * 128, row_off, q[d][2], q[d][3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) pf_mbar_arrive(&full_b[sb]);
+                if (loaded < total) load(q[d]);
+                it++;
+                if (++sb == PF_SB) { sb = 0; pb ^= 1; }
+            }
+        }
+    } else {
+        // ---- epilogue warps: thread = accumulator row (TMEM lane), warpgroup = 128-column half ----
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+        const uint32_t quad = warp & 3, half = (warp - 8) >> 2, ml = quad * 32 + lane;
+        uint32_t gcount = 0, slot = 0, spar = 0;
+        for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
+            const uint32_t n0 = (t / m_tiles) * PF_BN + half * 128, m = (t % m_tiles) * PF_BM + ml;
+            float total[128];
+#pragma unroll
+            for (uint32_t i = 0; i < 128; i++) total[i] = 0.0f;
+            for (uint32_t g = 0; g < groups; g++, gcount++) {
+                const uint32_t gi = g & (PF_CG - 1), buf = gcount & 1;
+                if (gi == 0 && !pf_wait(&sfull[slot], spar)) { failed = true; break; }
+                if (!pf_wait(&dfull[buf], (gcount >> 1) & 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // totals are kept in MMA units (2^-93): total += s * (D - corr * 2^-93), two columns per instruction
+                const float* S = sS + slot * PF_SLOT_FLOATS;
+                const float c = S[PF_CG * PF_BN + gi * PF_BM + ml];
+                const uint64_t c2 = pf_pack2(c, c);
+                const float4* sg = reinterpret_cast<const float4*>(S + gi * PF_BN + half * 128);
+#pragma unroll
+                for (uint32_t ch = 0; ch < 4; ch++) {
+                    float v[32];
+                    pf_tmem_ld32(tmem_base + ((quad * 32) << 16) + buf * PF_BN + half * 128 + ch * 32, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; i++) {
+                        const float4 s4 = sg[ch * 8 + i];
+                        const uint32_t o = ch * 32 + 4 * i;
+                        pf_fold2(total[o], total[o + 1], s4.x, s4.y, v[4 * i], v[4 * i + 1], c2);
+                        pf_fold2(total[o + 2], total[o + 3], s4.z, s4.w, v[4 * i + 2], v[4 * i + 3], c2);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) pf_mbar_arrive(&dempty[buf]);
+                if (gi == PF_CG - 1 || g + 1 == groups) {
+                    if (lane == 0) pf_mbar_arrive(&sempty[slot]);
+                    if (++slot == PF_SC) { slot = 0; spar ^= 1; }
+                }
+            }
+            if (!failed && m < a.M && n0 < a.N) {
+                YT* yrow = static_cast<YT*>(a.y) + (uint64_t)m * a.N + n0;
+                const uint32_t ncols = a.N - n0 < 128u ? a.N - n0 : 128u;
+#pragma unroll
+                for (uint32_t i = 0; i < 128; i += 8) {
+                    float v[8];
+#pragma unroll
+                    for (uint32_t e = 0; e < 8; e++) v[e] = total[i + e] * PF_UNSCALE;
+                    if (a.vec_store && i + 8 <= ncols) {
+                        if (a.bias) {
+                            const float4 b0 = __ldg(reinterpret_cast<const float4*>(a.bias + n0 + i));
+                            const float4 b1 = __ldg(reinterpret_cast<const float4*>(a.bias + n0 + i + 4));
+                            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                        }
+                        if constexpr (sizeof(YT) == 4) {
+                            *reinterpret_cast<float4*>(yrow + i) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(yrow + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                        } else {
+                            uint4 o;
+                            o.x = f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
+                            o.y = f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+                            o.z = f32_to_bf16_bits(v[4]) | ((uint32_t)f32_to_bf16_bits(v[5]) << 16);
+                            o.w = f32_to_bf16_bits(v[6]) | ((uint32_t)f32_to_bf16_bits(v[7]) << 16);
+                            *reinterpret_cast<uint4*>(yrow + i) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t e = 0; e < 8; e++) {
+                            if (i + e < ncols) {
+                                const float o = a.bias ? v[e] + __ldg(a.bias + n0 + i + e) : v[e];
+                                if constexpr (sizeof(YT) == 4) yrow[i + e] = o;
+                                else yrow[i + e] = f32_to_bf16_bits(o);
+                            }
+                        }
+                    }
                 }
             }
         }
@@ -335,7 +455,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
     if (failed) atomicExch(a.status, QB200_ERR_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
 }
 
 
@@ -401,26 +521,28 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     a.M = M;
     a.N = N;
     a.K = K;
-    uint32_t stages = PF_MAX_STAGES;
-    while (stages > 2 && 1024 + 2 * stages * 16384 + groups * 1024 + 256 > 227 * 1024) stages--;
-    a.stages = stages;
-    const uint32_t smem = 1024 + 2 * stages * 16384 + groups * 1024 + 256;
-    dim3 grid((N + PF_BN - 1) / PF_BN, (M + PF_BM - 1) / PF_BM);
-    static bool attr_set[2][64] = {};
+    const uint32_t ysz = y_dtype == QB200_F32 ? 4 : 2;
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    a.vec_store = (al16(f.y) && ((uint64_t)N * ysz) % 16 == 0 && (!f.bias || al16(f.bias))) ? 1u : 0u;
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
+    static int sm_count[64] = {};
+    if (!sm_count[dev & 63]) QB_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev));
+    const uint32_t tiles = ((N + PF_BN - 1) / PF_BN) * ((M + PF_BM - 1) / PF_BM);
+    const uint32_t grid = tiles < (uint32_t)sm_count[dev & 63] ? tiles : (uint32_t)sm_count[dev & 63];
+    static bool attr_set[2][64] = {};
     if (y_dtype == QB200_F32) {
         if (!attr_set[0][dev & 63]) {
-            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[0][dev & 63] = true;
         }
-        k_gemm_i4_tc<float><<<grid, PF_THREADS, smem, st>>>(map, a);
+        k_gemm_i4_tc<float><<<grid, PF_THREADS, PF_SMEM, st>>>(map, a);
     } else {
         if (!attr_set[1][dev & 63]) {
-            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[1][dev & 63] = true;
         }
-        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, smem, st>>>(map, a);
+        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(map, a);
     }
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
