@@ -17,10 +17,10 @@
 // CTAs that run together share code rows in L2).  The tile is wide in n because the int4 side
 // is the cheap one to fetch: per 64-k step a CTA pulls 16 KB of activations and 8 KB of codes
 // for 512 tensor-core cycles of work.  Roles, by warp:
-//   warp 0        TMA producer of X' tiles (128B-swizzled, ring of PF_SA stages)
+//   warp 0        TMA producer: X' tiles (128B-swizzled) and packed-code tiles (64B-swizzled)
 //   warp 1        MMA issuer (128 x 256 x 16, two 256-column TMEM accumulators)
 //   warps 2-3     stage the tile's scales and corrections, four groups at a time, transposed
-//   warps 4-7     unpack codes (held PF_PD k-steps ahead in registers) into the swizzled B ring
+//   warps 4-7     unpack the packed codes from shared memory into the swizzled B ring
 //   warps 8-15    TMEM epilogue: per-group promotion into 128 f32 totals per thread, final store
 // Registers are re-balanced between the roles with setmaxnreg (the epilogue keeps a 128 x 256
 // f32 tile).  All rings run across tile boundaries, so one tile's store overlaps the next
@@ -36,18 +36,19 @@
 namespace qb {
 
 constexpr uint32_t PF_BM = 128, PF_BN = 256, PF_BK = 64;  // tile; BK bf16 = one 128-byte swizzle row
-constexpr uint32_t PF_SA = 6, PF_SB = 3;                  // ring depths: X' stages (16 KB), B stages (32 KB)
-constexpr uint32_t PF_SC = 3, PF_CG = 4;                  // scale ring: slots, groups per slot
+constexpr uint32_t PF_SA = 4, PF_SB = 3;                  // ring depths: X' stages (16 KB), B stages (32 KB)
+constexpr uint32_t PF_SQ = 3;                             // ring of packed-code slots: 256 rows x 64 B = one k-group each
+constexpr uint32_t PF_SC = 2, PF_CG = 4;                  // scale ring: slots, groups per slot
 constexpr uint32_t PF_SLOT_FLOATS = PF_CG * (PF_BN + PF_BM);
-constexpr uint32_t PF_PD = 4;                             // k-steps of codes an unpack thread keeps in flight
 constexpr uint32_t PF_THREADS = 512;
-constexpr uint32_t PF_A_BYTES = PF_BM * 128, PF_B_BYTES = PF_BN * 128;
-constexpr uint32_t PF_SMEM = 1024 + PF_SA * PF_A_BYTES + PF_SB * PF_B_BYTES + PF_SC * PF_SLOT_FLOATS * 4 + 256;
+constexpr uint32_t PF_A_BYTES = PF_BM * 128, PF_B_BYTES = PF_BN * 128, PF_Q_BYTES = PF_BN * 64;
+constexpr uint32_t PF_SMEM =
+    1024 + PF_SA * PF_A_BYTES + PF_SB * PF_B_BYTES + PF_SQ * PF_Q_BYTES + PF_SC * PF_SLOT_FLOATS * 4 + 256;
 constexpr uint32_t PF_SPIN = 1u << 22;
 #define PF_UNSCALE 9903520314283042199192993792.0f  // 2^93
 #define PF_RESCALE 1.0097419586828951e-28f             // 2^-93
 
-// ---- pre-pass: X' = X * 2^40, corr[m, g] = 8 * sum_{k in g} X[m, k] -----------------------
+// ---- pre-pass: X' = X * 2^40, corr[g, m] = 8 * sum_{k in g} X[m, k] (group-major) -----------
 // One warp per (row, group of 128): lanes read 8 bytes each.
 __global__ void __launch_bounds__(256) k_prefill_prep(const uint16_t* __restrict__ x, uint32_t M, uint32_t K,
                                                       uint16_t* __restrict__ xs, float* __restrict__ corr) {
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(256) k_prefill_prep(const uint16_t* __restrict
     *reinterpret_cast<uint2*>(xs + off) = make_uint2(w[0], w[1]);
 #pragma unroll
     for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-    if (lane == 0) corr[(uint64_t)m * groups + g] = 8.0f * sum;
+    if (lane == 0) corr[(uint64_t)g * M + m] = 8.0f * sum;
 }
 
 // ---- PTX helpers ------------------------------------------------------------------------------
@@ -161,7 +162,7 @@ struct PrefillArgs {
     const uint32_t* codes;  // [N, K/8]
     const float* scales;    // [N, K/128]
     const float* bias;      // [N] or null
-    const float* corr;      // [M, K/128]: 8 * group sums of X
+    const float* corr;      // [K/128, M]: 8 * group sums of X
     void* y;                // [M, N] bf16 or f32
     int32_t* status;
     uint32_t M, N, K;
@@ -194,19 +195,23 @@ __device__ __forceinline__ void pf_unpack_row(uint8_t* dst, uint32_t row_off, co
 }
 
 template <typename YT>
-__global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, PrefillArgs a) {
+__global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
+                                                                 PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK;
     uint8_t* sA = smem;                                      // [SA][128 rows][128 B]
     uint8_t* sB = sA + PF_SA * PF_A_BYTES;                   // [SB][256 rows][128 B]
-    float* sS = reinterpret_cast<float*>(sB + PF_SB * PF_B_BYTES);  // [SC]{ scales [CG][256], corr [CG][128] }
+    uint8_t* sQ = sB + PF_SB * PF_B_BYTES;                   // [SQ][256 rows][64 B] packed codes
+    float* sS = reinterpret_cast<float*>(sQ + PF_SQ * PF_Q_BYTES);  // [SC]{ scales [CG][256], corr [CG][128] }
     uint64_t* bars = reinterpret_cast<uint64_t*>(sS + PF_SC * PF_SLOT_FLOATS);
     uint64_t* full_a = bars;
     uint64_t* empty_a = full_a + PF_SA;
     uint64_t* full_b = empty_a + PF_SA;
     uint64_t* empty_b = full_b + PF_SB;
-    uint64_t* sfull = empty_b + PF_SB;
+    uint64_t* full_q = empty_b + PF_SB;
+    uint64_t* empty_q = full_q + PF_SQ;
+    uint64_t* sfull = empty_q + PF_SQ;
     uint64_t* sempty = sfull + PF_SC;
     uint64_t* dfull = sempty + PF_SC;
     uint64_t* dempty = dfull + 2;
@@ -224,6 +229,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
         for (uint32_t s = 0; s < PF_SB; s++) {
             pf_mbar_init(&full_b[s], 4);
             pf_mbar_init(&empty_b[s], 1);
+        }
+        for (uint32_t s = 0; s < PF_SQ; s++) {
+            pf_mbar_init(&full_q[s], 1);
+            pf_mbar_init(&empty_q[s], 4);
         }
         for (uint32_t s = 0; s < PF_SC; s++) {
             pf_mbar_init(&sfull[s], 64);
@@ -248,12 +257,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0) {
-            // ---- TMA producer: X' tiles ----
+            // ---- TMA producer: per k-group one packed-code tile, per k-step one X' tile ----
             if (lane == 0) {
-                uint32_t sa = 0, par = 0, it = 0;
+                uint32_t sa = 0, par = 0, it = 0, sq = 0, qpar = 0, qit = 0;
                 for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
-                    const int32_t m0 = (int32_t)((t % m_tiles) * PF_BM);
+                    const int32_t m0 = (int32_t)((t % m_tiles) * PF_BM), n0 = (int32_t)((t / m_tiles) * PF_BN);
                     for (uint32_t s = 0; s < num_k; s++, it++) {
+                        if ((s & 1) == 0) {
+                            if (qit >= PF_SQ && !pf_wait(&empty_q[sq], qpar ^ 1)) { failed = true; break; }
+                            pf_mbar_expect_tx(&full_q[sq], PF_Q_BYTES);
+                            pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)(s * 8), n0, &full_q[sq]);  // x in u32 words
+                            qit++;
+                            if (++sq == PF_SQ) { sq = 0; qpar ^= 1; }
+                        }
                         if (it >= PF_SA && !pf_wait(&empty_a[sa], par ^ 1)) { failed = true; break; }
                         pf_mbar_expect_tx(&full_a[sa], PF_A_BYTES);
                         pf_tma_load_2d(sA + sa * PF_A_BYTES, &xmap, (int32_t)(s * PF_BK), m0, &full_a[sa]);
@@ -297,16 +313,21 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
 #pragma unroll
                     for (uint32_t i = 0; i < 4; i++) {
                         const uint32_t n = n0 + j + 64 * i;
+                        const float* src = a.scales + (uint64_t)n * groups + g0;
+                        if (n < a.N && g0 + PF_CG <= groups && (groups & 3u) == 0) {  // 16-byte aligned: one load
+                            const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+                            sv[i][0] = v.x; sv[i][1] = v.y; sv[i][2] = v.z; sv[i][3] = v.w;
+                        } else {
 #pragma unroll
-                        for (uint32_t g = 0; g < PF_CG; g++)
-                            sv[i][g] = (n < a.N && g0 + g < groups) ? __ldg(a.scales + (uint64_t)n * groups + g0 + g) : 0.0f;
+                            for (uint32_t g = 0; g < PF_CG; g++) sv[i][g] = (n < a.N && g0 + g < groups) ? __ldg(src + g) : 0.0f;
+                        }
                     }
 #pragma unroll
                     for (uint32_t i = 0; i < 2; i++) {
                         const uint32_t m = m0 + j + 64 * i;
 #pragma unroll
                         for (uint32_t g = 0; g < PF_CG; g++)
-                            cv[i][g] = (m < a.M && g0 + g < groups) ? __ldg(a.corr + (uint64_t)m * groups + g0 + g) : 0.0f;
+                            cv[i][g] = (m < a.M && g0 + g < groups) ? __ldg(a.corr + (uint64_t)(g0 + g) * a.M + m) : 0.0f;
                     }
                     if (cit >= PF_SC && !pf_wait(&sempty[slot], par ^ 1)) { failed = true; break; }
                     float* S = sS + slot * PF_SLOT_FLOATS;
@@ -325,55 +346,38 @@ __global__ void __launch_bounds__(PF_THREADS, 1) k_gemm_i4_tc(const __grid_const
         }
     } else if (warp < 8) {
         // ---- unpack warps: thread r owns rows r and r + 128 of the B tile ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         const uint32_t r = tid - 128;
         const uint32_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t total = my_tiles * num_k;
         const uint32_t row_off = r * 128 + ((r & 7) << 4);
-        const uint4 zero8 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // nibble 8 -> q + 8 = 0
-        // load cursor: runs PF_PD k-steps ahead of the unpacking, across tile boundaries
-        uint32_t lt = blockIdx.x, ls = 0, loaded = 0;
-        const uint4 *p0 = nullptr, *p1 = nullptr;
-        auto set_tile = [&](uint32_t t) {
-            const uint32_t n = (t / m_tiles) * PF_BN + r;
-            const uint8_t* base = reinterpret_cast<const uint8_t*>(a.codes);
-            p0 = (t < tiles && n < a.N) ? reinterpret_cast<const uint4*>(base + (uint64_t)n * (a.K >> 1)) : nullptr;
-            p1 = (t < tiles && n + 128 < a.N) ? reinterpret_cast<const uint4*>(base + (uint64_t)(n + 128) * (a.K >> 1)) : nullptr;
-        };
-        auto load = [&](uint4 (&q)[4]) {
-            q[0] = p0 ? __ldg(p0 + 2 * ls) : zero8;
-            q[1] = p0 ? __ldg(p0 + 2 * ls + 1) : zero8;
-            q[2] = p1 ? __ldg(p1 + 2 * ls) : zero8;
-            q[3] = p1 ? __ldg(p1 + 2 * ls + 1) : zero8;
-            loaded++;
-            if (++ls == num_k) { ls = 0; lt += gridDim.x; set_tile(lt); }
-        };
-        set_tile(lt);
-        uint4 q[PF_PD][4];
-#pragma unroll
-        for (uint32_t d = 0; d < PF_PD; d++) {
-            if (loaded < total) load(q[d]);
-        }
-        uint32_t sb = 0, pb = 0, it = 0;
-        while (it < total && !failed) {
-#pragma unroll
-            for (uint32_t d = 0; d < PF_PD; d++) {
-                if (it >= total) break;
-                if (it >= PF_SB && !pf_wait(&empty_b[sb], pb ^ 1)) { failed = true; break; }
-                uint8_t* dst = sB + sb * PF_B_BYTES;
-                pf_unpack_row(dst, row_off, q[d][0], q[d][1]);
-                pf_unpack_row(dst + 128 * 128, row_off, q[d][2], q[d][3]);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) pf_mbar_arrive(&full_b[sb]);
-                if (loaded < total) load(q[d]);
-                it++;
-                if (++sb == PF_SB) { sb = 0; pb ^= 1; }
+        // packed codes: row r of a slot is 64 bytes, its 16-byte chunk c sits at c ^ ((r >> 1) & 3)
+        const uint32_t q_row = r * 64, q_sw = ((r >> 1) & 3) << 4;
+        uint32_t sb = 0, pb = 0, sq = 0, qpar = 0;
+        for (uint32_t it = 0; it < total; it++) {
+            const uint32_t odd = it & 1;  // k-steps per tile are even: parity of the flat index = parity within the group
+            if (!odd && !pf_wait(&full_q[sq], qpar)) { failed = true; break; }
+            const uint8_t* qs = sQ + sq * PF_Q_BYTES + q_row;
+            const uint4 lo0 = *reinterpret_cast<const uint4*>(qs + (((2 * odd) << 4) ^ q_sw));
+            const uint4 hi0 = *reinterpret_cast<const uint4*>(qs + (((2 * odd + 1) << 4) ^ q_sw));
+            const uint4 lo1 = *reinterpret_cast<const uint4*>(qs + 128 * 64 + (((2 * odd) << 4) ^ q_sw));
+            const uint4 hi1 = *reinterpret_cast<const uint4*>(qs + 128 * 64 + (((2 * odd + 1) << 4) ^ q_sw));
+            if (it >= PF_SB && !pf_wait(&empty_b[sb], pb ^ 1)) { failed = true; break; }
+            uint8_t* dst = sB + sb * PF_B_BYTES;
+            pf_unpack_row(dst, row_off, lo0, hi0);
+            pf_unpack_row(dst + 128 * 128, row_off, lo1, hi1);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) {
+                pf_mbar_arrive(&full_b[sb]);
+                if (odd) pf_mbar_arrive(&empty_q[sq]);
             }
+            if (odd && ++sq == PF_SQ) { sq = 0; qpar ^= 1; }
+            if (++sb == PF_SB) { sb = 0; pb ^= 1; }
         }
     } else {
         // ---- epilogue warps: thread = accumulator row (TMEM lane), warpgroup = 128-column half ----
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
         const uint32_t quad = warp & 3, half = (warp - 8) >> 2, ml = quad * 32 + lane;
         uint32_t gcount = 0, slot = 0, spar = 0;
         for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
@@ -510,6 +514,15 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled failed with code " + std::to_string((int)cr));
+    // packed codes as a [N, K/8] u32 tensor: one box = 256 rows x 16 words (one k-group), 64-byte swizzle
+    CUtensorMap qmap;
+    const cuuint64_t qdims[2] = {K / 8, N};
+    const cuuint64_t qstrides[1] = {(cuuint64_t)K / 2};
+    const cuuint32_t qbox[2] = {16, PF_BN};
+    cr = enc(&qmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(f.codes), qdims, qstrides, qbox, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (codes) failed with code " + std::to_string((int)cr));
 
     PrefillArgs a;
     a.codes = static_cast<const uint32_t*>(f.codes);
@@ -536,13 +549,13 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
             QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[0][dev & 63] = true;
         }
-        k_gemm_i4_tc<float><<<grid, PF_THREADS, PF_SMEM, st>>>(map, a);
+        k_gemm_i4_tc<float><<<grid, PF_THREADS, PF_SMEM, st>>>(map, qmap, a);
     } else {
         if (!attr_set[1][dev & 63]) {
             QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[1][dev & 63] = true;
         }
-        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(map, a);
+        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(map, qmap, a);
     }
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
