@@ -115,15 +115,9 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
             return s;
         }
     }
-    if (qb::gemm_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev) &&
-        qb::gemm_i4_scratch_bytes(m, ql->in_dim) + 1024 + 8 * 16384 + (ql->in_dim / 128) * 512 < (1ull << 40) &&
-        (ql->in_dim / 128) * 1024 <= 160 * 1024) {
-        void* p = ql->scratch;
-        qb200_status s = grow(&p, &ql->scratch_bytes, qb::gemm_i4_scratch_bytes(m, ql->in_dim));
-        ql->scratch = static_cast<float*>(p);
-        if (s) return s;
+    if (qb::gemm_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev)) {
         ql->last_kernel = "gemm_tcgen05";
-        return qb::gemm_i4_forward(a, y_dtype, ql->scratch, ql->status, st);
+        return qb::gemm_i4_forward(a, y_dtype, nullptr, ql->status, st);
     }
     if (ql->layout == QB200_OUT_IN) {
         ql->last_kernel = "generic_rows";
