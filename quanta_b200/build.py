@@ -52,7 +52,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         deps += glob.glob(os.path.join(CSRC, "*.hpp")) + glob.glob(os.path.join(CSRC, "*.cuh"))
         if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(p) for p in deps):
             continue
-        flags = [f for f in NVCC_FLAGS if f != "-shared"]
+        flags = [f for f in NVCC_FLAGS if f != "-shared"] + os.environ.get("QB200_NVCC_EXTRA", "").split()
         cmd = [nvcc] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, p in procs:

@@ -30,6 +30,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include "forward.hpp"
@@ -38,12 +40,12 @@
 namespace qb {
 
 constexpr uint32_t PF_TN = 256, PF_TM = 256, PF_BK = 64;  // pair tile; BK bf16 = one 128-byte swizzle row
-constexpr uint32_t PF_SA = 4;                             // ring of unpacked weight stages (128 rows x 128 B)
-constexpr uint32_t PF_SX = 6;                             // ring of activation stages (128 rows x 128 B)
-constexpr uint32_t PF_SQ = 4;                             // ring of packed-code slots (128 rows x 64 B = one k-group)
+constexpr uint32_t PF_S = 5;    // ring of k-steps: 128 unpacked weight rows + 128 activation rows, 128 B each
+constexpr uint32_t PF_SQ = 4;   // ring of packed-code slots (128 rows x 64 B = one k-group)
 constexpr uint32_t PF_THREADS = 512;
 constexpr uint32_t PF_STAGE = 128 * 128, PF_Q_BYTES = 128 * 64;
-constexpr uint32_t PF_SMEM = 1024 + (PF_SA + PF_SX) * PF_STAGE + PF_SQ * PF_Q_BYTES + 512;
+constexpr uint32_t PF_Y_BYTES = 16384;  // output staging per 128-column half of the epilogue
+constexpr uint32_t PF_SMEM = 1024 + 2 * PF_S * PF_STAGE + PF_SQ * PF_Q_BYTES + 2 * PF_Y_BYTES + 512;
 constexpr uint32_t PF_SPIN = 1u << 22;
 
 // ---- PTX helpers ------------------------------------------------------------------------------
@@ -157,12 +159,27 @@ __device__ __forceinline__ void pf_fma2(float& t0, float& t1, uint64_t s2, float
         : "l"(s2), "f"(v0), "f"(v1));
 }
 
+#ifdef QB_PF_TRACE
+#define PF_TR_DECL long long tr_[6] = {0, 0, 0, 0, 0, 0}, tr_t = 0, tr_s = clock64(); (void)tr_t
+#define PF_TR_B tr_t = clock64()
+#define PF_TR_E(i) tr_[i] += clock64() - tr_t
+#define PF_TR_DUMP(role) do { tr_[5] = clock64() - tr_s; if (a.trace && blockIdx.x < 2) for (int i_ = 0; i_ < 6; i_++) a.trace[(blockIdx.x * 8 + role) * 6 + i_] = tr_[i_]; } while (0)
+#else
+#define PF_TR_DECL
+#define PF_TR_B
+#define PF_TR_E(i)
+#define PF_TR_DUMP(role)
+#endif
+
 struct PrefillArgs {
     const float* scales;  // [N, K/128]
     const float* bias;    // [N] or null
     void* y;              // [M, N] bf16 or f32
     int32_t* status;
     uint32_t M, N, K;
+    uint32_t tma_store;  // 1 when Y's base and row pitch are multiples of 16 bytes
+    long long* trace;
+    uint32_t dbg;
 };
 
 // One packed word -> eight bf16 values q / 64 in natural k order (four registers).
@@ -195,23 +212,23 @@ __device__ __forceinline__ void pf_unpack_row(uint8_t* dst, uint32_t row_off, co
 
 template <typename YT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
-    k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap, PrefillArgs a) {
+    k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
+                 const __grid_constant__ CUtensorMap ymap, PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK;
-    uint8_t* sA = smem;                   // [SA][128 weight rows][128 B], unpacked bf16
-    uint8_t* sX = sA + PF_SA * PF_STAGE;  // [SX][128 activation rows][128 B]
-    uint8_t* sQ = sX + PF_SX * PF_STAGE;  // [SQ][128 weight rows][64 B], packed codes
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + PF_SQ * PF_Q_BYTES);
-    uint64_t* full_x = bars;               // this CTA's activation tile has landed (TMA)
-    uint64_t* peer_x = full_x + PF_SX;     // leader: the other CTA's activation tile has landed
-    uint64_t* empty_x = peer_x + PF_SX;    // MMAs that read the stage are done (both CTAs)
-    uint64_t* full_a = empty_x + PF_SX;    // leader: both CTAs' unpacked weight stages are written
-    uint64_t* empty_a = full_a + PF_SA;    // MMAs that read the stage are done (both CTAs)
-    uint64_t* full_q = empty_a + PF_SA;    // packed-code slot has landed (TMA)
-    uint64_t* empty_q = full_q + PF_SQ;    // unpack warps are done with the slot
-    uint64_t* dfull = empty_q + PF_SQ;     // a group's accumulator is complete (both CTAs)
-    uint64_t* dempty = dfull + 2;          // leader: both CTAs' epilogues have read the accumulator
+    uint8_t* sA = smem;                  // [S][128 weight rows][128 B], unpacked bf16
+    uint8_t* sX = sA + PF_S * PF_STAGE;  // [S][128 activation rows][128 B]
+    uint8_t* sQ = sX + PF_S * PF_STAGE;  // [SQ][128 weight rows][64 B], packed codes
+    uint8_t* sY = sQ + PF_SQ * PF_Q_BYTES;  // [2 halves][16 KB] output staging for the TMA store
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sY + 2 * PF_Y_BYTES);
+    uint64_t* full = bars;               // leader: a k-step's operands are complete in BOTH CTAs
+    uint64_t* full_x = full + PF_S;      // non-leader: its own activation tile has landed (TMA)
+    uint64_t* empty = full_x + PF_S;     // the MMAs that read the stage are done (both CTAs)
+    uint64_t* full_q = empty + PF_S;     // packed-code slot has landed (TMA)
+    uint64_t* empty_q = full_q + PF_SQ;  // unpack warps are done with the slot
+    uint64_t* dfull = empty_q + PF_SQ;   // a group's accumulator is complete (both CTAs)
+    uint64_t* dempty = dfull + 2;        // leader: both CTAs' epilogues have read the accumulator
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -223,14 +240,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     const uint32_t total = my_tiles * num_k;   // k-steps this CTA goes through
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < PF_SX; s++) {
+        for (uint32_t s = 0; s < PF_S; s++) {
+            // the leader's TMA (with its bytes), the non-leader's "landed" message, four unpack warps in each CTA
+            pf_mbar_init(&full[s], 10);
             pf_mbar_init(&full_x[s], 1);
-            pf_mbar_init(&peer_x[s], 1);
-            pf_mbar_init(&empty_x[s], 1);
-        }
-        for (uint32_t s = 0; s < PF_SA; s++) {
-            pf_mbar_init(&full_a[s], 8);  // four unpack warps in each CTA
-            pf_mbar_init(&empty_a[s], 1);
+            pf_mbar_init(&empty[s], 1);
         }
         for (uint32_t s = 0; s < PF_SQ; s++) {
             pf_mbar_init(&full_q[s], 1);
@@ -257,60 +271,70 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         if (warp == 0) {
             // ---- TMA producer: per k-group one packed-code tile, per k-step one activation tile ----
             if (lane == 0) {
-                uint32_t sx = 0, px = 0, it = 0, sq = 0, pq = 0, qit = 0;
+                uint64_t* landed = rank == 0 ? full : full_x;  // the leader's tile counts towards `full` directly
+                uint32_t st = 0, par = 0, it = 0, sq = 0, pq = 0, qit = 0;
+                PF_TR_DECL;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
                     const int32_t x_row = (int32_t)((t % m_tiles) * PF_TM + rank * 128);
                     const int32_t q_row = (int32_t)((t / m_tiles) * PF_TN + rank * 128);
                     for (uint32_t s = 0; s < num_k; s++, it++) {
                         if ((s & 1) == 0) {
+                            PF_TR_B;
                             if (qit >= PF_SQ && !pf_wait(&empty_q[sq], pq ^ 1)) { failed = true; break; }
+                            PF_TR_E(0);
                             pf_mbar_expect_tx(&full_q[sq], PF_Q_BYTES);
                             pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)(s * 8), q_row, &full_q[sq]);  // x in u32 words
                             qit++;
                             if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
                         }
-                        if (it >= PF_SX && !pf_wait(&empty_x[sx], px ^ 1)) { failed = true; break; }
-                        pf_mbar_expect_tx(&full_x[sx], PF_STAGE);
-                        pf_tma_load_2d(sX + sx * PF_STAGE, &xmap, (int32_t)(s * PF_BK), x_row, &full_x[sx]);
-                        if (++sx == PF_SX) { sx = 0; px ^= 1; }
+                        PF_TR_B;
+                        if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
+                        PF_TR_E(1);
+                        pf_mbar_expect_tx(&landed[st], PF_STAGE);
+                        pf_tma_load_2d(sX + st * PF_STAGE, &xmap, (int32_t)(s * PF_BK), x_row, &landed[st]);
+                        if (++st == PF_S) { st = 0; par ^= 1; }
                     }
                 }
+                PF_TR_DUMP(0);
             }
         } else if (warp == 1) {
             // ---- MMA issuer (the pair's leader only) ----
             if (lane == 0 && rank == 0) {
                 // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 256 over the pair
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
-                uint32_t sx = 0, px = 0, sa = 0, pa = 0, gcount = 0;  // gcount: k-groups issued, over all tiles
+                uint32_t st = 0, par = 0, gcount = 0;  // gcount: k-groups issued, over all tiles
+                PF_TR_DECL;
                 for (uint32_t it = 0; it < total; it++) {
                     const uint32_t odd = it & 1, buf = gcount & 1;
+                    PF_TR_B;
                     if (!odd && gcount >= 2 && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
-                    if (!pf_wait(&full_x[sx], px) || !pf_wait(&peer_x[sx], px) || !pf_wait(&full_a[sa], pa)) {
-                        failed = true;
-                        break;
-                    }
+                    PF_TR_E(0);
+                    PF_TR_B;
+                    if (!pf_wait(&full[st], par)) { failed = true; break; }
+                    PF_TR_E(1);
+                    PF_TR_B;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t da = pf_desc(pf_smem(sA + sa * PF_STAGE)), db = pf_desc(pf_smem(sX + sx * PF_STAGE));
+                    const uint64_t da = pf_desc(pf_smem(sA + st * PF_STAGE)), db = pf_desc(pf_smem(sX + st * PF_STAGE));
                     const uint32_t d = tmem_base + buf * PF_TM;
 #pragma unroll
                     for (uint32_t kk = 0; kk < PF_BK / 16; kk++)
                         pf_mma_pair(d, da + 2 * kk, db + 2 * kk, idesc, (odd | kk) ? 1u : 0u);  // +32 bytes per k16 step
-                    pf_commit_pair(&empty_x[sx]);
-                    pf_commit_pair(&empty_a[sa]);
+                    pf_commit_pair(&empty[st]);
                     if (odd) { pf_commit_pair(&dfull[buf]); gcount++; }
-                    if (++sx == PF_SX) { sx = 0; px ^= 1; }
-                    if (++sa == PF_SA) { sa = 0; pa ^= 1; }
+                    if (++st == PF_S) { st = 0; par ^= 1; }
+                    PF_TR_E(4);
                 }
+                PF_TR_DUMP(1);
             }
         } else if (warp == 2) {
             // ---- non-leader: pass "activation tile landed" on to the leader's barrier ----
             if (lane == 0 && rank == 1) {
-                const uint32_t remote = pf_map_to_cta(pf_smem(&peer_x[0]), 0);
-                uint32_t sx = 0, px = 0;
+                const uint32_t remote = pf_map_to_cta(pf_smem(&full[0]), 0);
+                uint32_t st = 0, par = 0;
                 for (uint32_t it = 0; it < total; it++) {
-                    if (!pf_wait(&full_x[sx], px)) { failed = true; break; }
-                    pf_mbar_arrive_cluster(remote + sx * 8);
-                    if (++sx == PF_SX) { sx = 0; px ^= 1; }
+                    if (!pf_wait(&full_x[st], par)) { failed = true; break; }
+                    pf_mbar_arrive_cluster(remote + st * 8);
+                    if (++st == PF_S) { st = 0; par ^= 1; }
                 }
             }
         }
@@ -321,34 +345,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         const uint32_t row_off = r * 128 + ((r & 7) << 4);
         // packed codes: row r of a slot is 64 bytes, its 16-byte chunk c sits at c ^ ((r >> 1) & 3)
         const uint32_t q_row = r * 64, q_sw = ((r >> 1) & 3) << 4;
-        const uint32_t remote_full_a = pf_map_to_cta(pf_smem(&full_a[0]), 0);
-        uint32_t sa = 0, pa = 0, sq = 0, pq = 0;
+        const uint32_t remote_full = pf_map_to_cta(pf_smem(&full[0]), 0);
+        uint32_t st = 0, par = 0, sq = 0, pq = 0;
+        PF_TR_DECL;
         for (uint32_t it = 0; it < total; it++) {
             const uint32_t odd = it & 1;  // k-steps per tile are even: parity of the flat index = parity within the group
+            PF_TR_B;
             if (!odd && !pf_wait(&full_q[sq], pq)) { failed = true; break; }
+            PF_TR_E(0);
             const uint8_t* qs = sQ + sq * PF_Q_BYTES + q_row;
             const uint4 lo = *reinterpret_cast<const uint4*>(qs + (((2 * odd) << 4) ^ q_sw));
             const uint4 hi = *reinterpret_cast<const uint4*>(qs + (((2 * odd + 1) << 4) ^ q_sw));
-            if (it >= PF_SA && !pf_wait(&empty_a[sa], pa ^ 1)) { failed = true; break; }
-            pf_unpack_row(sA + sa * PF_STAGE, row_off, lo, hi);
+            PF_TR_B;
+            if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
+            PF_TR_E(1);
+            PF_TR_B;
+            pf_unpack_row(sA + st * PF_STAGE, row_off, lo, hi);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
-                pf_mbar_arrive_cluster(remote_full_a + sa * 8);
+                pf_mbar_arrive_cluster(remote_full + st * 8);
                 if (odd) pf_mbar_arrive(&empty_q[sq]);
             }
             if (odd && ++sq == PF_SQ) { sq = 0; pq ^= 1; }
-            if (++sa == PF_SA) { sa = 0; pa ^= 1; }
+            if (++st == PF_S) { st = 0; par ^= 1; }
+            PF_TR_E(2);
         }
+        if (lane == 0) PF_TR_DUMP(warp - 2);
     } else {
         // ---- epilogue warps: thread = weight row (TMEM lane), warpgroup = 128-column half of the m range ----
         asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
         const uint32_t quad = warp & 3, half = (warp - 8) >> 2, ml = quad * 32 + lane;
         const uint32_t remote_dempty = pf_map_to_cta(pf_smem(&dempty[0]), 0);
         const bool vec_scales = (groups & 3u) == 0;  // a row's scales start on a 16-byte boundary
+        const bool issuer = quad == 0 && lane == 0;  // the thread of this half that issues its TMA stores
+        constexpr uint32_t ROWS = PF_Y_BYTES / (128 * sizeof(YT));  // activation rows per staging pass
+        YT* stage = reinterpret_cast<YT*>(sY + half * PF_Y_BYTES);
         uint32_t gcount = 0;
+        PF_TR_DECL;
         for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-            const uint32_t n = (t / m_tiles) * PF_TN + rank * 128 + ml, m0 = (t % m_tiles) * PF_TM + half * 128;
+            const uint32_t n_cta = (t / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
+            const uint32_t m0 = (t % m_tiles) * PF_TM + half * 128;
             const bool n_ok = n < a.N;
             const float* sp = a.scales + (uint64_t)(n_ok ? n : 0) * groups;
             float total[128];
@@ -374,7 +411,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                 for (uint32_t gi = 0; gi < 4; gi++) {
                     if (g0 + gi >= groups) break;
                     const uint32_t buf = gcount & 1;
+                    PF_TR_B;
                     if (!pf_wait(&dfull[buf], (gcount >> 1) & 1)) { failed = true; break; }
+                    PF_TR_E(0);
+                    PF_TR_B;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t s2 = pf_pack2(cur[gi], cur[gi]);
 #pragma unroll
@@ -390,10 +430,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     __syncwarp();
                     if (lane == 0) pf_mbar_arrive_cluster(remote_dempty + buf * 8);
                     gcount++;
+                    PF_TR_E(1);
                 }
             }
-            if (!failed && n_ok) {  // column i of the accumulator is activation row m0 + i; lanes are consecutive n
-                const float b = a.bias ? __ldg(a.bias + n) : 0.0f;
+            PF_TR_B;
+            if (failed) break;
+            const float b = (a.bias && n_ok) ? __ldg(a.bias + n) : 0.0f;
+            if (a.tma_store) {
+                // column i of the accumulator is activation row m0 + i: ROWS rows at a time go through this half's
+                // staging buffer as [row][128 n] and leave by one TMA store, which clips at the edges of Y
+#pragma unroll
+                for (uint32_t p = 0; p < 128 / ROWS; p++) {
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous store has read the buffer
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+#pragma unroll
+                    for (uint32_t i = 0; i < ROWS; i++) {
+                        const float v = total[p * ROWS + i] + b;
+                        if constexpr (sizeof(YT) == 4) stage[i * 128 + ml] = v;
+                        else stage[i * 128 + ml] = f32_to_bf16_bits(v);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+                    if (issuer) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
+                                     "r"((int32_t)n_cta), "r"((int32_t)(m0 + p * ROWS)), "r"(pf_smem(stage))
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+            } else if (n_ok) {  // rows of Y that TMA cannot address: lanes are consecutive n, 2 or 4 bytes each
                 YT* yp = static_cast<YT*>(a.y) + (uint64_t)m0 * a.N + n;
 #pragma unroll
                 for (uint32_t i = 0; i < 128; i++) {
@@ -404,7 +469,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     }
                 }
             }
+            PF_TR_E(2);
         }
+        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before shared memory goes away
+        if (lane == 0 && (warp == 8 || warp == 12)) PF_TR_DUMP(warp == 8 ? 6 : 7);
     }
     if (failed) atomicExch(a.status, QB200_ERR_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -465,7 +533,22 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (codes) failed with code " + std::to_string((int)cr));
 
+    // Y as a [M, N] tensor: one box = (16 KB / 128 / element size) rows x 128 columns
+    const uint32_t ysz = y_dtype == QB200_F32 ? 4 : 2;
+    const bool tma_store = (reinterpret_cast<uintptr_t>(f.y) & 15u) == 0 && ((uint64_t)N * ysz) % 16 == 0;
+    CUtensorMap ymap = xmap;  // a valid map either way; unused without tma_store
+    if (tma_store) {
+        const cuuint64_t ydims[2] = {N, M};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)N * ysz};
+        const cuuint32_t ybox[2] = {128, PF_Y_BYTES / (128 * ysz)};
+        cr = enc(&ymap, y_dtype == QB200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, f.y, ydims,
+                 ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (output) failed with code " + std::to_string((int)cr));
+    }
+
     PrefillArgs a;
+    a.tma_store = tma_store ? 1u : 0u;
     a.scales = f.scales;
     a.bias = f.bias;
     a.y = f.y;
@@ -473,6 +556,15 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
     a.M = M;
     a.N = N;
     a.K = K;
+    a.trace = nullptr;
+    a.dbg = 0;
+#ifdef QB_PF_TRACE
+    static long long* trace_dev = nullptr;
+    if (!trace_dev) { cudaMalloc(&trace_dev, 2 * 8 * 6 * 8); }
+    cudaMemsetAsync(trace_dev, 0, 2 * 8 * 6 * 8, st);
+    a.trace = trace_dev;
+    a.dbg = getenv("QB_PF_DBG") ? (uint32_t)atoi(getenv("QB_PF_DBG")) : 0;
+#endif
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
     static int sm_count[64] = {};
@@ -486,15 +578,29 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
             QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[0][dev & 63] = true;
         }
-        k_gemm_i4_tc<float><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, a);
+        k_gemm_i4_tc<float><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
     } else {
         if (!attr_set[1][dev & 63]) {
             QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[1][dev & 63] = true;
         }
-        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, a);
+        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
     }
     QB_CUDA_TRY(cudaGetLastError());
+#ifdef QB_PF_TRACE
+    {
+        long long h[2 * 8 * 6];
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h, trace_dev, sizeof(h), cudaMemcpyDeviceToHost);
+        const char* roles[8] = {"tma  [wait_q wait_x - - - total]", "mma  [dempty full_x peer_x full_a issue total]", "unp4 [full_q empty_a work - - total]", "unp5", "unp6", "unp7", "epi8 [dfull work store - - total]", "epi12"};
+        for (int c = 0; c < 2; c++)
+            for (int r = 0; r < 8; r++) {
+                fprintf(stderr, "cta%d %-48s", c, roles[r]);
+                for (int i = 0; i < 6; i++) fprintf(stderr, " %9lld", h[(c * 8 + r) * 6 + i]);
+                fprintf(stderr, "\n");
+            }
+    }
+#endif
     return QB200_OK;
 }
 
