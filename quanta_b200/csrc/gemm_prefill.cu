@@ -19,9 +19,10 @@
 // of shape 256 x 256 x 16, issued by the pair's leader, reads both halves, so every byte staged
 // in shared memory feeds two tensor cores.  Each CTA keeps its 128 x 256 f32 accumulator, twice
 // (double buffered), in its own 512 TMEM columns.  Roles, by warp, in each CTA:
-//   warp 0        TMA producer: activation tiles (128B swizzle), packed-code tiles (64B swizzle)
+//   warp 0        TMA producer of activation tiles (128B swizzle)
 //   warp 1        TMEM allocation; in the leader, the MMA issuer
 //   warp 2        in the non-leader, tells the leader when an activation tile has landed
+//   warp 3        TMA producer of packed-code tiles (64B swizzle), up to PF_SQ k-groups ahead
 //   warps 4-7     unpack the packed codes from shared memory into the swizzled weight ring
 //   warps 8-15    TMEM epilogue: per-group promotion into 128 f32 totals per thread, final store
 // Registers are re-balanced between the roles with setmaxnreg.  All rings run across tile
@@ -269,24 +270,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0) {
-            // ---- TMA producer: per k-group one packed-code tile, per k-step one activation tile ----
+            // ---- TMA producer of activation tiles, one per k-step ----
             if (lane == 0) {
                 uint64_t* landed = rank == 0 ? full : full_x;  // the leader's tile counts towards `full` directly
-                uint32_t st = 0, par = 0, it = 0, sq = 0, pq = 0, qit = 0;
+                uint32_t st = 0, par = 0, it = 0;
                 PF_TR_DECL;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
                     const int32_t x_row = (int32_t)((t % m_tiles) * PF_TM + rank * 128);
-                    const int32_t q_row = (int32_t)((t / m_tiles) * PF_TN + rank * 128);
                     for (uint32_t s = 0; s < num_k; s++, it++) {
-                        if ((s & 1) == 0) {
-                            PF_TR_B;
-                            if (qit >= PF_SQ && !pf_wait(&empty_q[sq], pq ^ 1)) { failed = true; break; }
-                            PF_TR_E(0);
-                            pf_mbar_expect_tx(&full_q[sq], PF_Q_BYTES);
-                            pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)(s * 8), q_row, &full_q[sq]);  // x in u32 words
-                            qit++;
-                            if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
-                        }
                         PF_TR_B;
                         if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
                         PF_TR_E(1);
@@ -337,6 +328,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     if (++st == PF_S) { st = 0; par ^= 1; }
                 }
             }
+        } else if (warp == 3) {
+            // ---- TMA producer of packed-code tiles, one per k-group; runs ahead of the activation ring ----
+            if (lane == 0) {
+                uint32_t sq = 0, pq = 0, qit = 0;
+                for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
+                    const int32_t q_row = (int32_t)((t / m_tiles) * PF_TN + rank * 128);
+                    for (uint32_t g = 0; g < groups; g++, qit++) {
+                        if (qit >= PF_SQ && !pf_wait(&empty_q[sq], pq ^ 1)) { failed = true; break; }
+                        pf_mbar_expect_tx(&full_q[sq], PF_Q_BYTES);
+                        pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)(g * 16), q_row, &full_q[sq]);  // x in u32 words
+                        if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
+                    }
+                }
+            }
         }
     } else if (warp < 8) {
         // ---- unpack warps: thread r owns weight row r of this CTA's half ----
@@ -348,27 +353,34 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         const uint32_t remote_full = pf_map_to_cta(pf_smem(&full[0]), 0);
         uint32_t st = 0, par = 0, sq = 0, pq = 0;
         PF_TR_DECL;
-        for (uint32_t it = 0; it < total; it++) {
-            const uint32_t odd = it & 1;  // k-steps per tile are even: parity of the flat index = parity within the group
+        // one k-group (two k-steps, one packed-code slot) per iteration: one fence and one round of
+        // barrier latencies for 16 independent words per thread
+        for (uint32_t it = 0; it < total; it += 2) {
             PF_TR_B;
-            if (!odd && !pf_wait(&full_q[sq], pq)) { failed = true; break; }
+            if (!pf_wait(&full_q[sq], pq)) { failed = true; break; }
             PF_TR_E(0);
             const uint8_t* qs = sQ + sq * PF_Q_BYTES + q_row;
-            const uint4 lo = *reinterpret_cast<const uint4*>(qs + (((2 * odd) << 4) ^ q_sw));
-            const uint4 hi = *reinterpret_cast<const uint4*>(qs + (((2 * odd + 1) << 4) ^ q_sw));
+            uint4 q[4];
+#pragma unroll
+            for (uint32_t c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4*>(qs + ((c << 4) ^ q_sw));
+            const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
             PF_TR_B;
             if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
+            if (it + 1 >= PF_S && !pf_wait(&empty[st1], par1 ^ 1)) { failed = true; break; }
             PF_TR_E(1);
             PF_TR_B;
-            pf_unpack_row(sA + st * PF_STAGE, row_off, lo, hi);
+            pf_unpack_row(sA + st * PF_STAGE, row_off, q[0], q[1]);
+            pf_unpack_row(sA + st1 * PF_STAGE, row_off, q[2], q[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
             __syncwarp();
             if (lane == 0) {
                 pf_mbar_arrive_cluster(remote_full + st * 8);
-                if (odd) pf_mbar_arrive(&empty_q[sq]);
+                pf_mbar_arrive_cluster(remote_full + st1 * 8);
+                pf_mbar_arrive(&empty_q[sq]);
             }
-            if (odd && ++sq == PF_SQ) { sq = 0; pq ^= 1; }
-            if (++st == PF_S) { st = 0; par ^= 1; }
+            if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
+            st = st1 + 1 == PF_S ? 0 : st1 + 1;
+            par = st1 + 1 == PF_S ? par1 ^ 1 : par1;
             PF_TR_E(2);
         }
         if (lane == 0) PF_TR_DUMP(warp - 2);
