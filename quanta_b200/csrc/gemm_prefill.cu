@@ -84,6 +84,24 @@ __device__ __forceinline__ bool pf_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
+// One poll of a barrier phase (non-blocking): lets the next k-step's check overlap the MMA issue.
+__device__ __forceinline__ uint32_t pf_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(pf_smem(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ uint32_t pf_elect() {
+    uint32_t e;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(e));
+    return e;
+}
 __device__ __forceinline__ uint32_t pf_cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -290,10 +308,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             }
         } else if (warp == 1) {
             // ---- MMA issuer (the pair's leader only) ----
-            if (lane == 0 && rank == 0) {
+            // The whole warp runs the loop, so descriptors and addresses stay warp-uniform (an MMA issued
+            // from divergent code pays for moving each operand to the uniform registers); one elected
+            // lane issues.  The next k-step's barrier is polled before this step's MMAs are issued, so the
+            // poll's latency is hidden behind them.
+            if (rank == 0) {
+                const uint32_t elected = pf_elect();
                 // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 256 over the pair
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
                 uint32_t st = 0, par = 0, gcount = 0;  // gcount: k-groups issued, over all tiles
+                uint32_t ready = 0;                    // this k-step's `full` phase was seen complete by the early poll
                 PF_TR_DECL;
                 for (uint32_t it = 0; it < total; it++) {
                     const uint32_t odd = it & 1, buf = gcount & 1;
@@ -301,21 +325,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     if (!odd && gcount >= 2 && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
                     PF_TR_E(0);
                     PF_TR_B;
-                    if (!pf_wait(&full[st], par)) { failed = true; break; }
+                    if (!ready && !pf_wait(&full[st], par)) { failed = true; break; }
                     PF_TR_E(1);
                     PF_TR_B;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
+                    ready = it + 1 < total ? pf_test(&full[st1], par1) : 0;
                     const uint64_t da = pf_desc(pf_smem(sA + st * PF_STAGE)), db = pf_desc(pf_smem(sX + st * PF_STAGE));
                     const uint32_t d = tmem_base + buf * PF_TM;
+                    if (elected) {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < PF_BK / 16; kk++)
-                        pf_mma_pair(d, da + 2 * kk, db + 2 * kk, idesc, (odd | kk) ? 1u : 0u);  // +32 bytes per k16 step
-                    pf_commit_pair(&empty[st]);
-                    if (odd) { pf_commit_pair(&dfull[buf]); gcount++; }
-                    if (++st == PF_S) { st = 0; par ^= 1; }
+                        for (uint32_t kk = 0; kk < PF_BK / 16; kk++)
+                            pf_mma_pair(d, da + 2 * kk, db + 2 * kk, idesc, (odd | kk) ? 1u : 0u);  // +32 bytes per k16 step
+                        pf_commit_pair(&empty[st]);
+                        if (odd) pf_commit_pair(&dfull[buf]);
+                    }
+                    gcount += odd;
+                    st = st1;
+                    par = par1;
                     PF_TR_E(4);
                 }
-                PF_TR_DUMP(1);
+                if (elected) PF_TR_DUMP(1);
             }
         } else if (warp == 2) {
             // ---- non-leader: pass "activation tile landed" on to the leader's barrier ----
