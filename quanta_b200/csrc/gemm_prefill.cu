@@ -318,11 +318,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
                 uint32_t st = 0, par = 0, gcount = 0;  // gcount: k-groups issued, over all tiles
                 uint32_t ready = 0;                    // this k-step's `full` phase was seen complete by the early poll
+                uint32_t dready = 0;                   // the same for the next k-group's accumulator
                 PF_TR_DECL;
                 for (uint32_t it = 0; it < total; it++) {
                     const uint32_t odd = it & 1, buf = gcount & 1;
                     PF_TR_B;
-                    if (!odd && gcount >= 2 && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
+                    if (!odd && gcount >= 2 && !dready && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
                     PF_TR_E(0);
                     PF_TR_B;
                     if (!ready && !pf_wait(&full[st], par)) { failed = true; break; }
@@ -331,6 +332,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
                     ready = it + 1 < total ? pf_test(&full[st1], par1) : 0;
+                    // at a group's second k-step, poll for the accumulator the next group will use
+                    dready = (odd && gcount >= 1) ? pf_test(&dempty[buf ^ 1], (((gcount + 1) >> 1) & 1) ^ 1) : 0;
                     const uint64_t da = pf_desc(pf_smem(sA + st * PF_STAGE)), db = pf_desc(pf_smem(sX + st * PF_STAGE));
                     const uint32_t d = tmem_base + buf * PF_TM;
                     if (elected) {
@@ -421,7 +424,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         const uint32_t remote_dempty = pf_map_to_cta(pf_smem(&dempty[0]), 0);
         const bool vec_scales = (groups & 3u) == 0;  // a row's scales start on a 16-byte boundary
         const bool issuer = quad == 0 && lane == 0;  // the thread of this half that issues its TMA stores
-        constexpr uint32_t ROWS = PF_Y_BYTES / (128 * sizeof(YT));  // activation rows per staging pass
+        constexpr uint32_t ROWS = PF_Y_BYTES / 2 / (128 * sizeof(YT));  // activation rows per staging pass (two buffers)
         YT* stage = reinterpret_cast<YT*>(sY + half * PF_Y_BYTES);
         uint32_t gcount = 0;
         PF_TR_DECL;
@@ -479,23 +482,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             if (failed) break;
             const float b = (a.bias && n_ok) ? __ldg(a.bias + n) : 0.0f;
             if (a.tma_store) {
-                // column i of the accumulator is activation row m0 + i: ROWS rows at a time go through this half's
-                // staging buffer as [row][128 n] and leave by one TMA store, which clips at the edges of Y
+                // column i of the accumulator is activation row m0 + i: ROWS rows at a time go through one of this
+                // half's two staging buffers as [row][128 n] and leave by a TMA store, which clips at the edges of Y
 #pragma unroll
                 for (uint32_t p = 0; p < 128 / ROWS; p++) {
-                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous store has read the buffer
+                    YT* buf = stage + (p & 1) * (ROWS * 128);
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store before last has read `buf`
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
 #pragma unroll
-                    for (uint32_t i = 0; i < ROWS; i++) {
-                        const float v = total[p * ROWS + i] + b;
-                        if constexpr (sizeof(YT) == 4) stage[i * 128 + ml] = v;
-                        else stage[i * 128 + ml] = f32_to_bf16_bits(v);
+                    for (uint32_t i = 0; i < ROWS; i += 2) {
+                        const float v0 = total[p * ROWS + i] + b, v1 = total[p * ROWS + i + 1] + b;
+                        if constexpr (sizeof(YT) == 4) {
+                            buf[i * 128 + ml] = v0;
+                            buf[(i + 1) * 128 + ml] = v1;
+                        } else {
+                            uint16_t h0, h1;
+                            asm("{\n\t.reg .b32 t;\n\tcvt.rn.bf16x2.f32 t, %3, %2;\n\tmov.b32 {%0, %1}, t;\n\t}" : "=h"(h0), "=h"(h1) : "f"(v0), "f"(v1));
+                            buf[i * 128 + ml] = h0;
+                            buf[(i + 1) * 128 + ml] = h1;
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
                     if (issuer) {
                         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
-                                     "r"((int32_t)n_cta), "r"((int32_t)(m0 + p * ROWS)), "r"(pf_smem(stage))
+                                     "r"((int32_t)n_cta), "r"((int32_t)(m0 + p * ROWS)), "r"(pf_smem(buf))
                                      : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
@@ -575,14 +586,14 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (codes) failed with code " + std::to_string((int)cr));
 
-    // Y as a [M, N] tensor: one box = (16 KB / 128 / element size) rows x 128 columns
+    // Y as a [M, N] tensor: one box = (8 KB / 128 / element size) rows x 128 columns
     const uint32_t ysz = y_dtype == QB200_F32 ? 4 : 2;
     const bool tma_store = (reinterpret_cast<uintptr_t>(f.y) & 15u) == 0 && ((uint64_t)N * ysz) % 16 == 0;
     CUtensorMap ymap = xmap;  // a valid map either way; unused without tma_store
     if (tma_store) {
         const cuuint64_t ydims[2] = {N, M};
         const cuuint64_t ystrides[1] = {(cuuint64_t)N * ysz};
-        const cuuint32_t ybox[2] = {128, PF_Y_BYTES / (128 * ysz)};
+        const cuuint32_t ybox[2] = {128, PF_Y_BYTES / 2 / (128 * ysz)};
         cr = enc(&ymap, y_dtype == QB200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, f.y, ydims,
                  ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
