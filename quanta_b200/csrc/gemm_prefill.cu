@@ -378,7 +378,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         }
     } else if (warp < 8) {
         // ---- unpack warps: thread r owns weight row r of this CTA's half ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
         const uint32_t r = tid - 128;
         const uint32_t row_off = r * 128 + ((r & 7) << 4);
         // packed codes: row r of a slot is 64 bytes, its 16-byte chunk c sits at c ^ ((r >> 1) & 3)
@@ -419,7 +419,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         if (lane == 0) PF_TR_DUMP(warp - 2);
     } else {
         // ---- epilogue warps: thread = weight row (TMEM lane), warpgroup = 128-column half of the m range ----
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
         const uint32_t quad = warp & 3, half = (warp - 8) >> 2, ml = quad * 32 + lane;
         const uint32_t remote_dempty = pf_map_to_cta(pf_smem(&dempty[0]), 0);
         const bool vec_scales = (groups & 3u) == 0;  // a row's scales start on a 16-byte boundary
