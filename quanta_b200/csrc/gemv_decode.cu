@@ -421,9 +421,12 @@ bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
     return al(codes) && al(scales) && al(x);
 }
 
-// Rows per work item: the layer is cut into a multiple of 148 items of at most 16 * rb rows,
-// so the last wave of items is as full as the others.
-static uint32_t gemv_rows_per_item(uint32_t N, uint32_t rb) {
+// Rows per work item.  A launch with few items per CTA cuts the layer into a multiple of 148
+// items of at most 16 * rb rows, so the last wave of items is as full as the others; a launch
+// with many items per CTA (`full_tiles`) takes whole 16 * rb-row items instead — the MMA and the
+// unpack cost the same for a 28-row item as for a 32-row one, and the waves even out by number.
+static uint32_t gemv_rows_per_item(uint32_t N, uint32_t rb, bool full_tiles) {
+    if (full_tiles) return 16 * rb;
     const uint32_t tiles = (N + 16 * rb - 1) / (16 * rb), k = (tiles + 147) / 148;
     uint32_t rows = (N + 148 * k - 1) / (148 * k);
     return rows < 1 ? 1 : rows;
@@ -481,11 +484,14 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
     // overlap with the neighbouring launches); grouped launches take 32-row items.
     uint32_t rb = count > 1 ? 2 : 1;
     if (!reg_path) rb = 1;
+    uint64_t all_tiles = 0;
+    for (uint32_t i = 0; i < count; i++) all_tiles += (f[i].out_dim + 16 * rb - 1) / (16 * rb);
+    const bool full_tiles = all_tiles >= 8 * 148;  // eight or more items per CTA
     for (uint32_t base = 0, n = 0; base < count; base += n) {
         // as many layers as fit the descriptor table and, on the register path, the per-CTA item table
         n = 0;
         for (uint32_t items = 0; base + n < count && n < (uint32_t)GEMV_MAX_LAYERS; n++) {
-            const uint32_t N = (uint32_t)f[base + n].out_dim, rpi = gemv_rows_per_item(N, rb);
+            const uint32_t N = (uint32_t)f[base + n].out_dim, rpi = gemv_rows_per_item(N, rb, full_tiles);
             items += (N + rpi - 1) / rpi;
             if (reg_path && n > 0 && items > REG_MAX_ITEMS * 148) break;
         }
@@ -500,7 +506,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             ly.x = static_cast<const uint16_t*>(a.x);
             ly.y = a.y;
             ly.N = (uint32_t)a.out_dim;
-            ly.rows_per_item = gemv_rows_per_item(ly.N, rb);
+            ly.rows_per_item = gemv_rows_per_item(ly.N, rb, full_tiles);
             ly.item0 = items;
             items += (ly.N + ly.rows_per_item - 1) / ly.rows_per_item;
         }
