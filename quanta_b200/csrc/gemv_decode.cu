@@ -53,12 +53,16 @@ struct GemvBatch {
     int32_t* status;  // device status word (0 = ok, QB200_ERR_TIMEOUT on a wait that ran out)
     uint32_t count, total_items, M, K, stages;
     uint32_t async_scales;  // scales are not 16-byte aligned slabs: copy them element-wise
+    uint32_t red_cols;      // batch columns kept per row of partial sums (kernels with a service warp)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -380,10 +384,35 @@ __global__ void __launch_bounds__(WARPS * 32) k_gemv_i4(const __grid_constant__ 
 
 #include "gemv_reg.cuh"
 #include "gemv_reg_kernel.cuh"
+#include "gemv_reg_async.cuh"
 
 namespace qb {
 
 // ---- host side ------------------------------------------------------------------
+
+template <int NT, int RB, typename YT>
+static qb200_status launch_gemv_async(const GemvBatch& b, uint32_t smem, uint32_t ctas, cudaStream_t st) {
+    auto kern = k_gemv_i4_async<NT, RB, YT>;
+    static bool attr_set[64] = {};  // per instantiation and device
+    int dev = 0;
+    QB_CUDA_TRY(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        QB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev & 63] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(ASYNC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, b));
+    return QB200_OK;
+}
 
 template <int NT, int RB, int OCC, typename YT>
 static qb200_status launch_gemv_reg(const GemvBatch& b, uint32_t smem, uint32_t ctas, cudaStream_t st) {
@@ -523,15 +552,19 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             const uint32_t nt = M <= 8 ? 1 : 2;
             uint32_t occ = (nt == 1 && rb == 1) ? 2 : 1;
             ctas = items < 148 * occ ? items : 148 * occ;
-            const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : 200u) * 1024;
+            // the kernel with a service warp (nt == 1, rb == 2) keeps only the batch's columns of the
+            // partial sums, which for a single row frees the room of one more 68 KB stage
+            const bool service = nt == 1 && rb == 2;
+            b.red_cols = service ? (M <= 2 ? 2 : M <= 4 ? 4 : 8) : 0;
+            const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : service ? 226u : 200u) * 1024;
             uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
-            while (stages > 2 && reg_smem_layout(K, nt, rb, stages).total > budget) stages--;
+            while (stages > 2 && reg_smem_layout(K, nt, rb, stages, b.red_cols).total > budget) stages--;
             b.stages = stages;
-            const uint32_t smem = reg_smem_layout(K, nt, rb, stages).total;
+            const uint32_t smem = reg_smem_layout(K, nt, rb, stages, b.red_cols).total;
             qb200_status r;
 #define QB_LAUNCH(YT)                                                                                          \
     (nt == 2 ? (rb == 2 ? launch_gemv_reg<2, 2, 1, YT>(b, smem, ctas, st) : launch_gemv_reg<2, 1, 1, YT>(b, smem, ctas, st)) \
-             : rb == 2 ? launch_gemv_reg<1, 2, 1, YT>(b, smem, ctas, st)                                       \
+             : rb == 2 ? launch_gemv_async<1, 2, YT>(b, smem, ctas, st)                                     \
                        : (occ == 2 ? launch_gemv_reg<1, 1, 2, YT>(b, smem, ctas, st) : launch_gemv_reg<1, 1, 1, YT>(b, smem, ctas, st)))
             r = y_dtype == QB200_F32 ? QB_LAUNCH(float) : QB_LAUNCH(uint16_t);
 #undef QB_LAUNCH

@@ -24,9 +24,10 @@ constexpr uint32_t REG_MAX_ITEMS = 128;  // items per CTA and launch (descriptor
 struct RegSmem {
     uint32_t desc, red, scales, codes, total, stage_scales, stage_codes;
 };
-__host__ __device__ inline RegSmem reg_smem_layout(uint32_t K, uint32_t nt, uint32_t rb, uint32_t stages) {
+// `red_cols`: batch columns kept per row of partial sums (0: all of the MMA tile's nt * 8)
+__host__ __device__ inline RegSmem reg_smem_layout(uint32_t K, uint32_t nt, uint32_t rb, uint32_t stages, uint32_t red_cols = 0) {
     RegSmem L;
-    const uint32_t groups = K / 128, batch = nt * 8;
+    const uint32_t groups = K / 128, batch = red_cols ? red_cols : nt * 8;
     auto up = [](uint32_t v) { return (v + 127u) & ~127u; };
     L.desc = 128;  // barriers at 0
     L.red = L.desc + up(REG_MAX_ITEMS * (uint32_t)sizeof(RegItem));
