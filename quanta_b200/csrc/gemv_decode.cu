@@ -30,6 +30,7 @@
 // a single layer is the same kernel with one descriptor.
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <cstdlib>
 
 #include "forward.hpp"
 #include "quant_math.cuh"

@@ -12,6 +12,37 @@ namespace qb {
 
 constexpr uint32_t ASYNC_THREADS = REG_THREADS + 32;
 
+// shared-memory accesses and barrier polls on 32-bit shared addresses
+__device__ __forceinline__ uint4 async_lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float async_lds32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void async_sts64(uint32_t a, float x, float y) {
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(a), "f"(x), "f"(y) : "memory");
+}
+__device__ __forceinline__ bool async_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool async_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < GEMV_SPIN_LIMIT; i++)
+        if (async_try_wait(bar, parity)) return true;
+    return false;
+}
+
 template <int NT, int RB, typename YT>
 __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -113,15 +144,31 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
         }
     } else {
         // ---- compute warps ----
+        // The item loop works on 32-bit shared-memory addresses that are advanced, not recomputed:
+        // every instruction here is paid 16 x 28 times per CTA and layer.
         uint4 fa[NT][4], fb[NT][4];  // activation fragments of groups G0 / G1
         float ka[NT][2], kb[NT][2];  // their "+ 8" corrections for batch columns 2t, 2t + 1, in MMA units
         const uint16_t* cur_x = nullptr;
-        uint32_t st = 0, parity = 0;
+        const uint32_t bar0 = smem_u32(bars), done0 = smem_u32(done), vacant0 = smem_u32(vacant);
+        const uint32_t desc0 = smem_u32(s_desc);  // the item's activation pointer is the first field of its descriptor
+        // offsets inside a stage of this lane's four 16-byte code loads and four scales (row g / g + 8, group G0 / G1)
+        const uint32_t codes0 = smem_u32(smem + L.codes) + g * row_bytes + t * 16, scales0 = smem_u32(smem + L.scales) + g * groups * 4;
+        const uint32_t oc0 = G0c * 64, oc1 = 8 * row_bytes + G0c * 64, oc2 = G1c * 64, oc3 = 8 * row_bytes + G1c * 64;
+        const uint32_t os0 = G0c * 4, os1 = (8 * groups + G0c) * 4, os2 = G1c * 4, os3 = (8 * groups + G1c) * 4;
+        const uint32_t rb_codes = 16 * row_bytes, rb_scales = 16 * groups * 4;
+        // where this lane parks its partial sums inside a slot: row g (and g + 8) of row block rb, columns 2t, 2t + 1
+        const uint32_t red0 = smem_u32(s_red) + ((warp * RB * 16 + g) * BW + 2 * t) * 4;
+        const bool keeps = 2 * t < BW;  // NT == 1: columns past the batch are not kept
+        uint32_t st = 0, parity = 0, stage_codes = codes0, stage_scales = scales0;
         for (uint32_t j = 0; j < n_my; j++) {
-            if (!mbar_try_wait(&bars[st], parity) && !mbar_wait_bounded(&bars[st], parity)) { failed = true; break; }
-            const RegItem& it = s_desc[j];
-            if (it.x != cur_x) {  // uniform across the CTA: (re)load this warp's fragments
-                cur_x = it.x;
+            if (!async_try_wait(bar0 + st * 8, parity) && !async_wait_bounded(bar0 + st * 8, parity)) { failed = true; break; }
+            const uint32_t slot = j & 1, vpar = ((j >> 1) & 1) ^ 1;
+            // the slot's previous item has long been folded: polled here so that its latency overlaps the loads
+            if (j >= 2 && !async_try_wait(vacant0 + slot * 8, vpar) && !async_wait_bounded(vacant0 + slot * 8, vpar)) { failed = true; break; }
+            const uint16_t* x_now;
+            asm volatile("ld.shared.u64 %0, [%1];" : "=l"(x_now) : "r"(desc0 + j * (uint32_t)sizeof(RegItem)));
+            if (x_now != cur_x) {  // uniform across the CTA: (re)load this warp's fragments
+                cur_x = x_now;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     const uint32_t b = g + 8 * nt;
@@ -138,86 +185,74 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
                     kb[nt][1] = GEMV_EIGHT_X * __shfl_sync(0xFFFFFFFFu, s1, 8 * t + 4);
                 }
             }
-            const uint32_t slot = j & 1;
-            float* red = s_red + slot * SLOT;
-            float accs[RB][NT][4];
+            // every load of the item first
+            uint4 c[RB][4];
+            float sc[RB][4];
 #pragma unroll
-        for (int rb = 0; rb < RB; rb++) {
-        const uint8_t* codes = smem + L.codes + st * L.stage_codes + (rb * 16 + g) * row_bytes + t * 16;
-        const float* sc = reinterpret_cast<const float*>(smem + L.scales + st * L.stage_scales) + (rb * 16 + g) * groups;
-        float acc[NT][4];
-        if (!failed) {
-            const uint4 c0a = *reinterpret_cast<const uint4*>(codes + G0c * 64);
-            const uint4 c1a = *reinterpret_cast<const uint4*>(codes + 8 * row_bytes + G0c * 64);
-            const uint4 c0b = *reinterpret_cast<const uint4*>(codes + G1c * 64);
-            const uint4 c1b = *reinterpret_cast<const uint4*>(codes + 8 * row_bytes + G1c * 64);
-            const float s0a = sc[G0c], s1a = sc[8 * groups + G0c], s0b = v1 ? sc[G1c] : 0.0f,
-                        s1b = v1 ? sc[8 * groups + G1c] : 0.0f;
-            float pa[NT][4], pb[NT][4];  // one MMA chain per group (and batch tile)
-#define QB_STEP(J, W0A, W1A, W0B, W1B, FIRST)                                                \
-    {                                                                                        \
-        {                                                                                    \
-            QB_UNPACK(W0A, W1A)                                                              \
-            _Pragma("unroll") for (int nt = 0; nt < NT; nt++) {                              \
-                if (FIRST) mma_bf16_first(pa[nt], a0, a1, a2, a3, fa[nt][J].x, fa[nt][J].y); \
-                else mma_bf16(pa[nt], a0, a1, a2, a3, fa[nt][J].x, fa[nt][J].y);             \
-                mma_bf16(pa[nt], d0, d1, d2, d3, fa[nt][J].z, fa[nt][J].w);                  \
-            }                                                                                \
-        }                                                                                    \
-        {                                                                                    \
-            QB_UNPACK(W0B, W1B)                                                              \
-            _Pragma("unroll") for (int nt = 0; nt < NT; nt++) {                              \
-                if (FIRST) mma_bf16_first(pb[nt], a0, a1, a2, a3, fb[nt][J].x, fb[nt][J].y); \
-                else mma_bf16(pb[nt], a0, a1, a2, a3, fb[nt][J].x, fb[nt][J].y);             \
-                mma_bf16(pb[nt], d0, d1, d2, d3, fb[nt][J].z, fb[nt][J].w);                  \
-            }                                                                                \
-        }                                                                                    \
-    }
-            QB_STEP(0, c0a.x, c1a.x, c0b.x, c1b.x, true)
-            QB_STEP(1, c0a.y, c1a.y, c0b.y, c1b.y, false)
-            QB_STEP(2, c0a.z, c1a.z, c0b.z, c1b.z, false)
-            QB_STEP(3, c0a.w, c1a.w, c0b.w, c1b.w, false)
-#undef QB_STEP
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    // (p - 8 * sum x) is the group's sum of q * x in MMA units (2^-93); 2^93 is applied at the store
-                    const float da = pa[nt][i] - ka[nt][i & 1], db = pb[nt][i] - kb[nt][i & 1];
-                    acc[nt][i] = fmaf(i < 2 ? s0b : s1b, db, (i < 2 ? s0a : s1a) * da);
-                }
-        } else {
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
-        }
-
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) accs[rb][nt][i] = acc[nt][i];
-        }  // rb
-            // park the partial sums in red[slot][warp][row][batch] once the slot's previous item has been folded
-            if (j >= 2 && !mbar_try_wait(&vacant[slot], ((j >> 1) & 1) ^ 1) && !mbar_wait_bounded(&vacant[slot], ((j >> 1) & 1) ^ 1)) {
-                failed = true;
-                break;
+            for (int rb = 0; rb < RB; rb++) {
+                const uint32_t cr = stage_codes + rb * rb_codes, sr = stage_scales + rb * rb_scales;
+                c[rb][0] = async_lds128(cr + oc0);
+                c[rb][1] = async_lds128(cr + oc1);
+                c[rb][2] = async_lds128(cr + oc2);
+                c[rb][3] = async_lds128(cr + oc3);
+                sc[rb][0] = async_lds32(sr + os0);
+                sc[rb][1] = async_lds32(sr + os1);
+                sc[rb][2] = v1 ? async_lds32(sr + os2) : 0.0f;
+                sc[rb][3] = v1 ? async_lds32(sr + os3) : 0.0f;
             }
+            // 2 * RB independent MMA chains (row block x group), interleaved step by step
+            float pa[RB][NT][4], pb[RB][NT][4];
+#define QB_STEP(J, X, FIRST)                                                                         \
+    _Pragma("unroll") for (int rb = 0; rb < RB; rb++) {                                              \
+        {                                                                                            \
+            QB_UNPACK(c[rb][0].X, c[rb][1].X)                                                        \
+            _Pragma("unroll") for (int nt = 0; nt < NT; nt++) {                                      \
+                if (FIRST) mma_bf16_first(pa[rb][nt], a0, a1, a2, a3, fa[nt][J].x, fa[nt][J].y);     \
+                else mma_bf16(pa[rb][nt], a0, a1, a2, a3, fa[nt][J].x, fa[nt][J].y);                 \
+                mma_bf16(pa[rb][nt], d0, d1, d2, d3, fa[nt][J].z, fa[nt][J].w);                      \
+            }                                                                                        \
+        }                                                                                            \
+        {                                                                                            \
+            QB_UNPACK(c[rb][2].X, c[rb][3].X)                                                        \
+            _Pragma("unroll") for (int nt = 0; nt < NT; nt++) {                                      \
+                if (FIRST) mma_bf16_first(pb[rb][nt], a0, a1, a2, a3, fb[nt][J].x, fb[nt][J].y);     \
+                else mma_bf16(pb[rb][nt], a0, a1, a2, a3, fb[nt][J].x, fb[nt][J].y);                 \
+                mma_bf16(pb[rb][nt], d0, d1, d2, d3, fb[nt][J].z, fb[nt][J].w);                      \
+            }                                                                                        \
+        }                                                                                            \
+    }
+            QB_STEP(0, x, true)
+            QB_STEP(1, y, false)
+            QB_STEP(2, z, false)
+            QB_STEP(3, w, false)
+#undef QB_STEP
+            // park the partial sums in red[slot][warp][row][batch]: (p - 8 * sum x) is the group's sum of q * x in
+            // MMA units (2^-93); 2^93 is applied at the store
+            const uint32_t ra = red0 + slot * (SLOT * 4);
 #pragma unroll
             for (int rb = 0; rb < RB; rb++)
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    if (nt * 8 + 2 * t < BW) {  // columns past the batch are not kept
-                        float* base = red + (warp * RB * 16 + rb * 16) * BW + nt * 8;
-                        *reinterpret_cast<float2*>(base + g * BW + 2 * t) = make_float2(accs[rb][nt][0], accs[rb][nt][1]);
-                        *reinterpret_cast<float2*>(base + (g + 8) * BW + 2 * t) = make_float2(accs[rb][nt][2], accs[rb][nt][3]);
+                    float o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float da = pa[rb][nt][i] - ka[nt][i & 1], db = pb[rb][nt][i] - kb[nt][i & 1];
+                        o[i] = fmaf(sc[rb][i < 2 ? 2 : 3], db, sc[rb][i < 2 ? 0 : 1] * da);
+                    }
+                    if (nt == 0 ? keeps : nt * 8 + 2 * t < BW) {
+                        async_sts64(ra + (rb * 16 * BW + nt * 8) * 4, o[0], o[1]);
+                        async_sts64(ra + ((rb * 16 + 8) * BW + nt * 8) * 4, o[2], o[3]);
                     }
                 }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&done[slot]);  // releases the stage and publishes the partial sums
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(done0 + slot * 8) : "memory");  // releases the stage, publishes the sums
+            stage_codes += L.stage_codes;
+            stage_scales += L.stage_scales;
             if (++st == S) {
                 st = 0;
                 parity ^= 1;
+                stage_codes = codes0;
+                stage_scales = scales0;
             }
         }
     }

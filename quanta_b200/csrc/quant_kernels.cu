@@ -68,11 +68,15 @@ struct TileGeom {
     uint32_t chunks_per_row;  // gc / 8
     uint32_t chunks;          // gr * gc / 8 chunks per tile
     uint32_t lanes;           // G: lanes per tile (power of two <= 32)
+    uint32_t lane_shift;      // log2(lanes)
 };
 
-// CPL: chunks per lane (ceil(chunks / lanes)).  One group of `lanes` lanes
-// quantizes one tile; a warp holds 32 / lanes groups.
-template <int SRC, int BITS, int CPL>
+// CPL: chunks per lane (ceil(chunks / lanes)).  One group of `lanes` lanes quantizes one tile;
+// a warp holds 32 / lanes groups.  A group walks tiles with a grid stride and keeps the next
+// tile's chunks in flight while it works on the current one (PF).  All index arithmetic is
+// 32-bit and incremental: with 64-bit divisions per thread the kernel was bound by its own
+// address computation, not by memory.
+template <int SRC, int BITS, int CPL, bool PF>
 __global__ void __launch_bounds__(256) k_quantize_tiles(const void* __restrict__ w, TileGeom g,
                                                         void* __restrict__ codes,
                                                         float* __restrict__ scales) {
@@ -80,56 +84,97 @@ __global__ void __launch_bounds__(256) k_quantize_tiles(const void* __restrict__
     constexpr int LO = -HI - 1;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t sub = lane & (g.lanes - 1u);
-    const uint64_t groups_per_block = blockDim.x / g.lanes;
-    const uint64_t tile = (uint64_t)blockIdx.x * groups_per_block + threadIdx.x / g.lanes;
-    const bool tile_ok = tile < g.tr * g.tc;
-    const uint64_t t_r = tile_ok ? tile / g.tc : 0, t_c = tile_ok ? tile % g.tc : 0;
-    const uint64_t r0 = t_r * g.gr, c0 = t_c * g.gc;
-
-    float v[CPL][8];
-    bool ok[CPL];
-    uint64_t pos[CPL];
-    float m = 0.0f;
+    const uint32_t groups_per_block = blockDim.x >> g.lane_shift;
+    const uint32_t tiles = (uint32_t)(g.tr * g.tc), tc = (uint32_t)g.tc;  // the launcher keeps tiles below 2^31
+    const uint32_t stride = gridDim.x * groups_per_block;
+    uint32_t tile = blockIdx.x * groups_per_block + (threadIdx.x >> g.lane_shift);
+    // this lane's chunks inside a tile: the same for every tile
+    uint32_t rr[CPL], cc[CPL];
+    bool chunk_ok[CPL];
 #pragma unroll
     for (int i = 0; i < CPL; i++) {
-        uint32_t ch = sub + (uint32_t)i * g.lanes;
-        uint64_t r = r0 + ch / g.chunks_per_row;
-        uint64_t c = c0 + (uint64_t)(ch % g.chunks_per_row) * 8u;
-        ok[i] = tile_ok && ch < g.chunks && r < g.rows && c < g.cols;
-        pos[i] = r * g.cols + c;
-        if (ok[i]) {
-            load_chunk8<SRC>(w, pos[i], v[i]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[i][j] = 0.0f;
-        }
+        const uint32_t ch = sub + (uint32_t)i * g.lanes;
+        rr[i] = ch / g.chunks_per_row;
+        cc[i] = (ch - rr[i] * g.chunks_per_row) * 8u;
+        chunk_ok[i] = ch < g.chunks;
     }
-#pragma unroll
-    for (int i = 0; i < CPL; i++)
-#pragma unroll
-        for (int j = 0; j < 8; j++) m = fmaxf(m, abs_or_zero(v[i][j]));
-    for (uint32_t o = g.lanes >> 1; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    const float s = scale_from_maxabs(m, HI);
-    if (tile_ok && sub == 0) scales[tile] = s;
+    // tile coordinates advance by (stride / tc, stride % tc) with a carry
+    uint32_t t_r = tile / tc, t_c = tile - t_r * tc;
+    const uint32_t step_r = stride / tc, step_c = stride - step_r * tc;
 
+    float v[CPL][8], vn[CPL][8];
+    bool ok[CPL], okn[CPL];
+    uint64_t pos[CPL], posn[CPL];
+    auto fetch = [&](uint32_t t, uint32_t tr_, uint32_t tc_, float (&dst)[CPL][8], bool (&k)[CPL], uint64_t (&p)[CPL]) {
+        const uint64_t r0 = (uint64_t)tr_ * g.gr, c0 = (uint64_t)tc_ * g.gc;
 #pragma unroll
-    for (int i = 0; i < CPL; i++) {
-        if (!ok[i]) continue;
-        int q[8];
+        for (int i = 0; i < CPL; i++) {
+            const uint64_t r = r0 + rr[i], c = c0 + cc[i];
+            k[i] = t < tiles && chunk_ok[i] && r < g.rows && c < g.cols;
+            p[i] = r * g.cols + c;
+            if (k[i]) {
+                load_chunk8<SRC>(w, p[i], dst[i]);
+            } else {
 #pragma unroll
-        for (int j = 0; j < 8; j++) q[j] = quantize_code(v[i][j], s, LO, HI);
-        if constexpr (BITS == 4) {
-            uint32_t word = 0;
+                for (int j = 0; j < 8; j++) dst[i][j] = 0.0f;
+            }
+        }
+    };
+    fetch(tile, t_r, t_c, v, ok, pos);
+    // the trip count is the warp's, not the group's (the shuffles below need every lane): the warp's first
+    // group holds its lowest tile, and a group past the end only skips its loads and stores
+    uint32_t tile_w = tile - (lane >> g.lane_shift);
+    for (; tile_w < tiles; tile_w += stride) {
+        const uint32_t next = tile + stride;
+        uint32_t n_r = t_r + step_r, n_c = t_c + step_c;
+        if (n_c >= tc) {
+            n_c -= tc;
+            n_r++;
+        }
+        if constexpr (PF) fetch(next, n_r, n_c, vn, okn, posn);
+
+        float m = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; j++) word |= ((uint32_t)q[j] & 0xFu) << (4 * j);
-            static_cast<uint32_t*>(codes)[pos[i] >> 3] = word;  // cols % 8 == 0: word index = elem / 8
+        for (int i = 0; i < CPL; i++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) m = max_abs_ignoring_nan(m, v[i][j]);
+        for (uint32_t o = g.lanes >> 1; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        const float s = scale_from_maxabs(m, HI);
+        if (sub == 0 && tile < tiles) scales[tile] = s;
+        const bool fast = s >= 7.888609052210118e-31f && s <= 1.2676506002282294e30f;  // [2^-100, 2^100]
+        const float rinv = __frcp_rn(s);
+#pragma unroll
+        for (int i = 0; i < CPL; i++) {
+            if (!ok[i]) continue;
+            int q[8];
+            quantize_chunk8(v[i], s, rinv, fast, LO, HI, q);
+            if constexpr (BITS == 4) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) word |= ((uint32_t)q[j] & 0xFu) << (4 * j);
+                static_cast<uint32_t*>(codes)[pos[i] >> 3] = word;  // cols % 8 == 0: word index = elem / 8
+            } else {
+                uint2 out;
+                out.x = ((uint32_t)q[0] & 0xFFu) | (((uint32_t)q[1] & 0xFFu) << 8) | (((uint32_t)q[2] & 0xFFu) << 16) |
+                        (((uint32_t)q[3] & 0xFFu) << 24);
+                out.y = ((uint32_t)q[4] & 0xFFu) | (((uint32_t)q[5] & 0xFFu) << 8) | (((uint32_t)q[6] & 0xFFu) << 16) |
+                        (((uint32_t)q[7] & 0xFFu) << 24);
+                *reinterpret_cast<uint2*>(static_cast<int8_t*>(codes) + pos[i]) = out;
+            }
+        }
+        tile = next;
+        t_r = n_r;
+        t_c = n_c;
+        if constexpr (PF) {
+#pragma unroll
+            for (int i = 0; i < CPL; i++) {
+                ok[i] = okn[i];
+                pos[i] = posn[i];
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[i][j] = vn[i][j];
+            }
         } else {
-            uint2 out;
-            out.x = ((uint32_t)q[0] & 0xFFu) | (((uint32_t)q[1] & 0xFFu) << 8) | (((uint32_t)q[2] & 0xFFu) << 16) |
-                    (((uint32_t)q[3] & 0xFFu) << 24);
-            out.y = ((uint32_t)q[4] & 0xFFu) | (((uint32_t)q[5] & 0xFFu) << 8) | (((uint32_t)q[6] & 0xFFu) << 16) |
-                    (((uint32_t)q[7] & 0xFFu) << 24);
-            *reinterpret_cast<uint2*>(static_cast<int8_t*>(codes) + pos[i]) = out;
+            fetch(tile, t_r, t_c, v, ok, pos);
         }
     }
 }
@@ -258,15 +303,18 @@ static qb200_status launch_tiles(const void* w, const TileGeom& g, void* codes, 
     const uint32_t cpl = (g.chunks + g.lanes - 1) / g.lanes;
     const uint32_t block = 256;
     const uint64_t tiles = g.tr * g.tc, per_block = block / g.lanes;
-    const uint64_t blocks = (tiles + per_block - 1) / per_block;
-    if (blocks > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "quantize: matrix too large for one launch");
+    uint64_t blocks = (tiles + per_block - 1) / per_block;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint64_t cap = (uint64_t)sms * 16;  // a few rounds of resident blocks; every group then walks many tiles
+    if (blocks > cap) blocks = cap;
     dim3 grid((uint32_t)blocks);
     switch (cpl) {
-        case 1: k_quantize_tiles<SRC, BITS, 1><<<grid, block, 0, st>>>(w, g, codes, scales); break;
-        case 2: k_quantize_tiles<SRC, BITS, 2><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        case 1: k_quantize_tiles<SRC, BITS, 1, true><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        case 2: k_quantize_tiles<SRC, BITS, 2, true><<<grid, block, 0, st>>>(w, g, codes, scales); break;
         case 3:
-        case 4: k_quantize_tiles<SRC, BITS, 4><<<grid, block, 0, st>>>(w, g, codes, scales); break;
-        default: k_quantize_tiles<SRC, BITS, 8><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        case 4: k_quantize_tiles<SRC, BITS, 4, false><<<grid, block, 0, st>>>(w, g, codes, scales); break;
+        default: k_quantize_tiles<SRC, BITS, 8, false><<<grid, block, 0, st>>>(w, g, codes, scales); break;
     }
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
@@ -280,7 +328,7 @@ static qb200_status quantize_typed(const void* w, uint64_t rows, uint64_t cols, 
     const bool src_ok = aligned16(w) && (SRC == SRC_F32 || cols % 8 == 0);
     const bool dst_ok = BITS == 4 ? (reinterpret_cast<uintptr_t>(codes) & 3u) == 0
                                   : (reinterpret_cast<uintptr_t>(codes) & 7u) == 0;
-    if (cols % 8 == 0 && gc % 8 == 0 && chunks <= 256 && gr <= 0xFFFFFFFFull && src_ok && dst_ok) {
+    if (cols % 8 == 0 && gc % 8 == 0 && chunks <= 256 && gr <= 0xFFFFFFFFull && src_ok && dst_ok && tr * tc < (1ull << 31)) {
         TileGeom g;
         g.rows = rows; g.cols = cols; g.gr = (uint32_t)gr; g.gc = (uint32_t)gc; g.tr = tr; g.tc = tc;
         g.chunks_per_row = (uint32_t)(gc / 8);
@@ -288,6 +336,8 @@ static qb200_status quantize_typed(const void* w, uint64_t rows, uint64_t cols, 
         uint32_t lanes = 1;
         while (lanes < 32 && lanes < g.chunks) lanes <<= 1;
         g.lanes = lanes;
+        g.lane_shift = 0;
+        while ((1u << g.lane_shift) < lanes) g.lane_shift++;
         return launch_tiles<SRC, BITS>(w, g, codes, scales, st);
     }
     // generic: any grid, any alignment

@@ -160,6 +160,32 @@ def test_quantize_paths_bit_exact(shape, gran):
         assert (bits(m.dequantize().cpu().numpy()) == bits(o.dequantize_host(oc, os_, *shape, dtype.bits(), gr, gc))).all()
 
 
+@pytest.mark.parametrize("dtype,gran", [(qb.QuantDtype.Int4, qb.Group(1, 128)), (qb.QuantDtype.Int8, qb.Block(32, 32)),
+                                        (qb.QuantDtype.Int8, qb.Group(1, 128))])
+def test_quantize_near_ties_bit_exact(dtype, gran):
+    """The tile kernel rounds x * (1 / s) and falls back to the exact divide near half-integers: weights placed
+    on and within a few ulps of every rounding boundary k + 0.5 (and of every integer), for scales across the
+    f32 range, must still give the reference's codes bit for bit."""
+    hi = 127 if dtype.bits() == 8 else 7
+    rows, cols = 256, 256
+    rng = np.random.default_rng(17)
+    w = np.zeros((rows, cols), np.float32)
+    for r in range(rows):
+        # per row: a scale magnitude anywhere from subnormal-ish to huge, every column block shares it
+        m = np.float32(rng.uniform(0.5, 2.0) * 2.0 ** int(rng.integers(-120, 100)))
+        s = np.float32(m / np.float32(hi))
+        ks = rng.integers(-hi - 1, hi + 1, size=cols).astype(np.float32)
+        frac = rng.choice(np.array([0.5, 0.5, 0.5, 0.0, 0.25], np.float32), size=cols)
+        x = (ks + frac).astype(np.float32) * s
+        ulps = rng.integers(-6, 7, size=cols)
+        xi = x.view(np.int32) + ulps.astype(np.int32)  # step by a few ulps either way
+        x = np.clip(xi.view(np.float32), -m, m).astype(np.float32)
+        x[::32] = m  # every tile of either grid holds the row's maximum, so s is the tile's scale
+        w[r] = x
+    m_, oc, os_ = quantize_both(w, rows, cols, dtype, gran)
+    assert_quant_equal(m_, oc, os_, f"near ties {dtype.name} {gran!r}")
+
+
 def test_quantize_from_half_sources():
     rng = np.random.default_rng(9)
     w = (rng.standard_normal((64, 256)) * 0.02).astype(np.float32)
