@@ -199,6 +199,44 @@ def measure_extras(torch, qb, dev, only=None, small=False):
     ms = timed(lambda: qm.dequantize(), 10)
     out["dequantize_int4_1x128"] = {"write_GB/s": N * K * 4 / ms / 1e6, "ms": ms,
                                     "roofline_frac": (N * K * 4.5 + N * (K // 128) * 4) / ms / 1e6 / hbm, "shape": [N, K]}
+    # quantize-on-load at the whole checkpoint's size: 32 x [4096, 4096] + 32 x [11008, 4096] f32 (7.92 GB read),
+    # input resident in HBM, one quantize call per matrix
+    try:
+        mats = [torch.randn(4096, 4096, device=dev, generator=gen) * 0.02 for _ in range(32)]
+        mats += [torch.randn(11008, 4096, device=dev, generator=gen) * 0.02 for _ in range(32)]
+        elems = sum(t.numel() for t in mats)
+        for name, dt, gran, per_elem in [("checkpoint_int4_1x128", qb.QuantDtype.Int4, qb.Group(1, 128), 0.5 + 4 / 128),
+                                         ("checkpoint_int8_32x32", qb.QuantDtype.Int8, qb.Block(32, 32), 1 + 4 / 1024)]:
+            def run():
+                for t in mats:
+                    qb.QuantizedMatrix.quantize(t, dt, gran)
+            run()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms = e0.elapsed_time(e1)
+            out["quantize_" + name] = {"read_GB/s": elems * 4 / ms / 1e6, "ms": ms, "matrices": len(mats), "read_bytes": elems * 4,
+                                       "roofline_frac": elems * (4 + per_elem) / ms / 1e6 / hbm}
+        del mats
+    except torch.OutOfMemoryError as e:  # a smaller device: report why the line is missing
+        out["quantize_checkpoint"] = {"skipped": str(e)[:80]}
+    # decode GEMV at the other batch sizes of the configuration (M = 4, 16), grouped launch over 32 matrices
+    try:
+        lys = [qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(torch.randn(4096, 4096, device=dev, generator=gen) * 0.02,
+                                                                   qb.QuantDtype.Int4, qb.Group(1, 128)), None, qb.OUT_IN)
+               for _ in range(32)]
+        for mm in (4, 16):
+            xm = torch.randn(mm, 4096, device=dev, generator=gen).to(torch.bfloat16)
+            ms = timed(lambda: qb.QuantizedLinear.forward_many(lys, [xm] * 32, out_dtype=torch.float32), 50)
+            by = 32 * (4096 * 4096 // 2 + 4096 * 32 * 4 + mm * 4096 * 2 + mm * 4096 * 4)
+            out[f"decode_gemv_M{mm}"] = {"GB/s": by / ms / 1e6, "ms": ms, "roofline_frac": by / ms / 1e6 / hbm,
+                                         "kernel": lys[0].last_kernel(), "launch": "grouped, 32 matrices, no graph"}
+        del lys
+    except Exception as e:
+        out["decode_gemv_M"] = {"skipped": str(e)[:80]}
     ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
     ms = timed(lambda: ql.forward(x), 10)
     out["prefill_int4_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,

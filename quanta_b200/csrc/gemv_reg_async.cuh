@@ -46,7 +46,6 @@ __device__ __forceinline__ bool async_wait_bounded(uint32_t bar, uint32_t parity
 template <int NT, int RB, typename YT>
 __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr uint32_t BATCH = NT * 8;
     const uint32_t groups = a.K >> 7, row_bytes = a.K >> 1, S = a.stages;
     const uint32_t BW = a.red_cols;                 // batch columns kept per row of partial sums (>= M, even)
     const uint32_t SLOT = REG_WARPS * RB * 16 * BW;  // floats per slot of partial sums

@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(256) k_quantize_tiles(const void* __restrict__
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t sub = lane & (g.lanes - 1u);
     const uint32_t groups_per_block = blockDim.x >> g.lane_shift;
-    const uint32_t tiles = (uint32_t)(g.tr * g.tc), tc = (uint32_t)g.tc;  // the launcher keeps tiles below 2^31
+    // the launcher keeps tiles below 2^31 and rows, cols below 2^32
+    const uint32_t tiles = (uint32_t)(g.tr * g.tc), tc = (uint32_t)g.tc, rows = (uint32_t)g.rows, cols = (uint32_t)g.cols;
     const uint32_t stride = gridDim.x * groups_per_block;
     uint32_t tile = blockIdx.x * groups_per_block + (threadIdx.x >> g.lane_shift);
     // this lane's chunks inside a tile: the same for every tile
@@ -102,79 +103,81 @@ __global__ void __launch_bounds__(256) k_quantize_tiles(const void* __restrict__
     uint32_t t_r = tile / tc, t_c = tile - t_r * tc;
     const uint32_t step_r = stride / tc, step_c = stride - step_r * tc;
 
-    float v[CPL][8], vn[CPL][8];
-    bool ok[CPL], okn[CPL];
-    uint64_t pos[CPL], posn[CPL];
-    auto fetch = [&](uint32_t t, uint32_t tr_, uint32_t tc_, float (&dst)[CPL][8], bool (&k)[CPL], uint64_t (&p)[CPL]) {
-        const uint64_t r0 = (uint64_t)tr_ * g.gr, c0 = (uint64_t)tc_ * g.gc;
+    struct Buf {
+        float v[CPL][8];
+        bool ok[CPL];
+        uint64_t pos[CPL];
+    };
+    auto fetch = [&](uint32_t t, uint32_t tr_, uint32_t tc_, Buf& b) {
+        const uint32_t r0 = tr_ * g.gr, c0 = tc_ * g.gc;  // below 2^32: the tile starts inside the matrix
 #pragma unroll
         for (int i = 0; i < CPL; i++) {
-            const uint64_t r = r0 + rr[i], c = c0 + cc[i];
-            k[i] = t < tiles && chunk_ok[i] && r < g.rows && c < g.cols;
-            p[i] = r * g.cols + c;
-            if (k[i]) {
-                load_chunk8<SRC>(w, p[i], dst[i]);
+            const uint32_t r = r0 + rr[i], c = c0 + cc[i];
+            b.ok[i] = t < tiles && chunk_ok[i] && r < rows && c < cols;
+            b.pos[i] = (uint64_t)r * cols + c;
+            if (b.ok[i]) {
+                load_chunk8<SRC>(w, b.pos[i], b.v[i]);
             } else {
 #pragma unroll
-                for (int j = 0; j < 8; j++) dst[i][j] = 0.0f;
+                for (int j = 0; j < 8; j++) b.v[i][j] = 0.0f;
             }
         }
     };
-    fetch(tile, t_r, t_c, v, ok, pos);
-    // the trip count is the warp's, not the group's (the shuffles below need every lane): the warp's first
-    // group holds its lowest tile, and a group past the end only skips its loads and stores
-    uint32_t tile_w = tile - (lane >> g.lane_shift);
-    for (; tile_w < tiles; tile_w += stride) {
-        const uint32_t next = tile + stride;
-        uint32_t n_r = t_r + step_r, n_c = t_c + step_c;
-        if (n_c >= tc) {
-            n_c -= tc;
-            n_r++;
+    auto advance = [&]() {
+        tile += stride;
+        t_r += step_r;
+        t_c += step_c;
+        if (t_c >= tc) {
+            t_c -= tc;
+            t_r++;
         }
-        if constexpr (PF) fetch(next, n_r, n_c, vn, okn, posn);
-
+    };
+    auto process = [&](uint32_t t, const Buf& b) {
         float m = 0.0f;
 #pragma unroll
         for (int i = 0; i < CPL; i++)
 #pragma unroll
-            for (int j = 0; j < 8; j++) m = max_abs_ignoring_nan(m, v[i][j]);
+            for (int j = 0; j < 8; j++) m = max_abs_ignoring_nan(m, b.v[i][j]);
         for (uint32_t o = g.lanes >> 1; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
         const float s = scale_from_maxabs(m, HI);
-        if (sub == 0 && tile < tiles) scales[tile] = s;
+        if (sub == 0 && t < tiles) scales[t] = s;
         const bool fast = s >= 7.888609052210118e-31f && s <= 1.2676506002282294e30f;  // [2^-100, 2^100]
         const float rinv = __frcp_rn(s);
 #pragma unroll
         for (int i = 0; i < CPL; i++) {
-            if (!ok[i]) continue;
-            int q[8];
-            quantize_chunk8(v[i], s, rinv, fast, LO, HI, q);
-            if constexpr (BITS == 4) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int j = 0; j < 8; j++) word |= ((uint32_t)q[j] & 0xFu) << (4 * j);
-                static_cast<uint32_t*>(codes)[pos[i] >> 3] = word;  // cols % 8 == 0: word index = elem / 8
-            } else {
-                uint2 out;
-                out.x = ((uint32_t)q[0] & 0xFFu) | (((uint32_t)q[1] & 0xFFu) << 8) | (((uint32_t)q[2] & 0xFFu) << 16) |
-                        (((uint32_t)q[3] & 0xFFu) << 24);
-                out.y = ((uint32_t)q[4] & 0xFFu) | (((uint32_t)q[5] & 0xFFu) << 8) | (((uint32_t)q[6] & 0xFFu) << 16) |
-                        (((uint32_t)q[7] & 0xFFu) << 24);
-                *reinterpret_cast<uint2*>(static_cast<int8_t*>(codes) + pos[i]) = out;
-            }
+            if (!b.ok[i]) continue;
+            float n[8];
+            quantize_chunk8(b.v[i], s, rinv, fast, LO, HI, n);
+            if constexpr (BITS == 4) static_cast<uint32_t*>(codes)[b.pos[i] >> 3] = pack_int4x8(n);  // cols % 8 == 0
+            else *reinterpret_cast<uint2*>(static_cast<int8_t*>(codes) + b.pos[i]) = pack_int8x8(n);
         }
-        tile = next;
-        t_r = n_r;
-        t_c = n_c;
-        if constexpr (PF) {
-#pragma unroll
-            for (int i = 0; i < CPL; i++) {
-                ok[i] = okn[i];
-                pos[i] = posn[i];
-#pragma unroll
-                for (int j = 0; j < 8; j++) v[i][j] = vn[i][j];
-            }
-        } else {
-            fetch(tile, t_r, t_c, v, ok, pos);
+    };
+    // The trip count is the warp's, not the group's (the shuffles need every lane): the warp's first group
+    // holds its lowest tile, and a group past the end only skips its loads and stores.  With PF the loop is
+    // unrolled by two over a pair of buffers, so the tile in flight is never copied.
+    uint32_t tile_w = tile - (lane >> g.lane_shift);
+    if constexpr (PF) {
+        Buf b0, b1;
+        fetch(tile, t_r, t_c, b0);
+        while (tile_w < tiles) {
+            const uint32_t t0 = tile;
+            advance();
+            fetch(tile, t_r, t_c, b1);
+            process(t0, b0);
+            tile_w += stride;
+            if (tile_w >= tiles) break;
+            const uint32_t t1 = tile;
+            advance();
+            fetch(tile, t_r, t_c, b0);
+            process(t1, b1);
+            tile_w += stride;
+        }
+    } else {
+        Buf b0;
+        for (; tile_w < tiles; tile_w += stride) {
+            fetch(tile, t_r, t_c, b0);
+            process(tile, b0);
+            advance();
         }
     }
 }
@@ -328,7 +331,8 @@ static qb200_status quantize_typed(const void* w, uint64_t rows, uint64_t cols, 
     const bool src_ok = aligned16(w) && (SRC == SRC_F32 || cols % 8 == 0);
     const bool dst_ok = BITS == 4 ? (reinterpret_cast<uintptr_t>(codes) & 3u) == 0
                                   : (reinterpret_cast<uintptr_t>(codes) & 7u) == 0;
-    if (cols % 8 == 0 && gc % 8 == 0 && chunks <= 256 && gr <= 0xFFFFFFFFull && src_ok && dst_ok && tr * tc < (1ull << 31)) {
+    if (cols % 8 == 0 && gc % 8 == 0 && chunks <= 256 && gr <= 0xFFFFFFFFull && src_ok && dst_ok && tr * tc < (1ull << 31) && rows < (1ull << 32) &&
+        cols < (1ull << 32)) {
         TileGeom g;
         g.rows = rows; g.cols = cols; g.gr = (uint32_t)gr; g.gc = (uint32_t)gc; g.tr = tr; g.tc = tc;
         g.chunks_per_row = (uint32_t)(gc / 8);

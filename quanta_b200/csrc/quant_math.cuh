@@ -43,21 +43,48 @@ __device__ __forceinline__ int quantize_code(float x, float s, int lo, int hi) {
 // the same rounding interval and rte(d') == rte(d).  Otherwise — and for scales outside
 // [2^-100, 2^100], zero, infinite or NaN, where 1 / s is not trustworthy — the chunk is redone
 // with the exact divide.  A NaN weight fails the distance test (comparison with NaN is false)
-// and takes the exact path too.  Result: bit-identical to quantize_code for every input.
+// and takes the exact path too.  On the fast path no clamp is needed: |x| <= max|w| = m and
+// s = fl(m / hi) >= (m / hi)(1 - 2^-24) give |x / s| < hi + 0.5.  The codes come back as
+// integral floats (the packers below work in floating point).  Result: bit-identical to
+// quantize_code for every input.
 __device__ __forceinline__ void quantize_chunk8(const float (&x)[8], float s, float rinv, bool fast, int lo, int hi,
-                                                int (&q)[8]) {
+                                                float (&n)[8]) {
     bool redo = !fast;
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         const float d = __fmul_rn(x[j], rinv);
-        const float n = rintf(d);
-        redo |= !(fabsf(__fsub_rn(d, n)) < 0.49993896484375f);  // 0.5 - 2^-14
-        q[j] = min(max(__float2int_rn(n), lo), hi);
+        n[j] = rintf(d);
+        redo |= !(fabsf(__fsub_rn(d, n[j])) < 0.49993896484375f);  // 0.5 - 2^-14
     }
     if (redo) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) q[j] = quantize_code(x[j], s, lo, hi);
+        for (int j = 0; j < 8; j++) n[j] = (float)quantize_code(x[j], s, lo, hi);
     }
+}
+
+// Eight int4 codes (integral floats in [-8, 7]) -> one packed word, low nibble first.  Each
+// half is built by Horner in f32 (16 bits: exact) from q + 8, which is the nibble with its top
+// bit flipped; one XOR restores the two's-complement nibbles.
+__device__ __forceinline__ uint32_t pack_int4x8(const float (&n)[8]) {
+    float lo = fmaf(n[3], 16.0f, n[2]), hi = fmaf(n[7], 16.0f, n[6]);
+    lo = fmaf(lo, 16.0f, n[1]);
+    hi = fmaf(hi, 16.0f, n[5]);
+    lo = fmaf(lo, 16.0f, n[0] + 34952.0f);  // + 8 * (1 + 16 + 256 + 4096)
+    hi = fmaf(hi, 16.0f, n[4] + 34952.0f);
+    const uint32_t l = (uint32_t)__float2int_rn(lo), h = (uint32_t)__float2int_rn(hi);
+    return (l | (h << 16)) ^ 0x88888888u;
+}
+
+// Eight int8 codes (integral floats in [-128, 127]) -> two words of four bytes, low byte first.
+__device__ __forceinline__ uint2 pack_int8x8(const float (&n)[8]) {
+    uint32_t h[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)  // (q1 + 128) * 256 + (q0 + 128): 16 bits, exact in f32
+        h[i] = (uint32_t)__float2int_rn(fmaf(n[2 * i + 1], 256.0f, n[2 * i] + 32896.0f));
+    uint2 out;
+    out.x = (h[0] | (h[1] << 16)) ^ 0x80808080u;
+    out.y = (h[2] | (h[3] << 16)) ^ 0x80808080u;
+    return out;
 }
 
 // scale * f32(q): one multiply, never fused with anything (dtype.rs:245-247).
