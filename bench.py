@@ -228,12 +228,23 @@ def measure_extras(torch, qb, dev, only=None, small=False):
         lys = [qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(torch.randn(4096, 4096, device=dev, generator=gen) * 0.02,
                                                                    qb.QuantDtype.Int4, qb.Group(1, 128)), None, qb.OUT_IN)
                for _ in range(32)]
+        from quanta_b200 import _lib
+        lib = _lib.load()
+        hs = (_lib.vp * 32)(*[ql._h for ql in lys])
         for mm in (4, 16):
             xm = torch.randn(mm, 4096, device=dev, generator=gen).to(torch.bfloat16)
-            ms = timed(lambda: qb.QuantizedLinear.forward_many(lys, [xm] * 32, out_dtype=torch.float32), 50)
+            ym = torch.empty(32, mm, 4096, device=dev, dtype=torch.float32)
+            xp = (_lib.vp * 32)(*[xm.data_ptr()] * 32)
+            yp = (_lib.vp * 32)(*[ym[i].data_ptr() for i in range(32)])
+
+            def run():
+                st = lib.qb200_qlinear_forward_many(hs, 32, xp, _lib.BF16, mm, yp, _lib.F32, torch.cuda.current_stream(dev).cuda_stream)
+                if st:
+                    raise RuntimeError(_lib.last_error())
+            ms = timed(run, 200)
             by = 32 * (4096 * 4096 // 2 + 4096 * 32 * 4 + mm * 4096 * 2 + mm * 4096 * 4)
             out[f"decode_gemv_M{mm}"] = {"GB/s": by / ms / 1e6, "ms": ms, "roofline_frac": by / ms / 1e6 / hbm,
-                                         "kernel": lys[0].last_kernel(), "launch": "grouped, 32 matrices, no graph"}
+                                         "kernel": lys[0].last_kernel(), "launch": "grouped, 32 matrices per launch"}
         del lys
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}

@@ -557,7 +557,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             // partial sums, which for a single row frees the room of one more 68 KB stage
             const bool service = nt == 1 && rb == 2;
             b.red_cols = service ? (M <= 2 ? 2 : M <= 4 ? 4 : 8) : 0;
-            const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : service ? 226u : 200u) * 1024;
+            const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : service ? 227u : 200u) * 1024;
             uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
             while (stages > 2 && reg_smem_layout(K, nt, rb, stages, b.red_cols).total > budget) stages--;
             b.stages = stages;

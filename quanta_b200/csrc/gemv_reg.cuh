@@ -19,7 +19,7 @@ struct RegItem {
     const float* scales;
     uint32_t row0, nrows, N, pad;
 };
-constexpr uint32_t REG_MAX_ITEMS = 128;  // items per CTA and launch (descriptors: 7 KB of shared memory)
+constexpr uint32_t REG_MAX_ITEMS = 120;  // items per CTA and launch (descriptors: 6.6 KB of shared memory)
 
 struct RegSmem {
     uint32_t desc, red, scales, codes, total, stage_scales, stage_codes;
