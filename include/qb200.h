@@ -194,6 +194,30 @@ QB200_API qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, 
                                         const void* const* x_dev, int32_t x_dtype, uint64_t m,
                                         void* const* y_dev, int32_t y_dtype, void* stream);
 
+/* ---- fused all-gather for column-sharded layers (no counterpart in the reference: it has no
+ * multi-GPU code, crates/ml/quanta-nn/PARITY.md:76-79) ----
+ * Every rank of a node owns one gather buffer of the same layout (for example [world][layer][m][n]);
+ * the buffers are cudaMalloc allocations shared between the ranks' processes by CUDA IPC handles.
+ * qb200_qlinear_forward_many_gather is qb200_qlinear_forward_many whose kernel stores each output
+ * element into EVERY rank's buffer (plain stores to peer memory over NVLink, no collective):
+ * y_own[i] points into this rank's own buffer, gather_bases[p] is rank p's buffer as mapped in this
+ * process (gather_bases[rank] the own one), and the element goes to y_own[i] + (gather_bases[p] -
+ * gather_bases[rank]) for every p.  Decode shapes only (int4, grid 1x128, [out, in], bf16 x, m <= 8,
+ * in <= 4096), else QB200_ERR_NOT_SUPPORTED.  qb200_peer_signal_wait, issued on the same stream
+ * afterwards, publishes "this rank's outputs of this step are written" to every peer and waits for
+ * theirs; the wait is bounded (about a second), then QB200_ERR_TIMEOUT lands in status_dev.
+ * flag_arrays[p] is a zero-initialised array of 9 uint64 inside rank p's shared allocation. */
+QB200_API qb200_status qb200_peer_alloc(uint64_t bytes, void** dev_ptr, uint8_t* handle64);
+QB200_API qb200_status qb200_peer_open(const uint8_t* handle64, void** dev_ptr);
+QB200_API qb200_status qb200_peer_close(void* dev_ptr);
+QB200_API qb200_status qb200_peer_free(void* dev_ptr);
+QB200_API qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uint32_t count,
+                                               const void* const* x_dev, int32_t x_dtype, uint64_t m,
+                                               void* const* y_own, int32_t y_dtype, void* const* gather_bases,
+                                               uint32_t world, uint32_t rank, void* stream);
+QB200_API qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint32_t world, uint32_t rank,
+                                    int32_t* status_dev, void* stream);
+
 /* qb200_qlinear_forward_many over HOST buffers: every distinct input pointer is
  * copied to the device once, the forwards run, all outputs are copied back and
  * the call synchronises.  Staging buffers belong to layers[0] and grow on demand. */

@@ -25,11 +25,19 @@ qb200_status forward_generic(const FwdArgs& a, uint32_t bits, int x_dtype, int y
 // Decode GEMV on the tensor pipe (gemv_decode.cu): int4, 1x128 grid, OUT_IN, bf16 x, m <= 16.
 bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* scales, const void* x);
+// Fused all-gather: byte offsets from this rank's output buffer to every rank's copy of it (as mapped in
+// this process; the own entry is 0).  A kernel given a PeerSpec stores each output to all of them.
+struct PeerSpec {
+    uint32_t world = 0;
+    int64_t delta[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+};
 #ifdef __CUDACC__
 // QB200_ERR_NOT_SUPPORTED (no message) when no launch plan fits the shape.
 qb200_status gemv_i4_forward(const FwdArgs& a, int y_dtype, int32_t* status, cudaStream_t st);
 // One persistent launch over several layers that share K and m (x and y per layer).
-qb200_status gemv_i4_forward_many(const FwdArgs* a, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st);
+// With `peers`, only launch plans whose kernel can store to peer buffers are taken (else NOT_SUPPORTED).
+qb200_status gemv_i4_forward_many(const FwdArgs* a, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st,
+                                  const PeerSpec* peers = nullptr);
 #endif
 // Prefill GEMM on tcgen05 (gemm_prefill.cu): int4, 1x128 grid, OUT_IN, bf16 x, m >= 64.
 bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,

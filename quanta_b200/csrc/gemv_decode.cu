@@ -55,6 +55,8 @@ struct GemvBatch {
     uint32_t count, total_items, M, K, stages;
     uint32_t async_scales;  // scales are not 16-byte aligned slabs: copy them element-wise
     uint32_t red_cols;      // batch columns kept per row of partial sums (kernels with a service warp)
+    uint32_t n_peers;       // fused all-gather: every output is stored at y + peer_delta[p], p < n_peers (0: plain store)
+    int64_t peer_delta[8];
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -506,13 +508,14 @@ static qb200_status launch_gemv(const GemvBatch& b, const GemvShape& s, uint32_t
 
 // Grouped forward over `count` layers that share K and M.  Returns QB200_ERR_NOT_SUPPORTED
 // (without setting an error) when the shape does not fit the kernel.
-qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st) {
+qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st,
+                                  const PeerSpec* peers) {
     if (count == 0) return QB200_OK;
     const uint32_t K = (uint32_t)f[0].in_dim, M = (uint32_t)f[0].m;
     const bool reg_path = K / 128 <= 2 * REG_WARPS;
     // Row blocks per item: a lone small layer keeps 16-row items (more items to pipeline and to
     // overlap with the neighbouring launches); grouped launches take 32-row items.
-    uint32_t rb = count > 1 ? 2 : 1;
+    uint32_t rb = (count > 1 || peers) ? 2 : 1;
     if (!reg_path) rb = 1;
     uint64_t all_tiles = 0;
     for (uint32_t i = 0; i < count; i++) all_tiles += (f[i].out_dim + 16 * rb - 1) / (16 * rb);
@@ -544,6 +547,8 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
         for (uint32_t i = 0; i < n; i++)
             if (reinterpret_cast<uintptr_t>(b.layer[i].scales) & 15u) b.async_scales = 1;
         b.status = status;
+        b.n_peers = peers ? peers->world : 0;
+        for (uint32_t p = 0; p < 8; p++) b.peer_delta[p] = peers ? peers->delta[p] : 0;
         b.count = n;
         b.total_items = items;
         b.M = M;
@@ -556,6 +561,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             // the kernel with a service warp (nt == 1, rb == 2) keeps only the batch's columns of the
             // partial sums, which for a single row frees the room of one more 68 KB stage
             const bool service = nt == 1 && rb == 2;
+            if (peers && !service) return QB200_ERR_NOT_SUPPORTED;  // only the service warp stores to peers
             b.red_cols = service ? (M <= 2 ? 2 : M <= 4 ? 4 : 8) : 0;
             const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : service ? 227u : 200u) * 1024;
             uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
@@ -572,6 +578,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             if (r) return r;
             continue;
         }
+        if (peers) return QB200_ERR_NOT_SUPPORTED;
         GemvShape s;
         if (!gemv_shape(K, M, (items + ctas - 1) / ctas, n == 1, s)) return QB200_ERR_NOT_SUPPORTED;
         b.stages = s.stages;
@@ -586,7 +593,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
 }
 
 qb200_status gemv_i4_forward(const FwdArgs& f, int y_dtype, int32_t* status, cudaStream_t st) {
-    return gemv_i4_forward_many(&f, 1, y_dtype, status, st);
+    return gemv_i4_forward_many(&f, 1, y_dtype, status, st, nullptr);
 }
 
 }  // namespace qb

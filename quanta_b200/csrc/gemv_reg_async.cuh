@@ -133,7 +133,14 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
                         float v = 0.0f;
 #pragma unroll
                         for (int w = 0; w < REG_WARPS; w++) v += red[(w * RB * 16 + r) * BW + b];
-                        store_y<YT>(static_cast<YT*>(it.y) + (uint64_t)b * it.N + n, fmaf(v, GEMV_UNSCALE, bias));
+                        YT* yp = static_cast<YT*>(it.y) + (uint64_t)b * it.N + n;
+                        const float out = fmaf(v, GEMV_UNSCALE, bias);
+                        if (a.n_peers == 0) {
+                            store_y<YT>(yp, out);
+                        } else {  // fused all-gather: the same element of every rank's buffer (peer memory over NVLink)
+                            for (uint32_t p = 0; p < a.n_peers; p++)
+                                store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<uint8_t*>(yp) + a.peer_delta[p]), out);
+                        }
                     }
                 }
             }

@@ -179,6 +179,48 @@ qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t c
     return QB200_OK;
 }
 
+qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev,
+                                               int32_t x_dtype, uint64_t m, void* const* y_own, int32_t y_dtype,
+                                               void* const* gather_bases, uint32_t world, uint32_t rank, void* stream) {
+    if (count == 0 || m == 0) return QB200_OK;
+    if (!layers || !x_dev || !y_own || !gather_bases || world == 0 || world > 8 || rank >= world)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_gather: null argument or bad world / rank");
+    for (uint32_t p = 0; p < world; p++)
+        if (!gather_bases[p]) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_gather: null gather buffer");
+    std::vector<qb::FwdArgs> args(count);
+    for (uint32_t i = 0; i < count; i++) {
+        const qb200_qlinear* q = layers[i];
+        if (!q || !x_dev[i] || !y_own[i])
+            return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_gather: null entry " + std::to_string(i));
+        if (q->in_dim != layers[0]->in_dim ||
+            !qb::gemv_i4_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes, q->scales, x_dev[i]))
+            return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_gather: layer " + std::to_string(i) +
+                                                     " does not take the decode kernel (int4, 1x128, [out, in], bf16 x, m <= 8)");
+        qb::FwdArgs& a = args[i];
+        a.codes = q->codes;
+        a.scales = q->scales;
+        a.bias = q->bias;
+        a.x = x_dev[i];
+        a.y = y_own[i];
+        a.m = m;
+        a.in_dim = q->in_dim;
+        a.out_dim = q->out_dim;
+        a.gr = q->gr;
+        a.gc = q->gc;
+        a.tc = q->tc;
+    }
+    qb::PeerSpec peers;
+    peers.world = world;
+    for (uint32_t p = 0; p < world; p++)
+        peers.delta[p] = static_cast<int64_t>(reinterpret_cast<intptr_t>(gather_bases[p]) - reinterpret_cast<intptr_t>(gather_bases[rank]));
+    qb200_status s = qb::gemv_i4_forward_many(args.data(), count, y_dtype, layers[0]->status, static_cast<cudaStream_t>(stream), &peers);
+    if (s == QB200_ERR_NOT_SUPPORTED)
+        return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_gather: no launch plan with peer stores fits this shape (m <= 8, K <= 4096)");
+    if (s == QB200_OK)
+        for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_grouped_gather";
+    return s;
+}
+
 qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint32_t count, const void* const* x_host,
                                              int32_t x_dtype, uint64_t m, void* const* y_host, int32_t y_dtype) {
     if (count == 0 || m == 0) return QB200_OK;

@@ -8,6 +8,7 @@ NVLink on GPUs, gloo on CPU for the host-side tests).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Optional, Tuple
 
 import torch
@@ -15,7 +16,7 @@ import torch.distributed as dist
 
 from . import _lib as L
 from .nn_quant import QuantizedLinear
-from .quant import QuantError, QuantizedMatrix
+from .quant import QuantError, QuantizedMatrix, check as _check
 
 
 def shard_range(out_dim: int, world: int, rank: int, multiple: int = 1) -> Tuple[int, int]:
@@ -100,3 +101,93 @@ class TensorParallelLinear:
         if dist.get_world_size(self.group) == 1:
             return y
         return _gather(y, x.shape[0], self._widths, self.group)
+
+
+class _RawCuda:
+    """A raw device allocation seen through the CUDA array interface (torch.as_tensor aliases it)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class PeerGather:
+    """The fused all-gather of a group of column-sharded decode layers.
+
+    Every rank owns a gather buffer ``[world, count, m, n_local]`` (plus nine u64 of barrier
+    state) in a cudaMalloc allocation shared with the node's other ranks through CUDA IPC;
+    ``forward_many`` runs the grouped decode kernel, whose service warp stores each output
+    into every rank's buffer, and then the arrival barrier.  After it returns (stream order)
+    ``view()`` holds all ranks' outputs — no collective call.  Shapes the kernel does not take
+    raise QuantError(NOT_SUPPORTED); callers fall back to ``TensorParallelLinear``.
+    """
+
+    def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16")
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise QuantError(L.ERR_NOT_SUPPORTED, "PeerGather: at most 8 ranks (one NVSwitch node)")
+        self.count, self.m, self.n_local, self.dtype = count, m, n_local, dtype
+        self.item = 4 if dtype == torch.float32 else 2
+        self.slot_bytes = count * m * n_local * self.item
+        self.data_bytes = -(-self.world * self.slot_bytes // 256) * 256
+        lib = L.load()
+        own, handle = L.vp(), ctypes.create_string_buffer(64)
+        _check(lib.qb200_peer_alloc(self.data_bytes + 128, ctypes.byref(own), handle))
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(self.device)
+        every = torch.empty(self.world * 64, dtype=torch.uint8, device=self.device)
+        dist.all_gather_into_tensor(every, mine, group=group)
+        every = every.cpu().numpy().tobytes()
+        self._own = own.value
+        self.bases: List[int] = []
+        for p in range(self.world):
+            if p == self.rank:
+                self.bases.append(self._own)
+                continue
+            ptr = L.vp()
+            _check(lib.qb200_peer_open(every[64 * p: 64 * p + 64], ctypes.byref(ptr)))
+            self.bases.append(ptr.value)
+        self._bases_c = (L.vp * self.world)(*self.bases)
+        self._flags_c = (L.vp * self.world)(*[b + self.data_bytes for b in self.bases])
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores
+
+    def view(self) -> torch.Tensor:
+        """This rank's gather buffer as a tensor ``[world, count, m, n_local]`` (aliases the allocation)."""
+        shape = (self.world, self.count, self.m, self.n_local)
+        if self.dtype == torch.float32:
+            return torch.as_tensor(_RawCuda(self._own, shape, "<f4"), device=self.device)
+        return torch.as_tensor(_RawCuda(self._own, shape, "<i2"), device=self.device).view(torch.bfloat16)
+
+    def forward_many(self, layers: List[QuantizedLinear], xs: List[torch.Tensor]) -> torch.Tensor:
+        if len(layers) != self.count or len(xs) != self.count:
+            raise QuantError(L.ERR_INVALID_PARAM, f"PeerGather: built for {self.count} layers")
+        lib = L.load()
+        per_layer = self.m * self.n_local * self.item
+        own0 = self._own + self.rank * self.slot_bytes
+        hs = (L.vp * self.count)(*[ql._h for ql in layers])
+        xp = (L.vp * self.count)(*[x.data_ptr() for x in xs])
+        yp = (L.vp * self.count)(*[own0 + i * per_layer for i in range(self.count)])
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _check(lib.qb200_qlinear_forward_many_gather(hs, self.count, xp, L.BF16, self.m, yp,
+                                                      L.F32 if self.dtype == torch.float32 else L.BF16,
+                                                      self._bases_c, self.world, self.rank, stream))
+        _check(lib.qb200_peer_signal_wait(self._flags_c, self.world, self.rank, self.status.data_ptr(), stream))
+        return self.view()
+
+    def check(self) -> None:
+        """Synchronises and raises if a bounded wait of the barrier ran out."""
+        if int(self.status.item()) != 0:
+            raise QuantError(L.ERR_TIMEOUT, "PeerGather: a rank did not arrive within the barrier's poll limit")
+
+    def close(self) -> None:
+        lib = L.load()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # nobody unmaps while a peer may still store
+        for p, b in enumerate(self.bases):
+            if p != self.rank:
+                lib.qb200_peer_close(b)
+        dist.barrier(group=self.group)
+        lib.qb200_peer_free(self._own)
+        self.bases = []
