@@ -301,9 +301,19 @@ def run_ours(args):
     xp = (_lib.vp * LAYERS)(*[x.data_ptr()] * LAYERS)
     yp = (_lib.vp * LAYERS)(*[t.data_ptr() for t in ys])
     grouped = args.launch == "grouped"
+    # N > 1, grouped: the kernel stores the step's outputs into every rank's buffer itself (peer memory) and an
+    # arrival barrier follows; --gather nccl keeps the library all-gather for comparison
+    fused = world > 1 and grouped and args.gather == "fused" and m <= 8
+    pg = None
+    if fused:
+        from quanta_b200 import tp as _tp
+        pg = _tp.PeerGather(LAYERS, m, N_OUT, torch.float32)
 
     def step():
         cur = torch.cuda.current_stream(dev).cuda_stream  # the capture stream while a graph is recorded
+        if fused:
+            pg.forward_many(layers, [x] * LAYERS)
+            return
         if grouped:  # the 32 layers read the same x: one persistent launch streams all their codes
             st = lib.qb200_qlinear_forward_many(hs, LAYERS, xp, _lib.BF16, m, yp, _lib.F32, cur)
             if st:
@@ -371,7 +381,7 @@ def run_ours(args):
         tmax = torch.tensor([ms], device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms = float(tmax.item())
-    launches = (1 if grouped else LAYERS) * args.steps
+    launches = (2 if fused else 1 if grouped else LAYERS) * args.steps  # fused: the GEMV and the arrival barrier
     total_bytes = layer_bytes(m) * LAYERS * args.steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
 
@@ -410,7 +420,9 @@ def run_ours(args):
 
     if rank == 0:
         peak, which = measured_peak_gbs()
-        per_launch_s = ms * 1e-3 / launches
+        # the dominant kernel is launched once per step (grouped) or once per layer; at N > 1 the step's time also
+        # holds the exchange, so the fraction below is a lower bound there
+        per_launch_s = ms * 1e-3 / ((1 if grouped else LAYERS) * args.steps)
         achieved = layer_bytes(m) * (LAYERS if grouped else 1) / per_launch_s / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -420,7 +432,9 @@ def run_ours(args):
                        "layers_per_step": LAYERS, "l2": "inputs larger than L2 (32 distinct weight matrices, 286 MB)",
                        "kernel": layers[0].last_kernel(), "launch": ("one persistent launch per step" if grouped else "one launch per layer") +
                                  (", eager" if args.no_graph else ", cuda graph replay"),
-                       "parallelism": "single GPU" if world == 1 else (f"column-sharded x{world}, one all-gather of the step's outputs" if grouped
+                       "parallelism": "single GPU" if world == 1 else (
+                           f"column-sharded x{world}, outputs stored to every rank's buffer by the kernel (peer memory) + arrival barrier" if fused
+                           else f"column-sharded x{world}, one NCCL all-gather of the step's outputs" if grouped
                                         else f"column-sharded x{world}, all-gather per layer")},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": (1 if grouped else LAYERS) * m * K_IN * 2,
@@ -465,6 +479,8 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "per-layer"],
                     help="grouped: the step's layers go through qb200_qlinear_forward_many (one persistent launch); "
                          "per-layer: one qb200_qlinear_forward launch per layer")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1, grouped launch: fused = peer stores from the kernel + arrival barrier; nccl = all-gather after it")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
     ap.add_argument("--only", default=None, choices=["prefill", "quantize"], help="run only a side workload and print its numbers")
