@@ -248,6 +248,29 @@ def measure_extras(torch, qb, dev, only=None, small=False):
         del lys
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
+    # whole-model decode step: 32 Llama-7B-shaped blocks + vocabulary projection, int4 1x128 linears, batch 16,
+    # 1024 cached positions (KV bf16, 8.6 GB), random-initialised; one step = one CUDA graph replay
+    try:
+        from quanta_b200 import decoder as dec
+        torch.cuda.empty_cache()
+        stack = dec.DecoderStack(32, 4096, 32, 11008, 32000, 16, 1025, dev, seed=4)
+        stack.set_position(1024)
+        h0 = torch.randn(16, 4096, device=dev, generator=gen) * 0.02
+        for _ in range(2):
+            stack.step(h0)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            stack.step(h0)
+        ms = timed(g.replay, 20)
+        by = stack.weight_bytes + stack.kv_bytes(1025)
+        out["decode_step_llama7b_shape"] = {"tokens/s": 16 / ms * 1e3, "ms_per_step": ms, "batch": 16, "context": 1024,
+                                            "GB/s": by / ms / 1e6, "roofline_frac": by / ms / 1e6 / hbm, "bytes_per_step": by,
+                                            "launch": "cuda graph replay of the step"}
+        del stack, g
+        torch.cuda.empty_cache()
+    except Exception as e:  # the rest of the line must survive
+        out["decode_step_llama7b_shape"] = {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
     ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
     ms = timed(lambda: ql.forward(x), 10)
     out["prefill_int4_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,

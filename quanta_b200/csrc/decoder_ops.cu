@@ -1,0 +1,266 @@
+// The support ops of a decode step around the quantized linears (needed only to time the
+// whole-model configuration; the hot path is the linears).  f32 arithmetic, bf16 storage for
+// what feeds the next linear and for the KV cache.
+//
+// Reference semantics:
+//   RMSNorm   rrms = 1 / sqrt(sum(x^2) / c + eps), out = x * rrms * gamma
+//             (crates/ml/quanta-nn/src/norm.rs:192-225)
+//   RoPE      rotate-half: out[j] = x[j] cos[j] -/+ x[j +/- d/2] sin[j], the table built in f64 on
+//             the host (crates/sci/quanta-array/src/autograd/rope.rs:43-63, quanta-nn/src/rope.rs:23-58)
+//   SDPA      online softmax over the keys, score = scale * (q . k), keys >= kv_len masked
+//             (crates/ml/quanta-nn/src/kernel.rs:64-175)
+//   SwiGLU    out = a * s * b, s = 1 / (1 + exp(min(-a, 30)))
+//             (crates/ml/quanta-nn/src/activation.rs:145-162)
+#include <cstdint>
+#include <string>
+
+#include "common.hpp"
+#include "quant_math.cuh"
+
+namespace qb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+// h += delta (when given), out = bf16(rmsnorm(h) * gamma).  One block per row.
+__global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ h, const float* __restrict__ delta,
+                                                     const float* __restrict__ gamma, uint32_t c, float eps,
+                                                     uint16_t* __restrict__ out) {
+    __shared__ float s_part[8];
+    const uint64_t base = (uint64_t)blockIdx.x * c;
+    float sq = 0.0f;
+    for (uint32_t i = threadIdx.x; i < c; i += 256) {
+        float v = h[base + i];
+        if (delta) {
+            v += delta[base + i];
+            h[base + i] = v;
+        }
+        sq = fmaf(v, v, sq);
+    }
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot += s_part[w];
+    const float rrms = 1.0f / sqrtf(tot / (float)c + eps);
+    for (uint32_t i = threadIdx.x; i < c; i += 256) out[base + i] = f32_to_bf16_bits(h[base + i] * rrms * gamma[i]);
+}
+
+// q, k: rotate by the position's angles; q -> bf16 [b, heads, hd]; k, v -> the cache row `pos`.
+__global__ void __launch_bounds__(128) k_rope_append(const float* __restrict__ q, const float* __restrict__ k,
+                                                     const float* __restrict__ v, const float* __restrict__ cosv,
+                                                     const float* __restrict__ sinv, uint32_t heads, uint32_t hd,
+                                                     uint16_t* __restrict__ q_out, uint16_t* __restrict__ kcache,
+                                                     uint16_t* __restrict__ vcache, uint32_t ctx_max, uint32_t pos) {
+    const uint32_t b = blockIdx.x / heads, hh = blockIdx.x % heads, half = hd >> 1;
+    const uint64_t in = ((uint64_t)b * heads + hh) * hd;
+    const uint64_t cache = (((uint64_t)b * ctx_max + pos) * heads + hh) * hd;
+    for (uint32_t j = threadIdx.x; j < hd; j += blockDim.x) {
+        const uint32_t partner = j < half ? j + half : j - half;
+        const float pm = j < half ? -1.0f : 1.0f, c = cosv[j], s = sinv[j];
+        const float qr = q[in + j] * c + pm * q[in + partner] * s;
+        const float kr = k[in + j] * c + pm * k[in + partner] * s;
+        q_out[in + j] = f32_to_bf16_bits(qr);
+        kcache[cache + j] = f32_to_bf16_bits(kr);
+        vcache[cache + j] = f32_to_bf16_bits(v[in + j]);
+    }
+}
+
+// Decode attention, first pass: one block per (batch row, head, split of SDPA_SPLIT keys); a warp
+// takes one key at a time (a key's hd bf16 are one coalesced read: lane l holds elements 4l..4l+3
+// for hd = 128), keeps the online-softmax state (m, l) and its slice of the weighted V sum; the
+// block's warps are merged and the split's (m, l, acc) go to scratch.
+constexpr uint32_t SDPA_SPLIT = 128, SDPA_WARPS = 4;
+
+__global__ void __launch_bounds__(SDPA_WARPS * 32) k_sdpa_decode_split(const uint16_t* __restrict__ q,
+                                                                        const uint16_t* __restrict__ kcache,
+                                                                        const uint16_t* __restrict__ vcache, uint32_t heads,
+                                                                        uint32_t ctx_max, uint32_t kv_len, float scale,
+                                                                        uint32_t splits, float* __restrict__ scratch) {
+    constexpr uint32_t HD = 128;
+    __shared__ float s_m[SDPA_WARPS], s_l[SDPA_WARPS], s_acc[SDPA_WARPS][HD];
+    const uint32_t split = blockIdx.x % splits, bh = blockIdx.x / splits, b = bh / heads, hh = bh % heads;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint2 qv = *reinterpret_cast<const uint2*>(q + ((uint64_t)b * heads + hh) * HD + lane * 4);
+    const float q0 = bf16_bits_to_f32(qv.x & 0xFFFFu), q1 = bf16_bits_to_f32(qv.x >> 16);
+    const float q2 = bf16_bits_to_f32(qv.y & 0xFFFFu), q3 = bf16_bits_to_f32(qv.y >> 16);
+    float m = -3.0e38f, l = 0.0f, a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    const uint32_t k_end = min(kv_len, (split + 1) * SDPA_SPLIT);
+    for (uint32_t kj = split * SDPA_SPLIT + warp; kj < k_end; kj += SDPA_WARPS) {
+        const uint64_t row = (((uint64_t)b * ctx_max + kj) * heads + hh) * HD + lane * 4;
+        const uint2 kv = *reinterpret_cast<const uint2*>(kcache + row);
+        const uint2 vv = *reinterpret_cast<const uint2*>(vcache + row);
+        float dot = q0 * bf16_bits_to_f32(kv.x & 0xFFFFu);
+        dot = fmaf(q1, bf16_bits_to_f32(kv.x >> 16), dot);
+        dot = fmaf(q2, bf16_bits_to_f32(kv.y & 0xFFFFu), dot);
+        dot = fmaf(q3, bf16_bits_to_f32(kv.y >> 16), dot);
+        const float sk = scale * warp_sum(dot);
+        const float m_new = fmaxf(m, sk);
+        const float ra = expf(m - m_new), rb = expf(sk - m_new);
+        l = fmaf(l, ra, rb);
+        a0 = fmaf(a0, ra, rb * bf16_bits_to_f32(vv.x & 0xFFFFu));
+        a1 = fmaf(a1, ra, rb * bf16_bits_to_f32(vv.x >> 16));
+        a2 = fmaf(a2, ra, rb * bf16_bits_to_f32(vv.y & 0xFFFFu));
+        a3 = fmaf(a3, ra, rb * bf16_bits_to_f32(vv.y >> 16));
+        m = m_new;
+    }
+    if (lane == 0) {
+        s_m[warp] = m;
+        s_l[warp] = l;
+    }
+    s_acc[warp][lane * 4] = a0;
+    s_acc[warp][lane * 4 + 1] = a1;
+    s_acc[warp][lane * 4 + 2] = a2;
+    s_acc[warp][lane * 4 + 3] = a3;
+    __syncthreads();
+    if (threadIdx.x < HD) {  // merge the warps: thread = one of the hd outputs
+        float M = s_m[0];
+#pragma unroll
+        for (int w = 1; w < (int)SDPA_WARPS; w++) M = fmaxf(M, s_m[w]);
+        float L = 0.0f, A = 0.0f;
+#pragma unroll
+        for (int w = 0; w < (int)SDPA_WARPS; w++) {
+            const float r = expf(s_m[w] - M);
+            L = fmaf(s_l[w], r, L);
+            A = fmaf(s_acc[w][threadIdx.x], r, A);
+        }
+        float* o = scratch + ((uint64_t)bh * splits + split) * (HD + 2);
+        o[2 + threadIdx.x] = A;
+        if (threadIdx.x == 0) {
+            o[0] = M;
+            o[1] = L;
+        }
+    }
+}
+
+// Second pass: merge the splits of one (batch row, head); out = acc / l as bf16.
+__global__ void __launch_bounds__(128) k_sdpa_decode_merge(const float* __restrict__ scratch, uint32_t splits,
+                                                           uint16_t* __restrict__ out) {
+    constexpr uint32_t HD = 128;
+    const uint32_t bh = blockIdx.x;
+    const float* s = scratch + (uint64_t)bh * splits * (HD + 2);
+    float M = -3.0e38f;
+    for (uint32_t i = 0; i < splits; i++) M = fmaxf(M, s[i * (HD + 2)]);
+    float L = 0.0f, A = 0.0f;
+    for (uint32_t i = 0; i < splits; i++) {
+        const float r = expf(s[i * (HD + 2)] - M);
+        L = fmaf(s[i * (HD + 2) + 1], r, L);
+        A = fmaf(s[i * (HD + 2) + 2 + threadIdx.x], r, A);
+    }
+    out[(uint64_t)bh * HD + threadIdx.x] = f32_to_bf16_bits(A / L);
+}
+
+// out = silu(gate) * up as bf16, written in column slices: slice s holds columns
+// [start_s, start_s + width_s) of every row back to back ([n, width_s] each), so that a linear
+// whose input width exceeds the decode kernel's limit can run as one grouped launch over
+// contiguous inputs.
+struct SliceSpec {
+    uint32_t count;
+    uint32_t start[8], width[8];
+    uint64_t offset[8];  // element offset of the slice's [n, width] block in `out`
+};
+__global__ void __launch_bounds__(256) k_swiglu_sliced(const float* __restrict__ gate, const float* __restrict__ up,
+                                                       uint32_t n, uint32_t h, SliceSpec sp, uint16_t* __restrict__ out) {
+    const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (uint64_t)n * h) return;
+    const uint32_t row = (uint32_t)(i / h), col = (uint32_t)(i % h);
+    const float a = gate[i], b = up[i];
+    const float s = 1.0f / (1.0f + expf(fminf(-a, 30.0f)));
+    uint32_t sl = 0;
+    while (sl + 1 < sp.count && col >= sp.start[sl + 1]) sl++;
+    out[sp.offset[sl] + (uint64_t)row * sp.width[sl] + (col - sp.start[sl])] = f32_to_bf16_bits(a * s * b);
+}
+
+// y[i] = sum of `count` arrays (the partial outputs of a sliced linear).
+__global__ void __launch_bounds__(256) k_sum_arrays(const float* __restrict__ parts, uint32_t count, uint64_t n,
+                                                    float* __restrict__ y) {
+    const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float v = parts[i];
+    for (uint32_t p = 1; p < count; p++) v += parts[(uint64_t)p * n + i];
+    y[i] = v;
+}
+
+}  // namespace qb
+
+using qb::fail;
+
+extern "C" {
+
+qb200_status qb200_add_rmsnorm(float* h, const float* delta, const float* gamma, uint64_t n, uint64_t c, float eps,
+                               uint16_t* out_bf16, void* stream) {
+    if (!h || !gamma || !out_bf16) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: null pointer");
+    if (n == 0 || c == 0 || c > 0x7FFFFFFFull || n > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: bad shape");
+    qb::k_add_rmsnorm<<<(uint32_t)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(h, delta, gamma, (uint32_t)c, eps, out_bf16);
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+qb200_status qb200_rope_append(const float* q, const float* k, const float* v, const float* cos_row, const float* sin_row,
+                               uint32_t b, uint32_t heads, uint32_t hd, uint16_t* q_out, uint16_t* kcache, uint16_t* vcache,
+                               uint32_t ctx_max, uint32_t pos, void* stream) {
+    if (!q || !k || !v || !cos_row || !sin_row || !q_out || !kcache || !vcache)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_rope_append: null pointer");
+    if (hd == 0 || (hd & 1) || pos >= ctx_max || b == 0 || heads == 0)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_rope_append: head dim must be even and the position inside the cache");
+    qb::k_rope_append<<<b * heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(q, k, v, cos_row, sin_row, heads, hd, q_out, kcache,
+                                                                                vcache, ctx_max, pos);
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+uint64_t qb200_sdpa_decode_scratch_floats(uint32_t b, uint32_t heads, uint32_t kv_len) {
+    const uint64_t splits = (kv_len + qb::SDPA_SPLIT - 1) / qb::SDPA_SPLIT;
+    return (uint64_t)b * heads * splits * (128 + 2);
+}
+
+qb200_status qb200_sdpa_decode(const uint16_t* q, const uint16_t* kcache, const uint16_t* vcache, uint32_t b, uint32_t heads,
+                               uint32_t hd, uint32_t ctx_max, uint32_t kv_len, float scale, float* scratch, uint16_t* out,
+                               void* stream) {
+    if (!q || !kcache || !vcache || !scratch || !out) return fail(QB200_ERR_INVALID_PARAM, "qb200_sdpa_decode: null pointer");
+    if (hd != 128) return fail(QB200_ERR_NOT_SUPPORTED, "qb200_sdpa_decode: head dim 128 only, got " + std::to_string(hd));
+    if (kv_len == 0 || kv_len > ctx_max || b == 0 || heads == 0) return fail(QB200_ERR_INVALID_PARAM, "qb200_sdpa_decode: bad lengths");
+    const uint32_t splits = (kv_len + qb::SDPA_SPLIT - 1) / qb::SDPA_SPLIT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    qb::k_sdpa_decode_split<<<b * heads * splits, qb::SDPA_WARPS * 32, 0, st>>>(q, kcache, vcache, heads, ctx_max, kv_len, scale, splits,
+                                                                               scratch);
+    QB_CUDA_TRY(cudaGetLastError());
+    qb::k_sdpa_decode_merge<<<b * heads, 128, 0, st>>>(scratch, splits, out);
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+qb200_status qb200_swiglu_sliced(const float* gate, const float* up, uint64_t n, uint64_t h, const uint32_t* slice_widths,
+                                 uint32_t slices, uint16_t* out, void* stream) {
+    if (!gate || !up || !out || !slice_widths) return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: null pointer");
+    if (slices == 0 || slices > 8 || n == 0 || h == 0 || n * h > 0x7FFFFFFFFFull)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: 1..8 slices");
+    qb::SliceSpec sp = {};
+    sp.count = slices;
+    uint64_t start = 0;
+    for (uint32_t s = 0; s < slices; s++) {
+        sp.start[s] = (uint32_t)start;
+        sp.width[s] = slice_widths[s];
+        sp.offset[s] = n * start;
+        start += slice_widths[s];
+    }
+    if (start != h) return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: the slice widths must add up to the hidden width");
+    qb::k_swiglu_sliced<<<(uint32_t)((n * h + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate, up, (uint32_t)n, (uint32_t)h,
+                                                                                                        sp, out);
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+qb200_status qb200_sum_arrays(const float* parts, uint32_t count, uint64_t n, float* y, void* stream) {
+    if (!parts || !y || count == 0) return fail(QB200_ERR_INVALID_PARAM, "qb200_sum_arrays: null pointer");
+    if (n == 0) return QB200_OK;
+    qb::k_sum_arrays<<<(uint32_t)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(parts, count, n, y);
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+}  // extern "C"

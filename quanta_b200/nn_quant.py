@@ -289,8 +289,9 @@ class QuantizedLinear:
     def init(self, *_a, **_k) -> tuple:
         return ()
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """The tape-free spelling of ``Layer::apply`` (quant.rs:903-918): y = x @ deq(w) (+ b)."""
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The tape-free spelling of ``Layer::apply`` (quant.rs:903-918): y = x @ deq(w) (+ b).  ``out``: a
+        contiguous ``[m, out]`` tensor of the output dtype to write into (Mode B)."""
         if x.dim() != 2 or x.shape[1] != self._in:
             raise QuantError(L.ERR_INVALID_PARAM, f"QuantizedLinear: input shape {list(x.shape)}, layer wants [m, {self._in}]")
         if self._held is not None:
@@ -304,7 +305,12 @@ class QuantizedLinear:
             raise QuantError(L.ERR_INVALID_PARAM, f"QuantizedLinear: activations are f32 or bf16, got {x.dtype}")
         out_dtype = out_dtype or x.dtype
         x = x.contiguous()
-        y = torch.empty((x.shape[0], self._out), dtype=out_dtype, device=x.device)
+        if out is not None:
+            if out.shape != (x.shape[0], self._out) or out.dtype != out_dtype or not out.is_contiguous():
+                raise QuantError(L.ERR_INVALID_PARAM, "QuantizedLinear: out must be a contiguous [m, out] tensor of the output dtype")
+            y = out
+        else:
+            y = torch.empty((x.shape[0], self._out), dtype=out_dtype, device=x.device)
         with torch.cuda.device(x.device):
             check(L.load().qb200_qlinear_forward(self._h, x.data_ptr(), _ACT[x.dtype], x.shape[0], y.data_ptr(),
                                                  _ACT[out_dtype], _stream(x)))
