@@ -196,8 +196,9 @@ QB200_API qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, 
 
 /* ---- support ops of a decode step (needed to time the whole-model configuration; f32 arithmetic,
  * bf16 storage for what feeds the next linear and for the KV cache) ----
- * qb200_add_rmsnorm: h += delta (delta may be null), out = bf16(h * rrms * gamma), rrms = 1 / sqrt(sum(h^2) / c + eps)
- *   (crates/ml/quanta-nn/src/norm.rs:192-225).
+ * qb200_add_rmsnorm: h += delta[0] + ... + delta[delta_parts - 1] (arrays of n * c floats back to back, for example the
+ *   partial outputs of a sliced linear; delta_parts = 0: nothing is added), out = bf16(h * rrms * gamma),
+ *   rrms = 1 / sqrt(sum(h^2) / c + eps) (crates/ml/quanta-nn/src/norm.rs:192-225).
  * qb200_rope_append: rotate-half RoPE of q and k with one position's cos / sin rows ([hd] each, built in f64 on the
  *   host as crates/sci/quanta-array/src/autograd/rope.rs:43-63 does); q -> bf16 [b, heads, hd], rotated k and v ->
  *   row `pos` of the caches [b, ctx_max, heads, hd] (crates/ml/quanta-nn/src/rope.rs:23-58).
@@ -206,11 +207,12 @@ QB200_API qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, 
  *   qb200_sdpa_decode_scratch_floats(b, heads, kv_len) floats.
  * qb200_swiglu_sliced: out = a * s * b with s = 1 / (1 + exp(min(-a, 30))) (crates/ml/quanta-nn/src/activation.rs:
  *   145-162), a = gate[n, h], b = up[n, h]; the result is written as `slices` blocks [n, width_s] laid back to back
- *   (column slices of the [n, h] result), so a following linear wider than the decode kernel's input limit can run as
- *   a grouped launch over contiguous inputs.
+ *   (column slices of the [n, h] result; with pad_to > 0 every block is [n, pad_to] and the columns past the slice's
+ *   width are left as they are), so a following linear wider than the decode kernel's input limit can run as a
+ *   grouped launch over contiguous inputs of one width.
  * qb200_sum_arrays: y = parts[0] + ... + parts[count - 1], n floats each (the partial outputs of such a linear). */
-QB200_API qb200_status qb200_add_rmsnorm(float* h, const float* delta, const float* gamma, uint64_t n, uint64_t c,
-                                         float eps, uint16_t* out_bf16, void* stream);
+QB200_API qb200_status qb200_add_rmsnorm(float* h, const float* delta, uint32_t delta_parts, const float* gamma, uint64_t n,
+                                         uint64_t c, float eps, uint16_t* out_bf16, void* stream);
 QB200_API qb200_status qb200_rope_append(const float* q, const float* k, const float* v, const float* cos_row,
                                          const float* sin_row, uint32_t b, uint32_t heads, uint32_t hd, uint16_t* q_out,
                                          uint16_t* kcache, uint16_t* vcache, uint32_t ctx_max, uint32_t pos, void* stream);
@@ -219,7 +221,8 @@ QB200_API qb200_status qb200_sdpa_decode(const uint16_t* q, const uint16_t* kcac
                                          uint32_t heads, uint32_t hd, uint32_t ctx_max, uint32_t kv_len, float scale,
                                          float* scratch, uint16_t* out, void* stream);
 QB200_API qb200_status qb200_swiglu_sliced(const float* gate, const float* up, uint64_t n, uint64_t h,
-                                           const uint32_t* slice_widths, uint32_t slices, uint16_t* out, void* stream);
+                                           const uint32_t* slice_widths, uint32_t slices, uint32_t pad_to, uint16_t* out,
+                                           void* stream);
 QB200_API qb200_status qb200_sum_arrays(const float* parts, uint32_t count, uint64_t n, float* y, void* stream);
 
 /* ---- fused all-gather for column-sharded layers (no counterpart in the reference: it has no

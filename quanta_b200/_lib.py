@@ -51,11 +51,11 @@ SIGNATURES = {
     "qb200_qlinear_forward_static": (i32, [vp, vp, i32, u64, vp, i32, vp]),
     "qb200_qlinear_forward_many": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32, vp]),
     "qb200_qlinear_forward_many_host": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32]),
-    "qb200_add_rmsnorm": (i32, [vp, vp, vp, u64, u64, ctypes.c_float, vp, vp]),
+    "qb200_add_rmsnorm": (i32, [vp, vp, u32, vp, u64, u64, ctypes.c_float, vp, vp]),
     "qb200_rope_append": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, vp, vp, vp, u32, u32, vp]),
     "qb200_sdpa_decode_scratch_floats": (u64, [u32, u32, u32]),
     "qb200_sdpa_decode": (i32, [vp, vp, vp, u32, u32, u32, u32, u32, ctypes.c_float, vp, vp, vp]),
-    "qb200_swiglu_sliced": (i32, [vp, vp, u64, u64, P(u32), u32, vp, vp]),
+    "qb200_swiglu_sliced": (i32, [vp, vp, u64, u64, P(u32), u32, u32, vp, vp]),
     "qb200_sum_arrays": (i32, [vp, u32, u64, vp, vp]),
     "qb200_peer_alloc": (i32, [u64, P(vp), ctypes.c_char_p]),
     "qb200_peer_open": (i32, [ctypes.c_char_p, P(vp)]),

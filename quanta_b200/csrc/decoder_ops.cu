@@ -25,17 +25,20 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// h += delta (when given), out = bf16(rmsnorm(h) * gamma).  One block per row.
-__global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ h, const float* __restrict__ delta,
-                                                     const float* __restrict__ gamma, uint32_t c, float eps,
+// h += delta[0] + ... + delta[parts - 1] (arrays of n * c floats laid back to back; the partial outputs of a
+// sliced linear), out = bf16(rmsnorm(h) * gamma).  One block per row.
+__global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ h, const float* __restrict__ delta, uint32_t parts,
+                                                     uint64_t part_stride, const float* __restrict__ gamma, uint32_t c, float eps,
                                                      uint16_t* __restrict__ out) {
     __shared__ float s_part[8];
     const uint64_t base = (uint64_t)blockIdx.x * c;
     float sq = 0.0f;
     for (uint32_t i = threadIdx.x; i < c; i += 256) {
         float v = h[base + i];
-        if (delta) {
-            v += delta[base + i];
+        if (parts) {
+            float d = delta[base + i];
+            for (uint32_t p = 1; p < parts; p++) d += delta[p * part_stride + base + i];
+            v += d;
             h[base + i] = v;
         }
         sq = fmaf(v, v, sq);
@@ -90,22 +93,55 @@ __global__ void __launch_bounds__(SDPA_WARPS * 32) k_sdpa_decode_split(const uin
     const float q2 = bf16_bits_to_f32(qv.y & 0xFFFFu), q3 = bf16_bits_to_f32(qv.y >> 16);
     float m = -3.0e38f, l = 0.0f, a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
     const uint32_t k_end = min(kv_len, (split + 1) * SDPA_SPLIT);
-    for (uint32_t kj = split * SDPA_SPLIT + warp; kj < k_end; kj += SDPA_WARPS) {
-        const uint64_t row = (((uint64_t)b * ctx_max + kj) * heads + hh) * HD + lane * 4;
-        const uint2 kv = *reinterpret_cast<const uint2*>(kcache + row);
-        const uint2 vv = *reinterpret_cast<const uint2*>(vcache + row);
-        float dot = q0 * bf16_bits_to_f32(kv.x & 0xFFFFu);
-        dot = fmaf(q1, bf16_bits_to_f32(kv.x >> 16), dot);
-        dot = fmaf(q2, bf16_bits_to_f32(kv.y & 0xFFFFu), dot);
-        dot = fmaf(q3, bf16_bits_to_f32(kv.y >> 16), dot);
-        const float sk = scale * warp_sum(dot);
-        const float m_new = fmaxf(m, sk);
-        const float ra = expf(m - m_new), rb = expf(sk - m_new);
-        l = fmaf(l, ra, rb);
-        a0 = fmaf(a0, ra, rb * bf16_bits_to_f32(vv.x & 0xFFFFu));
-        a1 = fmaf(a1, ra, rb * bf16_bits_to_f32(vv.x >> 16));
-        a2 = fmaf(a2, ra, rb * bf16_bits_to_f32(vv.y & 0xFFFFu));
-        a3 = fmaf(a3, ra, rb * bf16_bits_to_f32(vv.y >> 16));
+    const uint64_t key_stride = (uint64_t)heads * HD;
+    const uint64_t row0 = ((uint64_t)b * ctx_max * heads + hh) * HD + lane * 4;
+    // four keys per iteration (keys kj, kj + W, kj + 2W, kj + 3W): eight independent 8-byte loads in flight per lane
+    constexpr uint32_t U = 4;
+    for (uint32_t kj = split * SDPA_SPLIT + warp; kj < k_end; kj += SDPA_WARPS * U) {
+        uint2 kv[U], vv[U];
+        bool ok[U];
+#pragma unroll
+        for (uint32_t u = 0; u < U; u++) {
+            const uint32_t key = kj + u * SDPA_WARPS;
+            ok[u] = key < k_end;
+            const uint64_t row = row0 + (uint64_t)(ok[u] ? key : kj) * key_stride;
+            kv[u] = *reinterpret_cast<const uint2*>(kcache + row);
+            vv[u] = *reinterpret_cast<const uint2*>(vcache + row);
+        }
+        float sk[U];
+#pragma unroll
+        for (uint32_t u = 0; u < U; u++) {
+            float dot = q0 * bf16_bits_to_f32(kv[u].x & 0xFFFFu);
+            dot = fmaf(q1, bf16_bits_to_f32(kv[u].x >> 16), dot);
+            dot = fmaf(q2, bf16_bits_to_f32(kv[u].y & 0xFFFFu), dot);
+            dot = fmaf(q3, bf16_bits_to_f32(kv[u].y >> 16), dot);
+            sk[u] = dot;
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1)
+#pragma unroll
+            for (uint32_t u = 0; u < U; u++) sk[u] += __shfl_xor_sync(0xFFFFFFFFu, sk[u], o);
+        float m_new = m;
+#pragma unroll
+        for (uint32_t u = 0; u < U; u++) {
+            sk[u] = ok[u] ? scale * sk[u] : -3.0e38f;
+            m_new = fmaxf(m_new, sk[u]);
+        }
+        const float ra = expf(m - m_new);
+        l *= ra;
+        a0 *= ra;
+        a1 *= ra;
+        a2 *= ra;
+        a3 *= ra;
+#pragma unroll
+        for (uint32_t u = 0; u < U; u++) {
+            const float rb = ok[u] ? expf(sk[u] - m_new) : 0.0f;
+            l += rb;
+            a0 = fmaf(rb, bf16_bits_to_f32(vv[u].x & 0xFFFFu), a0);
+            a1 = fmaf(rb, bf16_bits_to_f32(vv[u].x >> 16), a1);
+            a2 = fmaf(rb, bf16_bits_to_f32(vv[u].y & 0xFFFFu), a2);
+            a3 = fmaf(rb, bf16_bits_to_f32(vv[u].y >> 16), a3);
+        }
         m = m_new;
     }
     if (lane == 0) {
@@ -160,7 +196,7 @@ __global__ void __launch_bounds__(128) k_sdpa_decode_merge(const float* __restri
 // contiguous inputs.
 struct SliceSpec {
     uint32_t count;
-    uint32_t start[8], width[8];
+    uint32_t start[8], width[8], stride[8];  // stride: row pitch of the slice's block (>= width; the rest is not written)
     uint64_t offset[8];  // element offset of the slice's [n, width] block in `out`
 };
 __global__ void __launch_bounds__(256) k_swiglu_sliced(const float* __restrict__ gate, const float* __restrict__ up,
@@ -172,7 +208,7 @@ __global__ void __launch_bounds__(256) k_swiglu_sliced(const float* __restrict__
     const float s = 1.0f / (1.0f + expf(fminf(-a, 30.0f)));
     uint32_t sl = 0;
     while (sl + 1 < sp.count && col >= sp.start[sl + 1]) sl++;
-    out[sp.offset[sl] + (uint64_t)row * sp.width[sl] + (col - sp.start[sl])] = f32_to_bf16_bits(a * s * b);
+    out[sp.offset[sl] + (uint64_t)row * sp.stride[sl] + (col - sp.start[sl])] = f32_to_bf16_bits(a * s * b);
 }
 
 // y[i] = sum of `count` arrays (the partial outputs of a sliced linear).
@@ -191,11 +227,12 @@ using qb::fail;
 
 extern "C" {
 
-qb200_status qb200_add_rmsnorm(float* h, const float* delta, const float* gamma, uint64_t n, uint64_t c, float eps,
-                               uint16_t* out_bf16, void* stream) {
-    if (!h || !gamma || !out_bf16) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: null pointer");
+qb200_status qb200_add_rmsnorm(float* h, const float* delta, uint32_t delta_parts, const float* gamma, uint64_t n, uint64_t c,
+                               float eps, uint16_t* out_bf16, void* stream) {
+    if (!h || !gamma || !out_bf16 || (delta_parts && !delta)) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: null pointer");
     if (n == 0 || c == 0 || c > 0x7FFFFFFFull || n > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: bad shape");
-    qb::k_add_rmsnorm<<<(uint32_t)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(h, delta, gamma, (uint32_t)c, eps, out_bf16);
+    qb::k_add_rmsnorm<<<(uint32_t)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(h, delta, delta ? delta_parts : 0, n * c, gamma, (uint32_t)c, eps,
+                                                                                   out_bf16);
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
 }
@@ -235,7 +272,7 @@ qb200_status qb200_sdpa_decode(const uint16_t* q, const uint16_t* kcache, const 
 }
 
 qb200_status qb200_swiglu_sliced(const float* gate, const float* up, uint64_t n, uint64_t h, const uint32_t* slice_widths,
-                                 uint32_t slices, uint16_t* out, void* stream) {
+                                 uint32_t slices, uint32_t pad_to, uint16_t* out, void* stream) {
     if (!gate || !up || !out || !slice_widths) return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: null pointer");
     if (slices == 0 || slices > 8 || n == 0 || h == 0 || n * h > 0x7FFFFFFFFFull)
         return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: 1..8 slices");
@@ -243,9 +280,11 @@ qb200_status qb200_swiglu_sliced(const float* gate, const float* up, uint64_t n,
     sp.count = slices;
     uint64_t start = 0;
     for (uint32_t s = 0; s < slices; s++) {
+        if (pad_to && slice_widths[s] > pad_to) return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: a slice is wider than pad_to");
         sp.start[s] = (uint32_t)start;
         sp.width[s] = slice_widths[s];
-        sp.offset[s] = n * start;
+        sp.stride[s] = pad_to ? pad_to : slice_widths[s];
+        sp.offset[s] = pad_to ? n * pad_to * s : n * start;
         start += slice_widths[s];
     }
     if (start != h) return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: the slice widths must add up to the hidden width");

@@ -25,10 +25,12 @@ def _stream(dev) -> int:
 
 
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gamma: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None):
-    """h += delta (in place, when delta is given); returns bf16(rmsnorm(h) * gamma)."""
+    """h += delta (in place, when delta is given; a ``[parts, n, c]`` delta is summed over parts first);
+    returns bf16(rmsnorm(h) * gamma)."""
     n, c = h.shape
     out = torch.empty(n, c, dtype=torch.bfloat16, device=h.device) if out is None else out
-    _check(L.load().qb200_add_rmsnorm(h.data_ptr(), 0 if delta is None else delta.data_ptr(), gamma.data_ptr(), n, c, eps,
+    parts = 0 if delta is None else (delta.shape[0] if delta.dim() == 3 else 1)
+    _check(L.load().qb200_add_rmsnorm(h.data_ptr(), 0 if delta is None else delta.data_ptr(), parts, gamma.data_ptr(), n, c, eps,
                                       out.data_ptr(), _stream(h.device)))
     return out
 
@@ -59,10 +61,13 @@ def sdpa_scratch(b: int, heads: int, kv_len: int, device) -> torch.Tensor:
     return torch.empty(int(L.load().qb200_sdpa_decode_scratch_floats(b, heads, kv_len)), dtype=torch.float32, device=device)
 
 
-def swiglu_sliced(gate, up, widths: List[int], out):
+def swiglu_sliced(gate, up, widths: List[int], out, pad_to: int = 0):
+    """silu(gate) * up as bf16 in column slices: block s is ``[n, widths[s]]`` (``[n, pad_to]`` with pad_to > 0; the
+    padding columns are not written)."""
     n, h = gate.shape
     w = (ctypes.c_uint32 * len(widths))(*widths)
-    _check(L.load().qb200_swiglu_sliced(gate.data_ptr(), up.data_ptr(), n, h, w, len(widths), out.data_ptr(), _stream(gate.device)))
+    _check(L.load().qb200_swiglu_sliced(gate.data_ptr(), up.data_ptr(), n, h, w, len(widths), pad_to, out.data_ptr(),
+                                        _stream(gate.device)))
     return out
 
 
@@ -93,16 +98,20 @@ class DecoderStack:
         self.eps, self.rope_base, self.device = eps, rope_base, device
         gen = torch.Generator(device=device).manual_seed(seed)
 
-        def qlin(n_out, n_in):
+        def qlin(n_out, n_in, pad_to=0):
             w = torch.randn(n_out, n_in, device=device, generator=gen) * 0.02
+            if pad_to > n_in:  # zero weights for the padding columns of a slice (their codes and scales are zero)
+                w = torch.cat([w, torch.zeros(n_out, pad_to - n_in, device=device)], 1)
             return QuantizedLinear.new(QuantizedMatrix.quantize(w, QuantDtype.Int4, Group(1, 128)), None, L.OUT_IN)
 
+        # the down projection runs as column slices of its input, all padded to one width so that the slices are
+        # ONE grouped launch: W_down = [W_0 | W_1 | ...], y = sum_s x_s @ W_s^T
         self.down_widths = _slices(ffn)
+        self.down_pad = max(self.down_widths)
         self.layers = []
         for _ in range(n_layers):
             blk = {"qkv": [qlin(d, d) for _ in range(3)], "o": qlin(d, d), "gate_up": [qlin(ffn, d) for _ in range(2)],
-                   # the down projection as column slices of its input: W_down = [W_0 | W_1 | ...]
-                   "down": [qlin(d, w) for w in self.down_widths],
+                   "down": [qlin(d, w, self.down_pad) for w in self.down_widths],
                    "g1": torch.ones(d, device=device), "g2": torch.ones(d, device=device)}
             self.layers.append(blk)
         self.g_final = torch.ones(d, device=device)
@@ -121,18 +130,13 @@ class DecoderStack:
         self.att = torch.empty(batch, d, **bf)
         self.o = torch.empty(batch, d, **f32)
         self.gu = torch.empty(2, batch, ffn, **f32)
-        self.act = torch.empty(batch * ffn, **bf)  # sliced layout: [slice][batch][width]
+        self.act = torch.zeros(len(self.down_widths), batch, self.down_pad, **bf)  # [slice][batch][padded width]
         self.down_parts = torch.empty(len(self.down_widths), batch, d, **f32)
-        self.down = torch.empty(batch, d, **f32)
         self.logits = torch.empty(batch, vocab, **f32)
         self.scratch = sdpa_scratch(batch, heads, ctx_max, device)
         self.cos = torch.empty(hd, **f32)
         self.sin = torch.empty(hd, **f32)
-        self._act_views = []
-        off = 0
-        for w in self.down_widths:
-            self._act_views.append(self.act[off: off + batch * w].view(batch, w))
-            off += batch * w
+        self._act_views = [self.act[i] for i in range(len(self.down_widths))]
 
     @staticmethod
     def _bytes(ql: QuantizedLinear) -> int:
@@ -161,10 +165,9 @@ class DecoderStack:
             blk["o"].forward(self.att, out_dtype=f32, out=self.o)
             add_rmsnorm(self.h, self.o, blk["g2"], self.eps, self.xn)
             QuantizedLinear.forward_many(blk["gate_up"], [self.xn] * 2, out_dtype=f32, outs=[self.gu[0], self.gu[1]])
-            swiglu_sliced(self.gu[0], self.gu[1], self.down_widths, self.act)
+            swiglu_sliced(self.gu[0], self.gu[1], self.down_widths, self.act, self.down_pad)
             QuantizedLinear.forward_many(blk["down"], self._act_views, out_dtype=f32, outs=[p for p in self.down_parts])
-            sum_arrays(self.down_parts, self.down)
-            delta = self.down
+            delta = self.down_parts  # summed by the next add_rmsnorm
         add_rmsnorm(self.h, delta, self.g_final, self.eps, self.xn)
         self.lm_head.forward(self.xn, out_dtype=f32, out=self.logits)
         return self.logits

@@ -39,6 +39,11 @@ def test_add_rmsnorm_against_reference_arithmetic():
         close(out.to(torch.float32).cpu().numpy(), want, 1e-2)  # bf16 output: 2^-8 relative
         out2 = dec.add_rmsnorm(ht, None, torch.from_numpy(g).to(DEV), 1e-5)
         assert torch.equal(out, out2)
+        # a delta in parts is summed first
+        parts = rng.standard_normal((3, n, c)).astype(np.float32)
+        h3 = torch.from_numpy(h).to(DEV)
+        dec.add_rmsnorm(h3, torch.from_numpy(parts).to(DEV), torch.from_numpy(g).to(DEV), 1e-5)
+        assert np.array_equal(h3.cpu().numpy(), (h + ((parts[0] + parts[1]).astype(np.float32) + parts[2]).astype(np.float32)).astype(np.float32))
 
 
 def test_rope_append_and_sdpa_decode():
@@ -88,6 +93,14 @@ def test_swiglu_sliced_and_sum():
     for w in widths:
         close(got[off: off + n * w].reshape(n, w), want[:, col: col + w], 1e-2)
         off, col = off + n * w, col + w
+    padded = torch.full((3, n, 512), 7.0, dtype=torch.bfloat16, device=DEV)
+    dec.swiglu_sliced(torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV), widths, padded, 512)
+    pg = padded.to(torch.float32).cpu().numpy()
+    col = 0
+    for i, w in enumerate(widths):
+        close(pg[i, :, :w], want[:, col: col + w], 1e-2)
+        assert (pg[i, :, w:] == 7.0).all()  # padding columns untouched
+        col += w
     parts = rng.standard_normal((3, n, 64)).astype(np.float32)
     y = torch.empty(n, 64, device=DEV)
     dec.sum_arrays(torch.from_numpy(parts).to(DEV), y)
@@ -137,7 +150,7 @@ def test_decoder_stack_against_torch_composition():
         act = rb(g * torch.sigmoid(g) * u)
         col, down = 0, 0
         for ql, w in zip(blk["down"], st.down_widths):
-            down = down + lin(ql, act[:, col: col + w])
+            down = down + act[:, col: col + w] @ ql._w.dequantize().t()[:w]
             col += w
         h = h + down
     want = lin(st.lm_head, norm(h, st.g_final))
