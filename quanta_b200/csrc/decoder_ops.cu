@@ -26,31 +26,68 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // h += delta[0] + ... + delta[parts - 1] (arrays of n * c floats laid back to back; the partial outputs of a
-// sliced linear), out = bf16(rmsnorm(h) * gamma).  One block per row.
-__global__ void __launch_bounds__(256) k_add_rmsnorm(float* __restrict__ h, const float* __restrict__ delta, uint32_t parts,
-                                                     uint64_t part_stride, const float* __restrict__ gamma, uint32_t c, float eps,
-                                                     uint16_t* __restrict__ out) {
-    __shared__ float s_part[8];
+// sliced linear), out = bf16(rmsnorm(h) * gamma).  One block of 1024 threads per row, four consecutive
+// elements per thread and pass (the rows are short: latency, not bandwidth, is what this kernel has to hide).
+__global__ void __launch_bounds__(1024) k_add_rmsnorm(float* __restrict__ h, const float* __restrict__ delta, uint32_t parts,
+                                                      uint64_t part_stride, const float* __restrict__ gamma, uint32_t c, float eps,
+                                                      uint16_t* __restrict__ out) {
+    // launched with programmatic stream serialization: wait for the producer of the inputs, then let the
+    // consumer start its own prologue (a decode GEMV prefetches its weights there) under this kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float s_part[32];
     const uint64_t base = (uint64_t)blockIdx.x * c;
+    const bool vec = (c & 3u) == 0;  // rows start on 16-byte boundaries
     float sq = 0.0f;
-    for (uint32_t i = threadIdx.x; i < c; i += 256) {
-        float v = h[base + i];
-        if (parts) {
-            float d = delta[base + i];
-            for (uint32_t p = 1; p < parts; p++) d += delta[p * part_stride + base + i];
-            v += d;
-            h[base + i] = v;
+    if (vec) {
+        for (uint32_t i = threadIdx.x * 4; i < c; i += 4096) {
+            float4 v = *reinterpret_cast<const float4*>(h + base + i);
+            if (parts) {
+                float4 d = *reinterpret_cast<const float4*>(delta + base + i);
+                for (uint32_t p = 1; p < parts; p++) {
+                    const float4 e = *reinterpret_cast<const float4*>(delta + p * part_stride + base + i);
+                    d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+                }
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                *reinterpret_cast<float4*>(h + base + i) = v;
+            }
+            sq = fmaf(v.x, v.x, sq);
+            sq = fmaf(v.y, v.y, sq);
+            sq = fmaf(v.z, v.z, sq);
+            sq = fmaf(v.w, v.w, sq);
         }
-        sq = fmaf(v, v, sq);
+    } else {
+        for (uint32_t i = threadIdx.x; i < c; i += 1024) {
+            float v = h[base + i];
+            if (parts) {
+                float d = delta[base + i];
+                for (uint32_t p = 1; p < parts; p++) d += delta[p * part_stride + base + i];
+                v += d;
+                h[base + i] = v;
+            }
+            sq = fmaf(v, v, sq);
+        }
     }
     sq = warp_sum(sq);
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sq;
     __syncthreads();
     float tot = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 8; w++) tot += s_part[w];
+    for (int w = 0; w < 32; w++) tot += s_part[w];
     const float rrms = 1.0f / sqrtf(tot / (float)c + eps);
-    for (uint32_t i = threadIdx.x; i < c; i += 256) out[base + i] = f32_to_bf16_bits(h[base + i] * rrms * gamma[i]);
+    // every thread re-reads what it wrote itself (same indices), so no further barrier is needed
+    if (vec) {
+        for (uint32_t i = threadIdx.x * 4; i < c; i += 4096) {
+            const float4 v = *reinterpret_cast<const float4*>(h + base + i);
+            const float4 g = *reinterpret_cast<const float4*>(gamma + i);
+            uint2 o;
+            o.x = f32_to_bf16_bits(v.x * rrms * g.x) | ((uint32_t)f32_to_bf16_bits(v.y * rrms * g.y) << 16);
+            o.y = f32_to_bf16_bits(v.z * rrms * g.z) | ((uint32_t)f32_to_bf16_bits(v.w * rrms * g.w) << 16);
+            *reinterpret_cast<uint2*>(out + base + i) = o;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < c; i += 1024) out[base + i] = f32_to_bf16_bits(h[base + i] * rrms * gamma[i]);
+    }
 }
 
 // q, k: rotate by the position's angles; q -> bf16 [b, heads, hd]; k, v -> the cache row `pos`.
@@ -59,6 +96,10 @@ __global__ void __launch_bounds__(128) k_rope_append(const float* __restrict__ q
                                                      const float* __restrict__ sinv, uint32_t heads, uint32_t hd,
                                                      uint16_t* __restrict__ q_out, uint16_t* __restrict__ kcache,
                                                      uint16_t* __restrict__ vcache, uint32_t ctx_max, uint32_t pos) {
+    // launched with programmatic stream serialization: wait for the producer of the inputs, then let the
+    // consumer start its own prologue (a decode GEMV prefetches its weights there) under this kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t b = blockIdx.x / heads, hh = blockIdx.x % heads, half = hd >> 1;
     const uint64_t in = ((uint64_t)b * heads + hh) * hd;
     const uint64_t cache = (((uint64_t)b * ctx_max + pos) * heads + hh) * hd;
@@ -84,6 +125,10 @@ __global__ void __launch_bounds__(SDPA_WARPS * 32) k_sdpa_decode_split(const uin
                                                                         const uint16_t* __restrict__ vcache, uint32_t heads,
                                                                         uint32_t ctx_max, uint32_t kv_len, float scale,
                                                                         uint32_t splits, float* __restrict__ scratch) {
+    // launched with programmatic stream serialization: wait for the producer of the inputs, then let the
+    // consumer start its own prologue (a decode GEMV prefetches its weights there) under this kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr uint32_t HD = 128;
     __shared__ float s_m[SDPA_WARPS], s_l[SDPA_WARPS], s_acc[SDPA_WARPS][HD];
     const uint32_t split = blockIdx.x % splits, bh = blockIdx.x / splits, b = bh / heads, hh = bh % heads;
@@ -176,6 +221,10 @@ __global__ void __launch_bounds__(SDPA_WARPS * 32) k_sdpa_decode_split(const uin
 // Second pass: merge the splits of one (batch row, head); out = acc / l as bf16.
 __global__ void __launch_bounds__(128) k_sdpa_decode_merge(const float* __restrict__ scratch, uint32_t splits,
                                                            uint16_t* __restrict__ out) {
+    // launched with programmatic stream serialization: wait for the producer of the inputs, then let the
+    // consumer start its own prologue (a decode GEMV prefetches its weights there) under this kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr uint32_t HD = 128;
     const uint32_t bh = blockIdx.x;
     const float* s = scratch + (uint64_t)bh * splits * (HD + 2);
@@ -201,6 +250,10 @@ struct SliceSpec {
 };
 __global__ void __launch_bounds__(256) k_swiglu_sliced(const float* __restrict__ gate, const float* __restrict__ up,
                                                        uint32_t n, uint32_t h, SliceSpec sp, uint16_t* __restrict__ out) {
+    // launched with programmatic stream serialization: wait for the producer of the inputs, then let the
+    // consumer start its own prologue (a decode GEMV prefetches its weights there) under this kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (uint64_t)n * h) return;
     const uint32_t row = (uint32_t)(i / h), col = (uint32_t)(i % h);
@@ -214,11 +267,35 @@ __global__ void __launch_bounds__(256) k_swiglu_sliced(const float* __restrict__
 // y[i] = sum of `count` arrays (the partial outputs of a sliced linear).
 __global__ void __launch_bounds__(256) k_sum_arrays(const float* __restrict__ parts, uint32_t count, uint64_t n,
                                                     float* __restrict__ y) {
+    // launched with programmatic stream serialization: wait for the producer of the inputs, then let the
+    // consumer start its own prologue (a decode GEMV prefetches its weights there) under this kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     float v = parts[i];
     for (uint32_t p = 1; p < count; p++) v += parts[(uint64_t)p * n + i];
     y[i] = v;
+}
+
+}  // namespace qb
+
+namespace qb {
+
+// Every kernel of this file is launched with programmatic stream serialization (see the kernels' first lines).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), uint32_t grid, uint32_t block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace qb
@@ -231,9 +308,8 @@ qb200_status qb200_add_rmsnorm(float* h, const float* delta, uint32_t delta_part
                                float eps, uint16_t* out_bf16, void* stream) {
     if (!h || !gamma || !out_bf16 || (delta_parts && !delta)) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: null pointer");
     if (n == 0 || c == 0 || c > 0x7FFFFFFFull || n > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: bad shape");
-    qb::k_add_rmsnorm<<<(uint32_t)n, 256, 0, static_cast<cudaStream_t>(stream)>>>(h, delta, delta ? delta_parts : 0, n * c, gamma, (uint32_t)c, eps,
-                                                                                   out_bf16);
-    QB_CUDA_TRY(cudaGetLastError());
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_add_rmsnorm, (uint32_t)n, 1024, static_cast<cudaStream_t>(stream), h, delta, delta ? delta_parts : 0, n * c, gamma, (uint32_t)c, eps,
+                                                                                   out_bf16));
     return QB200_OK;
 }
 
@@ -244,9 +320,8 @@ qb200_status qb200_rope_append(const float* q, const float* k, const float* v, c
         return fail(QB200_ERR_INVALID_PARAM, "qb200_rope_append: null pointer");
     if (hd == 0 || (hd & 1) || pos >= ctx_max || b == 0 || heads == 0)
         return fail(QB200_ERR_INVALID_PARAM, "qb200_rope_append: head dim must be even and the position inside the cache");
-    qb::k_rope_append<<<b * heads, 128, 0, static_cast<cudaStream_t>(stream)>>>(q, k, v, cos_row, sin_row, heads, hd, q_out, kcache,
-                                                                                vcache, ctx_max, pos);
-    QB_CUDA_TRY(cudaGetLastError());
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_rope_append, b * heads, 128, static_cast<cudaStream_t>(stream), q, k, v, cos_row, sin_row, heads, hd, q_out, kcache,
+                                                                                vcache, ctx_max, pos));
     return QB200_OK;
 }
 
@@ -263,11 +338,9 @@ qb200_status qb200_sdpa_decode(const uint16_t* q, const uint16_t* kcache, const 
     if (kv_len == 0 || kv_len > ctx_max || b == 0 || heads == 0) return fail(QB200_ERR_INVALID_PARAM, "qb200_sdpa_decode: bad lengths");
     const uint32_t splits = (kv_len + qb::SDPA_SPLIT - 1) / qb::SDPA_SPLIT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    qb::k_sdpa_decode_split<<<b * heads * splits, qb::SDPA_WARPS * 32, 0, st>>>(q, kcache, vcache, heads, ctx_max, kv_len, scale, splits,
-                                                                               scratch);
-    QB_CUDA_TRY(cudaGetLastError());
-    qb::k_sdpa_decode_merge<<<b * heads, 128, 0, st>>>(scratch, splits, out);
-    QB_CUDA_TRY(cudaGetLastError());
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_sdpa_decode_split, b * heads * splits, qb::SDPA_WARPS * 32, st, q, kcache, vcache, heads, ctx_max, kv_len, scale, splits,
+                                                                               scratch));
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_sdpa_decode_merge, b * heads, 128, st, scratch, splits, out));
     return QB200_OK;
 }
 
@@ -288,17 +361,15 @@ qb200_status qb200_swiglu_sliced(const float* gate, const float* up, uint64_t n,
         start += slice_widths[s];
     }
     if (start != h) return fail(QB200_ERR_INVALID_PARAM, "qb200_swiglu_sliced: the slice widths must add up to the hidden width");
-    qb::k_swiglu_sliced<<<(uint32_t)((n * h + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(gate, up, (uint32_t)n, (uint32_t)h,
-                                                                                                        sp, out);
-    QB_CUDA_TRY(cudaGetLastError());
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_swiglu_sliced, (uint32_t)((n * h + 255) / 256), 256, static_cast<cudaStream_t>(stream), gate, up, (uint32_t)n, (uint32_t)h,
+                                                                                                        sp, out));
     return QB200_OK;
 }
 
 qb200_status qb200_sum_arrays(const float* parts, uint32_t count, uint64_t n, float* y, void* stream) {
     if (!parts || !y || count == 0) return fail(QB200_ERR_INVALID_PARAM, "qb200_sum_arrays: null pointer");
     if (n == 0) return QB200_OK;
-    qb::k_sum_arrays<<<(uint32_t)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(parts, count, n, y);
-    QB_CUDA_TRY(cudaGetLastError());
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_sum_arrays, (uint32_t)((n + 255) / 256), 256, static_cast<cudaStream_t>(stream), parts, count, n, y));
     return QB200_OK;
 }
 

@@ -107,7 +107,7 @@ class DecoderStack:
         # the down projection runs as column slices of its input, all padded to one width so that the slices are
         # ONE grouped launch: W_down = [W_0 | W_1 | ...], y = sum_s x_s @ W_s^T
         self.down_widths = _slices(ffn)
-        self.down_pad = max(self.down_widths)
+        self.down_pad = -(-max(self.down_widths) // 512) * 512  # rows of scales that are whole 16-byte units
         self.layers = []
         for _ in range(n_layers):
             blk = {"qkv": [qlin(d, d) for _ in range(3)], "o": qlin(d, d), "gate_up": [qlin(ffn, d) for _ in range(2)],
