@@ -264,8 +264,17 @@ qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint3
         yd[i] = static_cast<uint8_t*>(lead->y_stage) + y_off[i];
     }
     if (qb200_status s = qb200_qlinear_forward_many(layers, count, xd.data(), x_dtype, m, yd.data(), y_dtype, st)) return s;
-    for (uint32_t i = 0; i < count; i++)
-        QB_CUDA_TRY(cudaMemcpyAsync(y_host[i], yd[i], m * layers[i]->out_dim * dtype_size(y_dtype), cudaMemcpyDeviceToHost, st));
+    // outputs that are neighbours both on the host and in the staging buffer leave in one copy
+    for (uint32_t i = 0; i < count;) {
+        uint64_t bytes = m * layers[i]->out_dim * dtype_size(y_dtype);
+        uint32_t j = i + 1;
+        while (j < count && static_cast<uint8_t*>(y_host[i]) + bytes == y_host[j] && y_off[i] + bytes == y_off[j]) {
+            bytes += m * layers[j]->out_dim * dtype_size(y_dtype);
+            j++;
+        }
+        QB_CUDA_TRY(cudaMemcpyAsync(y_host[i], yd[i], bytes, cudaMemcpyDeviceToHost, st));
+        i = j;
+    }
     QB_CUDA_TRY(cudaStreamSynchronize(st));
     return QB200_OK;
 }
