@@ -329,8 +329,17 @@ def run_ours(args):
     fused = world > 1 and grouped and args.gather == "fused" and m <= 8
     pg = None
     if fused:
+        # every rank must take the same path: the ranks agree on whether all of them could map the peers' buffers
         from quanta_b200 import tp as _tp
-        pg = _tp.PeerGather(LAYERS, m, N_OUT, torch.float32)
+        ok = torch.ones(1, device=dev)
+        try:
+            pg = _tp.PeerGather(LAYERS, m, N_OUT, torch.float32)
+        except Exception as e:  # no peer access between these devices, or IPC refused: the library collective serves
+            print(f"bench.py: rank {rank}: fused all-gather unavailable ({type(e).__name__}: {str(e)[:100]}); using NCCL", file=sys.stderr)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            fused, pg = False, None
 
     def step():
         cur = torch.cuda.current_stream(dev).cuda_stream  # the capture stream while a graph is recorded

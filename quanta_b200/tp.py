@@ -132,9 +132,14 @@ class PeerGather:
         self.slot_bytes = count * m * n_local * self.item
         self.data_bytes = -(-self.world * self.slot_bytes // 256) * 256
         lib = L.load()
-        own, handle = L.vp(), ctypes.create_string_buffer(64)
-        _check(lib.qb200_peer_alloc(self.data_bytes + 128, ctypes.byref(own), handle))
         self.device = torch.device("cuda", torch.cuda.current_device())
+        # The ranks walk through the same collectives whatever happens locally, and agree at the end on
+        # whether every one of them mapped every buffer; then all raise or none does.
+        own, handle, err = L.vp(), ctypes.create_string_buffer(64), None
+        try:
+            _check(lib.qb200_peer_alloc(self.data_bytes + 128, ctypes.byref(own), handle))
+        except QuantError as e:
+            err = e
         mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).to(self.device)
         every = torch.empty(self.world * 64, dtype=torch.uint8, device=self.device)
         dist.all_gather_into_tensor(every, mine, group=group)
@@ -146,12 +151,26 @@ class PeerGather:
                 self.bases.append(self._own)
                 continue
             ptr = L.vp()
-            _check(lib.qb200_peer_open(every[64 * p: 64 * p + 64], ctypes.byref(ptr)))
+            if err is None:
+                try:
+                    _check(lib.qb200_peer_open(every[64 * p: 64 * p + 64], ctypes.byref(ptr)))
+                except QuantError as e:
+                    err = e
             self.bases.append(ptr.value)
+        ok = torch.tensor([0.0 if err is not None else 1.0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() == 0:
+            for p, b in enumerate(self.bases):
+                if b and p != self.rank:
+                    lib.qb200_peer_close(b)
+            dist.barrier(group=group)
+            if self._own:
+                lib.qb200_peer_free(self._own)
+            raise QuantError(L.ERR_NOT_SUPPORTED, "PeerGather: a rank could not allocate or map the peer buffers"
+                                                  + (f" ({err})" if err is not None else ""))
         self._bases_c = (L.vp * self.world)(*self.bases)
         self._flags_c = (L.vp * self.world)(*[b + self.data_bytes for b in self.bases])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores
 
     def view(self) -> torch.Tensor:
         """This rank's gather buffer as a tensor ``[world, count, m, n_local]`` (aliases the allocation)."""
