@@ -1,4 +1,4 @@
-// Prefill GEMM (M >= 64): Y[m, n] = sum_k X[m, k] * s[n, k/128] * q[n, k] over resident
+// Prefill GEMM (every M the decode kernel does not take: M > 16, or a wider input than it keeps on chip): Y[m, n] = sum_k X[m, k] * s[n, k/128] * q[n, k] over resident
 // packed-int4 codes `[N, K/8]` with a 1x128 f32 scale grid, bf16 activations, f32 accumulation.
 // Tensor-core bound: tcgen05.mma over CTA pairs (cta_group::2) with the accumulator in TMEM.
 //
@@ -538,7 +538,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
 bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x) {
     if (bits != 4 || gr != 1 || gc != 128 || layout != QB200_OUT_IN || x_dtype != QB200_BF16) return false;
-    if (m < 64 || m > 0x7FFFFFFF || in_dim % 128 != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
+    if (m == 0 || m > 0x7FFFFFFF || in_dim % 128 != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     return al(codes) && al(x);
 }

@@ -360,8 +360,8 @@ def test_decode_gemv_shapes(N, K):
         xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
         xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
         y = ql.forward(xt, out_dtype=torch.float32)
-        # the tensor-pipe GEMV keeps the activations on chip; shapes whose activations do not fit use the generic kernel
-        assert ql.last_kernel() == "gemv_mma" or (K > 4096 and ql.last_kernel() == "generic_rows")
+        # the tensor-pipe GEMV keeps the activations on chip; shapes whose activations do not fit use the tcgen05 GEMM
+        assert ql.last_kernel() == "gemv_mma" or (K > 4096 and ql.last_kernel() == "gemm_tcgen05")
         want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
         close(y.cpu().numpy(), want, 1e-4)   # exact codes, f32 accumulate: far inside the stated 1e-3
         yb = ql.forward(xt)                  # bf16 out
@@ -419,7 +419,7 @@ def test_forward_many_matches_per_layer_forward():
 
 # ---- the prefill GEMM on tcgen05 -------------------------------------------------
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 256, 256), (256, 384, 1024), (200, 300, 512), (64, 130, 2048), (333, 128, 4096)])
+@pytest.mark.parametrize("M,N,K", [(17, 256, 512), (40, 384, 1024), (128, 128, 128), (128, 256, 256), (256, 384, 1024), (200, 300, 512), (64, 130, 2048), (333, 128, 4096)])
 def test_prefill_gemm_against_oracle(M, N, K):
     """Stated staging: codes enter the tensor core as exact integers, activations as exact bf16, f32
     accumulation per 128-k group, the f32 scale applied to the group sum.  Checker: f64 accumulation of
