@@ -18,7 +18,11 @@ __global__ void __launch_bounds__(REG_THREADS, OCC) k_gemv_i4_reg(const __grid_c
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t n_my = blockIdx.x < a.total_items ? (a.total_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // a CTA takes a contiguous run of items: neighbours in a layer, so the activation fragments are reloaded
+    // only where the run crosses into a layer with another input
+    const uint32_t per_cta = a.total_items / gridDim.x, extra = a.total_items % gridDim.x;
+    const uint32_t n_my = per_cta + (blockIdx.x < extra ? 1u : 0u);
+    const uint32_t item_first = blockIdx.x * per_cta + min(blockIdx.x, extra);
     const bool async_scales = a.async_scales != 0;  // scales not 16-byte aligned: 4-byte async copies
     // this warp's two scale groups (the second may not exist for short K)
     const uint32_t G0 = warp, G1 = warp + REG_WARPS;
@@ -27,7 +31,7 @@ __global__ void __launch_bounds__(REG_THREADS, OCC) k_gemv_i4_reg(const __grid_c
 
     // Every item this CTA will process is described once, up front (thread i describes item i).
     for (uint32_t j = tid; j < n_my; j += REG_THREADS) {
-        const uint32_t item = blockIdx.x + j * gridDim.x;
+        const uint32_t item = item_first + j;
         uint32_t l = 0;
         while (l + 1 < a.count && item >= a.layer[l + 1].item0) l++;
         const GemvLayer& ly = a.layer[l];
