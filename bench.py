@@ -474,9 +474,9 @@ def run_ours(args):
                     "call": "qb200_qlinear_forward_many_host" if grouped else "qb200_qlinear_forward_host"},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # dram__bytes_read + write of one ncu capture of an 8-layer launch (72.28 MB),
+                         # dram__bytes_read + write of one ncu capture of an 8-layer launch (71.35 + 0.85 MB),
                          # scaled by the layers a launch processes (traffic grows in proportion)
-                         "traffic": 72.28e6 / 8 * (LAYERS if grouped else 1) if m == 1 else None,
+                         "traffic": 72.20e6 / 8 * (LAYERS if grouped else 1) if m == 1 else None,
                          "peak_source": which, "launch_us": per_launch_s * 1e6},
         }
         if world == 1 and not args.profile and not args.no_extras:
