@@ -196,6 +196,7 @@ struct PrefillArgs {
     void* y;              // [M, N] bf16 or f32
     int32_t* status;
     uint32_t M, N, K;
+    uint32_t ksplit;     // K ranges per output tile (1: the kernel writes Y itself)
     uint32_t tma_store;  // 1 when Y's base and row pitch are multiples of 16 bytes
     long long* trace;
     uint32_t dbg;
@@ -235,7 +236,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                  const __grid_constant__ CUtensorMap ymap, PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t groups = a.K >> 7, num_k = a.K / PF_BK;
+    // a work unit is one output tile over one of `ksplit` equal K ranges (whole scale groups); with ksplit > 1 the
+    // units' f32 partial tiles go to a workspace [ksplit, M, N] that a second kernel folds
+    const uint32_t row_groups = a.K >> 7, groups = row_groups / a.ksplit, num_k = 2 * groups;
     uint8_t* sA = smem;                  // [S][128 weight rows][128 B], unpacked bf16
     uint8_t* sX = sA + PF_S * PF_STAGE;  // [S][128 activation rows][128 B]
     uint8_t* sQ = sX + PF_S * PF_STAGE;  // [SQ][128 weight rows][64 B], packed codes
@@ -254,7 +257,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     const uint32_t rank = pf_cluster_rank();  // 0: the pair's leader
     const uint32_t pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
     const uint32_t m_tiles = (a.M + PF_TM - 1) / PF_TM, n_tiles = (a.N + PF_TN - 1) / PF_TN;
-    const uint32_t tiles = m_tiles * n_tiles;  // numbered m-fastest; this pair takes pair, pair + pairs, ...
+    const uint32_t tiles = m_tiles * n_tiles * a.ksplit;  // units: K range fastest, then m; this pair takes pair, pair + pairs, ...
     const uint32_t my_tiles = pair < tiles ? (tiles - pair + pairs - 1) / pairs : 0;
     const uint32_t total = my_tiles * num_k;   // k-steps this CTA goes through
 
@@ -294,13 +297,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                 uint32_t st = 0, par = 0, it = 0;
                 PF_TR_DECL;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-                    const int32_t x_row = (int32_t)((t % m_tiles) * PF_TM + rank * 128);
+                    const uint32_t tile = t / a.ksplit, k_first = (t % a.ksplit) * num_k;
+                    const int32_t x_row = (int32_t)((tile % m_tiles) * PF_TM + rank * 128);
                     for (uint32_t s = 0; s < num_k; s++, it++) {
                         PF_TR_B;
                         if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
                         PF_TR_E(1);
                         pf_mbar_expect_tx(&landed[st], PF_STAGE);
-                        pf_tma_load_2d(sX + st * PF_STAGE, &xmap, (int32_t)(s * PF_BK), x_row, &landed[st]);
+                        pf_tma_load_2d(sX + st * PF_STAGE, &xmap, (int32_t)((k_first + s) * PF_BK), x_row, &landed[st]);
                         if (++st == PF_S) { st = 0; par ^= 1; }
                     }
                 }
@@ -366,11 +370,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             if (lane == 0) {
                 uint32_t sq = 0, pq = 0, qit = 0;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-                    const int32_t q_row = (int32_t)((t / m_tiles) * PF_TN + rank * 128);
+                    const uint32_t tile = t / a.ksplit, g_first = (t % a.ksplit) * groups;
+                    const int32_t q_row = (int32_t)((tile / m_tiles) * PF_TN + rank * 128);
                     for (uint32_t g = 0; g < groups; g++, qit++) {
                         if (qit >= PF_SQ && !pf_wait(&empty_q[sq], pq ^ 1)) { failed = true; break; }
                         pf_mbar_expect_tx(&full_q[sq], PF_Q_BYTES);
-                        pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)(g * 16), q_row, &full_q[sq]);  // x in u32 words
+                        pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)((g_first + g) * 16), q_row, &full_q[sq]);  // x in u32 words
                         if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
                     }
                 }
@@ -422,17 +427,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
         const uint32_t quad = warp & 3, half = (warp - 8) >> 2, ml = quad * 32 + lane;
         const uint32_t remote_dempty = pf_map_to_cta(pf_smem(&dempty[0]), 0);
-        const bool vec_scales = (groups & 3u) == 0;  // a row's scales start on a 16-byte boundary
+        const bool vec_scales = ((row_groups | groups) & 3u) == 0;  // a unit's scales start on a 16-byte boundary
         const bool issuer = quad == 0 && lane == 0;  // the thread of this half that issues its TMA stores
         constexpr uint32_t ROWS = PF_Y_BYTES / 2 / (128 * sizeof(YT));  // activation rows per staging pass (two buffers)
         YT* stage = reinterpret_cast<YT*>(sY + half * PF_Y_BYTES);
         uint32_t gcount = 0;
         PF_TR_DECL;
         for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-            const uint32_t n_cta = (t / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
-            const uint32_t m0 = (t % m_tiles) * PF_TM + half * 128;
+            const uint32_t tile = t / a.ksplit, ks = t % a.ksplit;
+            const uint32_t n_cta = (tile / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
+            const uint32_t m0 = (tile % m_tiles) * PF_TM + half * 128;
             const bool n_ok = n < a.N;
-            const float* sp = a.scales + (uint64_t)(n_ok ? n : 0) * groups;
+            const float* sp = a.scales + (uint64_t)(n_ok ? n : 0) * row_groups + ks * groups;
             float total[128];
 #pragma unroll
             for (uint32_t i = 0; i < 128; i++) total[i] = 0.0f;
@@ -505,8 +511,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
                     if (issuer) {
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&ymap),
-                                     "r"((int32_t)n_cta), "r"((int32_t)(m0 + p * ROWS)), "r"(pf_smem(buf))
+                        asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(&ymap),
+                                     "r"((int32_t)n_cta), "r"((int32_t)(m0 + p * ROWS)), "r"((int32_t)ks), "r"(pf_smem(buf))
                                      : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
@@ -533,7 +539,45 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
 }
 
+// Folds the K ranges' partial tiles: y[m, n] = sum_s ws[s, m, n] (+ bias[n]), four outputs per thread.
+template <typename YT>
+__global__ void __launch_bounds__(256) k_gemm_i4_fold(const float* __restrict__ ws, uint32_t ksplit, uint64_t mn, uint32_t N,
+                                                      const float* __restrict__ bias, YT* __restrict__ y) {
+    const uint64_t i = ((uint64_t)blockIdx.x * 256 + threadIdx.x) * 4;  // N is a multiple of 4 on this path
+    if (i >= mn) return;
+    float4 v = *reinterpret_cast<const float4*>(ws + i);
+    for (uint32_t s = 1; s < ksplit; s++) {
+        const float4 e = *reinterpret_cast<const float4*>(ws + s * mn + i);
+        v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+    }
+    if (bias) {
+        const float4 b = *reinterpret_cast<const float4*>(bias + (uint32_t)(i % N));
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    if constexpr (sizeof(YT) == 4) {
+        *reinterpret_cast<float4*>(y + i) = v;
+    } else {
+        uint2 o;
+        o.x = f32_to_bf16_bits(v.x) | ((uint32_t)f32_to_bf16_bits(v.y) << 16);
+        o.y = f32_to_bf16_bits(v.z) | ((uint32_t)f32_to_bf16_bits(v.w) << 16);
+        *reinterpret_cast<uint2*>(y + i) = o;
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------
+
+// K ranges per output tile: when the output has fewer 256 x 256 tiles than the device has SM pairs, the K loop is cut
+// into equal runs of whole scale groups (at least four each) so that the idle pairs take a share.
+static uint32_t gemm_i4_ksplit(uint64_t m, uint64_t out_dim, uint64_t in_dim, const void* bias) {
+    const uint64_t tiles = ((out_dim + PF_TN - 1) / PF_TN) * ((m + PF_TM - 1) / PF_TM), pairs = 74;
+    const uint32_t groups = (uint32_t)(in_dim / 128);
+    if (tiles * 2 > pairs || out_dim % 4 != 0 || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u))) return 1;
+    uint32_t best = 1;
+    for (uint32_t s = 2; s <= pairs / tiles && s <= groups / 4; s++)
+        if (groups % s == 0) best = s;
+    return best;
+}
+
 
 bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x) {
@@ -543,8 +587,11 @@ bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
     return al(codes) && al(x);
 }
 
-// The prefill path reads the activations and the codes where they lie: no scratch.
-uint64_t gemm_i4_scratch_bytes(uint64_t, uint64_t) { return 0; }
+// Scratch: only the workspace of partial tiles when the K loop is split ([ksplit, m, out] f32).
+uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, const void* bias) {
+    const uint32_t ks = gemm_i4_ksplit(m, out_dim, in_dim, bias);
+    return ks > 1 ? (uint64_t)ks * m * out_dim * 4 : 0;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -562,8 +609,9 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* status, cudaStream_t st) {
+qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
     const uint32_t M = (uint32_t)f.m, N = (uint32_t)f.out_dim, K = (uint32_t)f.in_dim;
+    const uint32_t ksplit = scratch ? gemm_i4_ksplit(M, N, K, f.bias) : 1;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled is not available from this driver");
     // activations as a [M, K] bf16 tensor: one box = 128 rows x 64 elements (one 128-byte swizzle row each)
@@ -586,16 +634,20 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (codes) failed with code " + std::to_string((int)cr));
 
-    // Y as a [M, N] tensor: one box = (8 KB / 128 / element size) rows x 128 columns
-    const uint32_t ysz = y_dtype == QB200_F32 ? 4 : 2;
-    const bool tma_store = (reinterpret_cast<uintptr_t>(f.y) & 15u) == 0 && ((uint64_t)N * ysz) % 16 == 0;
+    // Y as a [1, M, N] tensor (the workspace of partial tiles as [ksplit, M, N] f32 when the K loop is split): one box =
+    // (8 KB / 128 / element size) rows x 128 columns of one plane
+    const int k_dtype = ksplit > 1 ? (int)QB200_F32 : y_dtype;  // what the GEMM kernel itself writes
+    void* k_out = ksplit > 1 ? scratch : f.y;
+    const uint32_t ysz = k_dtype == QB200_F32 ? 4 : 2;
+    const bool tma_store = (reinterpret_cast<uintptr_t>(k_out) & 15u) == 0 && ((uint64_t)N * ysz) % 16 == 0;
     CUtensorMap ymap = xmap;  // a valid map either way; unused without tma_store
     if (tma_store) {
-        const cuuint64_t ydims[2] = {N, M};
-        const cuuint64_t ystrides[1] = {(cuuint64_t)N * ysz};
-        const cuuint32_t ybox[2] = {128, PF_Y_BYTES / 2 / (128 * ysz)};
-        cr = enc(&ymap, y_dtype == QB200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, f.y, ydims,
-                 ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+        const cuuint64_t ydims[3] = {N, M, ksplit};
+        const cuuint64_t ystrides[2] = {(cuuint64_t)N * ysz, (cuuint64_t)M * N * ysz};
+        const cuuint32_t ybox[3] = {128, PF_Y_BYTES / 2 / (128 * ysz), 1};
+        const cuuint32_t estr3[3] = {1, 1, 1};
+        cr = enc(&ymap, k_dtype == QB200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, k_out, ydims,
+                 ystrides, ybox, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (output) failed with code " + std::to_string((int)cr));
     }
@@ -603,8 +655,9 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
     PrefillArgs a;
     a.tma_store = tma_store ? 1u : 0u;
     a.scales = f.scales;
-    a.bias = f.bias;
-    a.y = f.y;
+    a.bias = ksplit > 1 ? nullptr : f.bias;  // the fold kernel adds it
+    a.y = k_out;
+    a.ksplit = ksplit;
     a.status = status;
     a.M = M;
     a.N = N;
@@ -622,11 +675,11 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
     QB_CUDA_TRY(cudaGetDevice(&dev));
     static int sm_count[64] = {};
     if (!sm_count[dev & 63]) QB_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev));
-    const uint32_t tiles = ((N + PF_TN - 1) / PF_TN) * ((M + PF_TM - 1) / PF_TM);
+    const uint32_t tiles = ((N + PF_TN - 1) / PF_TN) * ((M + PF_TM - 1) / PF_TM) * ksplit;
     const uint32_t max_pairs = (uint32_t)sm_count[dev & 63] / 2;
     const uint32_t grid = 2 * (tiles < max_pairs ? tiles : max_pairs);  // one CTA per SM, in clusters of two
     static bool attr_set[2][64] = {};
-    if (y_dtype == QB200_F32) {
+    if (k_dtype == QB200_F32) {
         if (!attr_set[0][dev & 63]) {
             QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[0][dev & 63] = true;
@@ -640,6 +693,17 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void*, int32_t* stat
         k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
     }
     QB_CUDA_TRY(cudaGetLastError());
+    if (ksplit > 1) {
+        if (!tma_store) return fail(QB200_ERR_CUDA, "prefill GEMM: the split-K workspace is not 16-byte aligned");
+        const uint64_t mn = (uint64_t)M * N;
+        const uint32_t blocks = (uint32_t)((mn / 4 + 255) / 256);
+        if (y_dtype == QB200_F32)
+            k_gemm_i4_fold<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(scratch), ksplit, mn, N, f.bias, static_cast<float*>(f.y));
+        else
+            k_gemm_i4_fold<uint16_t><<<blocks, 256, 0, st>>>(static_cast<const float*>(scratch), ksplit, mn, N, f.bias,
+                                                             static_cast<uint16_t*>(f.y));
+        QB_CUDA_TRY(cudaGetLastError());
+    }
 #ifdef QB_PF_TRACE
     {
         long long h[2 * 8 * 6];

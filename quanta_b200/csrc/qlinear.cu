@@ -116,8 +116,16 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         }
     }
     if (qb::gemm_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev)) {
+        // outputs with few tiles split the K loop over the idle SM pairs: partial tiles in the handle's scratch
+        const uint64_t need = qb::gemm_i4_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->bias);
+        if (need) {
+            void* p = ql->scratch;
+            qb200_status s = grow(&p, &ql->scratch_bytes, need);
+            ql->scratch = static_cast<float*>(p);
+            if (s) return s;
+        }
         ql->last_kernel = "gemm_tcgen05";
-        return qb::gemm_i4_forward(a, y_dtype, nullptr, ql->status, st);
+        return qb::gemm_i4_forward(a, y_dtype, need ? ql->scratch : nullptr, ql->status, st);
     }
     if (ql->layout == QB200_OUT_IN) {
         ql->last_kernel = "generic_rows";
