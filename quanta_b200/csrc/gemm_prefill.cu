@@ -230,7 +230,7 @@ __device__ __forceinline__ void pf_unpack_row(uint8_t* dst, uint32_t row_off, co
     }
 }
 
-template <typename YT>
+template <typename YT, bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
                  const __grid_constant__ CUtensorMap ymap, PrefillArgs a) {
@@ -238,7 +238,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // a work unit is one output tile over one of `ksplit` equal K ranges (whole scale groups); with ksplit > 1 the
     // units' f32 partial tiles go to a workspace [ksplit, M, N] that a second kernel folds
-    const uint32_t row_groups = a.K >> 7, groups = row_groups / a.ksplit, num_k = 2 * groups;
+    const uint32_t ksplit = SPLIT ? a.ksplit : 1u;  // the unsplit instantiation folds every K-range term away
+    const uint32_t row_groups = a.K >> 7, groups = row_groups / ksplit, num_k = 2 * groups;
     uint8_t* sA = smem;                  // [S][128 weight rows][128 B], unpacked bf16
     uint8_t* sX = sA + PF_S * PF_STAGE;  // [S][128 activation rows][128 B]
     uint8_t* sQ = sX + PF_S * PF_STAGE;  // [SQ][128 weight rows][64 B], packed codes
@@ -257,7 +258,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     const uint32_t rank = pf_cluster_rank();  // 0: the pair's leader
     const uint32_t pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
     const uint32_t m_tiles = (a.M + PF_TM - 1) / PF_TM, n_tiles = (a.N + PF_TN - 1) / PF_TN;
-    const uint32_t tiles = m_tiles * n_tiles * a.ksplit;  // units: K range fastest, then m; this pair takes pair, pair + pairs, ...
+    const uint32_t tiles = m_tiles * n_tiles * ksplit;  // units: K range fastest, then m; this pair takes pair, pair + pairs, ...
     const uint32_t my_tiles = pair < tiles ? (tiles - pair + pairs - 1) / pairs : 0;
     const uint32_t total = my_tiles * num_k;   // k-steps this CTA goes through
 
@@ -297,7 +298,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                 uint32_t st = 0, par = 0, it = 0;
                 PF_TR_DECL;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-                    const uint32_t tile = t / a.ksplit, k_first = (t % a.ksplit) * num_k;
+                    const uint32_t tile = t / ksplit, k_first = (t % ksplit) * num_k;
                     const int32_t x_row = (int32_t)((tile % m_tiles) * PF_TM + rank * 128);
                     for (uint32_t s = 0; s < num_k; s++, it++) {
                         PF_TR_B;
@@ -370,7 +371,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             if (lane == 0) {
                 uint32_t sq = 0, pq = 0, qit = 0;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-                    const uint32_t tile = t / a.ksplit, g_first = (t % a.ksplit) * groups;
+                    const uint32_t tile = t / ksplit, g_first = (t % ksplit) * groups;
                     const int32_t q_row = (int32_t)((tile / m_tiles) * PF_TN + rank * 128);
                     for (uint32_t g = 0; g < groups; g++, qit++) {
                         if (qit >= PF_SQ && !pf_wait(&empty_q[sq], pq ^ 1)) { failed = true; break; }
@@ -434,7 +435,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         uint32_t gcount = 0;
         PF_TR_DECL;
         for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-            const uint32_t tile = t / a.ksplit, ks = t % a.ksplit;
+            const uint32_t tile = t / ksplit, ks = t % ksplit;
             const uint32_t n_cta = (tile / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
             const uint32_t m0 = (tile % m_tiles) * PF_TM + half * 128;
             const bool n_ok = n < a.N;
@@ -681,16 +682,25 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     static bool attr_set[2][64] = {};
     if (k_dtype == QB200_F32) {
         if (!attr_set[0][dev & 63]) {
-            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[0][dev & 63] = true;
         }
-        k_gemm_i4_tc<float><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+        if (ksplit > 1) {
+            static bool split_attr[64] = {};
+            if (!split_attr[dev & 63]) {
+                QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+                split_attr[dev & 63] = true;
+            }
+            k_gemm_i4_tc<float, true><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+        } else {
+            k_gemm_i4_tc<float, false><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+        }
     } else {
         if (!attr_set[1][dev & 63]) {
-            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
             attr_set[1][dev & 63] = true;
         }
-        k_gemm_i4_tc<uint16_t><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+        k_gemm_i4_tc<uint16_t, false><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
     }
     QB_CUDA_TRY(cudaGetLastError());
     if (ksplit > 1) {
