@@ -413,7 +413,7 @@ def run_ours(args):
         tmax = torch.tensor([ms], device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms = float(tmax.item())
-    launches = (2 if fused else 1 if grouped else LAYERS) * args.steps  # fused: the GEMV and the arrival barrier
+    launches = (1 if grouped else LAYERS) * args.steps  # fused all-gather: the arrival barrier runs inside the GEMV launch
     total_bytes = layer_bytes(m) * LAYERS * args.steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
 
@@ -465,7 +465,7 @@ def run_ours(args):
                        "kernel": layers[0].last_kernel(), "launch": ("one persistent launch per step" if grouped else "one launch per layer") +
                                  (", eager" if args.no_graph else ", cuda graph replay"),
                        "parallelism": "single GPU" if world == 1 else (
-                           f"column-sharded x{world}, outputs stored to every rank's buffer by the kernel (peer memory) + arrival barrier" if fused
+                           f"column-sharded x{world}, outputs stored to every rank's buffer by the kernel (peer memory), arrival barrier in the same launch" if fused
                            else f"column-sharded x{world}, one NCCL all-gather of the step's outputs" if grouped
                                         else f"column-sharded x{world}, all-gather per layer")},
             "clocks": clocks.summary(),

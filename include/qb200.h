@@ -234,10 +234,12 @@ QB200_API qb200_status qb200_sum_arrays(const float* parts, uint32_t count, uint
  * y_own[i] points into this rank's own buffer, gather_bases[p] is rank p's buffer as mapped in this
  * process (gather_bases[rank] the own one), and the element goes to y_own[i] + (gather_bases[p] -
  * gather_bases[rank]) for every p.  Decode shapes only (int4, grid 1x128, [out, in], bf16 x, m <= 8,
- * in <= 4096), else QB200_ERR_NOT_SUPPORTED.  qb200_peer_signal_wait, issued on the same stream
- * afterwards, publishes "this rank's outputs of this step are written" to every peer and waits for
- * theirs; the wait is bounded (about a second), then QB200_ERR_TIMEOUT lands in status_dev.
- * flag_arrays[p] is a zero-initialised array of 9 uint64 inside rank p's shared allocation. */
+ * in <= 4096), else QB200_ERR_NOT_SUPPORTED.  The arrival barrier — "this rank's outputs of this step
+ * are written" published to every peer, then a wait for theirs, bounded to about a second — runs inside
+ * the same launch when flag_arrays is given (its last CTA does it; a timeout lands in layers[0]'s status
+ * word, read with qb200_qlinear_check), or as qb200_peer_signal_wait on the same stream afterwards when
+ * flag_arrays is null (QB200_ERR_TIMEOUT then lands in status_dev).  flag_arrays[p] is a
+ * zero-initialised array of 16 uint64 inside rank p's shared allocation, as mapped in this process. */
 QB200_API qb200_status qb200_peer_alloc(uint64_t bytes, void** dev_ptr, uint8_t* handle64);
 QB200_API qb200_status qb200_peer_open(const uint8_t* handle64, void** dev_ptr);
 QB200_API qb200_status qb200_peer_close(void* dev_ptr);
@@ -245,7 +247,8 @@ QB200_API qb200_status qb200_peer_free(void* dev_ptr);
 QB200_API qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uint32_t count,
                                                const void* const* x_dev, int32_t x_dtype, uint64_t m,
                                                void* const* y_own, int32_t y_dtype, void* const* gather_bases,
-                                               uint32_t world, uint32_t rank, void* stream);
+                                               uint64_t* const* flag_arrays, uint32_t world, uint32_t rank,
+                                               void* stream);
 QB200_API qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint32_t world, uint32_t rank,
                                     int32_t* status_dev, void* stream);
 

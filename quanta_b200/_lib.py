@@ -61,7 +61,7 @@ SIGNATURES = {
     "qb200_peer_open": (i32, [ctypes.c_char_p, P(vp)]),
     "qb200_peer_close": (i32, [vp]),
     "qb200_peer_free": (i32, [vp]),
-    "qb200_qlinear_forward_many_gather": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32, P(vp), u32, u32, vp]),
+    "qb200_qlinear_forward_many_gather": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32, P(vp), P(vp), u32, u32, vp]),
     "qb200_peer_signal_wait": (i32, [P(vp), u32, u32, vp, vp]),
     "qb200_qlinear_check": (i32, [vp, vp]),
     "qb200_qlinear_forward_host": (i32, [vp, vp, i32, u64, vp, i32]),

@@ -30,6 +30,10 @@ bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
 struct PeerSpec {
     uint32_t world = 0;
     int64_t delta[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // with flags, the launch also runs the arrival barrier (its last CTA signals every peer and waits for theirs):
+    // flags[p] is rank p's barrier state (16 u64, zero-initialised) as mapped here
+    uint64_t* flags[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    uint32_t rank = 0;
 };
 #ifdef __CUDACC__
 // QB200_ERR_NOT_SUPPORTED (no message) when no launch plan fits the shape.

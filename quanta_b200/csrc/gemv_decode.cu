@@ -57,6 +57,8 @@ struct GemvBatch {
     uint32_t red_cols;      // batch columns kept per row of partial sums (kernels with a service warp)
     uint32_t n_peers;       // fused all-gather: every output is stored at y + peer_delta[p], p < n_peers (0: plain store)
     int64_t peer_delta[8];
+    uint64_t* peer_flags[8];  // every rank's barrier state as mapped here (null: the caller runs the barrier itself)
+    uint32_t rank;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -548,7 +550,11 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             if (reinterpret_cast<uintptr_t>(b.layer[i].scales) & 15u) b.async_scales = 1;
         b.status = status;
         b.n_peers = peers ? peers->world : 0;
-        for (uint32_t p = 0; p < 8; p++) b.peer_delta[p] = peers ? peers->delta[p] : 0;
+        for (uint32_t p = 0; p < 8; p++) {
+            b.peer_delta[p] = peers ? peers->delta[p] : 0;
+            b.peer_flags[p] = peers ? peers->flags[p] : nullptr;
+        }
+        b.rank = peers ? peers->rank : 0;
         b.count = n;
         b.total_items = items;
         b.M = M;

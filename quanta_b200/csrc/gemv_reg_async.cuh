@@ -152,6 +152,39 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
             if (lane == 0) mbar_arrive(&vacant[slot]);
             if (++st == S) st = 0;
         }
+        // Fused all-gather with the arrival barrier inside the launch: the CTA that finishes last tells every
+        // peer "this rank's outputs of this step are written" and waits, bounded, for theirs, so the launch ends
+        // when all ranks' outputs are here.  flags[p] is rank p's array {arrival of rank 0..7, step counter,
+        // count of finished CTAs}.
+        if (a.n_peers && a.peer_flags[0]) {
+            __threadfence_system();  // this CTA's peer stores before its count
+            uint32_t last = 0;
+            uint64_t* mine = a.peer_flags[a.rank];
+            if (lane == 0) last = atomicAdd(reinterpret_cast<unsigned int*>(mine + 9), 1u) == gridDim.x - 1 ? 1u : 0u;
+            last = __shfl_sync(0xFFFFFFFFu, last, 0);
+            if (last) {
+                __threadfence_system();  // the other CTAs' stores (ordered before their counts) before the flags
+                uint64_t step = 0;
+                if (lane == 0) {
+                    *reinterpret_cast<unsigned int*>(mine + 9) = 0;
+                    step = mine[8] + 1;
+                    mine[8] = step;
+                }
+                step = __shfl_sync(0xFFFFFFFFu, step, 0);
+                if (lane < a.n_peers) {
+                    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peer_flags[lane] + a.rank), "l"(step) : "memory");
+                    uint64_t v = 0;
+                    uint32_t spins = 0;
+                    for (;;) {
+                        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine + lane) : "memory");
+                        if (v >= step || ++spins >= (4u << 20)) break;
+                        __nanosleep(200);
+                    }
+                    if (v < step) atomicExch(a.status, QB200_ERR_TIMEOUT);
+                }
+                __threadfence_system();
+            }
+        }
     } else {
         // ---- compute warps ----
         // The item loop works on 32-bit shared-memory addresses that are advanced, not recomputed:

@@ -189,7 +189,8 @@ qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t c
 
 qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev,
                                                int32_t x_dtype, uint64_t m, void* const* y_own, int32_t y_dtype,
-                                               void* const* gather_bases, uint32_t world, uint32_t rank, void* stream) {
+                                               void* const* gather_bases, uint64_t* const* flag_arrays, uint32_t world,
+                                               uint32_t rank, void* stream) {
     if (count == 0 || m == 0) return QB200_OK;
     if (!layers || !x_dev || !y_own || !gather_bases || world == 0 || world > 8 || rank >= world)
         return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_gather: null argument or bad world / rank");
@@ -219,6 +220,12 @@ qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uin
     }
     qb::PeerSpec peers;
     peers.world = world;
+    peers.rank = rank;
+    if (flag_arrays)
+        for (uint32_t p = 0; p < world; p++) {
+            if (!flag_arrays[p]) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_gather: null flag array");
+            peers.flags[p] = flag_arrays[p];
+        }
     for (uint32_t p = 0; p < world; p++)
         peers.delta[p] = static_cast<int64_t>(reinterpret_cast<intptr_t>(gather_bases[p]) - reinterpret_cast<intptr_t>(gather_bases[rank]));
     qb200_status s = qb::gemv_i4_forward_many(args.data(), count, y_dtype, layers[0]->status, static_cast<cudaStream_t>(stream), &peers);

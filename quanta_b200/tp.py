@@ -121,7 +121,9 @@ class PeerGather:
     raise QuantError(NOT_SUPPORTED); callers fall back to ``TensorParallelLinear``.
     """
 
-    def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None):
+    def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None,
+                 fused_barrier: bool = True):
+        self.fused_barrier = fused_barrier
         if dtype not in (torch.float32, torch.bfloat16):
             raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16")
         self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
@@ -189,14 +191,21 @@ class PeerGather:
         xp = (L.vp * self.count)(*[x.data_ptr() for x in xs])
         yp = (L.vp * self.count)(*[own0 + i * per_layer for i in range(self.count)])
         stream = torch.cuda.current_stream(self.device).cuda_stream
+        # the launch's last CTA runs the arrival barrier (fused=False: a separate one-warp kernel after it)
         _check(lib.qb200_qlinear_forward_many_gather(hs, self.count, xp, L.BF16, self.m, yp,
                                                       L.F32 if self.dtype == torch.float32 else L.BF16,
-                                                      self._bases_c, self.world, self.rank, stream))
-        _check(lib.qb200_peer_signal_wait(self._flags_c, self.world, self.rank, self.status.data_ptr(), stream))
+                                                      self._bases_c, self._flags_c if self.fused_barrier else None,
+                                                      self.world, self.rank, stream))
+        if not self.fused_barrier:
+            _check(lib.qb200_peer_signal_wait(self._flags_c, self.world, self.rank, self.status.data_ptr(), stream))
+        self._lead = layers[0]
         return self.view()
 
     def check(self) -> None:
         """Synchronises and raises if a bounded wait of the barrier ran out."""
+        lead = getattr(self, "_lead", None)
+        if lead is not None:
+            _check(L.load().qb200_qlinear_check(lead._h, torch.cuda.current_stream(self.device).cuda_stream))
         if int(self.status.item()) != 0:
             raise QuantError(L.ERR_TIMEOUT, "PeerGather: a rank did not arrive within the barrier's poll limit")
 

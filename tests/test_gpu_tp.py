@@ -84,12 +84,13 @@ def _gather_worker(rank, world, port, ret):
             own = torch.stack([ql.forward(x, out_dtype=torch.float32) for ql in layers])  # [count, M, n_local]
             want = torch.empty(world, count, M, n_local, device=dev)
             dist.all_gather_into_tensor(want, own)  # the collective the fused path replaces
-            pg = tp.PeerGather(count, M, n_local, torch.float32)
-            for _ in range(3):  # the barrier counts steps: repeated use must keep working
-                got = pg.forward_many(layers, [x] * count)
-            pg.check()
-            ok = ok and layers[0].last_kernel() == "gemv_mma_grouped_gather" and torch.equal(got, want)
-            pg.close()
+            for fused_barrier in (True, False):  # the barrier inside the launch, or as its own kernel
+                pg = tp.PeerGather(count, M, n_local, torch.float32, fused_barrier=fused_barrier)
+                for _ in range(3):  # the barrier counts steps: repeated use must keep working
+                    got = pg.forward_many(layers, [x] * count)
+                pg.check()
+                ok = ok and layers[0].last_kernel() == "gemv_mma_grouped_gather" and torch.equal(got, want)
+                pg.close()
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
