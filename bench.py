@@ -156,6 +156,33 @@ def run_reference(args):
 # this build's arm
 # ---------------------------------------------------------------------------------------
 
+def measure_decode_step(torch, dev, gen, timed, hbm, n_layers):
+    """Whole-model decode step: `n_layers` Llama-7B-shaped blocks + vocabulary projection, int4 1x128 linears,
+    batch 16, 1024 cached positions (KV bf16), random-initialised; one step = one CUDA graph replay."""
+    try:
+        from quanta_b200 import decoder as dec
+        torch.cuda.empty_cache()
+        stack = dec.DecoderStack(n_layers, 4096, 32, 11008, 32000, 16, 1025, dev, seed=4)
+        stack.set_position(1024)
+        h0 = torch.randn(16, 4096, device=dev, generator=gen) * 0.02
+        for _ in range(2):
+            stack.step(h0)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            stack.step(h0)
+        ms = timed(g.replay, 20)
+        by = stack.weight_bytes + stack.kv_bytes(1025)
+        res = {"tokens/s": 16 / ms * 1e3, "ms_per_step": ms, "layers": n_layers, "batch": 16, "context": 1024,
+               "GB/s": by / ms / 1e6, "roofline_frac": by / ms / 1e6 / hbm, "bytes_per_step": by,
+               "launch": "cuda graph replay of the step"}
+        del stack, g
+        torch.cuda.empty_cache()
+        return res
+    except Exception as e:  # the rest of the line must survive
+        return {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
+
+
 def measure_extras(torch, qb, dev, only=None, small=False):
     """Secondary numbers of the same path on one GPU (device-resident inputs, CUDA events):
     the int4 prefill GEMM configuration and quantize-on-load, each with its roofline fraction."""
@@ -184,6 +211,8 @@ def measure_extras(torch, qb, dev, only=None, small=False):
     w = torch.randn(N, K, device=dev, generator=gen) * 0.02
     x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
     # quantize-on-load: f32 [11008, 4096] (180 MB, larger than L2) -> int4 1x128 and int8 32x32
+    if only == "decode_step":
+        return {"decode_step_llama7b_shape": measure_decode_step(torch, dev, gen, timed, hbm, 2 if small else 32)}
     if only == "prefill":
         qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
         ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
@@ -248,29 +277,7 @@ def measure_extras(torch, qb, dev, only=None, small=False):
         del lys
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
-    # whole-model decode step: 32 Llama-7B-shaped blocks + vocabulary projection, int4 1x128 linears, batch 16,
-    # 1024 cached positions (KV bf16, 8.6 GB), random-initialised; one step = one CUDA graph replay
-    try:
-        from quanta_b200 import decoder as dec
-        torch.cuda.empty_cache()
-        stack = dec.DecoderStack(32, 4096, 32, 11008, 32000, 16, 1025, dev, seed=4)
-        stack.set_position(1024)
-        h0 = torch.randn(16, 4096, device=dev, generator=gen) * 0.02
-        for _ in range(2):
-            stack.step(h0)
-        torch.cuda.synchronize(dev)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            stack.step(h0)
-        ms = timed(g.replay, 20)
-        by = stack.weight_bytes + stack.kv_bytes(1025)
-        out["decode_step_llama7b_shape"] = {"tokens/s": 16 / ms * 1e3, "ms_per_step": ms, "batch": 16, "context": 1024,
-                                            "GB/s": by / ms / 1e6, "roofline_frac": by / ms / 1e6 / hbm, "bytes_per_step": by,
-                                            "launch": "cuda graph replay of the step"}
-        del stack, g
-        torch.cuda.empty_cache()
-    except Exception as e:  # the rest of the line must survive
-        out["decode_step_llama7b_shape"] = {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
+    out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, timed, hbm, 32)
     ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
     ms = timed(lambda: ql.forward(x), 10)
     out["prefill_int4_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
@@ -515,7 +522,7 @@ def main():
                     help="N > 1, grouped launch: fused = peer stores from the kernel + arrival barrier; nccl = all-gather after it")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
-    ap.add_argument("--only", default=None, choices=["prefill", "quantize"], help="run only a side workload and print its numbers")
+    ap.add_argument("--only", default=None, choices=["prefill", "quantize", "decode_step"], help="run only a side workload and print its numbers")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced shape, for profiler captures")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
