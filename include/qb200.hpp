@@ -227,6 +227,26 @@ public:
         check(qb200_qlinear_forward(h_, x.data(), QB200_BF16, x.shape()[0], y.data(), QB200_F32, st));
         return y;
     }
+    // [layers[i].forward_bf16(*xs[i])...] in one call: layers that share the input width and take the decode path
+    // run as ONE persistent launch (fused Q/K/V or gate + up projections; qb200_qlinear_forward_many).
+    static std::vector<DeviceArray<float>> forward_many_bf16(const std::vector<const QuantizedLinear*>& layers,
+                                                             const std::vector<const DeviceArray<uint16_t>*>& xs,
+                                                             cudaStream_t st = nullptr) {
+        if (layers.size() != xs.size() || layers.empty()) throw Error(QB200_ERR_INVALID_PARAM, "forward_many: one input per layer");
+        const uint64_t m = xs[0]->shape()[0];
+        std::vector<DeviceArray<float>> ys;
+        std::vector<qb200_qlinear*> hs;
+        std::vector<const void*> xp;
+        std::vector<void*> yp;
+        for (size_t i = 0; i < layers.size(); i++) {
+            ys.emplace_back(std::vector<uint64_t>{m, layers[i]->out_dim()});
+            hs.push_back(layers[i]->h_);
+            xp.push_back(xs[i]->data());
+            yp.push_back(ys.back().data());
+        }
+        check(qb200_qlinear_forward_many(hs.data(), (uint32_t)hs.size(), xp.data(), QB200_BF16, m, yp.data(), QB200_F32, st));
+        return ys;
+    }
     const char* last_kernel() const { return qb200_qlinear_last_kernel(h_); }
     const QuantizedMatrix& weight() const { return *w_; }
 
@@ -236,6 +256,24 @@ private:
     DeviceArray<float> b_;
     qb200_qlinear* h_ = nullptr;
 };
+
+// The decode step's support ops (thin wrappers; semantics and reference anchors are in qb200.h).
+// h += delta (when given), returns bf16(rmsnorm(h) * gamma) — quanta-nn/src/norm.rs:192-225.
+inline DeviceArray<uint16_t> add_rmsnorm(DeviceArray<float>& h, const DeviceArray<float>* delta, const DeviceArray<float>& gamma,
+                                         float eps, cudaStream_t st = nullptr) {
+    DeviceArray<uint16_t> out({h.shape()[0], h.shape()[1]});
+    check(qb200_add_rmsnorm(h.data(), delta ? delta->data() : nullptr, delta ? 1u : 0u, gamma.data(), h.shape()[0], h.shape()[1], eps,
+                            out.data(), st));
+    return out;
+}
+// silu(gate) * up as bf16 — quanta-nn/src/activation.rs:145-162.
+inline DeviceArray<uint16_t> swiglu(const DeviceArray<float>& gate, const DeviceArray<float>& up, cudaStream_t st = nullptr) {
+    const uint64_t n = gate.shape()[0], h = gate.shape()[1];
+    DeviceArray<uint16_t> out({n, h});
+    const uint32_t width = (uint32_t)h;
+    check(qb200_swiglu_sliced(gate.data(), up.data(), n, h, &width, 1, 0, out.data(), st));
+    return out;
+}
 
 // quanta-nn/src/quant.rs:152-155: a named checkpoint leaf on the host side of save / load.
 struct QuantLeaf {

@@ -143,6 +143,61 @@ int main() {
             EXPECT(std::string(e.what()).find("bias") != std::string::npos);
         }
     }
+    // grouped decode launch == one forward per layer, bit for bit (the reference stacks layers and loops over
+    // Layer::apply, quanta-nn/tests/quant.rs:507-523); then the decode step's elementwise ops
+    {
+        const uint64_t n_out = 96, k = 256, m = 2;
+        std::vector<QuantizedLinear> layers;
+        for (int l = 0; l < 3; l++) {
+            auto wv = weights(n_out * k);
+            for (auto& x : wv) x *= 0.001f * (float)(l + 1);
+            layers.push_back(QuantizedLinear::new_(
+                QuantizedMatrix::quantize(DeviceArray<float>::from_slice(wv, {n_out, k}), QuantDtype::Int4, Granularity::Group(1, 128)), {},
+                QB200_OUT_IN));
+        }
+        std::vector<uint16_t> xb(m * k);
+        for (size_t i = 0; i < xb.size(); i++) {
+            float v = std::sin((float)i);
+            uint32_t bits;
+            std::memcpy(&bits, &v, 4);
+            xb[i] = (uint16_t)((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);  // dtype.rs:14-21
+        }
+        auto x = DeviceArray<uint16_t>::from_slice(xb, {m, k});
+        auto ys = QuantizedLinear::forward_many_bf16({&layers[0], &layers[1], &layers[2]}, {&x, &x, &x});
+        EXPECT(std::string(layers[0].last_kernel()) == "gemv_mma_grouped");
+        for (int l = 0; l < 3; l++) EXPECT(bits_eq(ys[l].to_vec(), layers[l].forward_bf16(x).to_vec()));
+
+        std::vector<float> hv(2 * 64), dv(2 * 64), gv(64, 1.5f);
+        for (size_t i = 0; i < hv.size(); i++) hv[i] = std::cos((float)i), dv[i] = 0.25f * (float)(i % 7);
+        auto h = DeviceArray<float>::from_slice(hv, {2, 64});
+        auto d = DeviceArray<float>::from_slice(dv, {2, 64});
+        auto normed = add_rmsnorm(h, &d, DeviceArray<float>::from_slice(gv, {64}), 1e-5f).to_vec();
+        auto hs = h.to_vec();
+        for (int r = 0; r < 2; r++) {
+            float sq = 0.0f;
+            for (int c = 0; c < 64; c++) {
+                EXPECT(hs[r * 64 + c] == hv[r * 64 + c] + dv[r * 64 + c]);
+                sq = sq + hs[r * 64 + c] * hs[r * 64 + c];
+            }
+            const float rrms = 1.0f / std::sqrt(sq / 64.0f + 1e-5f);  // norm.rs:192-212
+            for (int c = 0; c < 64; c++) {
+                uint32_t b = (uint32_t)normed[r * 64 + c] << 16;
+                float got;
+                std::memcpy(&got, &b, 4);
+                const float want = hs[r * 64 + c] * rrms * 1.5f;
+                EXPECT(std::fabs(got - want) <= 1e-2f * (1.0f + std::fabs(want)));
+            }
+        }
+        auto act = swiglu(DeviceArray<float>::from_slice({-40.0f, -1.0f, 0.0f, 2.0f}, {1, 4}), DeviceArray<float>::from_slice({1, 1, 1, 1}, {1, 4})).to_vec();
+        const float av[4] = {-40.0f, -1.0f, 0.0f, 2.0f};
+        for (int i = 0; i < 4; i++) {
+            uint32_t b = (uint32_t)act[i] << 16;
+            float got;
+            std::memcpy(&got, &b, 4);
+            const float want = av[i] * (1.0f / (1.0f + std::exp(std::fmin(-av[i], 30.0f))));  // activation.rs:145-162
+            EXPECT(std::fabs(got - want) <= 1e-2f * (1.0f + std::fabs(want)));
+        }
+    }
     std::printf(failures ? "%d FAILED\n" : "all C++ mirror tests passed\n", failures);
     return failures ? 1 : 0;
 }
