@@ -274,11 +274,28 @@ qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint3
     }
     std::vector<const void*> xd(count);
     std::vector<void*> yd(count);
+    // Outputs in pinned, device-mapped host memory are written by the kernels themselves (the stores cross PCIe
+    // while the launch is still streaming weights), which takes the device-to-host copy off the end of the call.
+    bool direct = m <= 16;  // the decode kernels store with plain instructions; the tcgen05 GEMM's TMA stores keep the staging path
+    for (uint32_t i = 0; i < count && direct; i++) direct = layers[i]->in_dim <= 4096 && layers[i]->bits == 4;
+    for (uint32_t i = 0; i < count && direct; i++) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, y_host[i]) != cudaSuccess || at.type != cudaMemoryTypeHost || !at.devicePointer) {
+            cudaGetLastError();
+            direct = false;
+        } else {
+            yd[i] = at.devicePointer;
+        }
+    }
     for (uint32_t i = 0; i < count; i++) {
         xd[i] = static_cast<uint8_t*>(lead->x_stage) + x_off[i];
-        yd[i] = static_cast<uint8_t*>(lead->y_stage) + y_off[i];
+        if (!direct) yd[i] = static_cast<uint8_t*>(lead->y_stage) + y_off[i];
     }
     if (qb200_status s = qb200_qlinear_forward_many(layers, count, xd.data(), x_dtype, m, yd.data(), y_dtype, st)) return s;
+    if (direct) {
+        QB_CUDA_TRY(cudaStreamSynchronize(st));
+        return QB200_OK;
+    }
     // outputs that are neighbours both on the host and in the staging buffer leave in one copy
     for (uint32_t i = 0; i < count;) {
         uint64_t bytes = m * layers[i]->out_dim * dtype_size(y_dtype);

@@ -459,3 +459,30 @@ def test_prefill_gemm_config3_full_size_properties():
     assert bool(((y2 - 2 * y).abs() <= 1e-5 * (1 + y.abs())).all())
     yb = ql.forward(x)
     assert bool(((yb.to(torch.float32) - ref).abs() <= 1e-2 * (1 + ref.abs())).all())
+
+
+def test_forward_many_host_pinned_and_pageable_outputs():
+    """qb200_qlinear_forward_many_host with outputs in pinned (device-mapped) memory, which the decode kernels write
+    directly, and in pageable memory, which goes through the staging buffer: both equal the device-side call."""
+    from quanta_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(11)
+    qls = []
+    for N in (512, 96, 1024):
+        w = torch.from_numpy((rng.standard_normal((N, 1024)) * 0.02).astype(np.float32)).to(DEV)
+        b = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).to(DEV)
+        qls.append(qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128)), b, qb.OUT_IN))
+    for M in (1, 5):
+        x = torch.randn(M, 1024).to(torch.bfloat16)
+        want = qb.QuantizedLinear.forward_many(qls, [x.to(DEV)] * 3, out_dtype=torch.float32)
+        n = len(qls)
+        hs = (_lib.vp * n)(*[q._h for q in qls])
+        xp = (_lib.vp * n)(*[x.data_ptr()] * n)
+        for pinned in (True, False):
+            ys = [torch.full((M, q.out_dim()), float("nan")) for q in qls]
+            if pinned:
+                ys = [y.pin_memory() for y in ys]
+            yp = (_lib.vp * n)(*[y.data_ptr() for y in ys])
+            assert lib.qb200_qlinear_forward_many_host(hs, n, xp, _lib.BF16, M, yp, _lib.F32) == 0, _lib.last_error()
+            for got, w_ in zip(ys, want):
+                assert torch.equal(got, w_.cpu()), f"pinned={pinned} M={M}"
