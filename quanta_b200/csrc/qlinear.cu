@@ -1,6 +1,8 @@
 // The QuantizedLinear handle: validation at construction (the reference's
 // QuantizedLinear::new, crates/ml/quanta-nn/src/quant.rs:853-862) and kernel
 // selection per forward (the body of Layer::apply, quant.rs:903-918).
+#include <cuda.h>
+
 #include <cstring>
 #include <string>
 #include <vector>
@@ -14,6 +16,29 @@ using qb::fail;
 namespace {
 
 uint64_t dtype_size(int32_t dt) { return dt == QB200_F32 ? 4 : 2; }
+
+// Base and size of the CUDA host allocation (cudaHostAlloc / cudaHostRegister) that holds p, from the driver.
+bool host_range(const void* p, void** base, size_t* size) {
+    typedef CUresult (*Fn)(void*, CUpointer_attribute, CUdeviceptr);
+    static Fn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<Fn>(f);
+    }
+    if (!fn) return false;
+    CUdeviceptr start = 0;
+    size_t sz = 0;
+    if (fn(&start, CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS ||
+        fn(&sz, CU_POINTER_ATTRIBUTE_RANGE_SIZE, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS || !start || !sz)
+        return false;
+    *base = reinterpret_cast<void*>(start);
+    *size = sz;
+    return true;
+}
 
 qb200_status grow(void** p, uint64_t* have, uint64_t need) {
     if (*have >= need) return QB200_OK;
@@ -278,13 +303,33 @@ qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint3
     // while the launch is still streaming weights), which takes the device-to-host copy off the end of the call.
     bool direct = m <= 16;  // the decode kernels store with plain instructions; the tcgen05 GEMM's TMA stores keep the staging path
     for (uint32_t i = 0; i < count && direct; i++) direct = layers[i]->in_dim <= 4096 && layers[i]->bits == 4;
+    // one query per host allocation: outputs inside the range of an allocation already seen reuse its mapping
+    const uint8_t *range_lo = nullptr, *range_hi = nullptr, *range_dev = nullptr;
     for (uint32_t i = 0; i < count && direct; i++) {
+        const uint8_t* p = static_cast<const uint8_t*>(y_host[i]);
+        const uint64_t bytes = m * layers[i]->out_dim * dtype_size(y_dtype);
+        if (range_lo && p >= range_lo && p + bytes <= range_hi) {
+            yd[i] = const_cast<uint8_t*>(range_dev + (p - range_lo));
+            continue;
+        }
         cudaPointerAttributes at;
-        if (cudaPointerGetAttributes(&at, y_host[i]) != cudaSuccess || at.type != cudaMemoryTypeHost || !at.devicePointer) {
+        if (cudaPointerGetAttributes(&at, p) != cudaSuccess || at.type != cudaMemoryTypeHost || !at.devicePointer) {
             cudaGetLastError();
             direct = false;
-        } else {
-            yd[i] = at.devicePointer;
+            break;
+        }
+        yd[i] = at.devicePointer;
+        void* base = nullptr;
+        size_t size = 0;
+        range_lo = nullptr;
+        if (host_range(p, &base, &size)) {  // without range information from the driver every pointer is queried
+            if (p + bytes > static_cast<const uint8_t*>(base) + size) {
+                direct = false;  // the output runs past the end of its allocation
+                break;
+            }
+            range_lo = static_cast<const uint8_t*>(base);
+            range_hi = range_lo + size;
+            range_dev = static_cast<const uint8_t*>(at.devicePointer) - (p - range_lo);
         }
     }
     for (uint32_t i = 0; i < count; i++) {
