@@ -254,7 +254,10 @@ QB200_API qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint
 
 /* qb200_qlinear_forward_many over HOST buffers: every distinct input pointer is
  * copied to the device once, the forwards run, all outputs are copied back and
- * the call synchronises.  Staging buffers belong to layers[0] and grow on demand. */
+ * the call synchronises.  Staging buffers belong to layers[0] and grow on demand.
+ * Decode-shaped calls whose outputs lie in pinned, device-mapped host memory
+ * (cudaHostAlloc / cudaHostRegister) skip the copy back: the kernel stores there
+ * itself while it is still streaming weights. */
 QB200_API qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint32_t count,
                                              const void* const* x_host, int32_t x_dtype, uint64_t m,
                                              void* const* y_host, int32_t y_dtype);
