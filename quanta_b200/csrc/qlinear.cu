@@ -377,9 +377,21 @@ qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, i
     if (qb200_status s = grow(&ql->y_stage, &ql->y_stage_bytes, yb)) return s;
     if (!ql->host_stream) QB_CUDA_TRY(cudaStreamCreateWithFlags(&ql->host_stream, cudaStreamNonBlocking));
     QB_CUDA_TRY(cudaMemcpyAsync(ql->x_stage, x_host, xb, cudaMemcpyHostToDevice, ql->host_stream));
-    if (qb200_status s = qb200_qlinear_forward(ql, ql->x_stage, x_dtype, m, ql->y_stage, y_dtype, ql->host_stream))
+    // a decode-shaped call with its output in pinned, device-mapped memory: the kernel stores there itself
+    void* y_direct = nullptr;
+    if (m <= 16 && ql->in_dim <= 4096 && ql->bits == 4) {
+        cudaPointerAttributes at;
+        void* base = nullptr;
+        size_t size = 0;
+        if (cudaPointerGetAttributes(&at, y_host) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer &&
+            host_range(y_host, &base, &size) && static_cast<uint8_t*>(y_host) + yb <= static_cast<uint8_t*>(base) + size)
+            y_direct = at.devicePointer;
+        else
+            cudaGetLastError();
+    }
+    if (qb200_status s = qb200_qlinear_forward(ql, ql->x_stage, x_dtype, m, y_direct ? y_direct : ql->y_stage, y_dtype, ql->host_stream))
         return s;
-    QB_CUDA_TRY(cudaMemcpyAsync(y_host, ql->y_stage, yb, cudaMemcpyDeviceToHost, ql->host_stream));
+    if (!y_direct) QB_CUDA_TRY(cudaMemcpyAsync(y_host, ql->y_stage, yb, cudaMemcpyDeviceToHost, ql->host_stream));
     QB_CUDA_TRY(cudaStreamSynchronize(ql->host_stream));
     return QB200_OK;
 }

@@ -486,3 +486,7 @@ def test_forward_many_host_pinned_and_pageable_outputs():
             assert lib.qb200_qlinear_forward_many_host(hs, n, xp, _lib.BF16, M, yp, _lib.F32) == 0, _lib.last_error()
             for got, w_ in zip(ys, want):
                 assert torch.equal(got, w_.cpu()), f"pinned={pinned} M={M}"
+            one = torch.full((M, qls[0].out_dim()), float("nan"))
+            one = one.pin_memory() if pinned else one
+            assert lib.qb200_qlinear_forward_host(qls[0]._h, x.data_ptr(), _lib.BF16, M, one.data_ptr(), _lib.F32) == 0, _lib.last_error()
+            assert torch.equal(one, qls[0].forward(x.to(DEV), out_dtype=torch.float32).cpu())
