@@ -9,6 +9,7 @@ NVLink on GPUs, gloo on CPU for the host-side tests).
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import List, Optional, Tuple
 
 import torch
@@ -101,6 +102,58 @@ class TensorParallelLinear:
         if dist.get_world_size(self.group) == 1:
             return y
         return _gather(y, x.shape[0], self._widths, self.group)
+
+
+def shard_columns(m: QuantizedMatrix, world: int, rank: int):
+    """Rank's block of input features (columns) of an ``[out, in]`` matrix, for the row-parallel pairing: returns
+    ``(shard or None, lo, hi)``.  Boundaries are multiples of the scale tile's width (and of the eight codes of a
+    packed int4 word), so no tile and no word straddles them; the shard's codes and scales are copies."""
+    rows, cols = m.shape()
+    gr, gc = m.tile()
+    mult = gc if m.dtype().bits() == 8 or gc % 8 == 0 else gc * 8 // math.gcd(gc, 8)
+    lo, hi = shard_range(cols, world, rank, mult)
+    if hi <= lo:
+        return None, lo, hi
+    if m.dtype().bits() == 8:
+        codes = m.codes()[:, lo:hi].contiguous()
+    else:
+        codes = m.codes()[:, lo // 8: -(-hi // 8)].contiguous()
+    scales = m.scales()[:, lo // gc: -(-hi // gc)].contiguous()
+    return QuantizedMatrix(codes, scales, rows, hi - lo, gr, min(gc, hi - lo), m.dtype(), m.granularity()), lo, hi
+
+
+class RowParallelLinear:
+    """A QuantizedLinear whose INPUT features are sharded over the ranks: every rank multiplies its slice of the
+    activations by its block of columns and the partial outputs are summed (all-reduce).  Paired after a
+    column-sharded layer it consumes that layer's local output as is, so a block of two linears needs one
+    collective instead of two.  The sum's order differs from the unsharded layer's: equal to 1e-4, not bit for bit."""
+
+    def __init__(self, local: Optional[QuantizedLinear], bias: Optional[torch.Tensor], out_dim: int, lo: int, hi: int, group=None):
+        self.local, self.bias, self._out, self.lo, self.hi, self.group = local, bias, out_dim, lo, hi, group
+
+    @classmethod
+    def new(cls, w: QuantizedMatrix, b: Optional[torch.Tensor] = None, group=None) -> "RowParallelLinear":
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        shard, lo, hi = shard_columns(w, world, rank)
+        local = None if shard is None else QuantizedLinear.new(shard, None, L.OUT_IN)
+        return cls(local, None if b is None else b.to(torch.float32), w.shape()[0], lo, hi, group)
+
+    def out_dim(self) -> int:
+        return self._out
+
+    def forward(self, x: torch.Tensor, sliced: bool = False) -> torch.Tensor:
+        """``x`` is the full ``[m, in]`` activation (this rank's columns are cut out) or, with ``sliced``, already
+        this rank's ``[m, hi - lo]`` block.  Returns the f32 ``[m, out]`` on every rank."""
+        if self.local is not None:
+            xs = x if sliced else x[:, self.lo: self.hi].contiguous()
+            y = self.local.forward(xs, out_dtype=torch.float32)
+        else:
+            y = torch.zeros((x.shape[0], self._out), dtype=torch.float32, device=x.device)
+        if dist.get_world_size(self.group) > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        if self.bias is not None:
+            y = y + self.bias.to(y.device).reshape(1, self._out)
+        return y
 
 
 class _RawCuda:

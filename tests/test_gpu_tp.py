@@ -40,6 +40,14 @@ def _worker(rank, world, port, ret):
                 want = full.forward(x, out_dtype=torch.float32)
                 got = tpl.forward(x, out_dtype=torch.float32)
                 ok = ok and got.shape == want.shape and bool(((got - want).abs() <= 1e-4 * (1 + want.abs())).all())
+            rpl = tp.RowParallelLinear.new(qm, b)  # input features sharded, partial outputs summed
+            for M in (1, 16, 128):
+                x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+                want = full.forward(x, out_dtype=torch.float32)
+                got = rpl.forward(x)
+                sliced = rpl.forward(x[:, rpl.lo: rpl.hi].contiguous(), sliced=True)
+                ok = ok and got.shape == want.shape and bool(((got - want).abs() <= 1e-4 * (1 + want.abs())).all())
+                ok = ok and bool(torch.equal(got, sliced))
         ret[rank] = ok
     finally:
         dist.destroy_process_group()

@@ -77,3 +77,51 @@ def test_sharded_forward_matches_full_forward(world, N, K, bits, gr, gc):
         p.join(120)
         assert p.exitcode == 0
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def _row_worker(rank, world, port, N, K, bits, gr, gc, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(13)
+        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+        x = rng.standard_normal((3, K)).astype(np.float32)
+        codes, scales = o.quantize_host(w, N, K, bits, gr, gc)
+        ct = torch.from_numpy(codes if bits == 8 else codes.view(np.int32))
+        gran = qb.granularity_from_grid(N, K, gr, gc, allow_block=True)
+        full = qb.QuantizedMatrix.from_parts(ct, [N, K], torch.from_numpy(scales), gran)
+        wd = o.dequantize_host(codes, scales, N, K, bits, gr, gc)
+        want = o.linear_forward_f64(x, wd, None, o.OUT_IN)
+        sh, lo, hi = tp.shard_columns(full, world, rank)
+        ok = lo % gc == 0 or lo == K
+        if sh is not None:
+            sc = sh.codes().numpy()
+            sc = sc if bits == 8 else sc.view(np.uint32)
+            part = o.dequantize_host(sc, sh.scales().numpy(), N, hi - lo, bits, gr, sh.tile()[1])
+            ok = ok and np.array_equal(part.view(np.uint32), np.ascontiguousarray(wd[:, lo:hi]).view(np.uint32))  # the shard IS the block
+            y = torch.from_numpy(o.linear_forward(np.ascontiguousarray(x[:, lo:hi]), part, None, o.OUT_IN))
+        else:
+            y = torch.zeros((3, N))
+        dist.all_reduce(y)  # what RowParallelLinear.forward does with the local outputs
+        ok = ok and bool((np.abs(y.numpy() - want) <= 1e-4 * (1 + np.abs(want))).all())
+        cover = torch.zeros(K)
+        cover[lo:hi] = 1
+        dist.all_reduce(cover)
+        ret[rank] = ok and bool((cover == 1).all())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,N,K,bits,gr,gc", [(2, 48, 512, 4, 1, 128), (3, 40, 384, 4, 1, 128), (2, 64, 96, 8, 32, 32),
+                                                  (3, 32, 128, 8, 1, 128)])
+def test_row_parallel_shards_sum_to_the_full_forward(world, N, K, bits, gr, gc):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_row_worker, args=(r, world, port, N, K, bits, gr, gc, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert all(ret.get(r) for r in range(world)), dict(ret)
