@@ -340,6 +340,41 @@ QB200_API qb200_status qb200_st_writer_finish(qb200_st_writer* w, const uint8_t*
 QB200_API qb200_status qb200_st_parse_quant_meta(const char* leaf, const char* value, uint32_t* bits,
                                        uint64_t* gr, uint64_t* gc, uint64_t* rows, uint64_t* cols);
 
+/* ---- quantized BLAS entries: integer codes for BOTH operands, per-tensor symmetric scales ----
+ * GemmQuantType (crates/sci/quanta-blas/src/mixed_quant.rs:22-31). */
+enum { QB200_Q8_SYMMETRIC = 0, QB200_Q4_SYMMETRIC = 1 };
+
+/* gemm_quant(): C <- alpha * (a_scale * A) * (b_scale * B) + beta * C; A [m, k] and B [k, n] row-major int8
+ * codes, one per i32 word; C [m, n] f32, read for beta * C and overwritten
+ * (crates/sci/quanta-blas/src/mixed_quant.rs:47-81; CPU twin crates/sci/quanta-blas/src/reference.rs:212-226).
+ * qty other than QB200_Q8_SYMMETRIC: QB200_ERR_INVALID_PARAM, as the reference errors.  All pointers are device
+ * memory; the call is asynchronous on `stream`.  The sum of code products is formed exactly in integers
+ * (tcgen05 kind::i8), where the reference accumulates the products in f32: equal bit for bit while the
+ * running sum stays below 2^24, and within the reference's own test tolerance (1e-3 * (1 + |want|)) beyond.
+ * Codes outside [-128, 127] and k > 131071 are not served: the first is reported by qb200_gemm_quant_check,
+ * the second returns QB200_ERR_NOT_SUPPORTED. */
+QB200_API qb200_status qb200_gemm_quant(int qty, uint32_t m, uint32_t n, uint32_t k, float alpha, float a_scale,
+                                        float b_scale, const int32_t* a_dev, const int32_t* b_dev, float beta,
+                                        float* c_dev, void* stream);
+/* gemm_quant4(): the same over int4 codes packed eight per u32 word by FLAT element index (word i / 8,
+ * nibble i % 8; A holds ceil(m * k / 8) words, B ceil(k * n / 8))
+ * (crates/sci/quanta-blas/src/mixed_quant.rs:104-127; reference.rs:235-262). */
+QB200_API qb200_status qb200_gemm_quant4(int qty, uint32_t m, uint32_t n, uint32_t k, float alpha, float a_scale,
+                                         float b_scale, const uint32_t* a_dev, const uint32_t* b_dev, float beta,
+                                         float* c_dev, void* stream);
+/* gemv_quant() / gemv_quant4(): A [m, n] codes, x [n] codes, y [m] f32 — gemm_quant(m, 1, n, ...)
+ * (crates/sci/quanta-blas/src/mixed_quant.rs:83-100, 129-147).  One pass over A's codes. */
+QB200_API qb200_status qb200_gemv_quant(int qty, uint32_t m, uint32_t n, float alpha, float a_scale, float x_scale,
+                                        const int32_t* a_dev, const int32_t* x_dev, float beta, float* y_dev,
+                                        void* stream);
+QB200_API qb200_status qb200_gemv_quant4(int qty, uint32_t m, uint32_t n, float alpha, float a_scale, float x_scale,
+                                         const uint32_t* a_dev, const uint32_t* x_dev, float beta, float* y_dev,
+                                         void* stream);
+/* Waits for `stream` and reports what the quantized BLAS kernels launched on it recorded since the last
+ * check: QB200_ERR_INVALID_PARAM for an int8 code out of range, QB200_ERR_TIMEOUT for a bounded wait that
+ * ran out.  The packed operands live in a buffer per (device, stream) that grows on demand and is reused. */
+QB200_API qb200_status qb200_gemm_quant_check(void* stream);
+
 #ifdef __cplusplus
 }
 #endif
