@@ -213,6 +213,31 @@ def measure_extras(torch, qb, dev, only=None, small=False):
     # quantize-on-load: f32 [11008, 4096] (180 MB, larger than L2) -> int4 1x128 and int8 32x32
     if only == "decode_step":
         return {"decode_step_llama7b_shape": measure_decode_step(torch, dev, gen, timed, hbm, 2 if small else 32)}
+    if only == "blas_quant":
+        # the quantized BLAS entries: int codes for both operands, one per i32 word (the reference's storage), so a call
+        # is two packing passes over 4 B per code and the tcgen05 kind::i8 GEMM; the GEMV entry reads A's codes once
+        from quanta_b200 import blas
+        del w, x
+        res = {}
+        q8 = blas.GemmQuantType.Q8Symmetric
+        for m, n, k in ([(1024, 1024, 2048)] if small else [(4096, 4096, 4096), (8192, 8192, 8192)]):
+            a = torch.randint(-128, 128, (m * k,), dtype=torch.int32, device=dev, generator=gen)
+            b = torch.randint(-128, 128, (k * n,), dtype=torch.int32, device=dev, generator=gen)
+            c = torch.zeros(m * n, device=dev)
+            ms = timed(lambda: blas.gemm_quant(q8, m, n, k, 1.0, 0.01, 0.01, a, b, 0.0, c), 3 if small else 10)
+            blas.check_stream(c)
+            res[f"gemm_quant_{m}x{n}x{k}"] = {"TOP/s": 2.0 * m * n * k / ms / 1e9, "ms": ms, "launches_per_call": 3,
+                                               "code_bytes_read": 4 * (m * k + k * n)}
+            del a, b, c
+        m, n = (4096, 4096) if small else (16384, 8192)
+        a = torch.randint(-128, 128, (m * n,), dtype=torch.int32, device=dev, generator=gen)
+        xq = torch.randint(-128, 128, (n,), dtype=torch.int32, device=dev, generator=gen)
+        y = torch.zeros(m, device=dev)
+        ms = timed(lambda: blas.gemv_quant(q8, m, n, 1.0, 0.01, 0.01, a, xq, 0.0, y), 3 if small else 10)
+        blas.check_stream(y)
+        res[f"gemv_quant_{m}x{n}"] = {"GB/s": 4.0 * m * n / ms / 1e6, "ms": ms, "roofline_frac": 4.0 * m * n / ms / 1e6 / hbm,
+                                      "bytes": 4 * m * n}
+        return res
     if only == "prefill":
         qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
         ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
@@ -522,7 +547,7 @@ def main():
                     help="N > 1, grouped launch: fused = peer stores from the kernel + arrival barrier; nccl = all-gather after it")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
-    ap.add_argument("--only", default=None, choices=["prefill", "quantize", "decode_step"], help="run only a side workload and print its numbers")
+    ap.add_argument("--only", default=None, choices=["prefill", "quantize", "decode_step", "blas_quant"], help="run only a side workload and print its numbers")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced shape, for profiler captures")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()

@@ -10,9 +10,9 @@
 // Three steps on the caller's stream:
 //   1. k_pack_rows:  A codes -> int8 [m, kp] (kp = k rounded up to 128, zero filled): K-major rows.
 //   2. k_pack_cols:  B codes -> int8 [n, kp], transposed through shared memory, so B is K-major as well.
-//   3. k_gemm_i8_tc: one CTA per 128 (m) x 256 (n) tile of C; a TMA warp fills a ring of 128-byte-swizzled
-//      stages (128 k each), one elected thread issues four tcgen05.mma (K = 32) per stage into a 256-column
-//      s32 accumulator in TMEM, four warps read it back (tcgen05.ld) and write alpha_eff * acc + beta * c.
+//   3. k_gemm_i8_tc: one persistent CTA per SM walks 128 (m) x 256 (n) tiles of C; a TMA warp fills a ring of 128-byte-swizzled
+//      stages (128 k each), one elected thread issues four tcgen05.mma (K = 32) per stage into one of two 256-column
+//      s32 accumulators in TMEM, four warps read the other one back (tcgen05.ld) and write alpha_eff * acc + beta * c.
 // n = 1 (the GEMV entries) skips all of it: one warp per row of A reads the codes once, HBM bound.
 // Every wait on an mbarrier is bounded; a wait that runs out records QB200_ERR_TIMEOUT in the status word
 // that qb200_gemm_quant_check reads.
@@ -227,12 +227,16 @@ __global__ void __launch_bounds__(BQ_THREADS, 1)
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BQ_S * BQ_STAGE);
     uint64_t* full = bars;           // a stage's two tiles have landed (TMA)
     uint64_t* empty = full + BQ_S;   // the MMAs that read the stage are done
-    uint64_t* dfull = empty + BQ_S;  // the accumulator is complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dfull + 1);
+    uint64_t* dfull = empty + BQ_S;  // [2] an accumulator is complete
+    uint64_t* dempty = dfull + 2;    // [2] the four epilogue warps have read it out of TMEM
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // persistent: this CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...; m runs fastest, so the CTAs of one
+    // round share B's tiles in L2.  The stage ring and the two accumulators run across tile boundaries, so one tile's
+    // read-out and store overlap the next tile's K loop.
     const uint32_t m_tiles = (a.m + BQ_TM - 1) / BQ_TM;
-    const uint32_t m_tile = blockIdx.x % m_tiles, n_tile = blockIdx.x / m_tiles;  // m fastest: neighbours share B's tile
+    const uint32_t tiles = m_tiles * ((a.n + BQ_TN - 1) / BQ_TN);
     const uint32_t num_k = a.kp / BQ_BK;
 
     if (tid == 0) {
@@ -240,11 +244,14 @@ __global__ void __launch_bounds__(BQ_THREADS, 1)
             bq_mbar_init(&full[s], 1);
             bq_mbar_init(&empty[s], 1);
         }
-        bq_mbar_init(dfull, 1);
+        for (uint32_t b = 0; b < 2; b++) {
+            bq_mbar_init(&dfull[b], 1);
+            bq_mbar_init(&dempty[b], 4);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // 256 TMEM columns: the 128 x 256 s32 accumulator
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(bq_smem(tmem_slot)) : "memory");
+    if (warp == 1) {  // all 512 TMEM columns: two 128 x 256 s32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(bq_smem(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -255,14 +262,17 @@ __global__ void __launch_bounds__(BQ_THREADS, 1)
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t st = 0, par = 0;
-            for (uint32_t it = 0; it < num_k; it++) {
-                if (it >= BQ_S && !bq_wait(&empty[st], par ^ 1)) { failed = true; break; }
-                uint8_t* sa = smem + st * BQ_STAGE;
-                bq_mbar_expect_tx(&full[st], BQ_STAGE);
-                bq_tma_load_2d(sa, &amap, (int32_t)(it * BQ_BK), (int32_t)(m_tile * BQ_TM), &full[st]);
-                bq_tma_load_2d(sa + BQ_A_BYTES, &bmap, (int32_t)(it * BQ_BK), (int32_t)(n_tile * BQ_TN), &full[st]);
-                if (++st == BQ_S) { st = 0; par ^= 1; }
+            uint32_t st = 0, par = 0, filled = 0;
+            for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
+                const uint32_t m_tile = t % m_tiles, n_tile = t / m_tiles;
+                for (uint32_t it = 0; it < num_k; it++, filled++) {
+                    if (filled >= BQ_S && !bq_wait(&empty[st], par ^ 1)) { failed = true; break; }
+                    uint8_t* sa = smem + st * BQ_STAGE;
+                    bq_mbar_expect_tx(&full[st], BQ_STAGE);
+                    bq_tma_load_2d(sa, &amap, (int32_t)(it * BQ_BK), (int32_t)(m_tile * BQ_TM), &full[st]);
+                    bq_tma_load_2d(sa + BQ_A_BYTES, &bmap, (int32_t)(it * BQ_BK), (int32_t)(n_tile * BQ_TN), &full[st]);
+                    if (++st == BQ_S) { st = 0; par ^= 1; }
+                }
             }
         }
         __syncwarp();
@@ -271,33 +281,40 @@ __global__ void __launch_bounds__(BQ_THREADS, 1)
         const uint32_t elected = bq_elect();
         // s32 accumulate, s8 x s8, both K-major, N = 256, M = 128
         const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((BQ_TN >> 3) << 17) | ((BQ_TM >> 4) << 24);
-        uint32_t st = 0, par = 0;
-        for (uint32_t it = 0; it < num_k; it++) {
-            if (!bq_wait(&full[st], par)) { failed = true; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = bq_desc(bq_smem(smem + st * BQ_STAGE)), db = bq_desc(bq_smem(smem + st * BQ_STAGE + BQ_A_BYTES));
-            if (elected) {
+        uint32_t st = 0, par = 0, lt = 0;  // lt: tiles this CTA has started
+        for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x, lt++) {
+            const uint32_t buf = lt & 1;
+            // the accumulator was last used by tile lt - 2: wait until its read-out is over
+            if (lt >= 2 && !bq_wait(&dempty[buf], ((lt >> 1) & 1) ^ 1)) { failed = true; break; }
+            for (uint32_t it = 0; it < num_k; it++) {
+                if (!bq_wait(&full[st], par)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = bq_desc(bq_smem(smem + st * BQ_STAGE)), db = bq_desc(bq_smem(smem + st * BQ_STAGE + BQ_A_BYTES));
+                if (elected) {
 #pragma unroll
-                for (uint32_t kk = 0; kk < BQ_BK / 32; kk++)
-                    bq_mma_i8(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (it | kk) ? 1u : 0u);  // +32 bytes per K = 32 step
-                bq_commit(&empty[st]);
+                    for (uint32_t kk = 0; kk < BQ_BK / 32; kk++)  // +32 bytes per K = 32 step
+                        bq_mma_i8(tmem_base + buf * BQ_TN, da + 2 * kk, db + 2 * kk, idesc, (it | kk) ? 1u : 0u);
+                    bq_commit(&empty[st]);
+                }
+                if (++st == BQ_S) { st = 0; par ^= 1; }
             }
-            if (++st == BQ_S) { st = 0; par ^= 1; }
+            if (elected && !failed) bq_commit(&dfull[buf]);
         }
-        if (elected && !failed) bq_commit(dfull);
     } else {
         // ---- epilogue: a warp reads the TMEM lanes of its quarter (warp index mod 4), a thread owns one row of C ----
         const uint32_t quarter = warp & 3;
-        const uint32_t row = m_tile * BQ_TM + quarter * 32 + lane;
-        if (!bq_wait(dfull, 0)) failed = true;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!failed) {
-            const bool vec = (a.n & 3) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0;
+        const bool vec = (a.n & 3) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0;
+        uint32_t lt = 0;
+        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, lt++) {
+            const uint32_t m_tile = t % m_tiles, n_tile = t / m_tiles, buf = lt & 1;
+            const uint32_t row = m_tile * BQ_TM + quarter * 32 + lane;
+            if (!bq_wait(&dfull[buf], (lt >> 1) & 1)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (uint32_t ch = 0; ch < BQ_TN / 32; ch++) {
                 const uint32_t col0 = n_tile * BQ_TN + ch * 32;
                 if (col0 >= a.n) break;  // warp-uniform
                 int32_t acc[32];
-                bq_tmem_ld32(tmem_base + ((quarter * 32) << 16) + ch * 32, acc);
+                bq_tmem_ld32(tmem_base + ((quarter * 32) << 16) + buf * BQ_TN + ch * 32, acc);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < a.m) {
                     float* cr = a.c + (uint64_t)row * a.n + col0;
@@ -318,12 +335,16 @@ __global__ void __launch_bounds__(BQ_THREADS, 1)
                     }
                 }
             }
+            // this warp's reads of the accumulator are complete (wait::ld above): hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bq_smem(&dempty[buf])) : "memory");
         }
     }
     if (failed) atomicOr(a.status, BQ_FLAG_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem_base) : "memory");
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
 }
 
 // ---- host side ----
@@ -443,7 +464,10 @@ static qb200_status bq_run(const char* who, uint32_t m, uint32_t n, uint32_t k, 
     }
     const uint64_t tiles = div_ceil(m, BQ_TM) * div_ceil(n, BQ_TN);
     if (tiles > 0x7FFFFFFFull) return fail(QB200_ERR_NOT_SUPPORTED, std::string(who) + ": too many output tiles");
-    k_gemm_i8_tc<<<(uint32_t)tiles, BQ_THREADS, BQ_SMEM, st>>>(amap, bmap, args);
+    static int sm_count[64] = {};
+    if (!sm_count[dev & 63]) QB_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev));
+    const uint32_t grid = tiles < (uint64_t)sm_count[dev & 63] ? (uint32_t)tiles : (uint32_t)sm_count[dev & 63];
+    k_gemm_i8_tc<<<grid, BQ_THREADS, BQ_SMEM, st>>>(amap, bmap, args);
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
 }
