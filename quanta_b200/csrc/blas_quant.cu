@@ -10,9 +10,13 @@
 // Three steps on the caller's stream:
 //   1. k_pack_rows:  A codes -> int8 [m, kp] (kp = k rounded up to 128, zero filled): K-major rows.
 //   2. k_pack_cols:  B codes -> int8 [n, kp], transposed through shared memory, so B is K-major as well.
-//   3. k_gemm_i8_tc: one persistent CTA per SM walks 128 (m) x 256 (n) tiles of C; a TMA warp fills a ring of 128-byte-swizzled
-//      stages (128 k each), one elected thread issues four tcgen05.mma (K = 32) per stage into one of two 256-column
-//      s32 accumulators in TMEM, four warps read the other one back (tcgen05.ld) and write alpha_eff * acc + beta * c.
+//   3. k_gemm_i8_tc: persistent, one CTA per SM, CTAs paired in clusters of two; a pair walks 256 (m) x 256 (n) tiles
+//      of C.  Per stage (128 k) each CTA's TMA warp fetches ITS 128 rows of A and ITS 128 rows of B (128-byte swizzle);
+//      one elected thread of the pair's leader issues four tcgen05.mma.cta_group::2 (256 x 256 x 32) that read both
+//      CTAs' halves, so every byte staged in shared memory feeds two tensor cores — at int8 rates a single CTA's
+//      shared-memory bandwidth (operand reads plus TMA fills) would cap the tensor pipe at about two thirds.
+//      Each CTA keeps its 128 rows of the accumulator in TMEM, twice; four warps read one back (tcgen05.ld) and
+//      write alpha_eff * acc + beta * c while the other is being accumulated.
 // n = 1 (the GEMV entries) skips all of it: one warp per row of A reads the codes once, HBM bound.
 // Every wait on an mbarrier is bounded; a wait that runs out records QB200_ERR_TIMEOUT in the status word
 // that qb200_gemm_quant_check reads.
@@ -27,10 +31,10 @@
 
 namespace qb {
 
-constexpr uint32_t BQ_TM = 128, BQ_TN = 256, BQ_BK = 128;  // tile of C; k per stage (128 int8 = one swizzle row)
-constexpr uint32_t BQ_S = 4;
-constexpr uint32_t BQ_THREADS = 192;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
-constexpr uint32_t BQ_A_BYTES = BQ_TM * BQ_BK, BQ_B_BYTES = BQ_TN * BQ_BK, BQ_STAGE = BQ_A_BYTES + BQ_B_BYTES;
+constexpr uint32_t BQ_TM = 256, BQ_TN = 256, BQ_BK = 128;  // a CTA pair's tile of C; k per stage (128 int8 = one swizzle row)
+constexpr uint32_t BQ_S = 6;
+constexpr uint32_t BQ_THREADS = 256;  // warp 0 TMA, warp 1 MMA + TMEM, warp 2 forwarder, warps 4-7 epilogue
+constexpr uint32_t BQ_HALF = 128 * BQ_BK, BQ_STAGE = 2 * BQ_HALF;  // per CTA and stage: 128 rows of A, 128 rows of B
 constexpr uint32_t BQ_SMEM = 1024 + BQ_S * BQ_STAGE + 256;
 constexpr uint32_t BQ_SPIN = 1u << 22;
 constexpr int32_t BQ_FLAG_RANGE = 1, BQ_FLAG_TIMEOUT = 2;
@@ -200,13 +204,37 @@ __device__ __forceinline__ void bq_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// When the MMAs issued so far have completed, arrive on the barrier.
-__device__ __forceinline__ void bq_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bq_smem(bar)) : "memory");
+// When the MMAs issued so far have completed, arrive on the barrier at this offset in BOTH CTAs of the pair.
+__device__ __forceinline__ void bq_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     bq_smem(bar)),
+                 "h"(both)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t bq_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Shared-memory address of this CTA mapped to the same offset in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t bq_map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+// Arrive on a barrier of a CTA of this cluster.  What the arrival publishes was ordered before it by its own fence
+// (the TMA's completion, tcgen05.fence for TMEM reads); default semantics, no cluster-scope release.
+__device__ __forceinline__ void bq_mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void bq_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void bq_tmem_ld32(uint32_t taddr, int32_t (&v)[32]) {
     asm volatile(
@@ -220,94 +248,116 @@ __device__ __forceinline__ void bq_tmem_ld32(uint32_t taddr, int32_t (&v)[32]) {
         : "memory");
 }
 
-__global__ void __launch_bounds__(BQ_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(BQ_THREADS, 1)
     k_gemm_i8_tc(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, BqArgs a) {
     extern __shared__ __align__(1024) uint8_t bq_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(bq_smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BQ_S * BQ_STAGE);
-    uint64_t* full = bars;           // a stage's two tiles have landed (TMA)
-    uint64_t* empty = full + BQ_S;   // the MMAs that read the stage are done
-    uint64_t* dfull = empty + BQ_S;  // [2] an accumulator is complete
-    uint64_t* dempty = dfull + 2;    // [2] the four epilogue warps have read it out of TMEM
+    uint64_t* full = bars;            // leader: a stage's tiles have landed in BOTH CTAs
+    uint64_t* full_x = full + BQ_S;   // non-leader: its own tiles have landed (TMA)
+    uint64_t* empty = full_x + BQ_S;  // the MMAs that read the stage are done (arrives in both CTAs)
+    uint64_t* dfull = empty + BQ_S;   // [2] an accumulator is complete (arrives in both CTAs)
+    uint64_t* dempty = dfull + 2;     // [2] leader: the epilogue warps of both CTAs have read it out of TMEM
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dempty + 2);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // persistent: this CTA takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...; m runs fastest, so the CTAs of one
-    // round share B's tiles in L2.  The stage ring and the two accumulators run across tile boundaries, so one tile's
-    // read-out and store overlap the next tile's K loop.
+    const uint32_t rank = bq_cluster_rank();  // 0: the pair's leader
+    // persistent: pair p takes tiles p, p + pairs, ...; m runs fastest, so the pairs of one round share B's tiles
+    // in L2.  The stage ring and the two accumulators run across tile boundaries, so one tile's read-out and store
+    // overlap the next tile's K loop.
+    const uint32_t pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
     const uint32_t m_tiles = (a.m + BQ_TM - 1) / BQ_TM;
     const uint32_t tiles = m_tiles * ((a.n + BQ_TN - 1) / BQ_TN);
     const uint32_t num_k = a.kp / BQ_BK;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < BQ_S; s++) {
-            bq_mbar_init(&full[s], 1);
+            bq_mbar_init(&full[s], 2);  // the leader's TMA (with its bytes) and the non-leader's "landed" message
+            bq_mbar_init(&full_x[s], 1);
             bq_mbar_init(&empty[s], 1);
         }
         for (uint32_t b = 0; b < 2; b++) {
             bq_mbar_init(&dfull[b], 1);
-            bq_mbar_init(&dempty[b], 4);
+            bq_mbar_init(&dempty[b], 8);  // four epilogue warps in each CTA
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // all 512 TMEM columns: two 128 x 256 s32 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(bq_smem(tmem_slot)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // all 512 TMEM columns of this CTA: two 128 x 256 s32 accumulators (this CTA's half of the rows)
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(bq_smem(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    bq_cluster_sync();  // both CTAs' barriers are initialised before either arrives on the other's
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
 
     if (warp == 0) {
+        // ---- TMA producer: this CTA's 128 rows of A and 128 rows of B per stage ----
         if (lane == 0) {
+            uint64_t* landed = rank == 0 ? full : full_x;
             uint32_t st = 0, par = 0, filled = 0;
-            for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x) {
-                const uint32_t m_tile = t % m_tiles, n_tile = t / m_tiles;
+            for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
+                const int32_t a_row = (int32_t)((t % m_tiles) * BQ_TM + rank * 128), b_row = (int32_t)((t / m_tiles) * BQ_TN + rank * 128);
                 for (uint32_t it = 0; it < num_k; it++, filled++) {
                     if (filled >= BQ_S && !bq_wait(&empty[st], par ^ 1)) { failed = true; break; }
                     uint8_t* sa = smem + st * BQ_STAGE;
-                    bq_mbar_expect_tx(&full[st], BQ_STAGE);
-                    bq_tma_load_2d(sa, &amap, (int32_t)(it * BQ_BK), (int32_t)(m_tile * BQ_TM), &full[st]);
-                    bq_tma_load_2d(sa + BQ_A_BYTES, &bmap, (int32_t)(it * BQ_BK), (int32_t)(n_tile * BQ_TN), &full[st]);
+                    bq_mbar_expect_tx(&landed[st], BQ_STAGE);
+                    bq_tma_load_2d(sa, &amap, (int32_t)(it * BQ_BK), a_row, &landed[st]);
+                    bq_tma_load_2d(sa + BQ_HALF, &bmap, (int32_t)(it * BQ_BK), b_row, &landed[st]);
                     if (++st == BQ_S) { st = 0; par ^= 1; }
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        // the whole warp walks the loop (waits and descriptors are warp-uniform); one elected lane issues
-        const uint32_t elected = bq_elect();
-        // s32 accumulate, s8 x s8, both K-major, N = 256, M = 128
-        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((BQ_TN >> 3) << 17) | ((BQ_TM >> 4) << 24);
-        uint32_t st = 0, par = 0, lt = 0;  // lt: tiles this CTA has started
-        for (uint32_t t = blockIdx.x; t < tiles && !failed; t += gridDim.x, lt++) {
-            const uint32_t buf = lt & 1;
-            // the accumulator was last used by tile lt - 2: wait until its read-out is over
-            if (lt >= 2 && !bq_wait(&dempty[buf], ((lt >> 1) & 1) ^ 1)) { failed = true; break; }
-            for (uint32_t it = 0; it < num_k; it++) {
-                if (!bq_wait(&full[st], par)) { failed = true; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = bq_desc(bq_smem(smem + st * BQ_STAGE)), db = bq_desc(bq_smem(smem + st * BQ_STAGE + BQ_A_BYTES));
-                if (elected) {
+        // ---- MMA issuer (the pair's leader): the whole warp walks the loop, one elected lane issues ----
+        if (rank == 0) {
+            const uint32_t elected = bq_elect();
+            // s32 accumulate, s8 x s8, both K-major, N = 256, M = 256 over the pair
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((BQ_TN >> 3) << 17) | ((BQ_TM >> 4) << 24);
+            uint32_t st = 0, par = 0, lt = 0;  // lt: tiles this pair has started
+            for (uint32_t t = pair; t < tiles && !failed; t += pairs, lt++) {
+                const uint32_t buf = lt & 1;
+                // the accumulator was last used by tile lt - 2: wait until its read-out is over in both CTAs
+                if (lt >= 2 && !bq_wait(&dempty[buf], ((lt >> 1) & 1) ^ 1)) { failed = true; break; }
+                for (uint32_t it = 0; it < num_k; it++) {
+                    if (!bq_wait(&full[st], par)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = bq_desc(bq_smem(smem + st * BQ_STAGE)), db = bq_desc(bq_smem(smem + st * BQ_STAGE + BQ_HALF));
+                    if (elected) {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < BQ_BK / 32; kk++)  // +32 bytes per K = 32 step
-                        bq_mma_i8(tmem_base + buf * BQ_TN, da + 2 * kk, db + 2 * kk, idesc, (it | kk) ? 1u : 0u);
-                    bq_commit(&empty[st]);
+                        for (uint32_t kk = 0; kk < BQ_BK / 32; kk++)  // +32 bytes per K = 32 step
+                            bq_mma_i8(tmem_base + buf * BQ_TN, da + 2 * kk, db + 2 * kk, idesc, (it | kk) ? 1u : 0u);
+                        bq_commit_pair(&empty[st]);
+                    }
+                    if (++st == BQ_S) { st = 0; par ^= 1; }
                 }
-                if (++st == BQ_S) { st = 0; par ^= 1; }
+                if (elected && !failed) bq_commit_pair(&dfull[buf]);
             }
-            if (elected && !failed) bq_commit(&dfull[buf]);
         }
-    } else {
+    } else if (warp == 2) {
+        // ---- non-leader: pass "tiles landed" on to the leader's barrier ----
+        if (lane == 0 && rank == 1) {
+            const uint32_t remote = bq_map_to_cta(bq_smem(&full[0]), 0);
+            uint32_t st = 0, par = 0;
+            for (uint32_t t = pair; t < tiles && !failed; t += pairs)
+                for (uint32_t it = 0; it < num_k; it++) {
+                    if (!bq_wait(&full_x[st], par)) { failed = true; break; }
+                    bq_mbar_arrive_cluster(remote + st * 8);
+                    if (++st == BQ_S) { st = 0; par ^= 1; }
+                }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
         // ---- epilogue: a warp reads the TMEM lanes of its quarter (warp index mod 4), a thread owns one row of C ----
         const uint32_t quarter = warp & 3;
         const bool vec = (a.n & 3) == 0 && (reinterpret_cast<uintptr_t>(a.c) & 15) == 0;
+        const uint32_t remote_dempty = bq_map_to_cta(bq_smem(&dempty[0]), 0);
         uint32_t lt = 0;
-        for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, lt++) {
+        for (uint32_t t = pair; t < tiles; t += pairs, lt++) {
             const uint32_t m_tile = t % m_tiles, n_tile = t / m_tiles, buf = lt & 1;
-            const uint32_t row = m_tile * BQ_TM + quarter * 32 + lane;
+            const uint32_t row = m_tile * BQ_TM + rank * 128 + quarter * 32 + lane;
             if (!bq_wait(&dfull[buf], (lt >> 1) & 1)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             for (uint32_t ch = 0; ch < BQ_TN / 32; ch++) {
@@ -335,16 +385,16 @@ __global__ void __launch_bounds__(BQ_THREADS, 1)
                     }
                 }
             }
-            // this warp's reads of the accumulator are complete (wait::ld above): hand it back to the MMA warp
+            // this warp's reads of the accumulator are complete (wait::ld above): hand it back to the leader's MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bq_smem(&dempty[buf])) : "memory");
+            if (lane == 0) bq_mbar_arrive_cluster(remote_dempty + buf * 8);
         }
     }
     if (failed) atomicOr(a.status, BQ_FLAG_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    bq_cluster_sync();  // neither CTA leaves while the other may still signal its barriers
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
 }
 
 // ---- host side ----
@@ -435,14 +485,14 @@ static qb200_status bq_run(const char* who, uint32_t m, uint32_t n, uint32_t k, 
     const cuuint64_t strides[1] = {kp};
     {
         const cuuint64_t dims[2] = {kp, m};
-        const cuuint32_t box[2] = {BQ_BK, BQ_TM};
+        const cuuint32_t box[2] = {BQ_BK, 128};
         CUresult cr = enc(&amap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a8, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, std::string(who) + ": cuTensorMapEncodeTiled (A) failed with code " + std::to_string((int)cr));
     }
     {
         const cuuint64_t dims[2] = {kp, n};
-        const cuuint32_t box[2] = {BQ_BK, BQ_TN};
+        const cuuint32_t box[2] = {BQ_BK, 128};
         CUresult cr = enc(&bmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b8, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, std::string(who) + ": cuTensorMapEncodeTiled (B) failed with code " + std::to_string((int)cr));
@@ -466,7 +516,8 @@ static qb200_status bq_run(const char* who, uint32_t m, uint32_t n, uint32_t k, 
     if (tiles > 0x7FFFFFFFull) return fail(QB200_ERR_NOT_SUPPORTED, std::string(who) + ": too many output tiles");
     static int sm_count[64] = {};
     if (!sm_count[dev & 63]) QB_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev));
-    const uint32_t grid = tiles < (uint64_t)sm_count[dev & 63] ? (uint32_t)tiles : (uint32_t)sm_count[dev & 63];
+    const uint64_t max_pairs = (uint64_t)sm_count[dev & 63] / 2;
+    const uint32_t grid = 2 * (uint32_t)(tiles < max_pairs ? tiles : max_pairs);  // one CTA per SM, in clusters of two
     k_gemm_i8_tc<<<grid, BQ_THREADS, BQ_SMEM, st>>>(amap, bmap, args);
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
