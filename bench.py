@@ -213,14 +213,15 @@ def measure_extras(torch, qb, dev, only=None, small=False):
     # quantize-on-load: f32 [11008, 4096] (180 MB, larger than L2) -> int4 1x128 and int8 32x32
     if only == "decode_step":
         return {"decode_step_llama7b_shape": measure_decode_step(torch, dev, gen, timed, hbm, 2 if small else 32)}
-    if only == "blas_quant":
+    if only in ("blas_quant", "blas_quant_brief"):
+        brief = only == "blas_quant_brief"
         # the quantized BLAS entries: int codes for both operands, one per i32 word (the reference's storage), so a call
         # is two packing passes over 4 B per code and the tcgen05 kind::i8 GEMM; the GEMV entry reads A's codes once
         from quanta_b200 import blas
         del w, x
         res = {}
         q8 = blas.GemmQuantType.Q8Symmetric
-        for m, n, k in ([(1024, 1024, 2048)] if small else [(4096, 4096, 4096), (8192, 8192, 8192)]):
+        for m, n, k in ([(1024, 1024, 2048)] if small else [(4096, 4096, 4096)] if brief else [(4096, 4096, 4096), (8192, 8192, 8192)]):
             a = torch.randint(-128, 128, (m * k,), dtype=torch.int32, device=dev, generator=gen)
             b = torch.randint(-128, 128, (k * n,), dtype=torch.int32, device=dev, generator=gen)
             c = torch.zeros(m * n, device=dev)
@@ -303,6 +304,10 @@ def measure_extras(torch, qb, dev, only=None, small=False):
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
     out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, timed, hbm, 32)
+    try:  # the quantized BLAS entries (int codes for both operands): one GEMM size and the GEMV
+        out["blas_quant"] = measure_extras(torch, qb, dev, only="blas_quant_brief")
+    except Exception as e:
+        out["blas_quant"] = {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
     ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
     ms = timed(lambda: ql.forward(x), 10)
     out["prefill_int4_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,

@@ -80,29 +80,32 @@ __global__ void k_pack_rows(const void* __restrict__ src, uint32_t rows, uint32_
 }
 
 // B [k, n] codes -> int8 [n, kp] (transposed), zero beyond k.  A block moves a 128 (k) x 32 (n) tile through
-// shared memory: reads run along n, writes are 16 bytes along k.
+// shared memory: reads run along n; a thread packs four consecutive k of its column into one word and parks it at
+// [n][k / 4] (pitch 33 words: no bank conflicts either way); writes are 16 bytes along k.
 template <int BITS>
 __global__ void __launch_bounds__(256) k_pack_cols(const void* __restrict__ src, uint32_t k, uint32_t n, uint32_t kp,
                                                     uint8_t* __restrict__ dst, int32_t* status) {
-    __shared__ uint8_t tile[128][36];
+    __shared__ uint32_t tile[32][33];
     const uint32_t n0 = blockIdx.x * 32, k0 = blockIdx.y * 128;
     const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     int32_t flag = 0;
-#pragma unroll 4
-    for (uint32_t i = 0; i < 16; i++) {
-        const uint32_t kk = i * 8 + ty;
-        int32_t v = 0;
-        if (k0 + kk < k && n0 + tx < n) v = bq_code<BITS>(src, (uint64_t)(k0 + kk) * n + n0 + tx, flag);
-        tile[kk][tx] = (uint8_t)v;
-    }
+    int32_t v[4][4];
+#pragma unroll
+    for (uint32_t i = 0; i < 4; i++)  // word q = ty + 8 i of the column: k = k0 + 4 q .. + 3
+#pragma unroll
+        for (uint32_t j = 0; j < 4; j++) {
+            const uint32_t kk = k0 + 4 * (ty + 8 * i) + j;
+            v[i][j] = (kk < k && n0 + tx < n) ? bq_code<BITS>(src, (uint64_t)kk * n + n0 + tx, flag) : 0;
+        }
+#pragma unroll
+    for (uint32_t i = 0; i < 4; i++)
+        tile[tx][ty + 8 * i] = ((uint32_t)v[i][0] & 0xFFu) | (((uint32_t)v[i][1] & 0xFFu) << 8) | (((uint32_t)v[i][2] & 0xFFu) << 16) |
+                               ((uint32_t)v[i][3] << 24);
     __syncthreads();
     const uint32_t row = threadIdx.x >> 3, chunk = threadIdx.x & 7;  // 32 rows of n, eight 16-byte pieces of k each
-    if (n0 + row < n) {
-        uint32_t w[4] = {0, 0, 0, 0};
-#pragma unroll
-        for (uint32_t j = 0; j < 16; j++) w[j >> 2] |= (uint32_t)tile[chunk * 16 + j][row] << (8 * (j & 3));
-        *reinterpret_cast<uint4*>(dst + (uint64_t)(n0 + row) * kp + k0 + chunk * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+    if (n0 + row < n)
+        *reinterpret_cast<uint4*>(dst + (uint64_t)(n0 + row) * kp + k0 + chunk * 16) =
+            make_uint4(tile[row][chunk * 4], tile[row][chunk * 4 + 1], tile[row][chunk * 4 + 2], tile[row][chunk * 4 + 3]);
     if (flag) atomicOr(status, flag);
 }
 
