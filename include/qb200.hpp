@@ -275,6 +275,36 @@ inline DeviceArray<uint16_t> swiglu(const DeviceArray<float>& gate, const Device
     return out;
 }
 
+// quanta-blas's quantized entries (crates/sci/quanta-blas/src/mixed_quant.rs:22-147): integer codes for both operands,
+// per-tensor symmetric scales, C f32 read for beta * C and overwritten.  Asynchronous on `st`.
+enum class GemmQuantType { Q8Symmetric = QB200_Q8_SYMMETRIC, Q4Symmetric = QB200_Q4_SYMMETRIC };
+inline void gemm_quant(GemmQuantType qty, uint32_t m, uint32_t n, uint32_t k, float alpha, float a_scale, float b_scale,
+                       const DeviceArray<int32_t>& a, const DeviceArray<int32_t>& b, float beta, DeviceArray<float>& c,
+                       cudaStream_t st = nullptr) {
+    if (a.len() != (uint64_t)m * k || b.len() != (uint64_t)k * n || c.len() != (uint64_t)m * n)
+        throw Error(QB200_ERR_LENGTH, "gemm_quant: A must be m x k, B k x n, C m x n");
+    check(qb200_gemm_quant((int)qty, m, n, k, alpha, a_scale, b_scale, a.data(), b.data(), beta, c.data(), st));
+}
+inline void gemm_quant4(GemmQuantType qty, uint32_t m, uint32_t n, uint32_t k, float alpha, float a_scale, float b_scale,
+                        const DeviceArray<uint32_t>& a, const DeviceArray<uint32_t>& b, float beta, DeviceArray<float>& c,
+                        cudaStream_t st = nullptr) {
+    if (a.len() != ((uint64_t)m * k + 7) / 8 || b.len() != ((uint64_t)k * n + 7) / 8 || c.len() != (uint64_t)m * n)
+        throw Error(QB200_ERR_LENGTH, "gemm_quant4: A must be ceil(m k / 8) words, B ceil(k n / 8), C m x n");
+    check(qb200_gemm_quant4((int)qty, m, n, k, alpha, a_scale, b_scale, a.data(), b.data(), beta, c.data(), st));
+}
+inline void gemv_quant(GemmQuantType qty, uint32_t m, uint32_t n, float alpha, float a_scale, float x_scale,
+                       const DeviceArray<int32_t>& a, const DeviceArray<int32_t>& x, float beta, DeviceArray<float>& y,
+                       cudaStream_t st = nullptr) {
+    gemm_quant(qty, m, 1, n, alpha, a_scale, x_scale, a, x, beta, y, st);
+}
+inline void gemv_quant4(GemmQuantType qty, uint32_t m, uint32_t n, float alpha, float a_scale, float x_scale,
+                        const DeviceArray<uint32_t>& a, const DeviceArray<uint32_t>& x, float beta, DeviceArray<float>& y,
+                        cudaStream_t st = nullptr) {
+    gemm_quant4(qty, m, 1, n, alpha, a_scale, x_scale, a, x, beta, y, st);
+}
+// Waits for the stream; throws for an int8 code out of range or a device wait that ran out.
+inline void gemm_quant_check(cudaStream_t st = nullptr) { check(qb200_gemm_quant_check(st)); }
+
 // quanta-nn/src/quant.rs:152-155: a named checkpoint leaf on the host side of save / load.
 struct QuantLeaf {
     bool quantized = false;

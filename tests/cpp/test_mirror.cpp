@@ -188,6 +188,58 @@ int main() {
                 EXPECT(std::fabs(got - want) <= 1e-2f * (1.0f + std::fabs(want)));
             }
         }
+        {
+            // quanta-blas/tests/gemm_quant.rs: the q8 "larger" and q4 "rectangular" cases against a plain f32 loop
+            // (reference.rs:104-131: codes cast to f32, left-to-right f32 sums, alpha_eff * acc + beta * c)
+            auto code = [](uint32_t i, uint32_t seed, uint32_t span) { return (int32_t)(((i * 2654435761u) ^ seed) % span) - (int32_t)(span / 2); };
+            const uint32_t m = 32, n = 24, k = 40;
+            std::vector<int32_t> a(m * k), b(k * n);
+            std::vector<float> c0(m * n);
+            for (uint32_t i = 0; i < m * k; i++) a[i] = code(i, 1, 64);
+            for (uint32_t i = 0; i < k * n; i++) b[i] = code(i, 2, 64);
+            for (uint32_t i = 0; i < m * n; i++) c0[i] = (float)i * 0.25f - 1.0f;
+            auto c = DeviceArray<float>::from_slice(c0, {m, n});
+            gemm_quant(GemmQuantType::Q8Symmetric, m, n, k, 1.0f, 0.02f, 0.03f, DeviceArray<int32_t>::from_slice(a, {m, k}),
+                       DeviceArray<int32_t>::from_slice(b, {k, n}), 0.5f, c);
+            gemm_quant_check();
+            auto got = c.to_vec();
+            const float ae = 1.0f * 0.02f * 0.03f;
+            for (uint32_t r = 0; r < m; r++)
+                for (uint32_t j = 0; j < n; j++) {
+                    float acc = 0.0f;
+                    for (uint32_t p = 0; p < k; p++) acc += (float)a[r * k + p] * (float)b[p * n + j];
+                    const float t1 = ae * acc, t2 = 0.5f * c0[r * n + j];
+                    EXPECT(got[r * n + j] == t1 + t2);
+                }
+            const uint32_t m4 = 3, n4 = 5, k4 = 7;  // k not a multiple of 8: rows start inside words
+            std::vector<int32_t> a4(m4 * k4), b4(k4 * n4);
+            for (uint32_t i = 0; i < m4 * k4; i++) a4[i] = code(i, 1, 16);
+            for (uint32_t i = 0; i < k4 * n4; i++) b4[i] = code(i, 2, 16);
+            auto pack = [](const std::vector<int32_t>& q) {
+                std::vector<uint32_t> w((q.size() + 7) / 8, 0u);
+                for (size_t i = 0; i < q.size(); i++) w[i / 8] |= ((uint32_t)q[i] & 0xFu) << (4 * (i % 8));
+                return w;
+            };
+            auto aw = pack(a4), bw = pack(b4);
+            DeviceArray<float> c4({m4, n4});
+            cuda_check(cudaMemset(c4.data(), 0, c4.bytes()), "cudaMemset");
+            gemm_quant4(GemmQuantType::Q4Symmetric, m4, n4, k4, 1.0f, 0.2f, 0.05f, DeviceArray<uint32_t>::from_slice(aw, {aw.size()}),
+                        DeviceArray<uint32_t>::from_slice(bw, {bw.size()}), 0.0f, c4);
+            gemm_quant_check();
+            auto got4 = c4.to_vec();
+            for (uint32_t r = 0; r < m4; r++)
+                for (uint32_t j = 0; j < n4; j++) {
+                    float acc = 0.0f;
+                    for (uint32_t p = 0; p < k4; p++) acc += (float)a4[r * k4 + p] * (float)b4[p * n4 + j];
+                    EXPECT(got4[r * n4 + j] == (1.0f * 0.2f * 0.05f) * acc);
+                }
+            bool threw = false;  // gemm_quant.rs:215-238: Q4 through the Q8 entry must error
+            try {
+                gemm_quant(GemmQuantType::Q4Symmetric, m, n, k, 1.0f, 0.1f, 0.1f, DeviceArray<int32_t>::from_slice(a, {m, k}),
+                           DeviceArray<int32_t>::from_slice(b, {k, n}), 0.0f, c);
+            } catch (const Error&) { threw = true; }
+            EXPECT(threw);
+        }
         auto act = swiglu(DeviceArray<float>::from_slice({-40.0f, -1.0f, 0.0f, 2.0f}, {1, 4}), DeviceArray<float>::from_slice({1, 1, 1, 1}, {1, 4})).to_vec();
         const float av[4] = {-40.0f, -1.0f, 0.0f, 2.0f};
         for (int i = 0; i < 4; i++) {
