@@ -266,6 +266,39 @@ __global__ void __launch_bounds__(256) k_dequant_chunks(const void* __restrict__
     __stcs(o + 1, b4);
 }
 
+// Fastest path: cols % 256 == 0 (and what the chunk path needs), sizes that fit 32 bits.  A warp takes 256
+// consecutive elements of a row per step: every store instruction writes 512 contiguous bytes (lane i the i-th
+// 16 bytes), the tile coordinates cost one 32-bit division per 256 elements, and nothing is 64-bit but the
+// element offset.
+template <int BITS>
+__global__ void __launch_bounds__(256) k_dequant_rows256(const void* __restrict__ codes, const float* __restrict__ scales,
+                                                          uint32_t rows, uint32_t cols, uint32_t gr, uint32_t gc, int gc_shift,
+                                                          uint32_t tc, float* __restrict__ out) {
+    const uint32_t lane = threadIdx.x & 31, segs = cols >> 8, items = rows * segs, warps = gridDim.x * 8;
+    for (uint32_t item = blockIdx.x * 8 + (threadIdx.x >> 5); item < items; item += warps) {
+        const uint32_t r = item / segs, seg = item - r * segs;
+        const float* srow = scales + (uint64_t)(r / gr) * tc;
+        const uint64_t e0 = (uint64_t)r * cols + seg * 256u;  // first element of the segment
+#pragma unroll
+        for (uint32_t k = 0; k < 2; k++) {
+            const uint32_t c = seg * 256u + k * 128u + lane * 4u;
+            const float s = __ldg(srow + (gc_shift >= 0 ? c >> gc_shift : c / gc));
+            int q[4];
+            if constexpr (BITS == 4) {
+                const uint32_t word = __ldcs(static_cast<const uint32_t*>(codes) + ((e0 + k * 128u) >> 3) + (lane >> 1));
+#pragma unroll
+                for (int j = 0; j < 4; j++) q[j] = int4_unpack(word, (lane & 1) * 4 + j);
+            } else {
+                const uint32_t word = __ldcs(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(codes) + e0 + k * 128u + lane * 4u));
+#pragma unroll
+                for (int j = 0; j < 4; j++) q[j] = (int)(int8_t)((word >> (8 * j)) & 0xFFu);
+            }
+            __stcs(reinterpret_cast<float4*>(out + e0 + k * 128u + lane * 4u),
+                   make_float4(dequantize_code(q[0], s), dequantize_code(q[1], s), dequantize_code(q[2], s), dequantize_code(q[3], s)));
+        }
+    }
+}
+
 template <int BITS>
 __global__ void k_dequant_generic(const void* __restrict__ codes, const float* __restrict__ scales,
                                   uint64_t rows, uint64_t cols, uint64_t gr, uint64_t gc, uint64_t tc,
@@ -398,7 +431,21 @@ qb200_status qb200_dequantize(const void* codes_dev, const float* scales_dev, ui
     const uint64_t tc = qb::div_ceil(cols, gc);
     const bool fast = cols % 8 == 0 && gc % 8 == 0 && qb::aligned16(out_dev) &&
                       (reinterpret_cast<uintptr_t>(codes_dev) & (bits == 4 ? 3u : 7u)) == 0;
-    if (fast) {
+    const bool fast256 = fast && cols % 256 == 0 && gc % 4 == 0 && rows * (cols / 256) < (1ull << 32) && cols < (1ull << 32) &&
+                         gr < (1ull << 32) && gc < (1ull << 32) && tc < (1ull << 32);
+    if (fast256) {
+        const uint64_t items = rows * (cols / 256), want = (items + 7) / 8;
+        const uint32_t grid = (uint32_t)(want < 148ull * 8 ? (want ? want : 1) : 148ull * 8);
+        int shift = -1;
+        if ((gc & (gc - 1)) == 0)
+            for (shift = 0; (1ull << shift) < gc; shift++) {}
+        if (bits == 4)
+            qb::k_dequant_rows256<4><<<grid, 256, 0, st>>>(codes_dev, scales_dev, (uint32_t)rows, (uint32_t)cols, (uint32_t)gr, (uint32_t)gc,
+                                                           shift, (uint32_t)tc, out_dev);
+        else
+            qb::k_dequant_rows256<8><<<grid, 256, 0, st>>>(codes_dev, scales_dev, (uint32_t)rows, (uint32_t)cols, (uint32_t)gr, (uint32_t)gc,
+                                                           shift, (uint32_t)tc, out_dev);
+    } else if (fast) {
         const uint64_t n = rows * (cols / 8), blocks = (n + 255) / 256;
         if (blocks > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "dequantize: matrix too large for one launch");
         if (bits == 4)

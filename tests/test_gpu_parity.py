@@ -490,3 +490,20 @@ def test_forward_many_host_pinned_and_pageable_outputs():
             one = one.pin_memory() if pinned else one
             assert lib.qb200_qlinear_forward_host(qls[0]._h, x.data_ptr(), _lib.BF16, M, one.data_ptr(), _lib.F32) == 0, _lib.last_error()
             assert torch.equal(one, qls[0].forward(x.to(DEV), out_dtype=torch.float32).cpu())
+
+
+@pytest.mark.parametrize("shape,dtype,gran", [
+    ((64, 256), qb.QuantDtype.Int4, qb.Group(1, 128)), ((96, 512), qb.QuantDtype.Int8, qb.Block(32, 32)),
+    ((33, 768), qb.QuantDtype.Int4, qb.Group(1, 96)), ((33, 768), qb.QuantDtype.Int8, qb.Group(1, 96)),
+    ((40, 1024), qb.QuantDtype.Int4, qb.PerTensor()), ((7, 256), qb.QuantDtype.Int8, qb.PerChannel(0)),
+    ((300, 2048), qb.QuantDtype.Int4, qb.Block(32, 32)),
+])
+def test_dequantize_row_segment_path_is_bit_exact(shape, dtype, gran):
+    # cols % 256 == 0: the kernel whose warps take 256 elements of a row per step; power-of-two and other tile widths
+    r, c = shape
+    w = np.random.default_rng(r + c).standard_normal(shape).astype(np.float32)
+    m, oc, os_ = quantize_both(w, r, c, dtype, gran)
+    gr, gc = gran.tile(r, c)
+    want = o.dequantize_host(oc, os_, r, c, dtype.bits(), gr, gc)
+    got = m.dequantize().cpu().numpy()
+    assert np.array_equal(bits(got), bits(want))
