@@ -205,6 +205,33 @@ def measure_extras(torch, qb, dev, only=None, small=False):
         torch.cuda.synchronize(dev)
         return e0.elapsed_time(e1) / iters
 
+    def timed_replay(fn, reps, iters=5):
+        """Device time of one `fn()`: `reps` calls captured into a CUDA graph, the graph replayed.  A quantize or
+        dequantize call is one 15 - 45 us kernel behind a Python wrapper whose own cost is of that order, so eager
+        calls leave the GPU idle between launches and would time the host."""
+        fn()
+        torch.cuda.synchronize(dev)
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(reps):
+                    fn()
+        except Exception:  # capture not possible: eager calls, host gaps included
+            torch.cuda.synchronize(dev)
+            return timed(fn, reps), "eager calls"
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / iters / reps
+        del g
+        return ms, f"cuda graph replay of {reps} calls"
+
     out = {}
     gen = torch.Generator(device=dev).manual_seed(2)
     M, N, K = (512, 2048, 4096) if small else (2048, 11008, 4096)
@@ -247,13 +274,14 @@ def measure_extras(torch, qb, dev, only=None, small=False):
                                       "peak_TFLOP/s": tf, "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}}
     for name, dt, gran, wbytes in [("quantize_int4_1x128", qb.QuantDtype.Int4, qb.Group(1, 128), N * K // 2 + N * (K // 128) * 4),
                                    ("quantize_int8_32x32", qb.QuantDtype.Int8, qb.Block(32, 32), N * K + (N // 32) * (K // 32) * 4)]:
-        ms = timed(lambda: qb.QuantizedMatrix.quantize(w, dt, gran), 10)
+        ms, how = timed_replay(lambda: qb.QuantizedMatrix.quantize(w, dt, gran), 10)
         out[name] = {"read_GB/s": N * K * 4 / ms / 1e6, "ms": ms, "roofline_frac": (N * K * 4 + wbytes) / ms / 1e6 / hbm,
-                     "shape": [N, K]}
+                     "shape": [N, K], "launch": how}
     qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
-    ms = timed(lambda: qm.dequantize(), 10)
+    ms, how = timed_replay(lambda: qm.dequantize(), 10)
     out["dequantize_int4_1x128"] = {"write_GB/s": N * K * 4 / ms / 1e6, "ms": ms,
-                                    "roofline_frac": (N * K * 4.5 + N * (K // 128) * 4) / ms / 1e6 / hbm, "shape": [N, K]}
+                                    "roofline_frac": (N * K * 4.5 + N * (K // 128) * 4) / ms / 1e6 / hbm, "shape": [N, K],
+                                    "launch": how}
     # quantize-on-load at the whole checkpoint's size: 32 x [4096, 4096] + 32 x [11008, 4096] f32 (7.92 GB read),
     # input resident in HBM, one quantize call per matrix
     try:
@@ -265,16 +293,10 @@ def measure_extras(torch, qb, dev, only=None, small=False):
             def run():
                 for t in mats:
                     qb.QuantizedMatrix.quantize(t, dt, gran)
-            run()
-            torch.cuda.synchronize(dev)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            run()
-            e1.record()
-            torch.cuda.synchronize(dev)
-            ms = e0.elapsed_time(e1)
+            ms, how = timed_replay(run, 1, iters=3)
             out["quantize_" + name] = {"read_GB/s": elems * 4 / ms / 1e6, "ms": ms, "matrices": len(mats), "read_bytes": elems * 4,
-                                       "roofline_frac": elems * (4 + per_elem) / ms / 1e6 / hbm}
+                                       "roofline_frac": elems * (4 + per_elem) / ms / 1e6 / hbm,
+                                       "launch": how.replace("1 calls", "the 64 quantize calls")}
         del mats
     except torch.OutOfMemoryError as e:  # a smaller device: report why the line is missing
         out["quantize_checkpoint"] = {"skipped": str(e)[:80]}

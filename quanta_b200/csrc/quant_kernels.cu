@@ -16,6 +16,7 @@
 // budget, or matrices whose rows are not 8-element aligned, take the three-pass
 // generic path (bit-pattern atomicMax into the scale grid, finalize, encode).
 #include <cstdint>
+#include <cstdlib>
 #include <string>
 
 #include "common.hpp"
@@ -267,34 +268,74 @@ __global__ void __launch_bounds__(256) k_dequant_chunks(const void* __restrict__
 }
 
 // Fastest path: cols % 256 == 0 (and what the chunk path needs), sizes that fit 32 bits.  A warp takes 256
-// consecutive elements of a row per step: every store instruction writes 512 contiguous bytes (lane i the i-th
-// 16 bytes), the tile coordinates cost one 32-bit division per 256 elements, and nothing is 64-bit but the
-// element offset.
+// consecutive elements of a row as one item: every store instruction writes 512 contiguous bytes (lane i the i-th
+// 16 bytes).  The kernel is bound by instruction issue, not by HBM, so the item loop is kept lean: the (row, segment)
+// pair advances incrementally (two divisions per warp, not per item), tile indices are shifts when the tile sizes
+// are powers of two, a lane's four int4 codes come out of its half-word with constant-position sign-extending bit
+// field extracts, and a warp issues the loads of four items before it converts and stores any of them.
 template <int BITS>
 __global__ void __launch_bounds__(256) k_dequant_rows256(const void* __restrict__ codes, const float* __restrict__ scales,
-                                                          uint32_t rows, uint32_t cols, uint32_t gr, uint32_t gc, int gc_shift,
-                                                          uint32_t tc, float* __restrict__ out) {
+                                                          uint32_t rows, uint32_t cols, uint32_t gr, uint32_t gc, int gr_shift,
+                                                          int gc_shift, uint32_t tc, float* __restrict__ out) {
+    constexpr uint32_t U = 4;
     const uint32_t lane = threadIdx.x & 31, segs = cols >> 8, items = rows * segs, warps = gridDim.x * 8;
-    for (uint32_t item = blockIdx.x * 8 + (threadIdx.x >> 5); item < items; item += warps) {
-        const uint32_t r = item / segs, seg = item - r * segs;
-        const float* srow = scales + (uint64_t)(r / gr) * tc;
-        const uint64_t e0 = (uint64_t)r * cols + seg * 256u;  // first element of the segment
+    const uint32_t step_r = warps / segs, step_s = warps - step_r * segs;  // how (row, segment) moves from item to item + warps
+    uint32_t item = blockIdx.x * 8 + (threadIdx.x >> 5);  // items < 2^31: item + U * warps cannot wrap
+    uint32_t r = item / segs, seg = item - r * segs;
+    const uint32_t lane_c = lane * 4u, lane_w = lane >> 1, half = (lane & 1u) * 16u;
+    while (item < items) {
+        uint32_t word[U][2];
+        float sc[U][2];
+        uint64_t e0[U];
+        bool ok[U];
 #pragma unroll
-        for (uint32_t k = 0; k < 2; k++) {
-            const uint32_t c = seg * 256u + k * 128u + lane * 4u;
-            const float s = __ldg(srow + (gc_shift >= 0 ? c >> gc_shift : c / gc));
-            int q[4];
-            if constexpr (BITS == 4) {
-                const uint32_t word = __ldcs(static_cast<const uint32_t*>(codes) + ((e0 + k * 128u) >> 3) + (lane >> 1));
+        for (uint32_t u = 0; u < U; u++) {
+            ok[u] = item < items;
+            if (ok[u]) {
+                const float* srow = scales + (uint64_t)(gr_shift >= 0 ? r >> gr_shift : r / gr) * tc;
+                e0[u] = (uint64_t)r * cols + seg * 256u;  // first element of the segment
 #pragma unroll
-                for (int j = 0; j < 4; j++) q[j] = int4_unpack(word, (lane & 1) * 4 + j);
-            } else {
-                const uint32_t word = __ldcs(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(codes) + e0 + k * 128u + lane * 4u));
-#pragma unroll
-                for (int j = 0; j < 4; j++) q[j] = (int)(int8_t)((word >> (8 * j)) & 0xFFu);
+                for (uint32_t k = 0; k < 2; k++) {
+                    const uint32_t c = seg * 256u + k * 128u + lane_c;
+                    sc[u][k] = __ldg(srow + (gc_shift >= 0 ? c >> gc_shift : c / gc));
+                    if constexpr (BITS == 4)
+                        word[u][k] = __ldcs(static_cast<const uint32_t*>(codes) + ((e0[u] >> 3) + k * 16u + lane_w));
+                    else
+                        word[u][k] = __ldcs(reinterpret_cast<const uint32_t*>(static_cast<const int8_t*>(codes) + e0[u] + k * 128u + lane_c));
+                }
             }
-            __stcs(reinterpret_cast<float4*>(out + e0 + k * 128u + lane * 4u),
-                   make_float4(dequantize_code(q[0], s), dequantize_code(q[1], s), dequantize_code(q[2], s), dequantize_code(q[3], s)));
+            item += warps;
+            seg += step_s;
+            r += step_r;
+            if (seg >= segs) {
+                seg -= segs;
+                r++;
+            }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < U; u++) {
+            if (ok[u]) {
+#pragma unroll
+                for (uint32_t k = 0; k < 2; k++) {
+                    int q0, q1, q2, q3;
+                    if constexpr (BITS == 4) {
+                        const uint32_t h = word[u][k] >> half;  // this lane's four nibbles in bits 0..15
+                        asm("bfe.s32 %0, %1, 0, 4;" : "=r"(q0) : "r"(h));
+                        asm("bfe.s32 %0, %1, 4, 4;" : "=r"(q1) : "r"(h));
+                        asm("bfe.s32 %0, %1, 8, 4;" : "=r"(q2) : "r"(h));
+                        asm("bfe.s32 %0, %1, 12, 4;" : "=r"(q3) : "r"(h));
+                    } else {
+                        const uint32_t w = word[u][k];
+                        asm("bfe.s32 %0, %1, 0, 8;" : "=r"(q0) : "r"(w));
+                        asm("bfe.s32 %0, %1, 8, 8;" : "=r"(q1) : "r"(w));
+                        asm("bfe.s32 %0, %1, 16, 8;" : "=r"(q2) : "r"(w));
+                        asm("bfe.s32 %0, %1, 24, 8;" : "=r"(q3) : "r"(w));
+                    }
+                    const float s = sc[u][k];
+                    __stcs(reinterpret_cast<float4*>(out + e0[u] + k * 128u + lane_c),
+                           make_float4(dequantize_code(q0, s), dequantize_code(q1, s), dequantize_code(q2, s), dequantize_code(q3, s)));
+                }
+            }
         }
     }
 }
@@ -431,20 +472,33 @@ qb200_status qb200_dequantize(const void* codes_dev, const float* scales_dev, ui
     const uint64_t tc = qb::div_ceil(cols, gc);
     const bool fast = cols % 8 == 0 && gc % 8 == 0 && qb::aligned16(out_dev) &&
                       (reinterpret_cast<uintptr_t>(codes_dev) & (bits == 4 ? 3u : 7u)) == 0;
-    const bool fast256 = fast && cols % 256 == 0 && gc % 4 == 0 && rows * (cols / 256) < (1ull << 32) && cols < (1ull << 32) &&
+    const bool fast256 = fast && cols % 256 == 0 && gc % 4 == 0 && rows * (cols / 256) < (1ull << 31) && cols < (1ull << 32) &&
                          gr < (1ull << 32) && gc < (1ull << 32) && tc < (1ull << 32);
     if (fast256) {
+        // exactly the blocks that are resident at once: a second, partial wave would leave SMs idle at the end
+        static int resident[2] = {0, 0};
+        int& res = resident[bits == 4 ? 0 : 1];
+        if (!res) {
+            int dev = 0, sms = 0, per_sm = 0;
+            QB_CUDA_TRY(cudaGetDevice(&dev));
+            QB_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            if (bits == 4) QB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qb::k_dequant_rows256<4>, 256, 0));
+            else QB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qb::k_dequant_rows256<8>, 256, 0));
+            res = sms * (per_sm > 0 ? per_sm : 1);
+        }
         const uint64_t items = rows * (cols / 256), want = (items + 7) / 8;
-        const uint32_t grid = (uint32_t)(want < 148ull * 8 ? (want ? want : 1) : 148ull * 8);
-        int shift = -1;
+        const uint32_t grid = (uint32_t)(want < (uint64_t)res ? (want ? want : 1) : (uint64_t)res);
+        int shift = -1, rshift = -1;  // tile sizes that are powers of two are indexed by shifts
         if ((gc & (gc - 1)) == 0)
             for (shift = 0; (1ull << shift) < gc; shift++) {}
+        if ((gr & (gr - 1)) == 0)
+            for (rshift = 0; (1ull << rshift) < gr; rshift++) {}
         if (bits == 4)
             qb::k_dequant_rows256<4><<<grid, 256, 0, st>>>(codes_dev, scales_dev, (uint32_t)rows, (uint32_t)cols, (uint32_t)gr, (uint32_t)gc,
-                                                           shift, (uint32_t)tc, out_dev);
+                                                           rshift, shift, (uint32_t)tc, out_dev);
         else
             qb::k_dequant_rows256<8><<<grid, 256, 0, st>>>(codes_dev, scales_dev, (uint32_t)rows, (uint32_t)cols, (uint32_t)gr, (uint32_t)gc,
-                                                           shift, (uint32_t)tc, out_dev);
+                                                           rshift, shift, (uint32_t)tc, out_dev);
     } else if (fast) {
         const uint64_t n = rows * (cols / 8), blocks = (n + 255) / 256;
         if (blocks > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "dequantize: matrix too large for one launch");
