@@ -507,3 +507,24 @@ def test_dequantize_row_segment_path_is_bit_exact(shape, dtype, gran):
     want = o.dequantize_host(oc, os_, r, c, dtype.bits(), gr, gc)
     got = m.dequantize().cpu().numpy()
     assert np.array_equal(bits(got), bits(want))
+
+
+@pytest.mark.parametrize("shape,dtype,gran", [
+    ((64, 4096), qb.QuantDtype.Int8, qb.PerChannel(0)), ((64, 4096), qb.QuantDtype.Int4, qb.PerChannel(0)),
+    ((300, 512), qb.QuantDtype.Int8, qb.PerTensor()), ((300, 512), qb.QuantDtype.Int4, qb.PerTensor()),
+    ((130, 192), qb.QuantDtype.Int4, qb.Block(64, 64)), ((9, 2056), qb.QuantDtype.Int8, qb.Group(1, 2056)),
+])
+def test_quantize_large_tiles_chunk_path_is_bit_exact(shape, dtype, gran):
+    # tiles of more than 2048 elements (whole rows, the whole matrix, big blocks): the two-pass chunk kernels
+    r, c = shape
+    w = (np.random.default_rng(r * c).standard_normal(shape) * 0.05).astype(np.float32)
+    w[1, 8] = np.nan
+    w[2, 16] = -3.75  # the tile's (or a tile's) maximum
+    m, oc, os_ = quantize_both(w, r, c, dtype, gran)
+    assert_quant_equal(m, oc, os_)
+    # bf16 source through the same path
+    wb = o.f32_to_bf16(w)
+    mb = qb.QuantizedMatrix.quantize(torch.from_numpy(wb.view(np.int16)).view(torch.bfloat16).to(DEV), dtype, gran)
+    gr, gc = gran.tile(r, c)
+    oc2, os2 = o.quantize_host(o.bf16_to_f32(wb), r, c, dtype.bits(), gr, gc)
+    assert_quant_equal(mb, oc2, os2)
