@@ -372,7 +372,9 @@ QB200_API qb200_status qb200_gemv_quant4(int qty, uint32_t m, uint32_t n, float 
                                          void* stream);
 /* Waits for `stream` and reports what the quantized BLAS kernels launched on it recorded since the last
  * check: QB200_ERR_INVALID_PARAM for an int8 code out of range, QB200_ERR_TIMEOUT for a bounded wait that
- * ran out.  The packed operands live in a buffer per (device, stream) that grows on demand and is reused. */
+ * ran out.  The packed operands live in a buffer per (device, stream) that grows on demand and is reused; growing it
+ * allocates and synchronises, so a caller that captures these entries into a CUDA graph runs the largest shape once
+ * on that stream before the capture. */
 QB200_API qb200_status qb200_gemm_quant_check(void* stream);
 
 #ifdef __cplusplus
