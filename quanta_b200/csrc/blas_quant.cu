@@ -61,21 +61,36 @@ __device__ __forceinline__ int32_t bq_code(const void* p, uint64_t idx, int32_t&
     return (int32_t)(w << (28 - 4 * (uint32_t)(idx & 7))) >> 28;
 }
 
-// A [rows, k] codes -> int8 [rows, kp], zero beyond k.  One thread per four output bytes.
+// A [rows, k] codes -> int8 [rows, kp], zero beyond k.  One thread per sixteen output bytes: four 16-byte loads of
+// i32 codes in flight per thread where the row allows it (int8 codes, k % 4 == 0, aligned base), scalar reads at
+// the ragged end of a row and for int4 codes; one block round per thread.
 template <int BITS>
-__global__ void k_pack_rows(const void* __restrict__ src, uint32_t rows, uint32_t k, uint32_t kp, uint32_t* __restrict__ dst,
-                            int32_t* status) {
-    const uint64_t words_per_row = kp >> 2, total = (uint64_t)rows * words_per_row;
+__global__ void __launch_bounds__(256) k_pack_rows(const void* __restrict__ src, uint32_t rows, uint32_t k, uint32_t kp,
+                                                    uint4* __restrict__ dst, int32_t* status, int vec_ok) {
+    const uint64_t units_per_row = kp >> 4, total = (uint64_t)rows * units_per_row;
+    const uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (i >= total) return;
     int32_t flag = 0;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t r = i / words_per_row;
-        const uint32_t c0 = (uint32_t)(i - r * words_per_row) * 4;
-        uint32_t out = 0;
+    const uint64_t r = i / units_per_row;
+    const uint32_t c0 = (uint32_t)(i - r * units_per_row) * 16;
+    uint32_t out[4] = {0, 0, 0, 0};
+    if (BITS == 8 && vec_ok && c0 + 16 <= k) {
+        const int4* p = reinterpret_cast<const int4*>(static_cast<const int32_t*>(src) + r * k + c0);
+        int4 v[4];
 #pragma unroll
-        for (uint32_t j = 0; j < 4; j++)
-            if (c0 + j < k) out |= ((uint32_t)bq_code<BITS>(src, r * k + c0 + j, flag) & 0xFFu) << (8 * j);
-        dst[i] = out;
+        for (int j = 0; j < 4; j++) v[j] = __ldcs(p + j);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int32_t lo = min(min(v[j].x, v[j].y), min(v[j].z, v[j].w)), hi = max(max(v[j].x, v[j].y), max(v[j].z, v[j].w));
+            if (lo < -128 || hi > 127) flag = BQ_FLAG_RANGE;
+            out[j] = ((uint32_t)v[j].x & 0xFFu) | (((uint32_t)v[j].y & 0xFFu) << 8) | (((uint32_t)v[j].z & 0xFFu) << 16) | ((uint32_t)v[j].w << 24);
+        }
+    } else {
+#pragma unroll
+        for (uint32_t j = 0; j < 16; j++)
+            if (c0 + j < k) out[j >> 2] |= ((uint32_t)bq_code<BITS>(src, r * k + c0 + j, flag) & 0xFFu) << (8 * (j & 3));
     }
+    dst[i] = make_uint4(out[0], out[1], out[2], out[3]);
     if (flag) atomicOr(status, flag);
 }
 
@@ -476,9 +491,10 @@ static qb200_status bq_run(const char* who, uint32_t m, uint32_t n, uint32_t k, 
     uint8_t* a8 = ws + a_off;
     uint8_t* b8 = ws + b_off;
     {
-        const uint64_t words = (uint64_t)m * (kp >> 2);
-        const uint32_t grid = (uint32_t)(words / 256 + 1 < 148u * 16 ? words / 256 + 1 : 148u * 16);
-        k_pack_rows<BITS><<<grid, 256, 0, st>>>(a, m, k, kp, reinterpret_cast<uint32_t*>(a8), status);
+        const uint64_t units = (uint64_t)m * (kp >> 4), blocks = (units + 255) / 256;
+        if (blocks > 0x7FFFFFFFull) return fail(QB200_ERR_NOT_SUPPORTED, std::string(who) + ": A is too large for one launch");
+        const int vec_ok = (k % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0) ? 1 : 0;
+        k_pack_rows<BITS><<<(uint32_t)blocks, 256, 0, st>>>(a, m, k, kp, reinterpret_cast<uint4*>(a8), status, vec_ok);
         QB_CUDA_TRY(cudaGetLastError());
         k_pack_cols<BITS><<<dim3((n + 31) / 32, kp / 128), 256, 0, st>>>(b, k, n, kp, b8, status);
         QB_CUDA_TRY(cudaGetLastError());
