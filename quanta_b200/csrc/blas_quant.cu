@@ -95,27 +95,40 @@ __global__ void __launch_bounds__(256) k_pack_rows(const void* __restrict__ src,
 }
 
 // B [k, n] codes -> int8 [n, kp] (transposed), zero beyond k.  A block moves a 128 (k) x 32 (n) tile through
-// shared memory: reads run along n; a thread packs four consecutive k of its column into one word and parks it at
-// [n][k / 4] (pitch 33 words: no bank conflicts either way); writes are 16 bytes along k.
+// shared memory.  A thread owns four consecutive k of four consecutive n: four 16-byte loads along n (int8 codes,
+// n % 4 == 0, aligned base; scalar reads otherwise), four words of four packed k each, parked at [n][k / 4]
+// (pitch 33 words: no bank conflicts either way); writes are 16 bytes along k.
 template <int BITS>
 __global__ void __launch_bounds__(256) k_pack_cols(const void* __restrict__ src, uint32_t k, uint32_t n, uint32_t kp,
-                                                    uint8_t* __restrict__ dst, int32_t* status) {
+                                                    uint8_t* __restrict__ dst, int32_t* status, int vec_ok) {
     __shared__ uint32_t tile[32][33];
     const uint32_t n0 = blockIdx.x * 32, k0 = blockIdx.y * 128;
-    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const uint32_t nq = threadIdx.x & 7, q = threadIdx.x >> 3;  // columns n0 + 4 nq .. + 3, rows k0 + 4 q .. + 3
+    const uint32_t nn = n0 + 4 * nq, kk = k0 + 4 * q;
     int32_t flag = 0;
-    int32_t v[4][4];
+    int32_t v[4][4];  // [k][n]
+    if (BITS == 8 && vec_ok && nn + 4 <= n && kk + 4 <= k) {
+        const int32_t* p = static_cast<const int32_t*>(src) + (uint64_t)kk * n + nn;
+        int4 r[4];
 #pragma unroll
-    for (uint32_t i = 0; i < 4; i++)  // word q = ty + 8 i of the column: k = k0 + 4 q .. + 3
+        for (int j = 0; j < 4; j++) r[j] = __ldcs(reinterpret_cast<const int4*>(p + (uint64_t)j * n));
 #pragma unroll
-        for (uint32_t j = 0; j < 4; j++) {
-            const uint32_t kk = k0 + 4 * (ty + 8 * i) + j;
-            v[i][j] = (kk < k && n0 + tx < n) ? bq_code<BITS>(src, (uint64_t)kk * n + n0 + tx, flag) : 0;
+        for (int j = 0; j < 4; j++) {
+            v[j][0] = r[j].x; v[j][1] = r[j].y; v[j][2] = r[j].z; v[j][3] = r[j].w;
+            const int32_t lo = min(min(r[j].x, r[j].y), min(r[j].z, r[j].w)), hi = max(max(r[j].x, r[j].y), max(r[j].z, r[j].w));
+            if (lo < -128 || hi > 127) flag = BQ_FLAG_RANGE;
         }
+    } else {
 #pragma unroll
-    for (uint32_t i = 0; i < 4; i++)
-        tile[tx][ty + 8 * i] = ((uint32_t)v[i][0] & 0xFFu) | (((uint32_t)v[i][1] & 0xFFu) << 8) | (((uint32_t)v[i][2] & 0xFFu) << 16) |
-                               ((uint32_t)v[i][3] << 24);
+        for (uint32_t j = 0; j < 4; j++)
+#pragma unroll
+            for (uint32_t e = 0; e < 4; e++)
+                v[j][e] = (kk + j < k && nn + e < n) ? bq_code<BITS>(src, (uint64_t)(kk + j) * n + nn + e, flag) : 0;
+    }
+#pragma unroll
+    for (uint32_t e = 0; e < 4; e++)
+        tile[4 * nq + e][q] = ((uint32_t)v[0][e] & 0xFFu) | (((uint32_t)v[1][e] & 0xFFu) << 8) | (((uint32_t)v[2][e] & 0xFFu) << 16) |
+                              ((uint32_t)v[3][e] << 24);
     __syncthreads();
     const uint32_t row = threadIdx.x >> 3, chunk = threadIdx.x & 7;  // 32 rows of n, eight 16-byte pieces of k each
     if (n0 + row < n)
@@ -496,7 +509,8 @@ static qb200_status bq_run(const char* who, uint32_t m, uint32_t n, uint32_t k, 
         const int vec_ok = (k % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0) ? 1 : 0;
         k_pack_rows<BITS><<<(uint32_t)blocks, 256, 0, st>>>(a, m, k, kp, reinterpret_cast<uint4*>(a8), status, vec_ok);
         QB_CUDA_TRY(cudaGetLastError());
-        k_pack_cols<BITS><<<dim3((n + 31) / 32, kp / 128), 256, 0, st>>>(b, k, n, kp, b8, status);
+        const int bvec_ok = (n % 4 == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0) ? 1 : 0;
+        k_pack_cols<BITS><<<dim3((n + 31) / 32, kp / 128), 256, 0, st>>>(b, k, n, kp, b8, status, bvec_ok);
         QB_CUDA_TRY(cudaGetLastError());
     }
     CUtensorMap amap, bmap;
