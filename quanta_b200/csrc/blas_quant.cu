@@ -151,15 +151,22 @@ __global__ void __launch_bounds__(256) k_gemv_q(const void* __restrict__ a, cons
         if ((k & 3) == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
             int32_t part = 0;  // at most k / 32 products of at most 2^14 each per lane before the fold below
             uint32_t since = 0;
-            for (uint32_t p = lane * 4; p < k; p += 128) {
-                const int4 av = *reinterpret_cast<const int4*>(ar + p);
-                const int4 xv = __ldg(reinterpret_cast<const int4*>(xs + p));
+            auto step = [&](const int4& av, const int4& xv) {
                 const int32_t lo = min(min(av.x, av.y), min(av.z, av.w)), hi = max(max(av.x, av.y), max(av.z, av.w));
                 const int32_t xlo = min(min(xv.x, xv.y), min(xv.z, xv.w)), xhi = max(max(xv.x, xv.y), max(xv.z, xv.w));
                 if (lo < -128 || hi > 127 || xlo < -128 || xhi > 127) flag = BQ_FLAG_RANGE;
                 part += av.x * xv.x + av.y * xv.y + av.z * xv.z + av.w * xv.w;
                 if (++since == 8192) { acc += part; part = 0; since = 0; }
+            };
+            uint32_t p = lane * 4;
+            for (; p + 384 < k; p += 512) {  // four 16-byte loads of A's codes in flight per lane
+                int4 av[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) av[u] = __ldcs(reinterpret_cast<const int4*>(ar + p + u * 128));
+#pragma unroll
+                for (int u = 0; u < 4; u++) step(av[u], __ldg(reinterpret_cast<const int4*>(xs + p + u * 128)));
             }
+            for (; p < k; p += 128) step(*reinterpret_cast<const int4*>(ar + p), __ldg(reinterpret_cast<const int4*>(xs + p)));
             acc += part;
         } else {
             for (uint32_t p = lane; p < k; p += 32)
