@@ -28,16 +28,17 @@ enum SrcType { SRC_F32 = 0, SRC_BF16 = 1, SRC_F16 = 2 };
 
 // ---- 8-element chunk loads --------------------------------------------------
 
-template <int SRC>
+// KEEP: the caller reads the chunk again soon, so it is loaded with the default policy instead of as a stream.
+template <int SRC, bool KEEP = false>
 __device__ __forceinline__ void load_chunk8(const void* base, uint64_t elem, float (&v)[8]) {
     if constexpr (SRC == SRC_F32) {
         const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem);
-        float4 a = __ldcs(p), b = __ldcs(p + 1);
+        float4 a = KEEP ? __ldg(p) : __ldcs(p), b = KEEP ? __ldg(p + 1) : __ldcs(p + 1);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     } else {
         const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + elem);
-        uint4 a = __ldcs(p);
+        uint4 a = KEEP ? __ldg(p) : __ldcs(p);
         uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -286,6 +287,62 @@ __global__ void __launch_bounds__(256) k_encode_chunks(const void* __restrict__ 
     }
 }
 
+// Whole-row tiles (per-channel scales along the rows, gr == 1 and gc == cols, rows longer than 2048 elements): one
+// warp per row reads the row twice, first for its max |w|, then to encode it.  The second read comes back from L2
+// (a row is a few KB and was just read), so W crosses HBM once.
+template <int SRC, int BITS>
+__global__ void __launch_bounds__(256) k_quantize_rows(const void* __restrict__ w, uint32_t rows, uint32_t cols,
+                                                        void* __restrict__ codes, float* __restrict__ scales) {
+    constexpr int HI = BITS == 8 ? 127 : 7;
+    constexpr int LO = -HI - 1;
+    const uint32_t lane = threadIdx.x & 31, row = blockIdx.x * 8 + (threadIdx.x >> 5), cpr = cols >> 3;
+    if (row >= rows) return;
+    const uint64_t base = (uint64_t)row * cols;
+    float m = 0.0f;
+    uint32_t ch = lane;
+    for (; ch + 96 < cpr; ch += 128) {  // four chunks (128 B of f32) in flight per lane
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; u++) load_chunk8<SRC, true>(w, base + (uint64_t)(ch + 32 * u) * 8, v[u]);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) m = max_abs_ignoring_nan(m, v[u][j]);
+    }
+    for (; ch < cpr; ch += 32) {
+        float v[8];
+        load_chunk8<SRC, true>(w, base + (uint64_t)ch * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; j++) m = max_abs_ignoring_nan(m, v[j]);
+    }
+#pragma unroll
+    for (uint32_t o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    const float s = scale_from_maxabs(m, HI);
+    if (lane == 0) scales[row] = s;
+    const bool fast = s >= 7.888609052210118e-31f && s <= 1.2676506002282294e30f;  // [2^-100, 2^100]
+    const float rinv = __frcp_rn(s);
+    auto encode = [&](uint32_t c, const float (&v)[8]) {
+        float q[8];
+        quantize_chunk8(v, s, rinv, fast, LO, HI, q);
+        const uint64_t pos = base + (uint64_t)c * 8;
+        if constexpr (BITS == 4) static_cast<uint32_t*>(codes)[pos >> 3] = pack_int4x8(q);  // cols % 8 == 0
+        else *reinterpret_cast<uint2*>(static_cast<int8_t*>(codes) + pos) = pack_int8x8(q);
+    };
+    ch = lane;
+    for (; ch + 96 < cpr; ch += 128) {
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; u++) load_chunk8<SRC>(w, base + (uint64_t)(ch + 32 * u) * 8, v[u]);
+#pragma unroll
+        for (int u = 0; u < 4; u++) encode(ch + 32 * u, v[u]);
+    }
+    for (; ch < cpr; ch += 32) {
+        float v[8];
+        load_chunk8<SRC>(w, base + (uint64_t)ch * 8, v);
+        encode(ch, v);
+    }
+}
+
 // ---- dequantize -------------------------------------------------------------
 
 // Fast path: cols % 8 == 0 and gc % 8 == 0, so one scale covers a chunk of 8.
@@ -490,6 +547,11 @@ static qb200_status quantize_typed(const void* w, uint64_t rows, uint64_t cols, 
         return launch_tiles<SRC, BITS>(w, g, codes, scales, st);
     }
     const int hi = BITS == 8 ? 127 : 7;
+    if (gr == 1 && gc == cols && cols % 8 == 0 && src_ok && dst_ok && rows < (1ull << 31) && cols < (1ull << 32)) {
+        k_quantize_rows<SRC, BITS><<<(uint32_t)((rows + 7) / 8), 256, 0, st>>>(w, (uint32_t)rows, (uint32_t)cols, codes, scales);
+        QB_CUDA_TRY(cudaGetLastError());
+        return QB200_OK;
+    }
     if (cols % 8 == 0 && gc % 8 == 0 && src_ok && dst_ok && rows * (cols / 8) < (1ull << 31) && tr * tc < (1ull << 32) &&
         gr < (1ull << 32) && gc < (1ull << 32)) {
         // large tiles: absmax, scales, encode over 8-element chunks
