@@ -53,6 +53,80 @@ __global__ void __launch_bounds__(256) k_forward_rows(FwdArgs a) {
     const XT* x = static_cast<const XT*>(a.x);
     const uint64_t srow = (n / a.gr) * tc;
     const bool chunk_scale = (a.gc & 7u) == 0;
+    // Aligned case (K % 8 == 0, one scale per chunk, 16-byte aligned activations, 8-byte aligned int8 codes, 32-bit
+    // sizes): codes and activations come in 8- and 16-byte loads, four chunks of codes in flight per lane, indices
+    // in 32 bits.  The arithmetic and its order are those of the general loop below, so the results are the same bits.
+    const bool vec = chunk_scale && (K & 7u) == 0 && K < (1ull << 32) && a.gc < (1ull << 32) &&
+                     (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.codes) & 7u) == 0;
+    if (vec) {
+        const uint32_t K32 = (uint32_t)K, gc32 = (uint32_t)a.gc, cpr = K32 >> 3;
+        const float* srow_p = a.scales + srow;
+        for (uint64_t m0 = (uint64_t)blockIdx.y * MT; m0 < a.m; m0 += (uint64_t)gridDim.y * MT) {
+            float acc[MT];
+#pragma unroll
+            for (int i = 0; i < MT; i++) acc[i] = 0.0f;
+            for (uint32_t c0 = lane; c0 < cpr; c0 += 128) {
+                uint2 cw[4];
+#pragma unroll
+                for (uint32_t u = 0; u < 4; u++) {
+                    const uint32_t ch = c0 + 32 * u;
+                    cw[u] = make_uint2(0u, 0u);
+                    if (ch < cpr) {
+                        if constexpr (BITS == 4) cw[u].x = __ldg(static_cast<const uint32_t*>(a.codes) + n * cpr + ch);
+                        else cw[u] = __ldg(reinterpret_cast<const uint2*>(static_cast<const int8_t*>(a.codes) + n * K + ((uint64_t)ch << 3)));
+                    }
+                }
+#pragma unroll
+                for (uint32_t u = 0; u < 4; u++) {
+                    const uint32_t ch = c0 + 32 * u;
+                    if (ch >= cpr) break;
+                    const uint32_t k0 = ch << 3;
+                    const float s = __ldg(srow_p + k0 / gc32);
+                    float wv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        int q;
+                        if constexpr (BITS == 4) q = int4_unpack(cw[u].x, j);
+                        else q = (int)(int8_t)(((j < 4 ? cw[u].x : cw[u].y) >> (8 * (j & 3))) & 0xFFu);
+                        wv[j] = s * (float)q;
+                    }
+#pragma unroll
+                    for (int i = 0; i < MT; i++) {
+                        if (m0 + i < a.m) {
+                            float xf[8];
+                            if constexpr (sizeof(XT) == 2) {
+                                const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (m0 + i) * K + k0));
+                                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) {
+                                    xf[2 * j] = bf16_bits_to_f32(xw[j] & 0xFFFFu);
+                                    xf[2 * j + 1] = bf16_bits_to_f32(xw[j] >> 16);
+                                }
+                            } else {
+                                const float4* xp = reinterpret_cast<const float4*>(x + (m0 + i) * K + k0);
+                                const float4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                                xf[0] = x0.x; xf[1] = x0.y; xf[2] = x0.z; xf[3] = x0.w;
+                                xf[4] = x1.x; xf[5] = x1.y; xf[6] = x1.z; xf[7] = x1.w;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; j++) acc[i] = fmaf(xf[j], wv[j], acc[i]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+                float v = acc[i];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+                if (lane == 0 && m0 + i < a.m) {
+                    if (a.bias) v += a.bias[n];
+                    store_out<YT>(static_cast<YT*>(a.y) + (m0 + i) * a.out_dim + n, v);
+                }
+            }
+        }
+        return;
+    }
     for (uint64_t m0 = (uint64_t)blockIdx.y * MT; m0 < a.m; m0 += (uint64_t)gridDim.y * MT) {
         float acc[MT];
 #pragma unroll
