@@ -233,7 +233,7 @@ QB200_API qb200_status qb200_sum_arrays(const float* parts, uint32_t count, uint
  * element into EVERY rank's buffer (plain stores to peer memory over NVLink, no collective):
  * y_own[i] points into this rank's own buffer, gather_bases[p] is rank p's buffer as mapped in this
  * process (gather_bases[rank] the own one), and the element goes to y_own[i] + (gather_bases[p] -
- * gather_bases[rank]) for every p.  Decode shapes only (int4, grid 1x128, [out, in], bf16 x, m <= 8,
+ * gather_bases[rank]) for every p.  Decode shapes only (int4, grid 1x128, [out, in], bf16 x, m <= 16,
  * in <= 4096), else QB200_ERR_NOT_SUPPORTED.  The arrival barrier — "this rank's outputs of this step
  * are written" published to every peer, then a wait for theirs, bounded to about a second — runs inside
  * the same launch when flag_arrays is given (its last CTA does it; a timeout lands in layers[0]'s status
@@ -251,6 +251,9 @@ QB200_API qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* l
                                                void* stream);
 QB200_API qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint32_t world, uint32_t rank,
                                     int32_t* status_dev, void* stream);
+/* Polls (about a quarter of a microsecond each) that an arrival barrier spends on one peer's flag before it
+ * gives up with QB200_ERR_TIMEOUT; process-wide, read at launch time, default 4 Mi (about a second). */
+QB200_API qb200_status qb200_peer_set_spin_limit(uint32_t polls);
 
 /* qb200_qlinear_forward_many over HOST buffers: every distinct input pointer is
  * copied to the device once, the forwards run, all outputs are copied back and
@@ -264,7 +267,8 @@ QB200_API qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* lay
 
 /* Synchronises `stream` and reads the handle's device status word: kernels whose
  * bounded waits (on an async copy) ran out of polls record QB200_ERR_TIMEOUT there
- * and return early instead of spinning.  No counterpart in the reference (its
+ * and return early instead of spinning.  A recorded error is reported once and the word is cleared.
+ * No counterpart in the reference (its
  * error taxonomy names Timeout, crates/gpu/quanta-core/src/api/error.rs:29-60). */
 QB200_API qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream);
 

@@ -63,6 +63,7 @@ SIGNATURES = {
     "qb200_peer_free": (i32, [vp]),
     "qb200_qlinear_forward_many_gather": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32, P(vp), P(vp), u32, u32, vp]),
     "qb200_peer_signal_wait": (i32, [P(vp), u32, u32, vp, vp]),
+    "qb200_peer_set_spin_limit": (i32, [u32]),
     "qb200_qlinear_check": (i32, [vp, vp]),
     "qb200_gemm_quant": (i32, [i32, u32, u32, u32, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, ctypes.c_float, vp, vp]),
     "qb200_gemm_quant4": (i32, [i32, u32, u32, u32, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, ctypes.c_float, vp, vp]),

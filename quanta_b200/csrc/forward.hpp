@@ -35,6 +35,8 @@ struct PeerSpec {
     uint64_t* flags[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint32_t rank = 0;
 };
+// Polls of a peer's arrival flag (about 0.25 us each) before a barrier gives up with QB200_ERR_TIMEOUT (peers.cu).
+uint32_t peer_spin_limit();
 #ifdef __CUDACC__
 // QB200_ERR_NOT_SUPPORTED (no message) when no launch plan fits the shape.
 qb200_status gemv_i4_forward(const FwdArgs& a, int y_dtype, int32_t* status, cudaStream_t st);

@@ -55,6 +55,8 @@ struct GemvBatch {
     uint32_t count, total_items, M, K, stages;
     uint32_t async_scales;  // scales are not 16-byte aligned slabs: copy them element-wise
     uint32_t red_cols;      // batch columns kept per row of partial sums (kernels with a service warp)
+    uint32_t red_stride;    // floats between rows of a slot of partial sums (>= red_cols)
+    uint32_t peer_spin_limit;  // polls of a peer's arrival flag before the barrier gives up
     uint32_t n_peers;       // fused all-gather: every output is stored at y + peer_delta[p], p < n_peers (0: plain store)
     int64_t peer_delta[8];
     uint64_t* peer_flags[8];  // every rank's barrier state as mapped here (null: the caller runs the barrier itself)
@@ -407,7 +409,7 @@ static qb200_status launch_gemv_async(const GemvBatch& b, uint32_t smem, uint32_
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
-    cfg.blockDim = dim3(ASYNC_THREADS);
+    cfg.blockDim = dim3(async_threads(NT));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -555,6 +557,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             b.peer_flags[p] = peers ? peers->flags[p] : nullptr;
         }
         b.rank = peers ? peers->rank : 0;
+        b.peer_spin_limit = peer_spin_limit();
         b.count = n;
         b.total_items = items;
         b.M = M;
@@ -562,25 +565,40 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
         uint32_t ctas = items < 148 ? items : 148;
         if (reg_path && (items + 147) / 148 <= REG_MAX_ITEMS) {  // activation fragments stay in registers
             const uint32_t nt = M <= 8 ? 1 : 2;
-            uint32_t occ = (nt == 1 && rb == 1) ? 2 : 1;
-            ctas = items < 148 * occ ? items : 148 * occ;
-            // the kernel with a service warp (nt == 1, rb == 2) keeps only the batch's columns of the
-            // partial sums, which for a single row frees the room of one more 68 KB stage
-            const bool service = nt == 1 && rb == 2;
+            // The kernel with a service warp serves 32-row items and every batch above 8; a lone layer with a
+            // small batch keeps 16-row items on the kernel whose warps fold together (two CTAs per SM).
+            static const bool exp_async11 = getenv("QB200_EXP_ASYNC11") != nullptr;  // EXPERIMENT
+            const bool service = nt == 2 || rb == 2 || exp_async11;
             if (peers && !service) return QB200_ERR_NOT_SUPPORTED;  // only the service warp stores to peers
-            b.red_cols = service ? (M <= 2 ? 2 : M <= 4 ? 4 : 8) : 0;
-            const uint32_t per_cta = (items + ctas - 1) / ctas, budget = (occ == 2 ? 113u : service ? 227u : 200u) * 1024;
-            uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
-            while (stages > 2 && reg_smem_layout(K, nt, rb, stages, b.red_cols).total > budget) stages--;
-            b.stages = stages;
-            const uint32_t smem = reg_smem_layout(K, nt, rb, stages, b.red_cols).total;
             qb200_status r;
-#define QB_LAUNCH(YT)                                                                                          \
-    (nt == 2 ? (rb == 2 ? launch_gemv_reg<2, 2, 1, YT>(b, smem, ctas, st) : launch_gemv_reg<2, 1, 1, YT>(b, smem, ctas, st)) \
-             : rb == 2 ? launch_gemv_async<1, 2, YT>(b, smem, ctas, st)                                     \
-                       : (occ == 2 ? launch_gemv_reg<1, 1, 2, YT>(b, smem, ctas, st) : launch_gemv_reg<1, 1, 1, YT>(b, smem, ctas, st)))
-            r = y_dtype == QB200_F32 ? QB_LAUNCH(float) : QB_LAUNCH(uint16_t);
+            if (service) {
+                // slots of partial sums keep only the batch's columns, which for a single row frees the room of
+                // one more 68 KB stage; 16-row sub-items (nt == 2) pad their rows against bank conflicts
+                b.red_cols = M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : (M + 1) & ~1u;
+                b.red_stride = nt == 2 ? async_red_stride(b.red_cols) : b.red_cols;
+                const uint32_t sub_rows = nt == 2 ? 16 : rb * 16;
+                ctas = items < 148 ? items : 148;
+                const uint32_t per_cta = (items + ctas - 1) / ctas;
+                uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
+                while (stages > 2 && async_smem_layout(K, rb, sub_rows, b.red_stride, stages).total > 227u * 1024) stages--;
+                b.stages = stages;
+                const uint32_t smem = async_smem_layout(K, rb, sub_rows, b.red_stride, stages).total;
+                if (smem > 227u * 1024) return QB200_ERR_NOT_SUPPORTED;
+#define QB_LAUNCH(YT)                                                                                        \
+    (nt == 2 ? (rb == 2 ? launch_gemv_async<2, 2, YT>(b, smem, ctas, st) : launch_gemv_async<2, 1, YT>(b, smem, ctas, st)) \
+             : (rb == 2 ? launch_gemv_async<1, 2, YT>(b, smem, ctas, st) : launch_gemv_async<1, 1, YT>(b, smem, ctas, st)))
+                r = y_dtype == QB200_F32 ? QB_LAUNCH(float) : QB_LAUNCH(uint16_t);
 #undef QB_LAUNCH
+            } else {
+                const uint32_t occ = 2;
+                ctas = items < 148 * occ ? items : 148 * occ;
+                const uint32_t per_cta = (items + ctas - 1) / ctas, budget = 113u * 1024;
+                uint32_t stages = per_cta < 2 ? 2 : (per_cta > 5 ? 5 : per_cta);
+                while (stages > 2 && reg_smem_layout(K, 1, 1, stages).total > budget) stages--;
+                b.stages = stages;
+                r = y_dtype == QB200_F32 ? launch_gemv_reg<1, 1, 2, float>(b, reg_smem_layout(K, 1, 1, stages).total, ctas, st)
+                                         : launch_gemv_reg<1, 1, 2, uint16_t>(b, reg_smem_layout(K, 1, 1, stages).total, ctas, st);
+            }
             if (r) return r;
             continue;
         }

@@ -6,11 +6,46 @@
 // output and stores.  The kernel is bound by the latency of each warp's own chain (copy landed
 // -> LDS -> unpack -> MMA chain -> store), so anything that a compute warp has to wait for
 // besides its own data costs bandwidth; a CTA-wide barrier per item did.
+//
+// NT = 1 (batch <= 8): an item's RB row blocks are multiplied together (2 * RB interleaved MMA
+// chains) and parked as one sub-item.  NT = 2 (batch <= 16): the activation fragments alone take
+// half the register file, so a warp multiplies one 16-row block at a time (four chains: two
+// groups x two batch tiles) and every row block is parked and folded as a sub-item of its own —
+// which also keeps the slots of partial sums at 16 rows.
 #pragma once
 
 namespace qb {
 
-constexpr uint32_t ASYNC_THREADS = REG_THREADS + 32;
+// Threads per CTA: sixteen compute warps and the service warp.  With the 16-column batch tile the compute warps
+// need more registers than an even split of the register file over 17 warps gives (registers are handed out per
+// group of four warps, so 17 warps are budgeted as 20: 96 each), so that kernel is launched with a whole fifth
+// warp group — three of its warps leave at once — which hands most of its registers to the compute warps.
+constexpr uint32_t ASYNC_THREADS = REG_THREADS + 32, ASYNC_THREADS_WIDE = REG_THREADS + 128;
+__host__ __device__ constexpr uint32_t async_threads(int nt) { return nt == 2 ? ASYNC_THREADS_WIDE : ASYNC_THREADS; }
+
+// Shared-memory carve-up of the service-warp kernel, identical on host and device.
+// sub_rows: rows folded at a time; red_stride: floats between rows of a slot of partial sums.
+struct AsyncSmem {
+    uint32_t desc, red, scales, codes, total, stage_scales, stage_codes, slot_floats;
+};
+__host__ __device__ inline AsyncSmem async_smem_layout(uint32_t K, uint32_t rb, uint32_t sub_rows, uint32_t red_stride,
+                                                       uint32_t stages) {
+    AsyncSmem L;
+    const uint32_t groups = K / 128;
+    auto up = [](uint32_t v) { return (v + 127u) & ~127u; };
+    L.desc = 128;  // barriers at 0: [S <= 8] codes landed, [2] slot parked, [2] slot folded
+    L.red = L.desc + up(REG_MAX_ITEMS * (uint32_t)sizeof(RegItem));
+    L.slot_floats = REG_WARPS * sub_rows * red_stride;
+    L.scales = L.red + up(2 * L.slot_floats * 4);
+    L.stage_scales = up(rb * 16 * groups * 4);
+    L.codes = L.scales + stages * L.stage_scales;
+    L.stage_codes = up(rb * 16 * (K / 2));
+    L.total = L.codes + stages * L.stage_codes;
+    return L;
+}
+// Row stride of a slot for `cols` kept batch columns: two floats of padding spread the rows over
+// the banks for the service warp's reads (lane = row); a pair of columns needs none.
+__host__ __device__ inline uint32_t async_red_stride(uint32_t cols) { return cols <= 2 ? cols : cols + 2; }
 
 // shared-memory accesses and barrier polls on 32-bit shared addresses
 __device__ __forceinline__ uint4 async_lds128(uint32_t a) {
@@ -44,14 +79,17 @@ __device__ __forceinline__ bool async_wait_bounded(uint32_t bar, uint32_t parity
 }
 
 template <int NT, int RB, typename YT>
-__global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
+__global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int SUBS = NT == 2 ? RB : 1;  // sub-items (parked and folded separately) per item
+    constexpr int RPS = RB / SUBS;          // row blocks per sub-item
+    constexpr uint32_t SUB_ROWS = RPS * 16;
     const uint32_t groups = a.K >> 7, row_bytes = a.K >> 1, S = a.stages;
-    const uint32_t BW = a.red_cols;                 // batch columns kept per row of partial sums (>= M, even)
-    const uint32_t SLOT = REG_WARPS * RB * 16 * BW;  // floats per slot of partial sums
-    const RegSmem L = reg_smem_layout(a.K, NT, RB, S, BW);
+    const uint32_t BW = a.red_cols;             // batch columns kept per row of partial sums (>= M, even)
+    const uint32_t RS = a.red_stride;           // floats between rows of a slot
+    const AsyncSmem L = async_smem_layout(a.K, RB, SUB_ROWS, RS, S);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [S] codes landed
-    uint64_t* done = bars + 8;                           // [2] all compute warps have parked the item's partial sums
+    uint64_t* done = bars + 8;                           // [2] all compute warps have parked the sub-item's partial sums
     uint64_t* vacant = bars + 10;                        // [2] the service warp has folded the slot
     float* s_red = reinterpret_cast<float*>(smem + L.red);
     RegItem* s_desc = reinterpret_cast<RegItem*>(smem + L.desc);     // one per item of this CTA
@@ -64,13 +102,9 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
     const uint32_t n_my = per_cta + (blockIdx.x < extra ? 1u : 0u);
     const uint32_t item_first = blockIdx.x * per_cta + min(blockIdx.x, extra);
     const bool async_scales = a.async_scales != 0;  // scales not 16-byte aligned: 4-byte async copies
-    // a compute warp's two scale groups (the second may not exist for short K)
-    const uint32_t G0 = warp, G1 = warp + REG_WARPS;
-    const bool v0 = G0 < groups, v1 = G1 < groups;
-    const uint32_t G0c = v0 ? G0 : 0, G1c = v1 ? G1 : 0;
 
     // Every item this CTA will process is described once, up front (thread i describes item i).
-    for (uint32_t j = tid; j < n_my; j += ASYNC_THREADS) {
+    for (uint32_t j = tid; j < n_my; j += async_threads(NT)) {
         const uint32_t item = item_first + j;
         uint32_t l = 0;
         while (l + 1 < a.count && item >= a.layer[l + 1].item0) l++;
@@ -113,46 +147,56 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == REG_WARPS)
-        for (uint32_t j = 0; j < S && j < n_my; j++) issue(j, j);
-    // The codes and scales do not depend on the previous kernel; everything below may.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
     bool failed = false;
-    if (warp == REG_WARPS) {
+    if (warp >= REG_WARPS) {
+        // 20 warps were launched with 96 registers each: 16 x 120 + 4 x 32 is the same total.  The two roles
+        // stay in separate branches to the end, so each is compiled for its own register budget.
+        if constexpr (NT == 2) {
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+            if (warp > REG_WARPS) return;
+        }
+        for (uint32_t j = 0; j < S && j < n_my; j++) issue(j, j);
+        // The codes and scales do not depend on the previous kernel; everything below may.
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         // ---- service warp: refill, fold, store ----
-        uint32_t st = 0;
-        for (uint32_t j = 0; j < n_my; j++) {
-            const uint32_t slot = j & 1;
-            if (!mbar_wait_bounded(&done[slot], (j >> 1) & 1)) { failed = true; break; }
-            if (j + S < n_my) issue(j + S, st);  // every compute warp has left the stage
+        // lane -> (row, batch column) of a sub-item: 32-row sub-items give every lane a row and all the columns;
+        // 16-row sub-items give a half-warp the even columns and the other half the odd ones (with the padded
+        // row stride both are free of bank conflicts, and a store instruction writes whole 64- or 128-byte runs)
+        const uint32_t row_l = SUB_ROWS == 32 ? lane : (lane & 15), b0 = SUB_ROWS == 32 ? 0 : (lane >> 4), bstep = SUB_ROWS == 32 ? 1 : 2;
+        uint32_t st = 0, q = 0;
+        for (uint32_t j = 0; j < n_my && !failed; j++) {
             const RegItem& it = s_desc[j];
-            const float* red = s_red + slot * SLOT;
-            for (uint32_t r = lane; r < RB * 16; r += 32) {  // lane = output row: consecutive lanes, consecutive outputs
+#pragma unroll 1
+            for (int s = 0; s < SUBS; s++, q++) {
+                const uint32_t slot = q & 1;
+                if (!mbar_wait_bounded(&done[slot], (q >> 1) & 1)) { failed = true; break; }
+                if (s == SUBS - 1 && j + S < n_my) issue(j + S, st);  // every compute warp has left the stage
+                const float* red = s_red + slot * L.slot_floats + row_l * RS;
+                const uint32_t r = s * SUB_ROWS + row_l;  // row inside the item
                 if (r < it.nrows) {
                     const uint32_t n = it.row0 + r;
                     const float bias = it.bias ? it.bias[n] : 0.0f;
-                    for (uint32_t b = 0; b < a.M; b++) {
+                    for (uint32_t b = b0; b < a.M; b += bstep) {
                         float v = 0.0f;
 #pragma unroll
-                        for (int w = 0; w < REG_WARPS; w++) v += red[(w * RB * 16 + r) * BW + b];
+                        for (int w = 0; w < REG_WARPS; w++) v += red[w * SUB_ROWS * RS + b];
                         YT* yp = static_cast<YT*>(it.y) + (uint64_t)b * it.N + n;
                         const float out = fmaf(v, GEMV_UNSCALE, bias);
                         if (a.n_peers == 0) {
                             store_y<YT>(yp, out);
-                        } else {  // fused all-gather: the same element of every rank's buffer (peer memory over NVLink)
+                        } else {  // fused exchange: the same element of every rank's buffer (peer memory over NVLink)
                             for (uint32_t p = 0; p < a.n_peers; p++)
                                 store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<uint8_t*>(yp) + a.peer_delta[p]), out);
                         }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&vacant[slot]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&vacant[slot]);
             if (++st == S) st = 0;
         }
-        // Fused all-gather with the arrival barrier inside the launch: the CTA that finishes last tells every
+        // Fused exchange with the arrival barrier inside the launch: the CTA that finishes last tells every
         // peer "this rank's outputs of this step are written" and waits, bounded, for theirs, so the launch ends
         // when all ranks' outputs are here.  flags[p] is rank p's array {arrival of rank 0..7, step counter,
         // count of finished CTAs}.
@@ -177,7 +221,7 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
                     uint32_t spins = 0;
                     for (;;) {
                         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine + lane) : "memory");
-                        if (v >= step || ++spins >= (4u << 20)) break;
+                        if (v >= step || ++spins >= a.peer_spin_limit) break;
                         __nanosleep(200);
                     }
                     if (v < step) atomicExch(a.status, QB200_ERR_TIMEOUT);
@@ -187,36 +231,41 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
         }
     } else {
         // ---- compute warps ----
+        if constexpr (NT == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        // a compute warp's two scale groups (the second may not exist for short K: it then re-reads the first
+        // group's codes against zero activations and a zero scale)
+        const bool v0 = warp < groups, v1 = warp + REG_WARPS < groups;
+        const uint32_t G0c = v0 ? warp : 0;
         // The item loop works on 32-bit shared-memory addresses that are advanced, not recomputed:
         // every instruction here is paid 16 x 28 times per CTA and layer.
-        uint4 fa[NT][4], fb[NT][4];  // activation fragments of groups G0 / G1
+        uint4 fa[NT][4], fb[NT][4];  // activation fragments of the two groups
         float ka[NT][2], kb[NT][2];  // their "+ 8" corrections for batch columns 2t, 2t + 1, in MMA units
         const uint16_t* cur_x = nullptr;
-        const uint32_t bar0 = smem_u32(bars), done0 = smem_u32(done), vacant0 = smem_u32(vacant);
-        const uint32_t desc0 = smem_u32(s_desc);  // the item's activation pointer is the first field of its descriptor
-        // offsets inside a stage of this lane's four 16-byte code loads and four scales (row g / g + 8, group G0 / G1)
-        const uint32_t codes0 = smem_u32(smem + L.codes) + g * row_bytes + t * 16, scales0 = smem_u32(smem + L.scales) + g * groups * 4;
-        const uint32_t oc0 = G0c * 64, oc1 = 8 * row_bytes + G0c * 64, oc2 = G1c * 64, oc3 = 8 * row_bytes + G1c * 64;
-        const uint32_t os0 = G0c * 4, os1 = (8 * groups + G0c) * 4, os2 = G1c * 4, os3 = (8 * groups + G1c) * 4;
-        const uint32_t rb_codes = 16 * row_bytes, rb_scales = 16 * groups * 4;
-        // where this lane parks its partial sums inside a slot: row g (and g + 8) of row block rb, columns 2t, 2t + 1
-        const uint32_t red0 = smem_u32(s_red) + ((warp * RB * 16 + g) * BW + 2 * t) * 4;
-        const bool keeps = 2 * t < BW;  // NT == 1: columns past the batch are not kept
-        uint32_t st = 0, parity = 0, stage_codes = codes0, stage_scales = scales0;
-        for (uint32_t j = 0; j < n_my; j++) {
-            if (!async_try_wait(bar0 + st * 8, parity) && !async_wait_bounded(bar0 + st * 8, parity)) { failed = true; break; }
-            const uint32_t slot = j & 1, vpar = ((j >> 1) & 1) ^ 1;
-            // the slot's previous item has long been folded: polled here so that its latency overlaps the loads
-            if (j >= 2 && !async_try_wait(vacant0 + slot * 8, vpar) && !async_wait_bounded(vacant0 + slot * 8, vpar)) { failed = true; break; }
+        const uint32_t sm0 = smem_u32(smem);  // stage barriers at +0, done at +64, vacant at +80
+        uint32_t dptr = smem_u32(s_desc);     // the item's activation pointer is the first field of its descriptor
+        // this lane's code loads of a row block: rows g and g + 8 of groups G0 and G1, 16 bytes each; its four scales
+        const uint32_t codes0 = smem_u32(smem + L.codes) + g * row_bytes + t * 16 + G0c * 64;
+        const uint32_t scales0 = smem_u32(smem + L.scales) + (g * groups + G0c) * 4;
+        const uint32_t c8 = 8 * row_bytes, s8 = 8 * groups * 4;
+        const uint32_t cg1 = v1 ? REG_WARPS * 64 : 0, sg1 = v1 ? REG_WARPS * 4 : 0;
+        // where this lane parks its partial sums inside a slot: row g (and g + 8) of a row block, columns 2t, 2t + 1
+        const uint32_t red0 = smem_u32(s_red) + ((warp * SUB_ROWS + g) * RS + 2 * t) * 4;
+        const bool keeps = 2 * t < BW;  // columns past the batch are not kept
+        const bool keeps1 = 8 + 2 * t < BW;
+        uint32_t st = 0, parity = 0, stage_codes = codes0, stage_scales = scales0, q = 0;
+        for (uint32_t j = 0; j < n_my; j++, dptr += (uint32_t)sizeof(RegItem)) {
+            if (!async_try_wait(sm0 + st * 8, parity) && !async_wait_bounded(sm0 + st * 8, parity)) { failed = true; break; }
             const uint16_t* x_now;
-            asm volatile("ld.shared.u64 %0, [%1];" : "=l"(x_now) : "r"(desc0 + j * (uint32_t)sizeof(RegItem)));
+            asm volatile("ld.shared.u64 %0, [%1];" : "=l"(x_now) : "r"(dptr));
             if (x_now != cur_x) {  // uniform across the CTA: (re)load this warp's fragments
                 cur_x = x_now;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     const uint32_t b = g + 8 * nt;
                     float s0 = load_fragment(cur_x, a.K, b, G0c, t, v0 && b < a.M, fa[nt]);
-                    float s1 = load_fragment(cur_x, a.K, b, G1c, t, v1 && b < a.M, fb[nt]);
+                    float s1 = load_fragment(cur_x, a.K, b, v1 ? warp + REG_WARPS : 0, t, v1 && b < a.M, fb[nt]);
                     s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, 1);
                     s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, 2);
                     s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, 1);
@@ -228,25 +277,31 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
                     kb[nt][1] = GEMV_EIGHT_X * __shfl_sync(0xFFFFFFFFu, s1, 8 * t + 4);
                 }
             }
-            // every load of the item first
-            uint4 c[RB][4];
-            float sc[RB][4];
+#pragma unroll 1
+            for (int s = 0; s < SUBS; s++, q++) {
+                const uint32_t slot = q & 1, vpar = ((q >> 1) & 1) ^ 1;
+                // the slot's previous sub-item has long been folded: polled here so that its latency overlaps the loads
+                const uint32_t vac = sm0 + 80 + slot * 8;
+                if (q >= 2 && !async_try_wait(vac, vpar) && !async_wait_bounded(vac, vpar)) { failed = true; break; }
+                // every load of the sub-item first
+                uint4 c[RPS][4];
+                float sc[RPS][4];
 #pragma unroll
-            for (int rb = 0; rb < RB; rb++) {
-                const uint32_t cr = stage_codes + rb * rb_codes, sr = stage_scales + rb * rb_scales;
-                c[rb][0] = async_lds128(cr + oc0);
-                c[rb][1] = async_lds128(cr + oc1);
-                c[rb][2] = async_lds128(cr + oc2);
-                c[rb][3] = async_lds128(cr + oc3);
-                sc[rb][0] = async_lds32(sr + os0);
-                sc[rb][1] = async_lds32(sr + os1);
-                sc[rb][2] = v1 ? async_lds32(sr + os2) : 0.0f;
-                sc[rb][3] = v1 ? async_lds32(sr + os3) : 0.0f;
-            }
-            // 2 * RB independent MMA chains (row block x group), interleaved step by step
-            float pa[RB][NT][4], pb[RB][NT][4];
+                for (int rb = 0; rb < RPS; rb++) {
+                    const uint32_t cr = stage_codes + (s * RPS + rb) * 2 * c8, sr = stage_scales + (s * RPS + rb) * 2 * s8;
+                    c[rb][0] = async_lds128(cr);
+                    c[rb][1] = async_lds128(cr + c8);
+                    c[rb][2] = async_lds128(cr + cg1);
+                    c[rb][3] = async_lds128(cr + cg1 + c8);
+                    sc[rb][0] = async_lds32(sr);
+                    sc[rb][1] = async_lds32(sr + s8);
+                    sc[rb][2] = v1 ? async_lds32(sr + sg1) : 0.0f;
+                    sc[rb][3] = v1 ? async_lds32(sr + sg1 + s8) : 0.0f;
+                }
+                // 2 * RPS * NT independent MMA chains (row block x group x batch tile), interleaved step by step
+                float pa[RPS][NT][4], pb[RPS][NT][4];
 #define QB_STEP(J, X, FIRST)                                                                         \
-    _Pragma("unroll") for (int rb = 0; rb < RB; rb++) {                                              \
+    _Pragma("unroll") for (int rb = 0; rb < RPS; rb++) {                                             \
         {                                                                                            \
             QB_UNPACK(c[rb][0].X, c[rb][1].X)                                                        \
             _Pragma("unroll") for (int nt = 0; nt < NT; nt++) {                                      \
@@ -264,31 +319,33 @@ __global__ void __launch_bounds__(ASYNC_THREADS, 1) k_gemv_i4_async(const __grid
             }                                                                                        \
         }                                                                                            \
     }
-            QB_STEP(0, x, true)
-            QB_STEP(1, y, false)
-            QB_STEP(2, z, false)
-            QB_STEP(3, w, false)
+                QB_STEP(0, x, true)
+                QB_STEP(1, y, false)
+                QB_STEP(2, z, false)
+                QB_STEP(3, w, false)
 #undef QB_STEP
-            // park the partial sums in red[slot][warp][row][batch]: (p - 8 * sum x) is the group's sum of q * x in
-            // MMA units (2^-93); 2^93 is applied at the store
-            const uint32_t ra = red0 + slot * (SLOT * 4);
+                // park the partial sums in red[slot][warp][row][batch]: (p - 8 * sum x) is the group's sum of q * x in
+                // MMA units (2^-93); 2^93 is applied at the store
+                const uint32_t ra = red0 + slot * (L.slot_floats * 4);
 #pragma unroll
-            for (int rb = 0; rb < RB; rb++)
+                for (int rb = 0; rb < RPS; rb++)
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    float o[4];
+                    for (int nt = 0; nt < NT; nt++) {
+                        float o[4];
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float da = pa[rb][nt][i] - ka[nt][i & 1], db = pb[rb][nt][i] - kb[nt][i & 1];
-                        o[i] = fmaf(sc[rb][i < 2 ? 2 : 3], db, sc[rb][i < 2 ? 0 : 1] * da);
+                        for (int i = 0; i < 4; i++) {
+                            const float da = pa[rb][nt][i] - ka[nt][i & 1], db = pb[rb][nt][i] - kb[nt][i & 1];
+                            o[i] = fmaf(sc[rb][i < 2 ? 2 : 3], db, sc[rb][i < 2 ? 0 : 1] * da);
+                        }
+                        if (nt == 0 ? keeps : keeps1) {
+                            async_sts64(ra + (rb * 16 * RS + nt * 8) * 4, o[0], o[1]);
+                            async_sts64(ra + ((rb * 16 + 8) * RS + nt * 8) * 4, o[2], o[3]);
+                        }
                     }
-                    if (nt == 0 ? keeps : nt * 8 + 2 * t < BW) {
-                        async_sts64(ra + (rb * 16 * BW + nt * 8) * 4, o[0], o[1]);
-                        async_sts64(ra + ((rb * 16 + 8) * BW + nt * 8) * 4, o[2], o[3]);
-                    }
-                }
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(done0 + slot * 8) : "memory");  // releases the stage, publishes the sums
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sm0 + 64 + slot * 8) : "memory");  // publishes the sums; the last sub-item's arrival also releases the stage
+            }
+            if (failed) break;
             stage_codes += L.stage_codes;
             stage_scales += L.stage_scales;
             if (++st == S) {

@@ -6,15 +6,18 @@
 // afterwards tells the peers "my outputs of step s are written" and waits, bounded, for theirs.
 // The buffers are ordinary cudaMalloc allocations shared between the node's processes with CUDA
 // IPC handles, which the caller exchanges through its own process group.
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <string>
 
-#include "common.hpp"
+#include "forward.hpp"
 
 namespace qb {
 
-constexpr uint32_t PEER_SPIN_LIMIT = 4u << 20;  // polls of ~0.25 us each: about a second, then QB200_ERR_TIMEOUT
+// polls of ~0.25 us each before a barrier gives up with QB200_ERR_TIMEOUT: about a second by default
+static std::atomic<uint32_t> g_peer_spin_limit{4u << 20};
+uint32_t peer_spin_limit() { return g_peer_spin_limit.load(std::memory_order_relaxed); }
 
 struct PeerFlags {
     uint64_t* flags[8];  // flags[p]: rank p's array {arrival of rank 0, ..., arrival of rank 7, own step counter}
@@ -22,7 +25,7 @@ struct PeerFlags {
 
 // One launch per step and rank.  The step number lives in device memory (slot 8 of the own flag
 // array), so a CUDA graph that replays this launch still counts.
-__global__ void k_peer_signal_wait(PeerFlags f, uint32_t world, uint32_t rank, int32_t* status) {
+__global__ void k_peer_signal_wait(PeerFlags f, uint32_t world, uint32_t rank, uint32_t spin_limit, int32_t* status) {
     __shared__ uint64_t s_step;
     if (threadIdx.x == 0) {
         s_step = f.flags[rank][8] + 1;
@@ -41,7 +44,7 @@ __global__ void k_peer_signal_wait(PeerFlags f, uint32_t world, uint32_t rank, i
         uint32_t spins = 0;
         for (;;) {
             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
-            if (v >= step || ++spins >= PEER_SPIN_LIMIT) break;
+            if (v >= step || ++spins >= spin_limit) break;
             __nanosleep(200);
         }
         if (v < step) atomicExch(status, QB200_ERR_TIMEOUT);
@@ -92,6 +95,12 @@ qb200_status qb200_peer_free(void* dev_ptr) {
     return QB200_OK;
 }
 
+qb200_status qb200_peer_set_spin_limit(uint32_t polls) {
+    if (polls == 0) return fail(QB200_ERR_INVALID_PARAM, "qb200_peer_set_spin_limit: the limit must be positive");
+    qb::g_peer_spin_limit.store(polls, std::memory_order_relaxed);
+    return QB200_OK;
+}
+
 qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint32_t world, uint32_t rank, int32_t* status_dev,
                                     void* stream) {
     if (!flag_arrays || !status_dev || world == 0 || world > 8 || rank >= world)
@@ -101,7 +110,7 @@ qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint32_t world
         if (!flag_arrays[p]) return fail(QB200_ERR_INVALID_PARAM, "qb200_peer_signal_wait: null flag array");
         f.flags[p] = flag_arrays[p];
     }
-    qb::k_peer_signal_wait<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, status_dev);
+    qb::k_peer_signal_wait<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, qb::peer_spin_limit(), status_dev);
     QB_CUDA_TRY(cudaGetLastError());
     return QB200_OK;
 }

@@ -229,7 +229,7 @@ qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uin
         if (q->in_dim != layers[0]->in_dim ||
             !qb::gemv_i4_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes, q->scales, x_dev[i]))
             return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_gather: layer " + std::to_string(i) +
-                                                     " does not take the decode kernel (int4, 1x128, [out, in], bf16 x, m <= 8)");
+                                                     " does not take the decode kernel (int4, 1x128, [out, in], bf16 x, m <= 16)");
         qb::FwdArgs& a = args[i];
         a.codes = q->codes;
         a.scales = q->scales;
@@ -255,7 +255,7 @@ qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uin
         peers.delta[p] = static_cast<int64_t>(reinterpret_cast<intptr_t>(gather_bases[p]) - reinterpret_cast<intptr_t>(gather_bases[rank]));
     qb200_status s = qb::gemv_i4_forward_many(args.data(), count, y_dtype, layers[0]->status, static_cast<cudaStream_t>(stream), &peers);
     if (s == QB200_ERR_NOT_SUPPORTED)
-        return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_gather: no launch plan with peer stores fits this shape (m <= 8, K <= 4096)");
+        return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_gather: no launch plan with peer stores fits this shape (m <= 16, K <= 4096)");
     if (s == QB200_OK)
         for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_grouped_gather";
     return s;
@@ -361,8 +361,12 @@ qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream) {
     int32_t st = 0;
     QB_CUDA_TRY(cudaMemcpyAsync(&st, ql->status, sizeof st, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
     QB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    if (st != 0) {  // reported once: the word is cleared so that the handle stays usable
+        QB_CUDA_TRY(cudaMemsetAsync(ql->status, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream)));
+        QB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    }
     if (st == QB200_ERR_TIMEOUT)
-        return fail(QB200_ERR_TIMEOUT, "QuantizedLinear: a device-side wait ran out of polls (an async copy never completed)");
+        return fail(QB200_ERR_TIMEOUT, "QuantizedLinear: a device-side wait ran out of polls (an async copy never completed, or a peer rank never arrived at the barrier)");
     if (st != 0) return fail(QB200_ERR_CUDA, "QuantizedLinear: device status " + std::to_string(st));
     return QB200_OK;
 }
