@@ -36,6 +36,24 @@ if ROOT not in sys.path:
 N_OUT, K_IN, GROUP = 4096, 4096, 128
 LAYERS = 32  # 32 x 8.9 MB = 286 MB of codes + scales, larger than the 126 MB L2
 METRIC = "QuantizedLinear weight GB/s (int4 decode GEMV)"
+NOMINAL_HBM_GBS = 8000.0  # the figure the workload's target is quoted against
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch divided by the layers it processed, from the
+# ncu capture summarised in profiles/gemv_i4_grouped_decode.md (an 8-layer launch; traffic grows in proportion to the
+# layers).  It describes the kernel as captured then; a changed kernel needs a new capture.
+TRAFFIC_PER_LAYER = {1: 72.20e6 / 8}
+TRAFFIC_SOURCE = "ncu capture of an 8-layer launch (profiles/gemv_i4_grouped_decode.md), scaled by the layers per launch"
+
+
+def workload_name(m: int) -> str:
+    """The workload both arms name in `config.workload` (the reference arm times a bounded sample of it)."""
+    return f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{m},{K_IN}], f32 out"
+
+
+def bench_config(m: int, world: int) -> dict:
+    """`config` of the JSON line, the same in both arms."""
+    return {"workload": workload_name(m), "layers_per_step": LAYERS,
+            "l2": f"inputs larger than L2 ({LAYERS} distinct weight matrices, {LAYERS * 8.9:.0f} MB)",
+            "parallelism": "single GPU" if world == 1 else f"column-sharded x{world} (weak scaling: one [{N_OUT},{K_IN}] shard per GPU), outputs all-gathered"}
 
 
 def layer_bytes(m: int) -> int:
@@ -121,6 +139,24 @@ def cpu_forward_gbs(m: int, threads: int, layers: int, reps: int):
     return layer_bytes(m) * layers * reps / dt / 1e9, dt
 
 
+def cpu_quantize_baseline():
+    """quantize_host / dequantize_host of the CPU restatement on ONE thread (the reference's loops are single-threaded:
+    crates/sci/quanta-array/src/quant.rs:293-413), on one [4096, 4096] matrix of the checkpoint workload."""
+    import oracle as o
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((4096, 4096), dtype=np.float32) * np.float32(0.02)
+    res = {"cores": 1, "kind": "port", "sample": "1 of the 64 matrices ([4096, 4096] f32, 67 MB read), single thread"}
+    for name, bits, gr, gc in [("int4_1x128", 4, 1, 128), ("int8_32x32", 8, 32, 32)]:
+        t0 = time.perf_counter()
+        c, sc = o.quantize_host(w, 4096, 4096, bits, gr, gc)
+        t1 = time.perf_counter()
+        o.dequantize_host(c, sc, 4096, 4096, bits, gr, gc)
+        t2 = time.perf_counter()
+        res["quantize_" + name + "_read_GB/s"] = w.nbytes / (t1 - t0) / 1e9
+        res["dequantize_" + name + "_write_GB/s"] = w.nbytes / (t2 - t1) / 1e9
+    return res
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -144,8 +180,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * t_total / max(steps, 1), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{args.m},{K_IN}]",
-                   "layers_per_step": layers},
+        "config": bench_config(args.m, max(args.gpus, 1)),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -156,34 +191,104 @@ def run_reference(args):
 # this build's arm
 # ---------------------------------------------------------------------------------------
 
-def measure_decode_step(torch, dev, gen, timed, hbm, n_layers):
+def measure_decode_step(torch, dev, gen, hbm, n_layers, world=1):
     """Whole-model decode step: `n_layers` Llama-7B-shaped blocks + vocabulary projection, int4 1x128 linears,
-    batch 16, 1024 cached positions (KV bf16), random-initialised; one step = one CUDA graph replay."""
+    batch 16, 1024 cached positions (KV bf16), random-initialised; one step = one CUDA graph replay.  With
+    world > 1 the stack is tensor-parallel over the ranks (whole heads per rank, two fused exchanges per block)."""
+    import torch.distributed as dist
+    stack = None
     try:
         from quanta_b200 import decoder as dec
         torch.cuda.empty_cache()
-        stack = dec.DecoderStack(n_layers, 4096, 32, 11008, 32000, 16, 1025, dev, seed=4)
+        if world > 1:
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        stack = dec.DecoderStack(n_layers, 4096, 32, 11008, 32000, 16, 1025, dev, seed=4, group=dist.group.WORLD if world > 1 else None)
         stack.set_position(1024)
-        h0 = torch.randn(16, 4096, device=dev, generator=gen) * 0.02
+        h0 = torch.randn(16, 4096, device=dev, generator=torch.Generator(device=dev).manual_seed(5)) * 0.02
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+
         for _ in range(2):
             stack.step(h0)
-        torch.cuda.synchronize(dev)
+        barrier()
+        if stack.arena is not None:
+            stack.arena.check()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             stack.step(h0)
-        ms = timed(g.replay, 20)
-        by = stack.weight_bytes + stack.kv_bytes(1025)
-        res = {"tokens/s": 16 / ms * 1e3, "ms_per_step": ms, "layers": n_layers, "batch": 16, "context": 1024,
-               "GB/s": by / ms / 1e6, "roofline_frac": by / ms / 1e6 / hbm, "bytes_per_step": by,
-               "launch": "cuda graph replay of the step"}
-        del stack, g
-        torch.cuda.empty_cache()
+        for _ in range(3):
+            g.replay()
+        iters = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(iters):
+            g.replay()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / iters
+        logits_ok = bool(torch.isfinite(stack.logits).all().item())
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            stack.arena.check()  # a barrier that timed out would have let the step run on stale partial sums
+            # every rank must hold the same logits after the last exchange
+            ref = stack.logits.clone()
+            dist.broadcast(ref, 0)
+            same = torch.tensor([1.0 if torch.equal(ref, stack.logits) and logits_ok else 0.0], device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            logits_ok = bool(same.item() == 1.0)
+        by = stack.weight_bytes + stack.kv_bytes(1025)  # per GPU
+        res = {"tokens/s": 16 / ms * 1e3, "ms_per_step": ms, "layers": n_layers, "batch": 16, "context": 1024, "n_gpus": world,
+               "bytes_per_step_per_gpu": by, "GB/s_per_gpu": by / ms / 1e6, "roofline_frac": by / ms / 1e6 / hbm,
+               "launch": "cuda graph replay of the step", "logits_finite_and_equal_on_all_ranks": logits_ok}
+        if world > 1:
+            # the exchanges' share of the step: the same graph with every exchange switched off (each rank stores only
+            # into its own buffer and nothing waits; the logits of that run mean nothing, only its time does)
+            stack.exchange = False
+            for _ in range(2):
+                stack.step(h0)
+            barrier()
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2):
+                stack.step(h0)
+            for _ in range(3):
+                g2.replay()
+            barrier()
+            e0.record()
+            for _ in range(iters):
+                g2.replay()
+            e1.record()
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            del g2
+            stack.exchange = True
+            res["ms_per_step_without_exchanges"] = float(t.item())
+            res["exchange_share_of_step"] = max(0.0, 1.0 - float(t.item()) / ms)
+            res["exchanges_per_step"] = 2 * n_layers + 1
+            res["nvlink_bytes_per_step_per_gpu"] = stack.exchange_bytes() * (world - 1)
+            res["parallelism"] = (f"tensor-parallel x{world}: whole heads per rank, row-parallel output and down projections, partial sums "
+                                  "stored to every rank by the producing kernel, arrival barrier in the same launch")
+        del g
         return res
     except Exception as e:  # the rest of the line must survive
-        return {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
+        return {"skipped": f"{type(e).__name__}: {str(e)[:160]}"}
+    finally:
+        if stack is not None:
+            try:
+                stack.close()
+            except Exception:
+                pass
+        del stack
+        torch.cuda.empty_cache()
 
 
-def measure_extras(torch, qb, dev, only=None, small=False):
+def measure_extras(torch, qb, dev, only=None, small=False, world=1):
     """Secondary numbers of the same path on one GPU (device-resident inputs, CUDA events):
     the int4 prefill GEMM configuration and quantize-on-load, each with its roofline fraction."""
     peaks = {}
@@ -234,12 +339,12 @@ def measure_extras(torch, qb, dev, only=None, small=False):
 
     out = {}
     gen = torch.Generator(device=dev).manual_seed(2)
+    if only == "decode_step" or world > 1:  # the one side workload that shards: the whole-model decode step
+        return {"decode_step_llama7b_shape": measure_decode_step(torch, dev, gen, hbm, 2 if small else 32, world)}
     M, N, K = (512, 2048, 4096) if small else (2048, 11008, 4096)
     w = torch.randn(N, K, device=dev, generator=gen) * 0.02
     x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
     # quantize-on-load: f32 [11008, 4096] (180 MB, larger than L2) -> int4 1x128 and int8 32x32
-    if only == "decode_step":
-        return {"decode_step_llama7b_shape": measure_decode_step(torch, dev, gen, timed, hbm, 2 if small else 32)}
     if only in ("blas_quant", "blas_quant_brief"):
         brief = only == "blas_quant_brief"
         # the quantized BLAS entries: int codes for both operands, one per i32 word (the reference's storage), so a call
@@ -325,7 +430,11 @@ def measure_extras(torch, qb, dev, only=None, small=False):
         del lys
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
-    out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, timed, hbm, 32)
+    out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, hbm, 32, 1)
+    try:  # the reference's quantize / dequantize are single-threaded host loops: the restatement timed the same way
+        out["cpu_quantize_baseline"] = cpu_quantize_baseline()
+    except Exception as e:
+        out["cpu_quantize_baseline"] = {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
     try:  # the quantized BLAS entries (int codes for both operands): one GEMM size and the GEMV
         out["blas_quant"] = measure_extras(torch, qb, dev, only="blas_quant_brief")
     except Exception as e:
@@ -352,16 +461,19 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # the ranks' own kernels store into peer memory; keep NVLink multicast objects out of it
         dist.init_process_group("nccl", device_id=dev)
 
     global LAYERS
     LAYERS = args.layers
     m = args.m
     lib = _lib.load()
-    if args.only:  # side workloads alone (used for profiling): prefill GEMM or quantize / dequantize
-        ex = measure_extras(torch, qb, dev, only=args.only, small=args.small)
+    if args.only:  # side workloads alone (used for profiling): prefill GEMM, quantize / dequantize, the decode step
+        ex = measure_extras(torch, qb, dev, only=args.only, small=args.small, world=world)
         if rank == 0:
             print(json.dumps({"only": args.only, "extras": ex}), flush=True)
+        if world > 1:
+            _leave(torch, dist, dev)
         return
     # device-side quantize-on-load of this rank's shards (seeded per rank)
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
@@ -371,8 +483,7 @@ def run_ours(args):
         qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, GROUP))
         layers.append(qb.QuantizedLinear.new(qm, None, qb.OUT_IN))
         del w
-    x = torch.randn(m, K_IN, device=dev, generator=gen).to(torch.bfloat16)
-    y = torch.empty(m, N_OUT, device=dev, dtype=torch.float32)
+    x = torch.randn(m, K_IN, device=dev, generator=torch.Generator(device=dev).manual_seed(99)).to(torch.bfloat16)  # the same on every rank
     y_all = torch.empty(world, m, N_OUT, device=dev, dtype=torch.float32) if world > 1 else None
     stream = torch.cuda.current_stream(dev)
 
@@ -383,9 +494,9 @@ def run_ours(args):
     xp = (_lib.vp * LAYERS)(*[x.data_ptr()] * LAYERS)
     yp = (_lib.vp * LAYERS)(*[t.data_ptr() for t in ys])
     grouped = args.launch == "grouped"
-    # N > 1, grouped: the kernel stores the step's outputs into every rank's buffer itself (peer memory) and an
-    # arrival barrier follows; --gather nccl keeps the library all-gather for comparison
-    fused = world > 1 and grouped and args.gather == "fused" and m <= 8
+    # N > 1, grouped: the kernel stores the step's outputs into every rank's buffer itself (peer memory) and the
+    # arrival barrier runs in the same launch; --gather nccl keeps the library all-gather for comparison
+    fused = world > 1 and grouped and args.gather == "fused" and m <= 16
     pg = None
     if fused:
         # every rank must take the same path: the ranks agree on whether all of them could map the peers' buffers
@@ -400,10 +511,10 @@ def run_ours(args):
         if ok.item() == 0:
             fused, pg = False, None
 
-    def step():
+    def one(parity=None):
         cur = torch.cuda.current_stream(dev).cuda_stream  # the capture stream while a graph is recorded
         if fused:
-            pg.forward_many(layers, [x] * LAYERS)
+            pg.forward_many(layers, [x] * LAYERS, parity)
             return
         if grouped:  # the 32 layers read the same x: one persistent launch streams all their codes
             st = lib.qb200_qlinear_forward_many(hs, LAYERS, xp, _lib.BF16, m, yp, _lib.F32, cur)
@@ -419,71 +530,130 @@ def run_ours(args):
             if world > 1:
                 dist.all_gather_into_tensor(y_all, t)
 
+    # A graph replay is TWO steps: the fused exchange alternates between two receive buffers step by step, and
+    # a replayed graph must keep that alternation, so the unit that is captured and timed is a pair.
+    def pair():
+        one(0)
+        one(1)
+
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(3):
-        step()
+    for _ in range(2):
+        pair()
     barrier()
-    eager_step = step
+    run_pair = pair
     if not args.no_graph:
-        # one CUDA graph per step: the launches keep their programmatic-dependency edges, so
-        # layer i+1's weight prefetch overlaps layer i's tail
+        # the launches keep their programmatic-dependency edges inside the graph, so the next launch's weight
+        # prefetch overlaps the current one's tail
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            eager_step()
-        step = graph.replay
+            pair()
+        run_pair = graph.replay
         stream = torch.cuda.current_stream(dev)
+    steps = max(2, args.steps + (args.steps & 1))  # whole pairs
+    pairs = steps // 2
+
+    def block():
+        for _ in range(pairs):
+            run_pair()
+
     # spin the clocks up for at least half a second before timing; the clock sampler runs from here
     # to the end of the timed region (same kernel, same load)
     clocks = ClockSampler(local)
     clocks.__enter__()
     # every rank must run the same number of steps (they hold collectives): rank 0 sizes the
-    # spin-up from ten timed steps and broadcasts the count
+    # spin-up and the number of timed blocks from a probe and broadcasts the counts
     for _ in range(max(args.warmup, 3)):
-        step()
+        run_pair()
     barrier()
-    t_spin = time.perf_counter()
-    for _ in range(10):
-        step()
+    t_probe = time.perf_counter()
+    block()
     barrier()
-    per_step = (time.perf_counter() - t_spin) / 10
-    n_spin = 0 if args.profile else int(min(max(0.5 / max(per_step, 1e-6), 1), 20000))
+    block_s = max(time.perf_counter() - t_probe, 1e-6)
+    n_spin = 0 if args.profile else int(min(max(0.5 / block_s, 1), 20000))
+    # the timed region is `n_blocks` blocks of `steps` steps, at least a quarter of a second in all; the block
+    # with the median time is the one reported
+    n_blocks = 1 if args.profile else int(min(max(0.25 / block_s, 3), 5000))
     if world > 1:
-        cnt = torch.tensor([n_spin], device=dev, dtype=torch.int64)
+        cnt = torch.tensor([n_spin, n_blocks], device=dev, dtype=torch.int64)
         dist.broadcast(cnt, 0)
-        n_spin = int(cnt.item())
+        n_spin, n_blocks = int(cnt[0].item()), int(cnt[1].item())
     for i in range(n_spin):
-        step()
-        if i % 64 == 63:
+        block()
+        if i % 16 == 15:
             torch.cuda.synchronize(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_blocks + 1)]
     barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
+    evs[0].record(stream)
+    for i in range(n_blocks):
+        block()
+        evs[i + 1].record(stream)
     barrier()
     clocks.__exit__()
-    ms = e0.elapsed_time(e1)
+    times = torch.tensor([evs[i].elapsed_time(evs[i + 1]) for i in range(n_blocks)], device=dev)
     if world > 1:
-        tmax = torch.tensor([ms], device=dev)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        ms = float(tmax.item())
-    launches = (1 if grouped else LAYERS) * args.steps  # fused all-gather: the arrival barrier runs inside the GEMV launch
-    total_bytes = layer_bytes(m) * LAYERS * args.steps * world
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)  # per block, the slowest rank
+    ms = float(times.median().item())
+    timed_region_s = float(times.sum().item()) * 1e-3
+    launches = (1 if grouped else LAYERS) * steps * n_blocks  # fused exchange: the arrival barrier runs inside the GEMV launch
+    total_bytes = layer_bytes(m) * LAYERS * steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
 
-    # end to end through the host-buffer entry point: pinned host X in, host Y out, every launch
+    # the multi-GPU numbers are only worth printing if the exchange delivered: no barrier timed out, and the
+    # gathered buffer equals an NCCL all-gather of the same outputs
+    gather_checked, device_status = None, 0
+    if world > 1:
+        try:
+            if fused:
+                pg.check()
+            else:
+                st = lib.qb200_qlinear_check(layers[0]._h, torch.cuda.current_stream(dev).cuda_stream)
+                if st:
+                    raise RuntimeError(_lib.last_error())
+        except Exception as e:
+            device_status = getattr(e, "code", -1)
+            print(f"bench.py: rank {rank}: device status after the timed region: {e}", file=sys.stderr)
+        st = lib.qb200_qlinear_forward_many(hs, LAYERS, xp, _lib.BF16, m, yp, _lib.F32, torch.cuda.current_stream(dev).cuda_stream)
+        if st:
+            raise RuntimeError(_lib.last_error())
+        dist.all_gather_into_tensor(y_cat_all, y_cat)
+        if fused:
+            got = pg.forward_many(layers, [x] * LAYERS)
+            pg.check()
+            same = torch.equal(got.reshape(world * LAYERS, m, N_OUT), y_cat_all)
+        else:
+            same = True  # the timed path IS the library collective
+        flag = torch.tensor([1.0 if same and device_status == 0 else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gather_checked = bool(flag.item() == 1.0)
+
+    # end to end through host buffers: pinned host X in, every layer's (at N > 1: every rank's) Y back on the host
     xh = torch.empty(m, K_IN, dtype=torch.bfloat16).pin_memory()
     xh.copy_(x.cpu())
-    yh = torch.empty(LAYERS, m, N_OUT, dtype=torch.float32).pin_memory()
+    xd = torch.empty_like(x)
+    xdp = (_lib.vp * LAYERS)(*[xd.data_ptr()] * LAYERS)
+    yh = torch.empty(world * LAYERS, m, N_OUT, dtype=torch.float32).pin_memory()
     xhp = (_lib.vp * LAYERS)(*[xh.data_ptr()] * LAYERS)
     yhp = (_lib.vp * LAYERS)(*[yh[i].data_ptr() for i in range(LAYERS)])
 
     def step_host():
+        if world > 1:  # copy in, the forward with its exchange, copy the gathered outputs out
+            cur = torch.cuda.current_stream(dev).cuda_stream
+            xd.copy_(xh, non_blocking=True)
+            if fused:
+                got = pg.forward_many(layers, [xd] * LAYERS)
+                yh.view(world, LAYERS, m, N_OUT).copy_(got, non_blocking=True)
+            else:
+                st = lib.qb200_qlinear_forward_many(hs, LAYERS, xdp, _lib.BF16, m, yp, _lib.F32, cur)
+                if st:
+                    raise RuntimeError(_lib.last_error())
+                dist.all_gather_into_tensor(y_cat_all, y_cat)
+                yh.copy_(y_cat_all, non_blocking=True)
+            torch.cuda.synchronize(dev)
+            return
         if grouped:  # one call: x copied once, one persistent launch, every layer's y copied back
             st = lib.qb200_qlinear_forward_many_host(hs, LAYERS, xhp, _lib.BF16, m, yhp, _lib.F32)
             if st:
@@ -494,11 +664,20 @@ def run_ours(args):
             if st:
                 raise RuntimeError(_lib.last_error())
 
-    for _ in range(0 if args.profile else 3):
+    for _ in range(0 if args.profile else 4):
         step_host()
     barrier()
     t0 = time.perf_counter()
-    e2e_steps = 1 if args.profile else max(1, min(args.steps, 20))
+    step_host()
+    step_host()
+    probe = max((time.perf_counter() - t0) / 2, 1e-6)
+    e2e_steps = 2 if args.profile else int(min(max(0.2 / probe, 20), 20000)) & ~1
+    if world > 1:
+        cnt = torch.tensor([e2e_steps], device=dev, dtype=torch.int64)
+        dist.broadcast(cnt, 0)
+        e2e_steps = int(cnt.item())
+    barrier()
+    t0 = time.perf_counter()
     for _ in range(e2e_steps):
         step_host()
     barrier()
@@ -509,37 +688,46 @@ def run_ours(args):
         e2e_s = float(tmax.item())
     e2e = layer_bytes(m) * LAYERS * e2e_steps * world / e2e_s / 1e9
 
+    extras = None
+    if not args.profile and not args.no_extras:
+        extras = measure_extras(torch, qb, dev, world=world)
     if rank == 0:
         peak, which = measured_peak_gbs()
         # the dominant kernel is launched once per step (grouped) or once per layer; at N > 1 the step's time also
         # holds the exchange, so the fraction below is a lower bound there
-        per_launch_s = ms * 1e-3 / ((1 if grouped else LAYERS) * args.steps)
+        per_launch_s = ms * 1e-3 / ((1 if grouped else LAYERS) * steps)
         achieved = layer_bytes(m) * (LAYERS if grouped else 1) / per_launch_s / 1e9
+        par = "single GPU" if world == 1 else f"column-sharded x{world}, every rank's outputs on every rank after each step"
         line = {
-            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 x int4 -> f32", "data": "synthetic",
-            "config": {"workload": f"int4 decode GEMV W[{N_OUT},{K_IN}] grid 1x{GROUP}, X bf16 [{m},{K_IN}], f32 out",
-                       "layers_per_step": LAYERS, "l2": "inputs larger than L2 (32 distinct weight matrices, 286 MB)",
-                       "kernel": layers[0].last_kernel(), "launch": ("one persistent launch per step" if grouped else "one launch per layer") +
-                                 (", eager" if args.no_graph else ", cuda graph replay"),
-                       "parallelism": "single GPU" if world == 1 else (
-                           f"column-sharded x{world}, outputs stored to every rank's buffer by the kernel (peer memory), arrival barrier in the same launch" if fused
-                           else f"column-sharded x{world}, one NCCL all-gather of the step's outputs" if grouped
-                                        else f"column-sharded x{world}, all-gather per layer")},
+            "config": bench_config(m, world),
+            "timing": {"blocks": n_blocks, "steps_per_block": steps, "reported": "median block, max over ranks per block",
+                       "timed_region_s": timed_region_s, "block_ms_min": float(times.min().item()), "block_ms_max": float(times.max().item())},
+            "impl_detail": {"kernel": layers[0].last_kernel(),
+                            "launch": ("one persistent launch per step" if grouped else "one launch per layer") +
+                                      (", eager" if args.no_graph else ", cuda graph replay of two steps"),
+                            "exchange": None if world == 1 else (
+                                "stored to every rank's buffer by the kernel (peer memory), two receive buffers used in turn, arrival barrier in the same launch" if fused
+                                else "one NCCL all-gather of the step's outputs" if grouped else "NCCL all-gather per layer")},
             "clocks": clocks.summary(),
-            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": (1 if grouped else LAYERS) * m * K_IN * 2,
-                    "d2h_bytes_per_step": LAYERS * m * N_OUT * 4,
-                    "call": "qb200_qlinear_forward_many_host" if grouped else "qb200_qlinear_forward_host"},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": (1 if grouped or world > 1 else LAYERS) * m * K_IN * 2,
+                    "d2h_bytes_per_step": world * LAYERS * m * N_OUT * 4, "steps": e2e_steps,
+                    "call": ("copy in + fused forward / exchange + copy out of the gathered outputs" if world > 1 else
+                             "qb200_qlinear_forward_many_host" if grouped else "qb200_qlinear_forward_host")},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # dram__bytes_read + write of one ncu capture of an 8-layer launch (71.35 + 0.85 MB),
-                         # scaled by the layers a launch processes (traffic grows in proportion)
-                         "traffic": 72.20e6 / 8 * (LAYERS if grouped else 1) if m == 1 else None,
+                         "frac_nominal": achieved / NOMINAL_HBM_GBS, "nominal_peak": NOMINAL_HBM_GBS,
+                         "traffic": TRAFFIC_PER_LAYER.get(m) * (LAYERS if grouped else 1) if TRAFFIC_PER_LAYER.get(m) else None,
+                         "traffic_source": TRAFFIC_SOURCE if TRAFFIC_PER_LAYER.get(m) else None,
                          "peak_source": which, "launch_us": per_launch_s * 1e6},
         }
-        if world == 1 and not args.profile and not args.no_extras:
-            line["extras"] = measure_extras(torch, qb, dev)
+        if world > 1:
+            line["gather_checked"] = gather_checked
+            line["device_status"] = device_status
+        if extras is not None:
+            line["extras"] = extras
         if world == 1 and not args.no_cpu and not args.profile:
             import oracle as o
             threads = o.max_threads()
@@ -551,11 +739,19 @@ def run_ours(args):
                                               f"f32 GEMM, {threads} OpenMP threads"}
         print(json.dumps(line), flush=True)
     if world > 1:
-        # leave without tearing the process group down: destroying it while a captured graph that
-        # holds collectives is alive can block
-        barrier()
-        sys.stdout.flush()
-        os._exit(0)
+        if gather_checked is False:
+            print("bench.py: the gathered outputs differ from the NCCL all-gather, or a device wait timed out", file=sys.stderr)
+        _leave(torch, dist, dev, 0 if gather_checked else 3)
+
+
+def _leave(torch, dist, dev, code=0):
+    """Leaves a multi-rank run without tearing the process group down: destroying it while a captured graph that
+    holds collectives is alive can block."""
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(code)
 
 
 def main():

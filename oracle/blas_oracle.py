@@ -5,10 +5,11 @@ codes cast to f32, the inner product accumulated in f32 left to right, ``alpha_e
 :212-226 and :235-262.  The loop over k is kept sequential; rows and columns are vectorised, which does not
 change any entry's order of operations.
 
-Parity pin: the reference's tests for this path (crates/sci/quanta-blas/tests/gemm_quant.rs) hold no literal
-outputs — they compare the device with this very function — so the pin is the property that those tests'
-inputs make exact: every running sum stays far below 2^24, where f32 accumulation is integer arithmetic, and
-``tests/test_blas_oracle.py`` checks this restatement against exact integer sums on those inputs.
+Parity pin: the two literal cases of the reference's own tests for these functions (``gemm_q8_sym_basic`` and
+``gemm_q4_sym_basic``, crates/sci/quanta-blas/src/reference.rs:1119-1148) are reproduced in ``tests/golden/kats.py`` and
+checked in ``tests/test_blas_oracle.py``; the device tests of the reference (crates/sci/quanta-blas/tests/gemm_quant.rs)
+compare the device with this very function on inputs whose running sums stay far below 2^24, where f32 accumulation
+is integer arithmetic, and the same file checks the restatement against exact integer sums on those inputs.
 """
 from __future__ import annotations
 

@@ -259,7 +259,7 @@ int qo_dequantize_host(const void* codes, uint64_t codes_len, const float* scale
  *
  * wd is the already-dequantized weight.  layout 0: wd is [in, out] (the
  * reference's Linear orientation, y = x @ wd); layout 1: wd is [out, in]
- * (y = x @ wd^T, the orientation BASELINE configs are written in).  The
+ * (y = x @ wd^T, the K-contiguous orientation of the decode and prefill workloads).  The
  * summation order over k is the same in both.  threads <= 1 runs serial;
  * otherwise output rows*cols are spread over OpenMP threads (the reference's
  * CPU lane spreads workgroups over available_parallelism() threads,

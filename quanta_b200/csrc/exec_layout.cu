@@ -1,0 +1,152 @@
+// Execution layouts of a QuantizedLinear handle, built once at creation.
+//
+// The fast int4 kernels read K-contiguous rows: codes `[out, in / 8]` with a 1 x 128 scale grid, at most 4096
+// inputs per launch.  Two stored layouts do not have that shape as they are:
+//   - the reference's own `[in, out]` weight with Group{axis: 0, size: 128} (QuantizedLinear::new takes
+//     `w: [in, out]`, crates/ml/quanta-nn/src/quant.rs:853-862): the nibbles run along `out`.  A transposed copy
+//     of codes and scales is a pure permutation — every dequantized weight s * q keeps its bits;
+//   - inputs wider than 4096 (a feed-forward down projection): the decode kernel keeps the activation
+//     fragments of at most 32 scale groups in registers, so the weight is cut into column runs of whole scale
+//     groups, every run padded with zero codes and zero scales to one width and stored with contiguous rows
+//     (an item of the decode kernel is ONE bulk copy).  A decode call is one grouped launch over the runs —
+//     each reads its window of the activations in place — and a fold of their f32 partial outputs.
+// Both are copies (+ 0.5 byte per weight each, + the scales): the stored buffers stay what accessors, writers
+// and the tcgen05 GEMM's tensor maps over `[out, in]` codes see.
+#include <cstdint>
+#include <string>
+
+#include "forward.hpp"
+#include "qlinear_handle.hpp"
+#include "quant_math.cuh"
+
+namespace qb {
+
+constexpr uint32_t SLICE_LIMIT = 4096;  // inputs the decode kernel serves per launch (two scale groups per warp)
+constexpr uint32_t SLICE_MAX = 8;
+
+// dst[n][kw] packs q(k = 8 kw + i, n), i = 0..7, low nibble first; src word (k, n >> 3) holds q(k, n) in nibble n & 7.
+// Threads run along n: the eight reads of a thread are shared by its seven neighbours (one word serves eight n).
+__global__ void __launch_bounds__(256) k_transpose_i4(const uint32_t* __restrict__ src, uint32_t in_dim, uint32_t out_dim,
+                                                      uint32_t src_words, uint32_t* __restrict__ dst) {
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x, kw = blockIdx.y;
+    if (n >= out_dim) return;
+    const uint32_t sh = 4 * (n & 7);
+    uint32_t w = 0;
+#pragma unroll
+    for (uint32_t i = 0; i < 8; i++) {
+        const uint32_t k = 8 * kw + i;
+        if (k < in_dim) w |= ((src[(uint64_t)k * src_words + (n >> 3)] >> sh) & 0xFu) << (4 * i);
+    }
+    dst[(uint64_t)n * (in_dim / 8) + kw] = w;
+}
+
+// dst[n][g] = src[g][n]
+__global__ void __launch_bounds__(256) k_transpose_f32(const float* __restrict__ src, uint32_t rows, uint32_t cols,
+                                                       float* __restrict__ dst) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c < cols) dst[(uint64_t)c * rows + r] = src[(uint64_t)r * cols + c];
+}
+
+// y[i] = sum_s parts[s][i] (+ bias[i % N]): the slices' partial outputs, summed in slice order.
+template <typename YT>
+__global__ void __launch_bounds__(256) k_fold_slices(const float* __restrict__ parts, uint32_t slices, uint64_t mn, uint32_t N,
+                                                     const float* __restrict__ bias, YT* __restrict__ y) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < mn; i += (uint64_t)gridDim.x * blockDim.x) {
+        float v = 0.0f;
+        for (uint32_t s = 0; s < slices; s++) v += parts[s * mn + i];
+        if (bias) v += bias[i % N];
+        if constexpr (sizeof(YT) == 4) y[i] = v;
+        else y[i] = f32_to_bf16_bits(v);
+    }
+}
+
+void free_exec_layout(qb200_qlinear* ql) {
+    if (ql->t_codes) cudaFree(ql->t_codes);
+    if (ql->t_scales) cudaFree(ql->t_scales);
+    if (ql->slice_codes) cudaFree(ql->slice_codes);
+    if (ql->slice_scales) cudaFree(ql->slice_scales);
+    if (ql->slice_partials) cudaFree(ql->slice_partials);
+    ql->t_codes = ql->slice_codes = nullptr;
+    ql->t_scales = ql->slice_scales = ql->slice_partials = nullptr;
+    ql->n_slices = 0;
+}
+
+qb200_status build_exec_layout(qb200_qlinear* ql) {
+    if (ql->bits != 4 || ql->in_dim % 128 != 0 || ql->in_dim == 0 || ql->out_dim == 0 || ql->out_dim > 0x7FFFFFFFull ||
+        ql->in_dim > (uint64_t)SLICE_LIMIT * SLICE_MAX)
+        return QB200_OK;
+    const uint32_t K = (uint32_t)ql->in_dim, N = (uint32_t)ql->out_dim, groups = K / 128;
+    if (ql->layout == QB200_IN_OUT) {
+        if (ql->gr != 128 || ql->gc != 1) return QB200_OK;  // only the documented int4 grid of an [in, out] weight
+        QB_CUDA_TRY(cudaMalloc(&ql->t_codes, (uint64_t)N * (K / 8) * 4));
+        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, (uint64_t)N * groups * 4));
+        k_transpose_i4<<<dim3((N + 255) / 256, K / 8), 256>>>(static_cast<const uint32_t*>(ql->codes), K, N, (N + 7) / 8,
+                                                               static_cast<uint32_t*>(ql->t_codes));
+        QB_CUDA_TRY(cudaGetLastError());
+        k_transpose_f32<<<dim3((N + 255) / 256, groups), 256>>>(ql->scales, groups, N, ql->t_scales);
+        QB_CUDA_TRY(cudaGetLastError());
+    } else if (ql->gr != 1 || ql->gc != 128) {
+        return QB200_OK;
+    }
+    if (K > SLICE_LIMIT) {
+        const uint32_t n = (K + SLICE_LIMIT - 1) / SLICE_LIMIT, base = groups / n, extra = groups % n;
+        uint32_t widest = 0, c0 = 0;
+        for (uint32_t s = 0; s < n; s++) {
+            ql->slice_col0[s] = c0;
+            ql->slice_width[s] = (base + (s < extra ? 1u : 0u)) * 128;
+            c0 += ql->slice_width[s];
+            widest = widest > ql->slice_width[s] ? widest : ql->slice_width[s];
+        }
+        const uint32_t pad = (widest + 511) / 512 * 512;  // rows of scales that are whole 16-byte units
+        const uint64_t cbytes = (uint64_t)n * N * (pad / 2), sbytes = (uint64_t)n * N * (pad / 128) * 4;
+        QB_CUDA_TRY(cudaMalloc(&ql->slice_codes, cbytes));
+        QB_CUDA_TRY(cudaMalloc(&ql->slice_scales, sbytes));
+        QB_CUDA_TRY(cudaMalloc(&ql->slice_partials, (uint64_t)n * 16 * N * 4));
+        QB_CUDA_TRY(cudaMemset(ql->slice_codes, 0, cbytes));
+        QB_CUDA_TRY(cudaMemset(ql->slice_scales, 0, sbytes));
+        const uint8_t* codes = static_cast<const uint8_t*>(ql->fast_codes());
+        const float* scales = ql->fast_scales();
+        for (uint32_t s = 0; s < n; s++) {
+            QB_CUDA_TRY(cudaMemcpy2D(static_cast<uint8_t*>(ql->slice_codes) + (uint64_t)s * N * (pad / 2), pad / 2,
+                                     codes + ql->slice_col0[s] / 2, K / 2, ql->slice_width[s] / 2, N, cudaMemcpyDeviceToDevice));
+            QB_CUDA_TRY(cudaMemcpy2D(ql->slice_scales + (uint64_t)s * N * (pad / 128), (pad / 128) * 4,
+                                     scales + ql->slice_col0[s] / 128, groups * 4, (ql->slice_width[s] / 128) * 4, N,
+                                     cudaMemcpyDeviceToDevice));
+        }
+        ql->n_slices = n;
+        ql->slice_pad = pad;
+    }
+    QB_CUDA_TRY(cudaDeviceSynchronize());
+    return QB200_OK;
+}
+
+qb200_status forward_sliced(qb200_qlinear* ql, const void* x, uint64_t m, void* y, int y_dtype, cudaStream_t st) {
+    const uint32_t n = ql->n_slices, pad = ql->slice_pad, N = (uint32_t)ql->out_dim;
+    FwdArgs a[SLICE_MAX];
+    for (uint32_t s = 0; s < n; s++) {
+        a[s].codes = static_cast<const uint8_t*>(ql->slice_codes) + (uint64_t)s * N * (pad / 2);
+        a[s].scales = ql->slice_scales + (uint64_t)s * N * (pad / 128);
+        a[s].bias = nullptr;  // added once, by the fold
+        a[s].x = static_cast<const uint16_t*>(x) + ql->slice_col0[s];
+        a[s].y = ql->slice_partials + (uint64_t)s * m * N;
+        a[s].m = m;
+        a[s].in_dim = pad;
+        a[s].out_dim = N;
+        a[s].gr = 1;
+        a[s].gc = 128;
+        a[s].tc = pad / 128;
+        a[s].x_stride = ql->in_dim;
+        a[s].k_valid = ql->slice_width[s];
+    }
+    if (qb200_status r = gemv_i4_forward_many(a, n, QB200_F32, ql->status, st)) return r;
+    const uint64_t mn = m * N;
+    const uint32_t blocks = (uint32_t)((mn + 255) / 256 > 592 ? 592 : (mn + 255) / 256);
+    if (y_dtype == QB200_F32)
+        k_fold_slices<float><<<blocks, 256, 0, st>>>(ql->slice_partials, n, mn, N, ql->bias, static_cast<float*>(y));
+    else
+        k_fold_slices<uint16_t><<<blocks, 256, 0, st>>>(ql->slice_partials, n, mn, N, ql->bias, static_cast<uint16_t*>(y));
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+}  // namespace qb

@@ -15,6 +15,9 @@ struct FwdArgs {
     void* y;              // [m, out_dim]
     uint64_t m, in_dim, out_dim;
     uint64_t gr, gc, tc;  // tile and scale-grid row length (ceil(cols/gc))
+    // decode GEMV only: x may be a column window of a wider activation matrix — rows `x_stride` elements apart
+    // (0: in_dim), of which only the first `k_valid` columns exist (0: in_dim; the rest read as zero)
+    uint64_t x_stride = 0, k_valid = 0;
 };
 
 #ifdef __CUDACC__
@@ -22,7 +25,7 @@ struct FwdArgs {
 qb200_status forward_generic(const FwdArgs& a, uint32_t bits, int x_dtype, int y_dtype, bool rows_kernel,
                              float* scratch, uint32_t slices, cudaStream_t st);
 #endif
-// Decode GEMV on the tensor pipe (gemv_decode.cu): int4, 1x128 grid, OUT_IN, bf16 x, m <= 16.
+// Decode GEMV on the tensor pipe (gemv_decode.cu): int4, 1x128 grid, OUT_IN, bf16 x, m <= 16, in_dim <= 4096.
 bool gemv_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* scales, const void* x);
 // Fused all-gather: byte offsets from this rank's output buffer to every rank's copy of it (as mapped in

@@ -11,6 +11,7 @@
 //                K (coalesced along N); K is split across warps and, for small
 //                N, across CTAs — partial sums go to a scratch buffer and a
 //                second kernel folds them, adds the bias and casts.
+#include <atomic>
 #include <cstdint>
 #include <string>
 
@@ -360,15 +361,21 @@ extern "C" qb200_status qb200_qlinear_forward_static(qb200_qlinear* ql, const vo
                         " partial sums, the built-in scratch holds " + std::to_string(qb::STATIC_SCRATCH_FLOATS) +
                         " (2 MiB); lower m or call qb200_qlinear_forward");
     // The array's name is a host-side stand-in here, not a device address: look the address up once
-    // per device, with that device current.
-    static float* scratch_of_device[64] = {};
+    // per device, with that device current.  Every GPU has its own copy of the array, so the address must be
+    // the one of the GPU that holds the handle's buffers and runs the kernels: the call is refused when another
+    // device is current.  Threads may race to fill an entry; they all store the same address.
+    static std::atomic<float*> scratch_of_device[64] = {};
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_static: device index out of range");
-    if (!scratch_of_device[dev]) {
-        float* p = nullptr;
-        QB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials));
-        scratch_of_device[dev] = p;
+    if (ql->device >= 0 && dev != ql->device)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_static: the handle's buffers live on device " +
+                                                 std::to_string(ql->device) + " but device " + std::to_string(dev) +
+                                                 " is current; make the handle's device current before the call");
+    float* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+    if (!scratch) {
+        QB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_static_partials));
+        scratch_of_device[dev].store(scratch, std::memory_order_release);
     }
     qb::FwdArgs a;
     a.codes = ql->codes;
@@ -383,6 +390,6 @@ extern "C" qb200_status qb200_qlinear_forward_static(qb200_qlinear* ql, const vo
     a.gc = ql->gc;
     a.tc = ql->tc;
     // Nothing needs clearing: the column kernel writes every partial sum the fold kernel reads.
-    return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, false, scratch_of_device[dev], slices,
-                               static_cast<cudaStream_t>(stream));
+    ql->last_kernel = "generic_cols";
+    return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, false, scratch, slices, static_cast<cudaStream_t>(stream));
 }

@@ -178,18 +178,6 @@ __device__ __forceinline__ void pf_fma2(float& t0, float& t1, uint64_t s2, float
         : "l"(s2), "f"(v0), "f"(v1));
 }
 
-#ifdef QB_PF_TRACE
-#define PF_TR_DECL long long tr_[6] = {0, 0, 0, 0, 0, 0}, tr_t = 0, tr_s = clock64(); (void)tr_t
-#define PF_TR_B tr_t = clock64()
-#define PF_TR_E(i) tr_[i] += clock64() - tr_t
-#define PF_TR_DUMP(role) do { tr_[5] = clock64() - tr_s; if (a.trace && blockIdx.x < 2) for (int i_ = 0; i_ < 6; i_++) a.trace[(blockIdx.x * 8 + role) * 6 + i_] = tr_[i_]; } while (0)
-#else
-#define PF_TR_DECL
-#define PF_TR_B
-#define PF_TR_E(i)
-#define PF_TR_DUMP(role)
-#endif
-
 struct PrefillArgs {
     const float* scales;  // [N, K/128]
     const float* bias;    // [N] or null
@@ -198,8 +186,6 @@ struct PrefillArgs {
     uint32_t M, N, K;
     uint32_t ksplit;     // K ranges per output tile (1: the kernel writes Y itself)
     uint32_t tma_store;  // 1 when Y's base and row pitch are multiples of 16 bytes
-    long long* trace;
-    uint32_t dbg;
 };
 
 // One packed word -> eight bf16 values q / 64 in natural k order (four registers).
@@ -296,20 +282,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             if (lane == 0) {
                 uint64_t* landed = rank == 0 ? full : full_x;  // the leader's tile counts towards `full` directly
                 uint32_t st = 0, par = 0, it = 0;
-                PF_TR_DECL;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
                     const uint32_t tile = t / ksplit, k_first = (t % ksplit) * num_k;
                     const int32_t x_row = (int32_t)((tile % m_tiles) * PF_TM + rank * 128);
                     for (uint32_t s = 0; s < num_k; s++, it++) {
-                        PF_TR_B;
                         if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
-                        PF_TR_E(1);
                         pf_mbar_expect_tx(&landed[st], PF_STAGE);
                         pf_tma_load_2d(sX + st * PF_STAGE, &xmap, (int32_t)((k_first + s) * PF_BK), x_row, &landed[st]);
                         if (++st == PF_S) { st = 0; par ^= 1; }
                     }
                 }
-                PF_TR_DUMP(0);
             }
         } else if (warp == 1) {
             // ---- MMA issuer (the pair's leader only) ----
@@ -324,16 +306,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                 uint32_t st = 0, par = 0, gcount = 0;  // gcount: k-groups issued, over all tiles
                 uint32_t ready = 0;                    // this k-step's `full` phase was seen complete by the early poll
                 uint32_t dready = 0;                   // the same for the next k-group's accumulator
-                PF_TR_DECL;
                 for (uint32_t it = 0; it < total; it++) {
                     const uint32_t odd = it & 1, buf = gcount & 1;
-                    PF_TR_B;
                     if (!odd && gcount >= 2 && !dready && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
-                    PF_TR_E(0);
-                    PF_TR_B;
                     if (!ready && !pf_wait(&full[st], par)) { failed = true; break; }
-                    PF_TR_E(1);
-                    PF_TR_B;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
                     ready = it + 1 < total ? pf_test(&full[st1], par1) : 0;
@@ -351,9 +327,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     gcount += odd;
                     st = st1;
                     par = par1;
-                    PF_TR_E(4);
                 }
-                if (elected) PF_TR_DUMP(1);
             }
         } else if (warp == 2) {
             // ---- non-leader: pass "activation tile landed" on to the leader's barrier ----
@@ -391,23 +365,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         const uint32_t q_row = r * 64, q_sw = ((r >> 1) & 3) << 4;
         const uint32_t remote_full = pf_map_to_cta(pf_smem(&full[0]), 0);
         uint32_t st = 0, par = 0, sq = 0, pq = 0;
-        PF_TR_DECL;
         // one k-group (two k-steps, one packed-code slot) per iteration: one fence and one round of
         // barrier latencies for 16 independent words per thread
         for (uint32_t it = 0; it < total; it += 2) {
-            PF_TR_B;
             if (!pf_wait(&full_q[sq], pq)) { failed = true; break; }
-            PF_TR_E(0);
             const uint8_t* qs = sQ + sq * PF_Q_BYTES + q_row;
             uint4 q[4];
 #pragma unroll
             for (uint32_t c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4*>(qs + ((c << 4) ^ q_sw));
             const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
-            PF_TR_B;
             if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
             if (it + 1 >= PF_S && !pf_wait(&empty[st1], par1 ^ 1)) { failed = true; break; }
-            PF_TR_E(1);
-            PF_TR_B;
             pf_unpack_row(sA + st * PF_STAGE, row_off, q[0], q[1]);
             pf_unpack_row(sA + st1 * PF_STAGE, row_off, q[2], q[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the tensor core
@@ -420,20 +388,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
             st = st1 + 1 == PF_S ? 0 : st1 + 1;
             par = st1 + 1 == PF_S ? par1 ^ 1 : par1;
-            PF_TR_E(2);
         }
-        if (lane == 0) PF_TR_DUMP(warp - 2);
     } else {
         // ---- epilogue warps: thread = weight row (TMEM lane), warpgroup = 128-column half of the m range ----
         asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
         const uint32_t quad = warp & 3, half = (warp - 8) >> 2, ml = quad * 32 + lane;
         const uint32_t remote_dempty = pf_map_to_cta(pf_smem(&dempty[0]), 0);
-        const bool vec_scales = ((row_groups | groups) & 3u) == 0;  // a unit's scales start on a 16-byte boundary
+        // a unit's scales start on a 16-byte boundary (rows of whole 16-byte units from an aligned base)
+        const bool vec_scales = ((row_groups | groups) & 3u) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 15u) == 0;
         const bool issuer = quad == 0 && lane == 0;  // the thread of this half that issues its TMA stores
         constexpr uint32_t ROWS = PF_Y_BYTES / 2 / (128 * sizeof(YT));  // activation rows per staging pass (two buffers)
         YT* stage = reinterpret_cast<YT*>(sY + half * PF_Y_BYTES);
         uint32_t gcount = 0;
-        PF_TR_DECL;
         for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
             const uint32_t tile = t / ksplit, ks = t % ksplit;
             const uint32_t n_cta = (tile / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
@@ -463,10 +429,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                 for (uint32_t gi = 0; gi < 4; gi++) {
                     if (g0 + gi >= groups) break;
                     const uint32_t buf = gcount & 1;
-                    PF_TR_B;
                     if (!pf_wait(&dfull[buf], (gcount >> 1) & 1)) { failed = true; break; }
-                    PF_TR_E(0);
-                    PF_TR_B;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t s2 = pf_pack2(cur[gi], cur[gi]);
 #pragma unroll
@@ -482,10 +445,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     __syncwarp();
                     if (lane == 0) pf_mbar_arrive_cluster(remote_dempty + buf * 8);
                     gcount++;
-                    PF_TR_E(1);
                 }
             }
-            PF_TR_B;
             if (failed) break;
             const float b = (a.bias && n_ok) ? __ldg(a.bias + n) : 0.0f;
             if (a.tma_store) {
@@ -529,10 +490,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
                     }
                 }
             }
-            PF_TR_E(2);
         }
         if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before shared memory goes away
-        if (lane == 0 && (warp == 8 || warp == 12)) PF_TR_DUMP(warp == 8 ? 6 : 7);
     }
     if (failed) atomicExch(a.status, QB200_ERR_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -663,15 +622,6 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     a.M = M;
     a.N = N;
     a.K = K;
-    a.trace = nullptr;
-    a.dbg = 0;
-#ifdef QB_PF_TRACE
-    static long long* trace_dev = nullptr;
-    if (!trace_dev) { cudaMalloc(&trace_dev, 2 * 8 * 6 * 8); }
-    cudaMemsetAsync(trace_dev, 0, 2 * 8 * 6 * 8, st);
-    a.trace = trace_dev;
-    a.dbg = getenv("QB_PF_DBG") ? (uint32_t)atoi(getenv("QB_PF_DBG")) : 0;
-#endif
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
     static int sm_count[64] = {};
@@ -714,20 +664,6 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
                                                              static_cast<uint16_t*>(f.y));
         QB_CUDA_TRY(cudaGetLastError());
     }
-#ifdef QB_PF_TRACE
-    {
-        long long h[2 * 8 * 6];
-        cudaStreamSynchronize(st);
-        cudaMemcpy(h, trace_dev, sizeof(h), cudaMemcpyDeviceToHost);
-        const char* roles[8] = {"tma  [wait_q wait_x - - - total]", "mma  [dempty full_x peer_x full_a issue total]", "unp4 [full_q empty_a work - - total]", "unp5", "unp6", "unp7", "epi8 [dfull work store - - total]", "epi12"};
-        for (int c = 0; c < 2; c++)
-            for (int r = 0; r < 8; r++) {
-                fprintf(stderr, "cta%d %-48s", c, roles[r]);
-                for (int i = 0; i < 6; i++) fprintf(stderr, " %9lld", h[(c * 8 + r) * 6 + i]);
-                fprintf(stderr, "\n");
-            }
-    }
-#endif
     return QB200_OK;
 }
 

@@ -17,7 +17,7 @@ struct RegItem {
     const float* bias;
     const uint8_t* codes;
     const float* scales;
-    uint32_t row0, nrows, N, pad;
+    uint32_t row0, nrows, N, layer;  // layer: index of the launch's layer descriptor (input row stride, valid columns)
 };
 constexpr uint32_t REG_MAX_ITEMS = 120;  // items per CTA and launch (descriptors: 6.6 KB of shared memory)
 
@@ -41,14 +41,15 @@ __host__ __device__ inline RegSmem reg_smem_layout(uint32_t K, uint32_t nt, uint
 
 // Activation fragment of one scale group for batch row b: the thread's 32 consecutive bf16,
 // permuted to the nibble order and scaled; returns their plain sum (for the "+ 8" correction).
-__device__ __forceinline__ float load_fragment(const uint16_t* __restrict__ x, uint32_t K, uint32_t b, uint32_t G,
-                                               uint32_t t, bool valid, uint4 (&frag)[4]) {
+// ldx: elements between the rows of x.  out_of_domain is set when an activation cannot take the 2^40 pre-scale.
+__device__ __forceinline__ float load_fragment(const uint16_t* __restrict__ x, uint32_t ldx, uint32_t b, uint32_t G,
+                                               uint32_t t, bool valid, uint4 (&frag)[4], bool& out_of_domain) {
     uint32_t klo = X_SCALE_LO, khi = X_SCALE_HI;
     const __nv_bfloat162 slo = *reinterpret_cast<const __nv_bfloat162*>(&klo);
     const __nv_bfloat162 shi = *reinterpret_cast<const __nv_bfloat162*>(&khi);
     uint32_t xr[16];
     if (valid) {
-        const uint4* xp = reinterpret_cast<const uint4*>(x + (uint64_t)b * K + G * 128 + t * 32);
+        const uint4* xp = reinterpret_cast<const uint4*>(x + (uint64_t)b * ldx + G * 128 + t * 32);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             uint4 v = __ldg(xp + i);
@@ -59,8 +60,13 @@ __device__ __forceinline__ float load_fragment(const uint16_t* __restrict__ x, u
         for (int i = 0; i < 16; i++) xr[i] = 0;
     }
     float sum = 0.0f;
+    uint32_t top = 0;  // the largest exponent field among the 32 activations
 #pragma unroll
-    for (int i = 0; i < 16; i++) sum += bf16_bits_to_f32(xr[i] & 0xFFFFu) + bf16_bits_to_f32(xr[i] >> 16);
+    for (int i = 0; i < 16; i++) {
+        sum += bf16_bits_to_f32(xr[i] & 0xFFFFu) + bf16_bits_to_f32(xr[i] >> 16);
+        top = max(top, max(xr[i] & 0x7F80u, (xr[i] >> 16) & 0x7F80u));
+    }
+    if (top >= ((127u + 87u) << 7)) out_of_domain = true;  // |x| >= 2^87, infinite or NaN: the 2^40 pre-scale would overflow
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         uint32_t o[4];

@@ -21,7 +21,18 @@ namespace qb {
 // group of four warps, so 17 warps are budgeted as 20: 96 each), so that kernel is launched with a whole fifth
 // warp group — three of its warps leave at once — which hands most of its registers to the compute warps.
 constexpr uint32_t ASYNC_THREADS = REG_THREADS + 32, ASYNC_THREADS_WIDE = REG_THREADS + 128;
-__host__ __device__ constexpr uint32_t async_threads(int nt) { return nt == 2 ? ASYNC_THREADS_WIDE : ASYNC_THREADS; }
+// The registers a warp group gains must have been given up by another group of the same CTA first (registers the
+// CTA never held cannot be claimed; a request that cannot be met waits for ever).  640 threads start with 96 each.
+constexpr uint32_t ASYNC_REGS_LAUNCH = 96, ASYNC_REGS_COMPUTE = 112, ASYNC_REGS_SERVICE = 32;
+static_assert((ASYNC_REGS_LAUNCH - ASYNC_REGS_SERVICE) * 4 >= (ASYNC_REGS_COMPUTE - ASYNC_REGS_LAUNCH) * REG_WARPS,
+              "the compute warps would wait for registers that nobody releases");
+static_assert(ASYNC_THREADS_WIDE * ASYNC_REGS_LAUNCH <= 65536 && ASYNC_THREADS_WIDE * (ASYNC_REGS_LAUNCH + 8) > 65536,
+              "the launch bound must make the compiler start every warp with ASYNC_REGS_LAUNCH registers");
+#define QB_STR2(x) #x
+#define QB_STR(x) QB_STR2(x)
+// NSERV service warps share the fold of a sub-item (a single warp folding eight or more batch columns for sixteen
+// partial sums each became the slowest stage of the pipeline).
+__host__ __device__ constexpr uint32_t async_threads(int nt, int nserv) { return nt == 2 ? ASYNC_THREADS_WIDE : REG_THREADS + 32 * nserv; }
 
 // Shared-memory carve-up of the service-warp kernel, identical on host and device.
 // sub_rows: rows folded at a time; red_stride: floats between rows of a slot of partial sums.
@@ -43,9 +54,10 @@ __host__ __device__ inline AsyncSmem async_smem_layout(uint32_t K, uint32_t rb, 
     L.total = L.codes + stages * L.stage_codes;
     return L;
 }
-// Row stride of a slot for `cols` kept batch columns: two floats of padding spread the rows over
-// the banks for the service warp's reads (lane = row); a pair of columns needs none.
-__host__ __device__ inline uint32_t async_red_stride(uint32_t cols) { return cols <= 2 ? cols : cols + 2; }
+// Row stride of a slot for `cols` kept batch columns (2, 4 or a multiple of 4): the service warps read a row four
+// columns at a time (16 bytes, lane = row), which is free of bank conflicts when the stride is an odd number of
+// 16-byte units (padded by one unit where it would be even).
+__host__ __device__ inline uint32_t async_red_stride(uint32_t cols) { return cols <= 2 ? cols : ((cols / 4) | 1u) * 4; }
 
 // shared-memory accesses and barrier polls on 32-bit shared addresses
 __device__ __forceinline__ uint4 async_lds128(uint32_t a) {
@@ -78,8 +90,8 @@ __device__ __forceinline__ bool async_wait_bounded(uint32_t bar, uint32_t parity
     return false;
 }
 
-template <int NT, int RB, typename YT>
-__global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
+template <int NT, int RB, int NSERV, typename YT>
+__global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int SUBS = NT == 2 ? RB : 1;  // sub-items (parked and folded separately) per item
     constexpr int RPS = RB / SUBS;          // row blocks per sub-item
@@ -104,7 +116,7 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
     const bool async_scales = a.async_scales != 0;  // scales not 16-byte aligned: 4-byte async copies
 
     // Every item this CTA will process is described once, up front (thread i describes item i).
-    for (uint32_t j = tid; j < n_my; j += async_threads(NT)) {
+    for (uint32_t j = tid; j < n_my; j += async_threads(NT, NSERV)) {
         const uint32_t item = item_first + j;
         uint32_t l = 0;
         while (l + 1 < a.count && item >= a.layer[l + 1].item0) l++;
@@ -113,6 +125,7 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
         d.row0 = (item - ly.item0) * ly.rows_per_item;
         d.nrows = min(ly.rows_per_item, ly.N - d.row0);
         d.N = ly.N;
+        d.layer = l;
         d.x = ly.x;
         d.y = ly.y;
         d.bias = ly.bias;
@@ -142,28 +155,31 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
         for (uint32_t s = 0; s < S; s++) mbar_init(&bars[s], async_scales ? 1 + 32 : 1);
         for (uint32_t s = 0; s < 2; s++) {
             mbar_init(&done[s], REG_WARPS);
-            mbar_init(&vacant[s], 1);
+            mbar_init(&vacant[s], NSERV);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     bool failed = false;
     if (warp >= REG_WARPS) {
-        // 20 warps were launched with 96 registers each: 16 x 120 + 4 x 32 is the same total.  The two roles
+        // 20 warps were launched with 96 registers each: 16 x 112 + 4 x 32 is the same total.  The two roles
         // stay in separate branches to the end, so each is compiled for its own register budget.
         if constexpr (NT == 2) {
-            asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
-            if (warp > REG_WARPS) return;
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 " QB_STR(32) ";");
+            static_assert(ASYNC_REGS_SERVICE == 32, "keep the instruction's literal and the constant together");
         }
-        for (uint32_t j = 0; j < S && j < n_my; j++) issue(j, j);
+        const uint32_t sw = warp - REG_WARPS;  // service warp 0 also refills the stages
+        if (sw >= NSERV) return;
+        if (sw == 0)
+            for (uint32_t j = 0; j < S && j < n_my; j++) issue(j, j);
         // The codes and scales do not depend on the previous kernel; everything below may.
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        // ---- service warp: refill, fold, store ----
-        // lane -> (row, batch column) of a sub-item: 32-row sub-items give every lane a row and all the columns;
-        // 16-row sub-items give a half-warp the even columns and the other half the odd ones (with the padded
-        // row stride both are free of bank conflicts, and a store instruction writes whole 64- or 128-byte runs)
-        const uint32_t row_l = SUB_ROWS == 32 ? lane : (lane & 15), b0 = SUB_ROWS == 32 ? 0 : (lane >> 4), bstep = SUB_ROWS == 32 ? 1 : 2;
+        // ---- service warps: refill, fold, store ----
+        // A unit of the fold is one row of the sub-item and four batch columns (two when only two are kept): sixteen
+        // 16-byte reads, one per compute warp, summed in warp order.  Units are dealt to the lanes row first, so a
+        // store instruction writes runs of consecutive outputs.
+        const uint32_t vec = BW < 4 ? BW : 4, units = SUB_ROWS * ((BW + 3) / 4);
         uint32_t st = 0, q = 0;
         for (uint32_t j = 0; j < n_my && !failed; j++) {
             const RegItem& it = s_desc[j];
@@ -171,23 +187,40 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
             for (int s = 0; s < SUBS; s++, q++) {
                 const uint32_t slot = q & 1;
                 if (!mbar_wait_bounded(&done[slot], (q >> 1) & 1)) { failed = true; break; }
-                if (s == SUBS - 1 && j + S < n_my) issue(j + S, st);  // every compute warp has left the stage
-                const float* red = s_red + slot * L.slot_floats + row_l * RS;
-                const uint32_t r = s * SUB_ROWS + row_l;  // row inside the item
-                if (r < it.nrows) {
+                if (sw == 0 && s == SUBS - 1 && j + S < n_my) issue(j + S, st);  // every compute warp has left the stage
+                for (uint32_t u = sw * 32 + lane; u < units; u += NSERV * 32) {
+                    const uint32_t row_l = u % SUB_ROWS, b0 = (u / SUB_ROWS) * 4;
+                    const uint32_t r = s * SUB_ROWS + row_l;  // row inside the item
+                    if (r >= it.nrows || b0 >= a.M) continue;
+                    const float* red = s_red + slot * L.slot_floats + row_l * RS + b0;
+                    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (vec == 4) {
+#pragma unroll 4
+                        for (int w = 0; w < REG_WARPS; w++) {
+                            const float4 p = *reinterpret_cast<const float4*>(red + w * SUB_ROWS * RS);
+                            v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int w = 0; w < REG_WARPS; w++) {
+                            const float2 p = *reinterpret_cast<const float2*>(red + w * SUB_ROWS * RS);
+                            v[0] += p.x; v[1] += p.y;
+                        }
+                    }
                     const uint32_t n = it.row0 + r;
                     const float bias = it.bias ? it.bias[n] : 0.0f;
-                    for (uint32_t b = b0; b < a.M; b += bstep) {
-                        float v = 0.0f;
 #pragma unroll
-                        for (int w = 0; w < REG_WARPS; w++) v += red[w * SUB_ROWS * RS + b];
-                        YT* yp = static_cast<YT*>(it.y) + (uint64_t)b * it.N + n;
-                        const float out = fmaf(v, GEMV_UNSCALE, bias);
-                        if (a.n_peers == 0) {
-                            store_y<YT>(yp, out);
-                        } else {  // fused exchange: the same element of every rank's buffer (peer memory over NVLink)
-                            for (uint32_t p = 0; p < a.n_peers; p++)
-                                store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<uint8_t*>(yp) + a.peer_delta[p]), out);
+                    for (uint32_t i = 0; i < 4; i++) {
+                        const uint32_t b = b0 + i;
+                        if (i < vec && b < a.M) {
+                            YT* yp = static_cast<YT*>(it.y) + (uint64_t)b * it.N + n;
+                            const float out = fmaf(v[i], GEMV_UNSCALE, bias);
+                            if (a.n_peers == 0) {
+                                store_y<YT>(yp, out);
+                            } else {  // fused exchange: the same element of every rank's buffer (peer memory over NVLink)
+                                for (uint32_t p = 0; p < a.n_peers; p++)
+                                    store_y<YT>(reinterpret_cast<YT*>(reinterpret_cast<uint8_t*>(yp) + a.peer_delta[p]), out);
+                            }
                         }
                     }
                 }
@@ -201,7 +234,11 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
         // when all ranks' outputs are here.  flags[p] is rank p's array {arrival of rank 0..7, step counter,
         // count of finished CTAs}.
         if (a.n_peers && a.peer_flags[0]) {
-            __threadfence_system();  // this CTA's peer stores before its count
+            __threadfence_system();  // this warp's peer stores before the count
+            if (NSERV > 1) {  // the other service warps' stores too: they join on a named barrier after their fences
+                asm volatile("bar.sync 1, %0;" ::"r"(NSERV * 32) : "memory");
+                if (sw != 0) goto service_done;
+            }
             uint32_t last = 0;
             uint64_t* mine = a.peer_flags[a.rank];
             if (lane == 0) last = atomicAdd(reinterpret_cast<unsigned int*>(mine + 9), 1u) == gridDim.x - 1 ? 1u : 0u;
@@ -229,9 +266,13 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
                 __threadfence_system();
             }
         }
+    service_done:;
     } else {
         // ---- compute warps ----
-        if constexpr (NT == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+        if constexpr (NT == 2) {
+            asm volatile("setmaxnreg.inc.sync.aligned.u32 " QB_STR(112) ";");
+            static_assert(ASYNC_REGS_COMPUTE == 112, "keep the instruction's literal and the constant together");
+        }
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
         // a compute warp's two scale groups (the second may not exist for short K: it then re-reads the first
@@ -252,7 +293,7 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
         const uint32_t cg1 = v1 ? REG_WARPS * 64 : 0, sg1 = v1 ? REG_WARPS * 4 : 0;
         // where this lane parks its partial sums inside a slot: row g (and g + 8) of a row block, columns 2t, 2t + 1
         const uint32_t red0 = smem_u32(s_red) + ((warp * SUB_ROWS + g) * RS + 2 * t) * 4;
-        const bool keeps = 2 * t < BW;  // columns past the batch are not kept
+        const bool keeps = 2 * t < BW;  // columns past the kept ones are not parked
         const bool keeps1 = 8 + 2 * t < BW;
         uint32_t st = 0, parity = 0, stage_codes = codes0, stage_scales = scales0, q = 0;
         for (uint32_t j = 0; j < n_my; j++, dptr += (uint32_t)sizeof(RegItem)) {
@@ -261,11 +302,16 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
             asm volatile("ld.shared.u64 %0, [%1];" : "=l"(x_now) : "r"(dptr));
             if (x_now != cur_x) {  // uniform across the CTA: (re)load this warp's fragments
                 cur_x = x_now;
+                uint32_t li;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(li) : "r"(dptr + (uint32_t)offsetof(RegItem, layer)));
+                const uint32_t ldx = a.layer[li].ldx, kvalid = a.layer[li].kvalid;  // columns past kvalid read as zero
+                const uint32_t G1c = v1 ? warp + REG_WARPS : 0;
+                bool ood = false;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     const uint32_t b = g + 8 * nt;
-                    float s0 = load_fragment(cur_x, a.K, b, G0c, t, v0 && b < a.M, fa[nt]);
-                    float s1 = load_fragment(cur_x, a.K, b, v1 ? warp + REG_WARPS : 0, t, v1 && b < a.M, fb[nt]);
+                    float s0 = load_fragment(cur_x, ldx, b, G0c, t, v0 && b < a.M && G0c * 128 + t * 32 < kvalid, fa[nt], ood);
+                    float s1 = load_fragment(cur_x, ldx, b, G1c, t, v1 && b < a.M && G1c * 128 + t * 32 < kvalid, fb[nt], ood);
                     s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, 1);
                     s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, 2);
                     s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, 1);
@@ -276,6 +322,7 @@ __global__ void __launch_bounds__(async_threads(NT), 1) k_gemv_i4_async(const __
                     kb[nt][0] = GEMV_EIGHT_X * __shfl_sync(0xFFFFFFFFu, s1, 8 * t);
                     kb[nt][1] = GEMV_EIGHT_X * __shfl_sync(0xFFFFFFFFu, s1, 8 * t + 4);
                 }
+                if (ood) atomicExch(a.status, QB200_ERR_INVALID_PARAM);  // reported by qb200_qlinear_check
             }
 #pragma unroll 1
             for (int s = 0; s < SUBS; s++, q++) {

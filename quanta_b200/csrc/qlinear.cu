@@ -50,6 +50,29 @@ qb200_status grow(void** p, uint64_t* have, uint64_t need) {
     return QB200_OK;
 }
 
+// The forward's arguments over what the fast int4 kernels read (the transposed copy of an [in, out] weight when
+// there is one, else the stored buffers).
+qb::FwdArgs fast_args(const qb200_qlinear* q, const void* x, void* y, uint64_t m) {
+    qb::FwdArgs a;
+    a.codes = q->fast_codes();
+    a.scales = q->fast_scales();
+    a.bias = q->bias;
+    a.x = x;
+    a.y = y;
+    a.m = m;
+    a.in_dim = q->in_dim;
+    a.out_dim = q->out_dim;
+    a.gr = q->fast_gr();
+    a.gc = q->fast_gc();
+    a.tc = q->t_codes ? q->in_dim / 128 : q->tc;
+    return a;
+}
+
+bool decode_eligible(const qb200_qlinear* q, uint64_t m, int x_dtype, const void* x) {
+    return q->fast_view() && qb::gemv_i4_eligible(q->bits, q->fast_gr(), q->fast_gc(), QB200_OUT_IN, q->in_dim, q->out_dim, m,
+                                                  x_dtype, q->fast_codes(), q->fast_scales(), x);
+}
+
 }  // namespace
 
 extern "C" {
@@ -77,6 +100,11 @@ qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev
         return fail(QB200_ERR_CUDA, "QuantizedLinear: no CUDA device is available (this library has no CPU path)");
     }
     auto* ql = new qb200_qlinear();
+    {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, codes_dev) == cudaSuccess && at.type == cudaMemoryTypeDevice) ql->device = at.device;
+        else cudaGetLastError();
+    }
     ql->codes = codes_dev;
     ql->scales = scales_dev;
     ql->bias = bias_dev;
@@ -94,12 +122,17 @@ qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev
         delete ql;
         return fail(QB200_ERR_CUDA, "QuantizedLinear: could not allocate the device status word");
     }
+    if (qb200_status s = qb::build_exec_layout(ql)) {  // transposed / sliced copies for the fast int4 kernels
+        qb200_qlinear_destroy(ql);
+        return s;
+    }
     *out = ql;
     return QB200_OK;
 }
 
 void qb200_qlinear_destroy(qb200_qlinear* ql) {
     if (!ql) return;
+    qb::free_exec_layout(ql);
     if (ql->status) cudaFree(ql->status);
     if (ql->scratch) cudaFree(ql->scratch);
     if (ql->x_stage) cudaFree(ql->x_stage);
@@ -120,6 +153,33 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward: activations are f32 or bf16");
     if (m == 0) return QB200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (decode_eligible(ql, m, x_dtype, x_dev)) {
+        qb200_status s = qb::gemv_i4_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, ql->status, st);
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            ql->last_kernel = "gemv_mma";
+            return s;
+        }
+    }
+    if (ql->n_slices && m <= 16 && x_dtype == QB200_BF16 && (reinterpret_cast<uintptr_t>(x_dev) & 15u) == 0) {
+        qb200_status s = qb::forward_sliced(ql, x_dev, m, y_dev, y_dtype, st);
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            ql->last_kernel = "gemv_mma_sliced";
+            return s;
+        }
+    }
+    if (ql->fast_view() && qb::gemm_i4_eligible(ql->bits, ql->fast_gr(), ql->fast_gc(), QB200_OUT_IN, ql->in_dim, ql->out_dim, m,
+                                                x_dtype, ql->fast_codes(), x_dev)) {
+        // outputs with few tiles split the K loop over the idle SM pairs: partial tiles in the handle's scratch
+        const uint64_t need = qb::gemm_i4_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->bias);
+        if (need) {
+            void* p = ql->scratch;
+            qb200_status s = grow(&p, &ql->scratch_bytes, need);
+            ql->scratch = static_cast<float*>(p);
+            if (s) return s;
+        }
+        ql->last_kernel = "gemm_tcgen05";
+        return qb::gemm_i4_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
+    }
     qb::FwdArgs a;
     a.codes = ql->codes;
     a.scales = ql->scales;
@@ -132,26 +192,6 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     a.gr = ql->gr;
     a.gc = ql->gc;
     a.tc = ql->tc;
-    if (qb::gemv_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes,
-                             ql->scales, x_dev)) {
-        qb200_status s = qb::gemv_i4_forward(a, y_dtype, ql->status, st);
-        if (s != QB200_ERR_NOT_SUPPORTED) {
-            ql->last_kernel = "gemv_mma";
-            return s;
-        }
-    }
-    if (qb::gemm_i4_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev)) {
-        // outputs with few tiles split the K loop over the idle SM pairs: partial tiles in the handle's scratch
-        const uint64_t need = qb::gemm_i4_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->bias);
-        if (need) {
-            void* p = ql->scratch;
-            qb200_status s = grow(&p, &ql->scratch_bytes, need);
-            ql->scratch = static_cast<float*>(p);
-            if (s) return s;
-        }
-        ql->last_kernel = "gemm_tcgen05";
-        return qb::gemm_i4_forward(a, y_dtype, need ? ql->scratch : nullptr, ql->status, st);
-    }
     if (ql->layout == QB200_OUT_IN) {
         ql->last_kernel = "generic_rows";
         return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, true, nullptr, 1, st);
@@ -177,29 +217,11 @@ qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t c
             return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many: null entry " + std::to_string(i));
     // One persistent launch when every layer takes the decode GEMV and they share the input width.
     bool grouped = count > 1 && (y_dtype == QB200_F32 || y_dtype == QB200_BF16);
-    for (uint32_t i = 0; i < count && grouped; i++) {
-        const qb200_qlinear* q = layers[i];
-        grouped = q->in_dim == layers[0]->in_dim &&
-                  qb::gemv_i4_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes,
-                                       q->scales, x_dev[i]);
-    }
+    for (uint32_t i = 0; i < count && grouped; i++)
+        grouped = layers[i]->in_dim == layers[0]->in_dim && decode_eligible(layers[i], m, x_dtype, x_dev[i]);
     if (grouped) {
         std::vector<qb::FwdArgs> args(count);
-        for (uint32_t i = 0; i < count; i++) {
-            const qb200_qlinear* q = layers[i];
-            qb::FwdArgs& a = args[i];
-            a.codes = q->codes;
-            a.scales = q->scales;
-            a.bias = q->bias;
-            a.x = x_dev[i];
-            a.y = y_dev[i];
-            a.m = m;
-            a.in_dim = q->in_dim;
-            a.out_dim = q->out_dim;
-            a.gr = q->gr;
-            a.gc = q->gc;
-            a.tc = q->tc;
-        }
+        for (uint32_t i = 0; i < count; i++) args[i] = fast_args(layers[i], x_dev[i], y_dev[i], m);
         qb200_status s = qb::gemv_i4_forward_many(args.data(), count, y_dtype, layers[0]->status,
                                                   static_cast<cudaStream_t>(stream));
         if (s != QB200_ERR_NOT_SUPPORTED) {
@@ -226,22 +248,10 @@ qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uin
         const qb200_qlinear* q = layers[i];
         if (!q || !x_dev[i] || !y_own[i])
             return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_gather: null entry " + std::to_string(i));
-        if (q->in_dim != layers[0]->in_dim ||
-            !qb::gemv_i4_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes, q->scales, x_dev[i]))
+        if (q->in_dim != layers[0]->in_dim || !decode_eligible(q, m, x_dtype, x_dev[i]))
             return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_gather: layer " + std::to_string(i) +
-                                                     " does not take the decode kernel (int4, 1x128, [out, in], bf16 x, m <= 16)");
-        qb::FwdArgs& a = args[i];
-        a.codes = q->codes;
-        a.scales = q->scales;
-        a.bias = q->bias;
-        a.x = x_dev[i];
-        a.y = y_own[i];
-        a.m = m;
-        a.in_dim = q->in_dim;
-        a.out_dim = q->out_dim;
-        a.gr = q->gr;
-        a.gc = q->gc;
-        a.tc = q->tc;
+                                                     " does not take the decode kernel (int4, 1x128, [out, in], bf16 x, m <= 16, in <= 4096)");
+        args[i] = fast_args(q, x_dev[i], y_own[i], m);
     }
     qb::PeerSpec peers;
     peers.world = world;
@@ -301,8 +311,11 @@ qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint3
     std::vector<void*> yd(count);
     // Outputs in pinned, device-mapped host memory are written by the kernels themselves (the stores cross PCIe
     // while the launch is still streaming weights), which takes the device-to-host copy off the end of the call.
-    bool direct = m <= 16;  // the decode kernels store with plain instructions; the tcgen05 GEMM's TMA stores keep the staging path
-    for (uint32_t i = 0; i < count && direct; i++) direct = layers[i]->in_dim <= 4096 && layers[i]->bits == 4;
+    // Only calls that the dispatcher sends to the decode kernels qualify (they store with plain instructions; the
+    // tcgen05 GEMM's TMA stores and split-K workspace keep the staging path): the same test the dispatcher applies.
+    bool direct = true;
+    for (uint32_t i = 0; i < count && direct; i++)
+        direct = decode_eligible(layers[i], m, x_dtype, lead->x_stage) || (layers[i]->n_slices && m <= 16 && x_dtype == QB200_BF16);
     // one query per host allocation: outputs inside the range of an allocation already seen reuse its mapping
     const uint8_t *range_lo = nullptr, *range_hi = nullptr, *range_dev = nullptr;
     for (uint32_t i = 0; i < count && direct; i++) {
@@ -367,6 +380,9 @@ qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream) {
     }
     if (st == QB200_ERR_TIMEOUT)
         return fail(QB200_ERR_TIMEOUT, "QuantizedLinear: a device-side wait ran out of polls (an async copy never completed, or a peer rank never arrived at the barrier)");
+    if (st == QB200_ERR_INVALID_PARAM)
+        return fail(QB200_ERR_INVALID_PARAM, "QuantizedLinear: an activation given to the decode kernel is not finite or lies outside its "
+                                             "domain |x| < 2^87; the outputs of that call are not valid");
     if (st != 0) return fail(QB200_ERR_CUDA, "QuantizedLinear: device status " + std::to_string(st));
     return QB200_OK;
 }
@@ -383,7 +399,7 @@ qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, i
     QB_CUDA_TRY(cudaMemcpyAsync(ql->x_stage, x_host, xb, cudaMemcpyHostToDevice, ql->host_stream));
     // a decode-shaped call with its output in pinned, device-mapped memory: the kernel stores there itself
     void* y_direct = nullptr;
-    if (m <= 16 && ql->in_dim <= 4096 && ql->bits == 4) {
+    if (decode_eligible(ql, m, x_dtype, ql->x_stage) || (ql->n_slices && m <= 16 && x_dtype == QB200_BF16)) {
         cudaPointerAttributes at;
         void* base = nullptr;
         size_t size = 0;

@@ -13,6 +13,7 @@ struct qb200_qlinear {
     uint64_t rows = 0, cols = 0, gr = 0, gc = 0, tc = 0;
     uint32_t bits = 0;
     int32_t layout = QB200_IN_OUT;
+    int device = -1;  // the device that holds the codes (-1: unknown)
     uint64_t in_dim = 0, out_dim = 0;
     // split-K partial sums of the column kernel (grow-only)
     float* scratch = nullptr;
@@ -22,6 +23,36 @@ struct qb200_qlinear {
     void* y_stage = nullptr;
     uint64_t x_stage_bytes = 0, y_stage_bytes = 0;
     cudaStream_t host_stream = nullptr;
+    // Execution layout, built once at creation where the stored layout does not feed the fast int4 kernels as it is
+    // (copies: the stored codes and scales stay the record that accessors and writers see).
+    //   t_codes / t_scales: an `[in, out]` matrix with Group{axis: 0, size: 128} transposed to `[out, in]` with a
+    //     1 x 128 grid (a permutation of the nibbles and of the scales);
+    //   slices: inputs wider than the decode kernel keeps in registers (4096) cut into `n_slices` column runs of whole
+    //     scale groups, each padded with zero codes and zero scales to `slice_pad` columns, rows contiguous.
+    void* t_codes = nullptr;
+    float* t_scales = nullptr;
+    void* slice_codes = nullptr;     // [n_slices][out_dim][slice_pad / 8] u32
+    float* slice_scales = nullptr;   // [n_slices][out_dim][slice_pad / 128]
+    float* slice_partials = nullptr; // [n_slices][16][out_dim] f32: the slices' partial outputs of one decode call
+    uint32_t n_slices = 0, slice_pad = 0;
+    uint32_t slice_col0[8] = {}, slice_width[8] = {};
     int32_t* status = nullptr;  // device word written by kernels whose bounded waits ran out
     const char* last_kernel = "";
+
+    // what the fast int4 kernels read: the transposed copy when there is one, else the stored buffers
+    bool fast_view() const { return t_codes != nullptr || layout == QB200_OUT_IN; }
+    const void* fast_codes() const { return t_codes ? t_codes : codes; }
+    const float* fast_scales() const { return t_codes ? t_scales : scales; }
+    uint64_t fast_gr() const { return t_codes ? 1 : gr; }
+    uint64_t fast_gc() const { return t_codes ? 128 : gc; }
 };
+
+namespace qb {
+// exec_layout.cu
+qb200_status build_exec_layout(qb200_qlinear* ql);
+void free_exec_layout(qb200_qlinear* ql);
+#ifdef __CUDACC__
+// decode forward (m <= 16, bf16 x) of a handle with column slices: one grouped launch over the slices, then the fold
+qb200_status forward_sliced(qb200_qlinear* ql, const void* x, uint64_t m, void* y, int y_dtype, cudaStream_t st);
+#endif
+}  // namespace qb

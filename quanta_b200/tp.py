@@ -1,7 +1,7 @@
 """Column-sharded tensor parallelism for QuantizedLinear (one process per GPU).
 
 The reference has no distributed code (``crates/ml/quanta-nn/PARITY.md:76-79``); this module is
-the sharding the BASELINE configuration asks for.  Output features are independent, so rank p owns a
+the sharding of large layers over the GPUs of one node.  Output features are independent, so rank p owns a
 contiguous block of rows of the ``[out, in]`` codes and scales — a slice, no data movement — and
 the shard outputs are all-gathered along the feature axis (``torch.distributed``: NCCL over
 NVLink on GPUs, gloo on CPU for the host-side tests).
@@ -163,29 +163,30 @@ class _RawCuda:
         self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
 
 
-class PeerGather:
-    """The fused all-gather of a group of column-sharded decode layers.
+class PeerArena:
+    """One device allocation per rank, shared with the node's other ranks through CUDA IPC, cut into named
+    buffers of the same layout on every rank, plus the barrier state (16 u64) of the arrival barrier.
 
-    Every rank owns a gather buffer ``[world, count, m, n_local]`` (plus nine u64 of barrier
-    state) in a cudaMalloc allocation shared with the node's other ranks through CUDA IPC;
-    ``forward_many`` runs the grouped decode kernel, whose service warp stores each output
-    into every rank's buffer, and then the arrival barrier.  After it returns (stream order)
-    ``view()`` holds all ranks' outputs — no collective call.  Shapes the kernel does not take
-    raise QuantError(NOT_SUPPORTED); callers fall back to ``TensorParallelLinear``.
-    """
+    ``push`` runs the grouped decode kernel with peer stores: every output element is written to the same
+    offset of EVERY rank's arena (plain stores over NVLink, no collective), and the launch's last CTA runs the
+    arrival barrier, so when the launch ends all ranks' outputs are here.  What a rank writes and where is the
+    caller's layout: giving every rank its own slot of a buffer makes the exchange an all-gather (column
+    shards) or, with the consumer summing the slots, an all-reduce of partial outputs (row-parallel layers).
 
-    def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None,
-                 fused_barrier: bool = True):
-        self.fused_barrier = fused_barrier
-        if dtype not in (torch.float32, torch.bfloat16):
-            raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16")
+    A buffer that one exchange fills may be written again only after every rank has finished reading it.  The
+    barrier of the NEXT exchange proves exactly that (a rank signals it after its own reads, in stream order),
+    so two exchanges in a row must use different buffers, and a buffer is free again once another exchange
+    has completed in between."""
+
+    def __init__(self, sizes, group=None):
         self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
-            raise QuantError(L.ERR_NOT_SUPPORTED, "PeerGather: at most 8 ranks (one NVSwitch node)")
-        self.count, self.m, self.n_local, self.dtype = count, m, n_local, dtype
-        self.item = 4 if dtype == torch.float32 else 2
-        self.slot_bytes = count * m * n_local * self.item
-        self.data_bytes = -(-self.world * self.slot_bytes // 256) * 256
+            raise QuantError(L.ERR_NOT_SUPPORTED, "PeerArena: at most 8 ranks (one NVSwitch node)")
+        self.offsets, off = {}, 0
+        for name, nbytes in sizes.items():
+            self.offsets[name] = off
+            off += -(-int(nbytes) // 256) * 256
+        self.data_bytes = max(off, 256)
         lib = L.load()
         self.device = torch.device("cuda", torch.cuda.current_device())
         # The ranks walk through the same collectives whatever happens locally, and agree at the end on
@@ -221,48 +222,54 @@ class PeerGather:
             dist.barrier(group=group)
             if self._own:
                 lib.qb200_peer_free(self._own)
-            raise QuantError(L.ERR_NOT_SUPPORTED, "PeerGather: a rank could not allocate or map the peer buffers"
+            self.bases = []
+            raise QuantError(L.ERR_NOT_SUPPORTED, "PeerArena: a rank could not allocate or map the peer buffers"
                                                   + (f" ({err})" if err is not None else ""))
         self._bases_c = (L.vp * self.world)(*self.bases)
         self._flags_c = (L.vp * self.world)(*[b + self.data_bytes for b in self.bases])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._lead = None
 
-    def view(self) -> torch.Tensor:
-        """This rank's gather buffer as a tensor ``[world, count, m, n_local]`` (aliases the allocation)."""
-        shape = (self.world, self.count, self.m, self.n_local)
-        if self.dtype == torch.float32:
-            return torch.as_tensor(_RawCuda(self._own, shape, "<f4"), device=self.device)
-        return torch.as_tensor(_RawCuda(self._own, shape, "<i2"), device=self.device).view(torch.bfloat16)
+    def address(self, name: str, byte_offset: int = 0) -> int:
+        """Device address of a byte of this rank's own copy of buffer `name`."""
+        return self._own + self.offsets[name] + byte_offset
 
-    def forward_many(self, layers: List[QuantizedLinear], xs: List[torch.Tensor]) -> torch.Tensor:
-        if len(layers) != self.count or len(xs) != self.count:
-            raise QuantError(L.ERR_INVALID_PARAM, f"PeerGather: built for {self.count} layers")
+    def tensor(self, name: str, shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """This rank's copy of buffer `name` as a tensor (aliases the allocation)."""
+        if dtype == torch.float32:
+            return torch.as_tensor(_RawCuda(self.address(name), shape, "<f4"), device=self.device)
+        if dtype == torch.bfloat16:
+            return torch.as_tensor(_RawCuda(self.address(name), shape, "<i2"), device=self.device).view(torch.bfloat16)
+        raise QuantError(L.ERR_INVALID_PARAM, "PeerArena: buffers are viewed as f32 or bf16")
+
+    def push(self, layers: List[QuantizedLinear], xs: List[torch.Tensor], own_addresses: List[int], m: int,
+             out_dtype: torch.dtype = torch.float32, fused_barrier: bool = True) -> None:
+        """layers[i](xs[i]) -> `own_addresses[i]` (inside this rank's arena) and the same offset of every peer's
+        arena, then the arrival barrier (inside the launch, or as a one-warp kernel after it)."""
+        n = len(layers)
         lib = L.load()
-        per_layer = self.m * self.n_local * self.item
-        own0 = self._own + self.rank * self.slot_bytes
-        hs = (L.vp * self.count)(*[ql._h for ql in layers])
-        xp = (L.vp * self.count)(*[x.data_ptr() for x in xs])
-        yp = (L.vp * self.count)(*[own0 + i * per_layer for i in range(self.count)])
+        hs = (L.vp * n)(*[ql._h for ql in layers])
+        xp = (L.vp * n)(*[x.data_ptr() for x in xs])
+        yp = (L.vp * n)(*own_addresses)
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        # the launch's last CTA runs the arrival barrier (fused=False: a separate one-warp kernel after it)
-        _check(lib.qb200_qlinear_forward_many_gather(hs, self.count, xp, L.BF16, self.m, yp,
-                                                      L.F32 if self.dtype == torch.float32 else L.BF16,
-                                                      self._bases_c, self._flags_c if self.fused_barrier else None,
+        _check(lib.qb200_qlinear_forward_many_gather(hs, n, xp, L.BF16, m, yp, L.F32 if out_dtype == torch.float32 else L.BF16,
+                                                      self._bases_c, self._flags_c if fused_barrier else None,
                                                       self.world, self.rank, stream))
-        if not self.fused_barrier:
+        if not fused_barrier:
             _check(lib.qb200_peer_signal_wait(self._flags_c, self.world, self.rank, self.status.data_ptr(), stream))
         self._lead = layers[0]
-        return self.view()
 
     def check(self) -> None:
-        """Synchronises and raises if a bounded wait of the barrier ran out."""
-        lead = getattr(self, "_lead", None)
-        if lead is not None:
-            _check(L.load().qb200_qlinear_check(lead._h, torch.cuda.current_stream(self.device).cuda_stream))
+        """Synchronises and raises if a bounded wait of a barrier ran out."""
+        if self._lead is not None:
+            _check(L.load().qb200_qlinear_check(self._lead._h, torch.cuda.current_stream(self.device).cuda_stream))
         if int(self.status.item()) != 0:
-            raise QuantError(L.ERR_TIMEOUT, "PeerGather: a rank did not arrive within the barrier's poll limit")
+            self.status.zero_()
+            raise QuantError(L.ERR_TIMEOUT, "PeerArena: a rank did not arrive within the barrier's poll limit")
 
     def close(self) -> None:
+        if not self.bases:
+            return
         lib = L.load()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)  # nobody unmaps while a peer may still store
@@ -272,3 +279,51 @@ class PeerGather:
         dist.barrier(group=self.group)
         lib.qb200_peer_free(self._own)
         self.bases = []
+
+
+class PeerGather:
+    """The fused all-gather of a group of column-sharded decode layers.
+
+    Every rank owns TWO gather buffers ``[world, count, m, n_local]`` in a PeerArena and alternates between them
+    call by call: a rank that has left the barrier of call s may start call s + 1 and store into its peers'
+    buffers while a slower peer still reads the outputs of call s, so call s + 1 must not touch the buffer of
+    call s; by the time call s + 2 reuses it, the barrier of call s + 1 has shown that every rank is done
+    reading.  ``forward_many`` returns the buffer of this call (valid until the call after the next one).
+    Shapes the kernel does not take raise QuantError(NOT_SUPPORTED); callers fall back to
+    ``TensorParallelLinear``."""
+
+    def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None,
+                 fused_barrier: bool = True):
+        self.fused_barrier = fused_barrier
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16")
+        self.count, self.m, self.n_local, self.dtype = count, m, n_local, dtype
+        self.item = 4 if dtype == torch.float32 else 2
+        world = dist.get_world_size(group)
+        self.slot_bytes = count * m * n_local * self.item
+        self.arena = PeerArena({"g0": world * self.slot_bytes, "g1": world * self.slot_bytes}, group)
+        self.world, self.rank, self.device = self.arena.world, self.arena.rank, self.arena.device
+        self.calls = 0
+
+    def view(self, parity: Optional[int] = None) -> torch.Tensor:
+        """The gather buffer ``[world, count, m, n_local]`` the last call filled (aliases the allocation)."""
+        parity = (self.calls - 1) & 1 if parity is None else parity
+        return self.arena.tensor("g%d" % parity, (self.world, self.count, self.m, self.n_local), self.dtype)
+
+    def forward_many(self, layers: List[QuantizedLinear], xs: List[torch.Tensor], parity: Optional[int] = None) -> torch.Tensor:
+        """Runs the call into buffer `parity` (default: alternating).  A caller that captures calls into a CUDA graph
+        captures an even number of them, so that replays keep alternating."""
+        if len(layers) != self.count or len(xs) != self.count:
+            raise QuantError(L.ERR_INVALID_PARAM, f"PeerGather: built for {self.count} layers")
+        parity = self.calls & 1 if parity is None else parity
+        per_layer = self.m * self.n_local * self.item
+        own0 = self.arena.address("g%d" % parity, self.rank * self.slot_bytes)
+        self.arena.push(layers, xs, [own0 + i * per_layer for i in range(self.count)], self.m, self.dtype, self.fused_barrier)
+        self.calls += 1
+        return self.view(parity)
+
+    def check(self) -> None:
+        self.arena.check()
+
+    def close(self) -> None:
+        self.arena.close()

@@ -192,3 +192,12 @@ META_REJECT = [
     ("q8s;gr=1;gr=2;gc=1;rows=1;cols=1", "duplicate"), ("q8s;gr=1;gc=1;rows=1;cols=1;zp=3", "zp"),
     ("q8s;gr;gc=1;rows=1;cols=1", "key=value"),
 ]
+
+
+# crates/sci/quanta-blas/src/reference.rs:1119-1148 — the two literal cases of the quantized-GEMM oracle's own tests
+# (gemm_q8_sym_basic, gemm_q4_sym_basic): m, n, k, alpha, a_scale, b_scale, A codes, B codes, beta, expected C.
+GEMM_Q8_SYM_BASIC = {"m": 2, "n": 2, "k": 2, "alpha": 1.0, "a_scale": 0.5, "b_scale": 0.25, "a": [2, 4, 6, 8],
+                     "b": [1, 0, 0, 1], "beta": 0.0, "c": [0.25, 0.5, 0.75, 1.0]}
+# int4 codes, each matrix packed into one u32 word by flat index (nibbles 0..3)
+GEMM_Q4_SYM_BASIC = {"m": 2, "n": 2, "k": 2, "alpha": 1.0, "a_scale": 1.0, "b_scale": 2.0, "a": [1, 2, 3, -1],
+                     "b": [1, 0, 0, 1], "beta": 0.0, "c": [2.0, 4.0, 6.0, -2.0]}

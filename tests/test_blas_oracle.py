@@ -1,10 +1,12 @@
-"""The quantized-GEMM oracle against exact integer arithmetic on the input family and shapes of the reference's
-own tests (crates/sci/quanta-blas/tests/gemm_quant.rs), where every running sum is far below 2^24."""
+"""The quantized-GEMM oracle against the two literal cases the reference's own tests hold
+(crates/sci/quanta-blas/src/reference.rs:1119-1148) and against exact integer arithmetic on the input family and
+shapes of crates/sci/quanta-blas/tests/gemm_quant.rs, where every running sum is far below 2^24."""
 import numpy as np
 import pytest
 
 import oracle as o
 from oracle import blas_oracle as bo
+from tests.golden import kats
 
 Q8_CASES = [(4, 4, 4, 1.0, 0.0, 0.05, 0.05), (3, 5, 7, 1.0, 0.0, 0.1, 0.02), (6, 4, 5, 2.0, -1.0, 0.05, 0.05),
             (1, 8, 6, 1.0, 0.0, 0.05, 0.05), (8, 1, 6, 1.0, 0.0, 0.05, 0.05), (32, 24, 40, 1.0, 0.5, 0.02, 0.03)]
@@ -51,3 +53,24 @@ def test_int4_flat_packing_matches_the_scalar_pack():
     for i, v in enumerate(q.reshape(-1)):
         words[i // 8] = L.qo_int4_pack(words[i // 8], i % 8, int(v))
     assert list(bo.int4_pack_flat(q)) == words
+
+
+def test_reference_literal_cases_pin_the_oracle():
+    """gemm_q8_sym_basic / gemm_q4_sym_basic: literal inputs and outputs from the reference's tests."""
+    c8 = kats.GEMM_Q8_SYM_BASIC
+    got = bo.gemm_q8_sym(c8["m"], c8["n"], c8["k"], c8["alpha"], c8["a_scale"], c8["b_scale"], np.array(c8["a"], np.int32),
+                         np.array(c8["b"], np.int32), c8["beta"], np.zeros(4, np.float32))
+    assert got.reshape(-1).tolist() == c8["c"]
+    c4 = kats.GEMM_Q4_SYM_BASIC
+    L = o.lib()
+
+    def pack(codes):  # int4_pack over nibbles 0..3 of one word, as the reference's test does
+        w = 0
+        for i, q in enumerate(codes):
+            w = L.qo_int4_pack(w, i, q)
+        return np.array([w], np.uint32)
+
+    aw, bw = pack(c4["a"]), pack(c4["b"])
+    assert np.array_equal(aw, bo.int4_pack_flat(np.array(c4["a"]))) and np.array_equal(bw, bo.int4_pack_flat(np.array(c4["b"])))
+    got = bo.gemm_q4_sym(c4["m"], c4["n"], c4["k"], c4["alpha"], c4["a_scale"], c4["b_scale"], aw, bw, c4["beta"], np.zeros(4, np.float32))
+    assert got.reshape(-1).tolist() == c4["c"]

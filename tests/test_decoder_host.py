@@ -18,12 +18,12 @@ def test_rope_rows_match_the_restatement_and_the_reference_formula():
     assert (c == 1).all() and (s == 0).all()
 
 
-def test_slices_cover_the_width_in_whole_groups():
-    for width in (128, 4096, 4224, 11008, 14336, 28672):
-        w = dec._slices(width)
+def test_split_groups_covers_the_width_in_whole_groups():
+    for width, n in [(128, 1), (4096, 1), (4224, 2), (11008, 3), (14336, 4), (28672, 7), (1408, 1)]:
+        w = dec._split_groups(width // 128, n)
         assert sum(w) == width and all(x % 128 == 0 and 0 < x <= 4096 for x in w)
-        assert len(w) == -(-width // 4096) and max(w) - min(w) <= 128
-    assert dec._slices(11008) == [3712, 3712, 3584]
+        assert len(w) == n and max(w) - min(w) <= 128
+    assert dec._split_groups(86, 3) == [3712, 3712, 3584]
 
 
 def test_oracle_ops_agree_with_float64_math():

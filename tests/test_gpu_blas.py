@@ -8,6 +8,7 @@ import torch
 import quanta_b200 as qb
 from oracle import blas_oracle as bo
 from quanta_b200 import blas
+from tests.golden import kats
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -134,3 +135,19 @@ def test_loud_errors():
     with pytest.raises(qb.QuantError, match="outside"):
         blas.check_stream(c)
     blas.check_stream(c)  # reported once, then clear
+
+
+def test_reference_literal_cases_on_the_gpu():
+    """The reference's own literal cases (crates/sci/quanta-blas/src/reference.rs:1119-1148) through the C ABI."""
+    c8 = kats.GEMM_Q8_SYM_BASIC
+    c = torch.zeros(4, device=DEV)
+    blas.gemm_quant(Q8, c8["m"], c8["n"], c8["k"], c8["alpha"], c8["a_scale"], c8["b_scale"], _dev_i32(np.array(c8["a"], np.int32)),
+                    _dev_i32(np.array(c8["b"], np.int32)), c8["beta"], c)
+    blas.check_stream(c)
+    assert c.cpu().tolist() == c8["c"]
+    c4 = kats.GEMM_Q4_SYM_BASIC
+    c = torch.zeros(4, device=DEV)
+    blas.gemm_quant4(Q4, c4["m"], c4["n"], c4["k"], c4["alpha"], c4["a_scale"], c4["b_scale"],
+                     _dev_i32(bo.int4_pack_flat(np.array(c4["a"]))), _dev_i32(bo.int4_pack_flat(np.array(c4["b"]))), c4["beta"], c)
+    blas.check_stream(c)
+    assert c.cpu().tolist() == c4["c"]

@@ -199,7 +199,7 @@ def test_quantize_from_half_sources():
             assert_quant_equal(m, oc, os_, f"{tdt}")
 
 
-# ---- BASELINE configs at oracle-sized inputs -----------------------------------
+# ---- the benchmark workloads at oracle-sized inputs -----------------------------------
 
 def test_config1_int8_block32_cpu_runnable():
     g = np.random.default_rng(0)
@@ -318,7 +318,7 @@ def test_mode_a_load_equals_device_dequantize_bitwise():
         assert torch.equal(arr.view(torch.int32), want.view(torch.int32))
 
 
-# ---- size-independent properties at full BASELINE sizes -------------------------
+# ---- size-independent properties at the full workload sizes -------------------------
 
 def test_full_size_properties_config3_shape():
     """int4 1x128 over [11008, 4096]: the s/2 round-trip bound, clamp-freeness, idempotence of
@@ -360,8 +360,9 @@ def test_decode_gemv_shapes(N, K):
         xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
         xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
         y = ql.forward(xt, out_dtype=torch.float32)
-        # the tensor-pipe GEMV keeps the activations on chip; shapes whose activations do not fit use the tcgen05 GEMM
-        assert ql.last_kernel() == "gemv_mma" or (K > 4096 and ql.last_kernel() == "gemm_tcgen05")
+        # the tensor-pipe GEMV keeps the activations of at most 4096 inputs in registers; wider inputs run as column
+        # slices of the weight (one grouped launch over the slices and a fold)
+        assert ql.last_kernel() == ("gemv_mma" if K <= 4096 else "gemv_mma_sliced")
         want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
         close(y.cpu().numpy(), want, 1e-4)   # exact codes, f32 accumulate: far inside the stated 1e-3
         yb = ql.forward(xt)                  # bf16 out
@@ -444,7 +445,7 @@ def test_prefill_gemm_against_oracle(M, N, K):
 
 
 def test_prefill_gemm_config3_full_size_properties():
-    """int4 prefill at the BASELINE size (X [2048, 4096], W [11008, 4096]): against an f32 matmul over the
+    """int4 prefill at the full workload size (X [2048, 4096], W [11008, 4096]): against an f32 matmul over the
     bit-exact dequantized weight, and linearity in x."""
     gen = torch.Generator(device=DEV).manual_seed(2)
     w = torch.randn(11008, 4096, device=DEV, generator=gen) * 0.02
@@ -528,3 +529,157 @@ def test_quantize_large_tiles_chunk_path_is_bit_exact(shape, dtype, gran):
     gr, gc = gran.tile(r, c)
     oc2, os2 = o.quantize_host(o.bf16_to_f32(wb), r, c, dtype.bits(), gr, gc)
     assert_quant_equal(mb, oc2, os2)
+
+
+# ---- bit-for-bit at the full sizes of the quantize-on-load and prefill workloads ------------------
+
+@pytest.mark.parametrize("shape,dtype,gran", [
+    ((11008, 4096), qb.QuantDtype.Int4, qb.Group(1, 128)),
+    ((11008, 4096), qb.QuantDtype.Int8, qb.Block(32, 32)),
+    ((4096, 4096), qb.QuantDtype.Int8, qb.Block(32, 32)),
+    ((4096, 4096), qb.QuantDtype.Int4, qb.Group(1, 128)),
+])
+def test_full_size_codes_scales_and_dequantize_bit_exact(shape, dtype, gran):
+    """The checkpoint's two matrix shapes, both grids: every code, every scale and every dequantized weight against
+    the oracle (45 M elements take the CPU restatement about a second)."""
+    r, c = shape
+    g = np.random.default_rng(3 + r)
+    w = g.standard_normal((r, c), dtype=np.float32) * np.float32(0.02)
+    m, oc, os_ = quantize_both(w, r, c, dtype, gran)
+    assert_quant_equal(m, oc, os_, f"{shape} {dtype.name}")
+    gr, gc = gran.tile(r, c)
+    host = o.dequantize_host(oc, os_, r, c, dtype.bits(), gr, gc)
+    assert (bits(m.dequantize().cpu().numpy()) == bits(host)).all()
+
+
+# ---- the reference's own orientation, `[in, out]` with groups along the inputs, on the fast kernels ---------
+
+def _one_hot_rows(ks, K):
+    x = np.zeros((len(ks), K), np.float32)
+    for i, k in enumerate(ks):
+        x[i, k] = 1.0
+    return torch.from_numpy(o.f32_to_bf16(x).view(np.int16)).view(torch.bfloat16).to(DEV)
+
+
+@pytest.mark.parametrize("K,N", [(1024, 520), (4096, 264), (256, 136), (11008, 72)])
+def test_in_out_int4_takes_the_fast_kernels_and_its_execution_copy_is_a_permutation(K, N):
+    """QuantizedLinear::new(w: [in, out]) with Group{axis: 0, size: 128} (crates/ml/quanta-nn/src/quant.rs:853-862):
+    the handle transposes codes and scales once.  One-hot activations read single weights back through the decode
+    kernel: 1.0 * (s * q) with every other product zero is exact, so the outputs must equal the oracle's dequantized
+    weights of the ORIGINAL record bit for bit."""
+    rng = np.random.default_rng(K + N)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    m, oc, os_ = quantize_both(w, K, N, qb.QuantDtype.Int4, qb.Group(0, 128))
+    wd = o.dequantize_host(oc, os_, K, N, 4, 128, 1)   # [in, out]
+    ql = qb.QuantizedLinear.new(m, None, qb.IN_OUT)
+    ks = sorted(set([0, 1, 2, 3, 4, 5, 6, 7, 127, 128 % K, K // 2 + 3, K - 8, K - 1] + list(rng.integers(0, K, 3))))
+    ks = [int(k) for k in ks][:16]
+    y = ql.forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
+    assert ql.last_kernel() == ("gemv_mma" if K <= 4096 else "gemv_mma_sliced")
+    assert (bits(y.cpu().numpy()) == bits(wd[ks])).all()
+    # dense activations, decode and prefill batch sizes, against the f64 checker over the dequantized record
+    bias = rng.standard_normal(N).astype(np.float32)
+    qlb = qb.QuantizedLinear.new(m, t(bias), qb.IN_OUT)
+    for M, kernel, tol in [(3, "gemv_mma" if K <= 4096 else "gemv_mma_sliced", 1e-4), (16, None, 1e-4), (40, "gemm_tcgen05", 1e-3)]:
+        xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+        got = qlb.forward(xt, out_dtype=torch.float32).cpu().numpy()
+        if kernel:
+            assert qlb.last_kernel() == kernel
+        close(got, o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.IN_OUT, threads=8), tol)
+    # f32 activations keep the generic column kernel (the fast kernels take bf16)
+    xf = torch.randn(2, K, device=DEV)
+    qlb.forward(xf)
+    assert qlb.last_kernel() == "generic_cols"
+    # the record itself is untouched: it still dequantizes to the oracle's matrix
+    assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(qlb._h, None) == 0
+
+
+def test_sliced_decode_of_a_wide_layer_matches_per_slice_sums():
+    """A `[4096, 11008]` layer at M <= 16 (a feed-forward down projection called on its own): three column slices in one
+    launch plus the fold; with bf16 output; through the host-buffer entry point with pinned outputs."""
+    rng = np.random.default_rng(12)
+    N, K = 512, 11008
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int4, qb.Group(1, 128))
+    wd = o.dequantize_host(oc, os_, N, K, 4, 1, 128)
+    ql = qb.QuantizedLinear.new(m, t(bias), qb.OUT_IN)
+    ks = [0, 3711, 3712, 7423, 7424, 11007, 5000, 1]    # first and last column of every slice
+    y = ql.forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemv_mma_sliced"
+    want = wd[:, ks].T + bias[None, :]
+    assert (bits(y.cpu().numpy()) == bits(want.astype(np.float32))).all()
+    for M in (1, 7, 16):
+        xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+        want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
+        yd = ql.forward(xt, out_dtype=torch.float32).cpu().numpy()
+        close(yd, want, 1e-4)
+        close(ql.forward(xt).to(torch.float32).cpu().numpy(), want, 1e-2)
+        assert (bits(ql.forward_host(xb)) == bits(yd)).all()   # host buffers in and out: the same kernels
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
+def test_decode_domain_limit_is_checked():
+    """The decode kernel scales activations by 2^40 inside bf16: |x| < 2^87 is its domain.  Just inside, the result
+    matches the oracle; at 2^87 and for non-finite activations the call is flagged and qb200_qlinear_check reports
+    it (the reference's f32 path would return a finite number for a finite x: the difference is loud, not silent)."""
+    from quanta_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(8)
+    N, K = 256, 512
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int4, qb.Group(1, 128))
+    wd = o.dequantize_host(oc, os_, N, K, 4, 1, 128)
+    ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    x = rng.standard_normal((2, K)).astype(np.float32)
+    x[0, 5] = 2.0 ** 86
+    x[1, 300] = -(2.0 ** 86) * 1.5
+    xb = o.f32_to_bf16(x)
+    xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    y = ql.forward(xt, out_dtype=torch.float32).cpu().numpy()
+    assert ql.last_kernel() == "gemv_mma" and lib.qb200_qlinear_check(ql._h, None) == 0
+    want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, None, o.OUT_IN, threads=2)
+    assert np.isfinite(y).all()
+    close(y / 2.0 ** 80, want / 2.0 ** 80, 1e-4)
+    for bad in (2.0 ** 87, np.inf, np.nan):
+        x2 = x.copy()
+        x2[1, 17] = bad
+        xb2 = o.f32_to_bf16(x2)
+        ql.forward(torch.from_numpy(xb2.view(np.int16)).view(torch.bfloat16).to(DEV), out_dtype=torch.float32)
+        assert lib.qb200_qlinear_check(ql._h, None) == _lib.ERR_INVALID_PARAM
+        assert "2^87" in _lib.last_error()
+        assert lib.qb200_qlinear_check(ql._h, None) == 0   # reported once
+
+
+def test_host_entry_with_unaligned_scales_keeps_the_staging_path():
+    """Scales that are not 16-byte aligned take the layer off the decode kernel (the tcgen05 GEMM serves it); the
+    host-buffer entry point must then not hand pinned host memory to that kernel's TMA stores but stage the outputs
+    on the device, and still return the right numbers."""
+    from quanta_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(31)
+    N, K, M = 384, 1024, 4
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int4, qb.Group(1, 128))
+    wd = o.dequantize_host(oc, os_, N, K, 4, 1, 128)
+    base = torch.zeros(N * (K // 128) + 4, device=DEV)
+    shifted = base[1: 1 + N * (K // 128)].view(N, K // 128)
+    shifted.copy_(m.scales())
+    assert shifted.data_ptr() % 16 == 4
+    odd = qb.QuantizedMatrix.from_parts(m.codes(), [N, K], shifted, qb.Group(1, 128))
+    ql = qb.QuantizedLinear.new(odd, None, qb.OUT_IN)
+    xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, None, o.OUT_IN, threads=4)
+    xh = torch.from_numpy(xb.view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+    yh = torch.full((M, N), float("nan")).pin_memory()
+    hs, xp, yp = (_lib.vp * 1)(ql._h), (_lib.vp * 1)(xh.data_ptr()), (_lib.vp * 1)(yh.data_ptr())
+    assert lib.qb200_qlinear_forward_many_host(hs, 1, xp, _lib.BF16, M, yp, _lib.F32) == 0, _lib.last_error()
+    assert ql.last_kernel() == "gemm_tcgen05"
+    close(yh.numpy(), want, 1e-3)
+    y2 = np.full((M, N), np.nan, np.float32)
+    assert (bits(ql.forward_host(xb, y2)) == bits(yh.numpy())).all()

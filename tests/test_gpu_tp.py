@@ -86,18 +86,25 @@ def _gather_worker(rank, world, port, ret):
             w = torch.randn(n_local, K, device=dev, generator=gen) * 0.02
             b = torch.randn(n_local, device=dev, generator=gen)
             layers.append(qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128)), b, qb.OUT_IN))
-        for M in (1, 4, 8):
+        for M in (1, 4, 8, 11, 16):
             xg = torch.Generator(device=dev).manual_seed(7 + M)  # the same activations on every rank
-            x = torch.randn(M, K, device=dev, generator=xg).to(torch.bfloat16)
-            own = torch.stack([ql.forward(x, out_dtype=torch.float32) for ql in layers])  # [count, M, n_local]
-            want = torch.empty(world, count, M, n_local, device=dev)
-            dist.all_gather_into_tensor(want, own)  # the collective the fused path replaces
+            xs = [torch.randn(M, K, device=dev, generator=xg).to(torch.bfloat16) for _ in range(5)]  # another x every step
+            wants = []
+            for x in xs:
+                own = torch.stack([ql.forward(x, out_dtype=torch.float32) for ql in layers])  # [count, M, n_local]
+                want = torch.empty(world, count, M, n_local, device=dev)
+                dist.all_gather_into_tensor(want, own)  # the collective the fused path replaces
+                wants.append(want)
             for fused_barrier in (True, False):  # the barrier inside the launch, or as its own kernel
                 pg = tp.PeerGather(count, M, n_local, torch.float32, fused_barrier=fused_barrier)
-                for _ in range(3):  # the barrier counts steps: repeated use must keep working
-                    got = pg.forward_many(layers, [x] * count)
+                # every step's gathered buffer is read while the next step may already be storing into the peers:
+                # the two receive buffers used in turn keep a step's outputs intact until they have been compared
+                gots = []
+                for x in xs:  # the barrier counts steps: repeated use must keep working
+                    gots.append(pg.forward_many(layers, [x] * count).clone())
                 pg.check()
-                ok = ok and layers[0].last_kernel() == "gemv_mma_grouped_gather" and torch.equal(got, want)
+                ok = ok and layers[0].last_kernel() == "gemv_mma_grouped_gather"
+                ok = ok and all(torch.equal(g, w) for g, w in zip(gots, wants))
                 pg.close()
         ret[rank] = ok
     finally:
@@ -112,6 +119,66 @@ def test_fused_all_gather_two_gpus():
     ret = ctx.Manager().dict()
     port = _free_port()
     procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert ret.get(0) and ret.get(1)
+
+
+def _stack_worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from quanta_b200 import decoder as dec
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        # a small Llama-shaped stack: 8 heads of 128, FFN of 21 scale groups (ragged over 2 ranks), ragged vocabulary
+        args = dict(n_layers=2, d=1024, heads=8, ffn=2688, vocab=1001, batch=16, ctx_max=65, device=dev, seed=4)
+        single = dec.DecoderStack(**args)
+        sharded = dec.DecoderStack(**args, group=dist.group.WORLD)
+        h0 = torch.randn(16, 1024, device=dev, generator=torch.Generator(device=dev).manual_seed(3)) * 0.5
+        ok = True
+        for pos in (63, 64):
+            single.set_position(pos)
+            sharded.set_position(pos)
+            want = single.step(h0).clone()
+            got = sharded.step(h0).clone()
+            sharded.arena.check()
+            # the same codes and scales, the f32 sums over ranks in another order; logits are O(1)
+            ok = ok and bool(((got - want).abs() <= 1e-2 * (1 + want.abs())).all())
+            ref = got.clone()
+            dist.broadcast(ref, 0)
+            ok = ok and torch.equal(ref, got)  # bit-identical on every rank: all ranks sum the slots in one order
+        # the step as a CUDA graph, replayed: the barrier's step counter lives in device memory
+        sharded.set_position(64)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            sharded.step(h0)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        sharded.arena.check()
+        ok = ok and bool(((sharded.logits - want).abs() <= 1e-2 * (1 + want.abs())).all())
+        del g
+        sharded.close()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_decoder_stack_two_gpus():
+    """The tensor-parallel decoder stack (whole heads per rank, fused exchanges) against the single-GPU stack that
+    holds the same codes."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_stack_worker, args=(r, 2, port, ret)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

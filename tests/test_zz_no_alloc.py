@@ -34,14 +34,18 @@ def _layer(in_dim, out_dim, dtype, gran, seed):
 def _static(ql, x, out_dtype):
     y = torch.empty((x.shape[0], ql.out_dim()), dtype=out_dtype, device=x.device)
     act = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]  # the driver's count of free device bytes, after the output exists
     st = _lib.load().qb200_qlinear_forward_static(ql._h, x.data_ptr(), act[x.dtype], x.shape[0], y.data_ptr(),
                                                   act[out_dtype], ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
     return st, y
 
 
 def test_static_forward_matches_the_ordinary_forward_twice_in_a_row():
     lib = _lib.load()
-    cases = [(4096, 256, qb.QuantDtype.Int4, qb.Group(0, 128)),   # small out, long K: K is split, scratch in use
+    cases = [(4096, 256, qb.QuantDtype.Int4, qb.Group(0, 64)),    # small out, long K: K is split, scratch in use
              (1024, 520, qb.QuantDtype.Int8, qb.PerChannel(1)),
              (512, 4096, qb.QuantDtype.Int4, qb.Group(0, 8))]     # wide out: one slice, no scratch
     for in_dim, out_dim, dt, gran in cases:
@@ -56,11 +60,12 @@ def test_static_forward_matches_the_ordinary_forward_twice_in_a_row():
                 torch.cuda.synchronize()
                 # same kernels, same K slicing: the tolerance of the forward tests (1e-4) is met with equality
                 assert torch.equal(got, want), (in_dim, out_dim, m, call)
+                assert ql.last_kernel() == "generic_cols"
     assert lib.qb200_qlinear_check(ql._h, None) == 0
 
 
 def test_static_forward_refuses_what_does_not_fit_and_other_layouts():
-    ql = _layer(4096, 2048, qb.QuantDtype.Int4, qb.Group(0, 128), seed=1)
+    ql = _layer(4096, 2048, qb.QuantDtype.Int4, qb.Group(0, 64), seed=1)
     m = 72  # 4 K slices x 72 x 2048 partial sums = 589 824 > 2^19
     x = torch.zeros(m, 4096, device=DEV)
     st, _ = _static(ql, x, torch.float32)
