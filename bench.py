@@ -235,7 +235,7 @@ def measure_decode_step(torch, dev, gen, hbm, n_layers, world=1):
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-            stack.arena.check()  # a barrier that timed out would have let the step run on stale partial sums
+            stack.arena.check()  # a consumer that gave up waiting would have let the step run on missing partial sums
             # every rank must hold the same logits after the last exchange
             ref = stack.logits.clone()
             dist.broadcast(ref, 0)
@@ -272,8 +272,8 @@ def measure_decode_step(torch, dev, gen, hbm, n_layers, world=1):
             res["exchange_share_of_step"] = max(0.0, 1.0 - float(t.item()) / ms)
             res["exchanges_per_step"] = 2 * n_layers + 1
             res["nvlink_bytes_per_step_per_gpu"] = stack.exchange_bytes() * (world - 1)
-            res["parallelism"] = (f"tensor-parallel x{world}: whole heads per rank, row-parallel output and down projections, partial sums "
-                                  "stored to every rank by the producing kernel, arrival barrier in the same launch")
+            res["parallelism"] = (f"tensor-parallel x{world}: whole heads per rank, row-parallel output and down projections; the producing "
+                                  "kernels push their partial sums to every rank as self-validating elements, the consumers poll (no barrier)")
         del g
         return res
     except Exception as e:  # the rest of the line must survive

@@ -255,6 +255,36 @@ QB200_API qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint
  * gives up with QB200_ERR_TIMEOUT; process-wide, read at launch time, default 4 Mi (about a second). */
 QB200_API qb200_status qb200_peer_set_spin_limit(uint32_t polls);
 
+/* ---- pushed exchanges for tensor-parallel decode (no counterpart in the reference) ----
+ * The barrier of qb200_qlinear_forward_many_gather costs several microseconds per exchange (a system-scope fence
+ * waits for the peers to acknowledge every store in flight, then the flags travel).  A decode step of a sharded
+ * model makes dozens of exchanges of a few hundred KB, so here the data validates itself instead: every output is
+ * stored as ONE 8-byte element {f32 bits, exchange number} into the same offset of every rank's arena
+ * (arena_bases[p] as mapped in this process, arena_bases[rank] the own one; slot_own[i] is where layer i's
+ * `[m, out]` elements start inside the own arena, 8 bytes each), and the launch ends without any fence or wait.
+ * The consumers poll each element until it carries the exchange number they expect:
+ *   qb200_add_rmsnorm_pushed — qb200_add_rmsnorm over `parts` pushed arrays of n * c elements laid back to back
+ *     (for example one partial output per rank of a row-parallel layer), summed in part order;
+ *   qb200_gather_pushed — part r holds `rows` x w_r elements of a column-sharded output (w_r = cols / parts, one
+ *     more for the first cols % parts ranks), parts `part_stride` elements apart; they are written as f32 into
+ *     columns [lo_r, lo_r + w_r) of dst (rows dst_stride floats apart).
+ * state_own is this rank's zero-initialised array of 16 uint64 (device memory): word 8 counts the exchanges this
+ * rank has launched, which is the number the next consumer expects — every rank must go through the same
+ * sequence of pushes and consumers.  A buffer may be pushed into again only after another exchange (into another
+ * buffer) has been consumed in between: a rank cannot finish that one before every rank has read the first.
+ * Waits are bounded by qb200_peer_set_spin_limit; a consumer that gives up writes QB200_ERR_TIMEOUT to status_dev
+ * (an int32 in device memory, zero-initialised) and uses zeros.  Decode shapes only, all layers in ONE launch
+ * (else QB200_ERR_NOT_SUPPORTED).  Exchange numbers are 32 bits wide. */
+QB200_API qb200_status qb200_qlinear_forward_many_push(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev,
+                                                       int32_t x_dtype, uint64_t m, void* const* slot_own, void* const* arena_bases,
+                                                       uint32_t world, uint32_t rank, uint64_t* state_own, void* stream);
+QB200_API qb200_status qb200_add_rmsnorm_pushed(float* h, const void* pushed, uint32_t parts, const uint64_t* state_own,
+                                                const float* gamma, uint64_t n, uint64_t c, float eps, uint16_t* out_bf16,
+                                                int32_t* status_dev, void* stream);
+QB200_API qb200_status qb200_gather_pushed(const void* pushed, uint32_t parts, uint64_t part_stride, uint32_t rows, uint64_t cols,
+                                           const uint64_t* state_own, float* dst, uint64_t dst_stride, int32_t* status_dev,
+                                           void* stream);
+
 /* qb200_qlinear_forward_many over HOST buffers: every distinct input pointer is
  * copied to the device once, the forwards run, all outputs are copied back and
  * the call synchronises.  Staging buffers belong to layers[0] and grow on demand.

@@ -14,7 +14,7 @@
 #include <cstdint>
 #include <string>
 
-#include "common.hpp"
+#include "forward.hpp"
 #include "quant_math.cuh"
 
 namespace qb {
@@ -87,6 +87,129 @@ __global__ void __launch_bounds__(1024) k_add_rmsnorm(float* __restrict__ h, con
         }
     } else {
         for (uint32_t i = threadIdx.x; i < c; i += 1024) out[base + i] = f32_to_bf16_bits(h[base + i] * rrms * gamma[i]);
+    }
+}
+
+// ---- consumers of pushed outputs (self-validating 8-byte elements: f32 bits + the number of the exchange) ----
+// A rank's producer kernel has stored its part into every rank's buffer with plain 8-byte stores over NVLink; there
+// is no barrier.  The consumer polls each element until its flag is the exchange it expects (state[8], the count of
+// exchanges this rank itself has completed: every rank goes through the same sequence of exchanges).  Waits are
+// bounded: a thread that runs out of polls records QB200_ERR_TIMEOUT in `status`, and every other thread gives up
+// as soon as it sees that word set, so a rank that never delivers costs one wait, not one per element.
+
+// Two consecutive elements (16 bytes, each half validated on its own); false when the polls ran out.
+__device__ __forceinline__ bool pushed_load2(const uint4* p, uint32_t flag, uint32_t limit, int32_t* status, float& a, float& b) {
+    uint4 v;
+    for (uint32_t spins = 0;; spins++) {
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+        if (v.y == flag && v.w == flag) break;
+        if (spins >= limit || ((spins & 15u) == 15u && *reinterpret_cast<volatile int32_t*>(status) != 0)) {
+            atomicExch(status, QB200_ERR_TIMEOUT);
+            a = b = 0.0f;
+            return false;
+        }
+        __nanosleep(64);
+    }
+    a = __uint_as_float(v.x);
+    b = __uint_as_float(v.z);
+    return true;
+}
+__device__ __forceinline__ bool pushed_load1(const uint2* p, uint32_t flag, uint32_t limit, int32_t* status, float& a) {
+    uint2 v;
+    for (uint32_t spins = 0;; spins++) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+        if (v.y == flag) break;
+        if (spins >= limit || ((spins & 15u) == 15u && *reinterpret_cast<volatile int32_t*>(status) != 0)) {
+            atomicExch(status, QB200_ERR_TIMEOUT);
+            a = 0.0f;
+            return false;
+        }
+        __nanosleep(64);
+    }
+    a = __uint_as_float(v.x);
+    return true;
+}
+
+// k_add_rmsnorm over pushed parts: h += part[0] + ... + part[parts - 1] in part order (the same order on every rank,
+// so the residual stream stays bit-identical across ranks), out = bf16(rmsnorm(h) * gamma).
+__global__ void __launch_bounds__(1024) k_add_rmsnorm_pushed(float* __restrict__ h, const uint2* __restrict__ pushed, uint32_t parts,
+                                                             uint64_t part_stride, const uint64_t* __restrict__ state,
+                                                             const float* __restrict__ gamma, uint32_t c, float eps,
+                                                             uint16_t* __restrict__ out, uint32_t limit, int32_t* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the local producer has bumped state[8]
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float s_part[32];
+    const uint32_t flag = (uint32_t)state[8];
+    const uint64_t base = (uint64_t)blockIdx.x * c;
+    const bool vec = (c & 3u) == 0;
+    float sq = 0.0f;
+    if (vec) {
+        for (uint32_t i = threadIdx.x * 4; i < c; i += 4096) {
+            float4 v = *reinterpret_cast<const float4*>(h + base + i);
+            float4 d = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (uint32_t p = 0; p < parts; p++) {
+                const uint4* q = reinterpret_cast<const uint4*>(pushed + p * part_stride + base + i);
+                float e0, e1, e2, e3;
+                pushed_load2(q, flag, limit, status, e0, e1);
+                pushed_load2(q + 1, flag, limit, status, e2, e3);
+                if (p == 0) d = make_float4(e0, e1, e2, e3);
+                else { d.x += e0; d.y += e1; d.z += e2; d.w += e3; }
+            }
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            *reinterpret_cast<float4*>(h + base + i) = v;
+            sq = fmaf(v.x, v.x, sq);
+            sq = fmaf(v.y, v.y, sq);
+            sq = fmaf(v.z, v.z, sq);
+            sq = fmaf(v.w, v.w, sq);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < c; i += 1024) {
+            float v = h[base + i], d = 0.0f;
+            for (uint32_t p = 0; p < parts; p++) {
+                float e;
+                pushed_load1(pushed + p * part_stride + base + i, flag, limit, status, e);
+                d = p == 0 ? e : d + e;
+            }
+            v += d;
+            h[base + i] = v;
+            sq = fmaf(v, v, sq);
+        }
+    }
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 32; w++) tot += s_part[w];
+    const float rrms = 1.0f / sqrtf(tot / (float)c + eps);
+    if (vec) {
+        for (uint32_t i = threadIdx.x * 4; i < c; i += 4096) {
+            const float4 v = *reinterpret_cast<const float4*>(h + base + i);
+            const float4 g = *reinterpret_cast<const float4*>(gamma + i);
+            uint2 o;
+            o.x = f32_to_bf16_bits(v.x * rrms * g.x) | ((uint32_t)f32_to_bf16_bits(v.y * rrms * g.y) << 16);
+            o.y = f32_to_bf16_bits(v.z * rrms * g.z) | ((uint32_t)f32_to_bf16_bits(v.w * rrms * g.w) << 16);
+            *reinterpret_cast<uint2*>(out + base + i) = o;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < c; i += 1024) out[base + i] = f32_to_bf16_bits(h[base + i] * rrms * gamma[i]);
+    }
+}
+
+// Gathers column-sharded pushed outputs into a dense matrix: part r holds `rows` x w_r elements packed row by row,
+// w_r = base + (r < extra ? 1 : 0) columns starting at column r * base + min(r, extra) of dst (rows `dst_stride` apart).
+__global__ void __launch_bounds__(256) k_gather_pushed(const uint2* __restrict__ pushed, uint32_t parts, uint64_t part_stride,
+                                                       uint32_t rows, uint32_t base, uint32_t extra, const uint64_t* __restrict__ state,
+                                                       float* __restrict__ dst, uint64_t dst_stride, uint32_t limit, int32_t* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t flag = (uint32_t)state[8];
+    const uint32_t p = blockIdx.y, w = base + (p < extra ? 1u : 0u), lo = p * base + (p < extra ? p : extra);
+    const uint64_t total = (uint64_t)rows * w;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        float v;
+        pushed_load1(pushed + p * part_stride + i, flag, limit, status, v);
+        dst[(i / w) * dst_stride + lo + (i % w)] = v;
     }
 }
 
@@ -310,6 +433,39 @@ qb200_status qb200_add_rmsnorm(float* h, const float* delta, uint32_t delta_part
     if (n == 0 || c == 0 || c > 0x7FFFFFFFull || n > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm: bad shape");
     QB_CUDA_TRY(qb::launch_pdl(qb::k_add_rmsnorm, (uint32_t)n, 1024, static_cast<cudaStream_t>(stream), h, delta, delta ? delta_parts : 0, n * c, gamma, (uint32_t)c, eps,
                                                                                    out_bf16));
+    return QB200_OK;
+}
+
+qb200_status qb200_add_rmsnorm_pushed(float* h, const void* pushed, uint32_t parts, const uint64_t* state_own, const float* gamma,
+                                      uint64_t n, uint64_t c, float eps, uint16_t* out_bf16, int32_t* status_dev, void* stream) {
+    if (!h || !gamma || !out_bf16 || !pushed || !state_own || !status_dev || parts == 0)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm_pushed: null pointer or no parts");
+    if (n == 0 || c == 0 || c > 0x7FFFFFFFull || n > 0x7FFFFFFFull) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm_pushed: bad shape");
+    if (reinterpret_cast<uintptr_t>(pushed) & 15u) return fail(QB200_ERR_INVALID_PARAM, "qb200_add_rmsnorm_pushed: the pushed buffer must be 16-byte aligned");
+    QB_CUDA_TRY(qb::launch_pdl(qb::k_add_rmsnorm_pushed, (uint32_t)n, 1024, static_cast<cudaStream_t>(stream), h, static_cast<const uint2*>(pushed),
+                               parts, n * c, state_own, gamma, (uint32_t)c, eps, out_bf16, qb::peer_spin_limit(), status_dev));
+    return QB200_OK;
+}
+
+qb200_status qb200_gather_pushed(const void* pushed, uint32_t parts, uint64_t part_stride, uint32_t rows, uint64_t cols,
+                                 const uint64_t* state_own, float* dst, uint64_t dst_stride, int32_t* status_dev, void* stream) {
+    if (!pushed || !state_own || !dst || !status_dev || parts == 0 || rows == 0 || cols < parts || cols > 0x7FFFFFFFull || dst_stride < cols)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_gather_pushed: null pointer or bad shape");
+    const uint32_t base = (uint32_t)(cols / parts), extra = (uint32_t)(cols % parts);
+    const uint64_t widest = (uint64_t)rows * (base + (extra ? 1 : 0));
+    if (part_stride < widest) return fail(QB200_ERR_INVALID_PARAM, "qb200_gather_pushed: parts overlap (part_stride below rows x widest shard)");
+    const uint32_t bx = (uint32_t)((widest + 255) / 256 > 64 ? 64 : (widest + 255) / 256);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(bx, parts);
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qb::k_gather_pushed, static_cast<const uint2*>(pushed), parts, part_stride, rows, base, extra, state_own,
+                                   dst, dst_stride, qb::peer_spin_limit(), status_dev));
     return QB200_OK;
 }
 

@@ -38,6 +38,9 @@ struct PeerSpec {
     uint64_t* flags[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint32_t rank = 0;
 };
+// Internal output type of the decode GEMV beside QB200_F32 / QB200_BF16: pushed self-validating elements (8 bytes:
+// f32 bits + exchange number) for every rank; flags[rank] is then this rank's own state array and no barrier runs.
+constexpr int QB_Y_PUSHED = 100;
 // Polls of a peer's arrival flag (about 0.25 us each) before a barrier gives up with QB200_ERR_TIMEOUT (peers.cu).
 uint32_t peer_spin_limit();
 #ifdef __CUDACC__

@@ -57,6 +57,7 @@ struct GemvBatch {
     int64_t peer_delta[8];
     uint64_t* peer_flags[8];  // every rank's barrier state as mapped here (null: the caller runs the barrier itself)
     uint32_t rank;
+    uint32_t ll_mode;  // outputs are LLPair elements stamped with the exchange number; no barrier in the launch
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -115,6 +116,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// An output pushed to the ranks of a node as a self-validating element: the f32 bits and the number of the exchange
+// that wrote them, stored (and polled by the consumer) as ONE 8-byte access, so that no fence and no barrier
+// has to order data and flag — the element is either the old pair or the new one.
+struct LLPair {
+    uint32_t bits, flag;
+};
+__device__ __forceinline__ void store_ll(LLPair* p, float v, uint32_t flag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(flag) : "memory");
 }
 
 template <typename YT>
@@ -246,6 +257,8 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
             b.peer_flags[p] = peers ? peers->flags[p] : nullptr;
         }
         b.rank = peers ? peers->rank : 0;
+        b.ll_mode = y_dtype == QB_Y_PUSHED ? 1 : 0;
+        if (b.ll_mode && (!peers || !peers->flags[peers->rank] || n < count)) return QB200_ERR_NOT_SUPPORTED;  // one launch, one exchange number
         b.peer_spin_limit = peer_spin_limit();
         b.count = n;
         b.total_items = items;
@@ -269,7 +282,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
     (nt == 2 ? (rb == 2 ? launch_gemv_async<2, 2, 2, YT>(b, smem, ctas, st) : launch_gemv_async<2, 1, 2, YT>(b, smem, ctas, st)) \
      : M > 4 ? (rb == 2 ? launch_gemv_async<1, 2, 2, YT>(b, smem, ctas, st) : launch_gemv_async<1, 1, 2, YT>(b, smem, ctas, st)) \
              : (rb == 2 ? launch_gemv_async<1, 2, 1, YT>(b, smem, ctas, st) : launch_gemv_async<1, 1, 1, YT>(b, smem, ctas, st)))
-        const qb200_status r = y_dtype == QB200_F32 ? QB_LAUNCH(float) : QB_LAUNCH(uint16_t);
+        const qb200_status r = y_dtype == QB200_F32 ? QB_LAUNCH(float) : y_dtype == QB_Y_PUSHED ? QB_LAUNCH(LLPair) : QB_LAUNCH(uint16_t);
 #undef QB_LAUNCH
         if (r) return r;
     }

@@ -175,6 +175,14 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
         // The codes and scales do not depend on the previous kernel; everything below may.
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        // pushed outputs carry the number of this exchange: one more than the count of exchanges this rank has
+        // completed (bumped by the launch's last CTA; read after the previous grid is complete)
+        uint32_t ll_flag = 0;
+        if constexpr (sizeof(YT) == 8) {
+            uint64_t done_count;
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(done_count) : "l"(a.peer_flags[a.rank] + 8) : "memory");
+            ll_flag = (uint32_t)done_count + 1u;
+        }
         // ---- service warps: refill, fold, store ----
         // A unit of the fold is one row of the sub-item and four batch columns (two when only two are kept): sixteen
         // 16-byte reads, one per compute warp, summed in warp order.  Units are dealt to the lanes row first, so a
@@ -215,7 +223,10 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
                         if (i < vec && b < a.M) {
                             YT* yp = static_cast<YT*>(it.y) + (uint64_t)b * it.N + n;
                             const float out = fmaf(v[i], GEMV_UNSCALE, bias);
-                            if (a.n_peers == 0) {
+                            if constexpr (sizeof(YT) == 8) {  // pushed: the same self-validating element into every rank's buffer
+                                for (uint32_t p = 0; p < a.n_peers; p++)
+                                    store_ll(reinterpret_cast<LLPair*>(reinterpret_cast<uint8_t*>(yp) + a.peer_delta[p]), out, ll_flag);
+                            } else if (a.n_peers == 0) {
                                 store_y<YT>(yp, out);
                             } else {  // fused exchange: the same element of every rank's buffer (peer memory over NVLink)
                                 for (uint32_t p = 0; p < a.n_peers; p++)
@@ -233,40 +244,78 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
         // peer "this rank's outputs of this step are written" and waits, bounded, for theirs, so the launch ends
         // when all ranks' outputs are here.  flags[p] is rank p's array {arrival of rank 0..7, step counter,
         // count of finished CTAs}.
-        if (a.n_peers && a.peer_flags[0]) {
-            __threadfence_system();  // this warp's peer stores before the count
-            if (NSERV > 1) {  // the other service warps' stores too: they join on a named barrier after their fences
-                asm volatile("bar.sync 1, %0;" ::"r"(NSERV * 32) : "memory");
-                if (sw != 0) goto service_done;
+        // Ordering, with as few system-scope fences as it takes (one costs microseconds: it waits for the peers to
+        // acknowledge every store in flight): each service warp fences its own peer stores once (sys scope) and
+        // joins the CTA's other service warp; the CTA's count is a release / acquire at GPU scope, so the last CTA
+        // has every CTA's fenced stores before it; its flag stores are releases at system scope and its polls
+        // acquires, which is all the consumer of the gathered buffer needs — no fence follows.
+        if constexpr (sizeof(YT) == 8) {
+            // pushed outputs need no ordering; the launch's last CTA only records that this exchange is done
+            if (NSERV > 1) asm volatile("bar.sync 1, %0;" ::"r"(NSERV * 32) : "memory");
+            if (sw == 0 && lane == 0) {
+                uint64_t* mine = a.peer_flags[a.rank];
+                if (atomicAdd(reinterpret_cast<unsigned int*>(mine + 9), 1u) == gridDim.x - 1) {
+                    *reinterpret_cast<unsigned int*>(mine + 9) = 0;
+                    mine[8] = ll_flag;
+                }
             }
+        } else if (a.n_peers && a.peer_flags[0]) {
+#ifdef QB200_TIMING
+            uint64_t tf0, tf1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tf0));
+#endif
+            asm volatile("fence.acq_rel.sys;" ::: "memory");  // this warp's peer stores before the count
+#ifdef QB200_TIMING
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tf1));
+            if (blockIdx.x == 0 && sw == 0 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.peer_flags[a.rank] + 14), tf1 - tf0);
+#endif
+            // the other service warps' stores too: they join on a named barrier after their fences
+            if (NSERV > 1) asm volatile("bar.sync 1, %0;" ::"r"(NSERV * 32) : "memory");
             uint32_t last = 0;
             uint64_t* mine = a.peer_flags[a.rank];
-            if (lane == 0) last = atomicAdd(reinterpret_cast<unsigned int*>(mine + 9), 1u) == gridDim.x - 1 ? 1u : 0u;
-            last = __shfl_sync(0xFFFFFFFFu, last, 0);
+            if (sw == 0 && lane == 0) {
+                uint32_t old;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(mine + 9) : "memory");
+                last = old == gridDim.x - 1 ? 1u : 0u;
+            }
+            last = __shfl_sync(0xFFFFFFFFu, last, 0);  // service warp 0 of the last CTA only
             if (last) {
-                __threadfence_system();  // the other CTAs' stores (ordered before their counts) before the flags
+#ifdef QB200_TIMING
+                uint64_t tm0, tm1, tm2;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm0));
+#endif
                 uint64_t step = 0;
                 if (lane == 0) {
                     *reinterpret_cast<unsigned int*>(mine + 9) = 0;
                     step = mine[8] + 1;
                     mine[8] = step;
                 }
-                step = __shfl_sync(0xFFFFFFFFu, step, 0);
+                step = __shfl_sync(0xFFFFFFFFu, step, 0);  // (the shuffle also carries lane 0's acquire to the lanes that publish)
                 if (lane < a.n_peers) {
                     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peer_flags[lane] + a.rank), "l"(step) : "memory");
+#ifdef QB200_TIMING
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm1));
+#endif
                     uint64_t v = 0;
                     uint32_t spins = 0;
                     for (;;) {
                         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(mine + lane) : "memory");
                         if (v >= step || ++spins >= a.peer_spin_limit) break;
-                        __nanosleep(200);
+                        __nanosleep(100);
                     }
+#ifdef QB200_TIMING
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm2));
+                    if (lane != a.rank) {  // the wait for a peer: ns from the count to the publish, from the publish to the arrival, polls
+                        atomicAdd(reinterpret_cast<unsigned long long*>(mine + 10), tm1 - tm0);
+                        atomicAdd(reinterpret_cast<unsigned long long*>(mine + 11), tm2 - tm1);
+                        atomicAdd(reinterpret_cast<unsigned long long*>(mine + 12), 1ull);
+                        atomicAdd(reinterpret_cast<unsigned long long*>(mine + 13), (unsigned long long)spins);
+                    }
+#endif
                     if (v < step) atomicExch(a.status, QB200_ERR_TIMEOUT);
                 }
-                __threadfence_system();
             }
         }
-    service_done:;
     } else {
         // ---- compute warps ----
         if constexpr (NT == 2) {

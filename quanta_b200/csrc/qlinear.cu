@@ -271,6 +271,38 @@ qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uin
     return s;
 }
 
+qb200_status qb200_qlinear_forward_many_push(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev, int32_t x_dtype,
+                                             uint64_t m, void* const* slot_own, void* const* arena_bases, uint32_t world, uint32_t rank,
+                                             uint64_t* state_own, void* stream) {
+    if (count == 0 || m == 0) return QB200_OK;
+    if (!layers || !x_dev || !slot_own || !arena_bases || !state_own || world == 0 || world > 8 || rank >= world)
+        return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_push: null argument or bad world / rank");
+    std::vector<qb::FwdArgs> args(count);
+    for (uint32_t i = 0; i < count; i++) {
+        const qb200_qlinear* q = layers[i];
+        if (!q || !x_dev[i] || !slot_own[i] || (reinterpret_cast<uintptr_t>(slot_own[i]) & 7u))
+            return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_push: null or misaligned entry " + std::to_string(i));
+        if (q->in_dim != layers[0]->in_dim || !decode_eligible(q, m, x_dtype, x_dev[i]))
+            return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_push: layer " + std::to_string(i) +
+                                                     " does not take the decode kernel (int4, 1x128, [out, in], bf16 x, m <= 16, in <= 4096)");
+        args[i] = fast_args(q, x_dev[i], slot_own[i], m);
+    }
+    qb::PeerSpec peers;
+    peers.world = world;
+    peers.rank = rank;
+    for (uint32_t p = 0; p < world; p++) {
+        if (!arena_bases[p]) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_push: null arena");
+        peers.delta[p] = static_cast<int64_t>(reinterpret_cast<intptr_t>(arena_bases[p]) - reinterpret_cast<intptr_t>(arena_bases[rank]));
+    }
+    peers.flags[rank] = state_own;
+    qb200_status s = qb::gemv_i4_forward_many(args.data(), count, qb::QB_Y_PUSHED, layers[0]->status, static_cast<cudaStream_t>(stream), &peers);
+    if (s == QB200_ERR_NOT_SUPPORTED)
+        return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_push: the layers do not fit ONE launch of the decode kernel");
+    if (s == QB200_OK)
+        for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_grouped_push";
+    return s;
+}
+
 qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint32_t count, const void* const* x_host,
                                              int32_t x_dtype, uint64_t m, void* const* y_host, int32_t y_dtype) {
     if (count == 0 || m == 0) return QB200_OK;

@@ -108,7 +108,9 @@ class StackPlan:
     over whole scale groups of the FFN width, SwiGLU is local, and the down projection is row-parallel over the
     same columns, cut into `down_slices` runs of at most 4096 inputs padded to one width: buffer "d" holds
     `[world, down_slices, batch, d]` partial outputs.  The vocabulary projection is column-sharded and its
-    logits are gathered in buffer "v" `[world, batch, v_max]`."""
+    logits are gathered from buffer "v" `[world, batch, v_max]`.  Buffer elements are 8 bytes: the exchanges are
+    pushed (every value travels with the number of its exchange and the consumers poll for it; no barrier), and
+    consecutive exchanges alternate between "o" and "d", which is what makes reusing a buffer safe."""
     world: int
     rank: int
     d: int
@@ -149,19 +151,21 @@ class StackPlan:
         return StackPlan(world, rank, d, heads, ffn, vocab, batch, h_lo * hd, h_hi * hd, g_lo * 128, g_hi * 128, v_lo, v_hi,
                          v0[1] - v0[0], tuple(_split_groups(g_hi - g_lo, n_slices)), pad, n_slices)
 
+    ELEM = 8  # bytes of a pushed element: the f32 bits and the number of the exchange that wrote them
+
     def arena_sizes(self) -> Dict[str, int]:
-        return {"o": self.world * self.batch * self.d * 4,
-                "d": self.world * self.down_slices * self.batch * self.d * 4,
-                "v": self.world * self.batch * self.v_max * 4}
+        return {"o": self.world * self.batch * self.d * self.ELEM,
+                "d": self.world * self.down_slices * self.batch * self.d * self.ELEM,
+                "v": self.world * self.batch * self.v_max * self.ELEM}
 
     def o_offset(self, rank: int) -> int:
-        return rank * self.batch * self.d * 4
+        return rank * self.batch * self.d * self.ELEM
 
     def d_offset(self, rank: int, s: int) -> int:
-        return (rank * self.down_slices + s) * self.batch * self.d * 4
+        return (rank * self.down_slices + s) * self.batch * self.d * self.ELEM
 
     def v_offset(self, rank: int) -> int:
-        return rank * self.batch * self.v_max * 4
+        return rank * self.batch * self.v_max * self.ELEM
 
 
 def _rows_of(m: QuantizedMatrix, lo: int, hi: int) -> QuantizedMatrix:
@@ -193,13 +197,13 @@ class DecoderStack:
     and differs from it only in the order of the f32 sums across ranks."""
 
     def __init__(self, n_layers: int, d: int, heads: int, ffn: int, vocab: int, batch: int, ctx_max: int, device,
-                 seed: int = 4, eps: float = 1e-5, rope_base: float = 10000.0, group=None, fused_barrier: bool = True):
+                 seed: int = 4, eps: float = 1e-5, rope_base: float = 10000.0, group=None):
         if d % heads or (d // heads) != 128:
             raise QuantError(L.ERR_NOT_SUPPORTED, "DecoderStack: head dim 128 only")
         self.n_layers, self.d, self.heads, self.ffn, self.vocab, self.batch, self.ctx_max = n_layers, d, heads, ffn, vocab, batch, ctx_max
         self.eps, self.rope_base, self.device = eps, rope_base, device
-        self.group, self.fused_barrier = group, fused_barrier
-        self.exchange = True  # False: every push stays local and nothing waits (for timing the step without its exchanges)
+        self.group = group
+        self.exchange = True  # False: step() leaves every exchange out (for timing what the exchanges cost)
         world = rank = 0
         if group is not None:
             import torch.distributed as dist
@@ -261,19 +265,19 @@ class DecoderStack:
         self.cos = torch.empty(hd, **f32)
         self.sin = torch.empty(hd, **f32)
         self._act_views = [self.act[i] for i in range(ns)]
+        self.logits = torch.empty(batch, vocab, **f32)
         if self.arena is None:
             self.o = torch.empty(1, batch, d, **f32)
             self.down_parts = torch.empty(ns, batch, d, **f32)
-            self.logits = torch.empty(batch, vocab, **f32)
         else:
             a = self.arena
-            self.o = a.tensor("o", (self.world, batch, d))
-            self.down_parts = a.tensor("d", (self.world * ns, batch, d))
-            self.logits_parts = a.tensor("v", (self.world, batch * p.v_max))  # slot r: [batch, rows of rank r] packed
-            self.logits = torch.empty(batch, vocab, **f32)
             self._o_own = [a.address("o", p.o_offset(rank))]
             self._d_own = [a.address("d", p.d_offset(rank, s)) for s in range(ns)]
             self._v_own = [a.address("v", p.v_offset(rank))]
+            # what the exchanges are timed against: the same launches storing plain f32 locally
+            self._o_local = torch.empty(1, batch, d, **f32)
+            self._d_local = torch.empty(ns, batch, d, **f32)
+            self._v_local = torch.empty(batch, p.v_hi - p.v_lo, **f32)
 
     @staticmethod
     def _bytes(ql: QuantizedLinear) -> int:
@@ -285,9 +289,9 @@ class DecoderStack:
 
     def exchange_bytes(self) -> int:
         """Bytes this rank stores into EACH peer per step (partial outputs of the output and down projections,
-        its slice of the logits)."""
+        its slice of the logits; 8 bytes per value)."""
         p = self.plan
-        return self.n_layers * (1 + p.down_slices) * self.batch * self.d * 4 + self.batch * (p.v_hi - p.v_lo) * 4
+        return (self.n_layers * (1 + p.down_slices) * self.batch * self.d + self.batch * (p.v_hi - p.v_lo)) * p.ELEM
 
     def set_position(self, pos: int):
         c, s = rope_rows(pos, self.d // self.heads, self.rope_base)
@@ -298,49 +302,69 @@ class DecoderStack:
     def step(self, h0: torch.Tensor) -> torch.Tensor:
         """One decode step from the embedded tokens h0 [batch, d] (f32, the same on every rank) at the position
         given to set_position; returns the logits [batch, vocab] (on every rank)."""
+        if self.arena is not None and not self.exchange:
+            return self._step_without_exchanges(h0)
         f32 = torch.float32
         self.h.copy_(h0)
         pos, kv_len, scale = self.pos, self.pos + 1, 1.0 / math.sqrt(self.d // self.heads)
-        a, B = self.arena, self.batch
-        push = self._push if self.exchange else self._push_local
+        a, B, W, ns = self.arena, self.batch, self.world, self.plan.down_slices
+        first = True
+        for li, blk in enumerate(self.layers):
+            if a is None or first:
+                add_rmsnorm(self.h, None if first else self.down_parts, blk["g1"], self.eps, self.xn)
+            else:  # the down projection's partial outputs of every rank and slice, pushed into buffer "d"
+                a.add_rmsnorm_pushed(self.h, "d", W * ns, blk["g1"], self.eps, self.xn)
+            first = False
+            QuantizedLinear.forward_many(blk["qkv"], [self.xn] * 3, out_dtype=f32, outs=[self.qkv[0], self.qkv[1], self.qkv[2]])
+            rope_append(self.qkv[0], self.qkv[1], self.qkv[2], self.cos, self.sin, self.heads_local, self.qb, self.kcache[li], self.vcache[li], pos)
+            sdpa_decode(self.qb, self.kcache[li], self.vcache[li], kv_len, scale, self.scratch, self.att)
+            if a is None:
+                blk["o"].forward(self.att, out_dtype=f32, out=self.o[0])
+                add_rmsnorm(self.h, self.o, blk["g2"], self.eps, self.xn)
+            else:  # partial outputs over this rank's heads -> slot `rank` of every rank's buffer "o"
+                a.push_pushed([blk["o"]], [self.att], self._o_own, B)
+                a.add_rmsnorm_pushed(self.h, "o", W, blk["g2"], self.eps, self.xn)
+            QuantizedLinear.forward_many(blk["gate_up"], [self.xn] * 2, out_dtype=f32, outs=[self.gu[0], self.gu[1]])
+            swiglu_sliced(self.gu[0], self.gu[1], self.down_widths, self.act, self.down_pad)
+            if a is None:
+                QuantizedLinear.forward_many(blk["down"], self._act_views, out_dtype=f32, outs=[p for p in self.down_parts])
+            else:
+                a.push_pushed(blk["down"], self._act_views, self._d_own, B)
+        if a is None:
+            add_rmsnorm(self.h, self.down_parts if self.layers else None, self.g_final, self.eps, self.xn)
+            self.lm_head.forward(self.xn, out_dtype=f32, out=self.logits)
+            return self.logits
+        if self.layers:
+            a.add_rmsnorm_pushed(self.h, "d", W * ns, self.g_final, self.eps, self.xn)
+        else:
+            add_rmsnorm(self.h, None, self.g_final, self.eps, self.xn)
+        # the logits: a block with no layers would push twice in a row into nothing in between; the vocabulary
+        # buffer is a third one, so the alternation of "o" and "d" is not disturbed
+        a.push_pushed([self.lm_head], [self.xn], self._v_own, B)
+        a.gather_pushed("v", W, B * self.plan.v_max, B, self.vocab, self.logits)
+        return self.logits
+
+    def _step_without_exchanges(self, h0: torch.Tensor) -> torch.Tensor:
+        """The sharded step with every exchange left out: each rank keeps its own partial outputs (plain f32, local)
+        and nothing waits.  Its logits mean nothing; its time is what the exchanges are measured against."""
+        f32 = torch.float32
+        self.h.copy_(h0)
+        pos, kv_len, scale = self.pos, self.pos + 1, 1.0 / math.sqrt(self.d // self.heads)
         delta = None
         for li, blk in enumerate(self.layers):
             add_rmsnorm(self.h, delta, blk["g1"], self.eps, self.xn)
             QuantizedLinear.forward_many(blk["qkv"], [self.xn] * 3, out_dtype=f32, outs=[self.qkv[0], self.qkv[1], self.qkv[2]])
             rope_append(self.qkv[0], self.qkv[1], self.qkv[2], self.cos, self.sin, self.heads_local, self.qb, self.kcache[li], self.vcache[li], pos)
             sdpa_decode(self.qb, self.kcache[li], self.vcache[li], kv_len, scale, self.scratch, self.att)
-            if a is None:
-                blk["o"].forward(self.att, out_dtype=f32, out=self.o[0])
-            else:  # partial outputs over this rank's heads -> slot `rank` of every rank's buffer
-                push([blk["o"]], [self.att], self._o_own)
-            add_rmsnorm(self.h, self.o, blk["g2"], self.eps, self.xn)
+            QuantizedLinear.forward_many([blk["o"]], [self.att], out_dtype=f32, outs=[self._o_local[0]])
+            add_rmsnorm(self.h, self._o_local, blk["g2"], self.eps, self.xn)
             QuantizedLinear.forward_many(blk["gate_up"], [self.xn] * 2, out_dtype=f32, outs=[self.gu[0], self.gu[1]])
             swiglu_sliced(self.gu[0], self.gu[1], self.down_widths, self.act, self.down_pad)
-            if a is None:
-                QuantizedLinear.forward_many(blk["down"], self._act_views, out_dtype=f32, outs=[p for p in self.down_parts])
-            else:
-                push(blk["down"], self._act_views, self._d_own)
-            delta = self.down_parts  # summed by the next add_rmsnorm
+            QuantizedLinear.forward_many(blk["down"], self._act_views, out_dtype=f32, outs=[p for p in self._d_local])
+            delta = self._d_local
         add_rmsnorm(self.h, delta, self.g_final, self.eps, self.xn)
-        if a is None:
-            self.lm_head.forward(self.xn, out_dtype=f32, out=self.logits)
-            return self.logits
-        push([self.lm_head], [self.xn], self._v_own)
-        p = self.plan
-        for r in range(self.world):  # rank r's rows of the vocabulary
-            lo, hi = shard_units(self.vocab, self.world, r)
-            self.logits[:, lo:hi].copy_(self.logits_parts[r, : self.batch * (hi - lo)].view(self.batch, hi - lo))
+        QuantizedLinear.forward_many([self.lm_head], [self.xn], out_dtype=f32, outs=[self._v_local])
         return self.logits
-
-    def _push(self, layers, xs, own):
-        self.arena.push(layers, xs, own, self.batch, torch.float32, self.fused_barrier)
-
-    def _push_local(self, layers, xs, own):
-        n = len(layers)
-        hs = (L.vp * n)(*[ql._h for ql in layers])
-        xp = (L.vp * n)(*[x.data_ptr() for x in xs])
-        yp = (L.vp * n)(*own)
-        _check(L.load().qb200_qlinear_forward_many(hs, n, xp, L.BF16, self.batch, yp, L.F32, _stream(self.device)))
 
     def close(self):
         if self.arena is not None:

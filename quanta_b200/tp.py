@@ -259,6 +259,37 @@ class PeerArena:
             _check(lib.qb200_peer_signal_wait(self._flags_c, self.world, self.rank, self.status.data_ptr(), stream))
         self._lead = layers[0]
 
+    # ---- pushed exchanges: self-validating 8-byte elements, no barrier (see qb200_qlinear_forward_many_push) ----
+
+    def state_address(self) -> int:
+        """This rank's 16-word state array (word 8: the exchanges it has launched)."""
+        return self._own + self.data_bytes
+
+    def push_pushed(self, layers: List[QuantizedLinear], xs: List[torch.Tensor], own_addresses: List[int], m: int) -> None:
+        """layers[i](xs[i]) stored as {f32 bits, exchange number} elements at `own_addresses[i]` of this rank's arena and at
+        the same offset of every peer's; the launch neither fences nor waits — the consumers poll the elements."""
+        n = len(layers)
+        hs = (L.vp * n)(*[ql._h for ql in layers])
+        xp = (L.vp * n)(*[x.data_ptr() for x in xs])
+        yp = (L.vp * n)(*own_addresses)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _check(L.load().qb200_qlinear_forward_many_push(hs, n, xp, L.BF16, m, yp, self._bases_c, self.world, self.rank,
+                                                        self.state_address(), stream))
+        self._lead = layers[0]
+
+    def add_rmsnorm_pushed(self, h: torch.Tensor, name: str, parts: int, gamma: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+        """h += the `parts` pushed arrays of buffer `name` (summed in part order); returns bf16(rmsnorm(h) * gamma)."""
+        n, c = h.shape
+        _check(L.load().qb200_add_rmsnorm_pushed(h.data_ptr(), self.address(name), parts, self.state_address(), gamma.data_ptr(), n, c, eps,
+                                                 out.data_ptr(), self.status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream))
+        return out
+
+    def gather_pushed(self, name: str, parts: int, part_stride: int, rows: int, cols: int, dst: torch.Tensor) -> torch.Tensor:
+        """Column shards of a `[rows, cols]` output pushed by the `parts` ranks into buffer `name` -> dense f32 `dst`."""
+        _check(L.load().qb200_gather_pushed(self.address(name), parts, part_stride, rows, cols, self.state_address(), dst.data_ptr(),
+                                            dst.stride(0), self.status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream))
+        return dst
+
     def check(self) -> None:
         """Synchronises and raises if a bounded wait of a barrier ran out."""
         if self._lead is not None:

@@ -43,10 +43,10 @@ def test_stack_plan_llama7b_shape(world):
         assert sizes == plans[0].arena_sizes()
         o_slots = [p.o_offset(r) for r in range(world)]
         d_slots = [p.d_offset(r, s) for r in range(world) for s in range(p.down_slices)]
-        part = 16 * 4096 * 4
+        part = 16 * 4096 * p.ELEM
         assert o_slots == [i * part for i in range(world)] and o_slots[-1] + part == sizes["o"]
         assert d_slots == [i * part for i in range(world * p.down_slices)] and d_slots[-1] + part == sizes["d"]
-        assert p.v_offset(world - 1) + 16 * p.v_max * 4 == sizes["v"] and p.v_max >= p.v_hi - p.v_lo
+        assert p.v_offset(world - 1) + 16 * p.v_max * p.ELEM == sizes["v"] and p.v_max >= p.v_hi - p.v_lo
     if world == 1:
         assert plans[0].down_widths == (3712, 3712, 3584) and plans[0].down_pad == 4096
     if world == 8:
@@ -88,19 +88,19 @@ def _worker(rank, world, port, ret):
 
         dq_o, dq_d, dq_v = deq(w_o), deq(w_d), deq(w_v)
         # exchange 1: the output projection over this rank's heads -> slot `rank` of buffer "o"; sum of slots
-        buf_o = np.zeros(p.arena_sizes()["o"] // 4, np.float32)
+        buf_o = np.zeros(p.arena_sizes()["o"] // p.ELEM, np.float32)
         part = att[:, p.q_lo:p.q_hi] @ dq_o[:, p.q_lo:p.q_hi].T
-        lo = p.o_offset(rank) // 4
+        lo = p.o_offset(rank) // p.ELEM
         mine = torch.from_numpy(part.reshape(-1).copy())
         every = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(every, mine)
         for r in range(world):  # what the peers' stores put into this rank's buffer
-            buf_o[p.o_offset(r) // 4: p.o_offset(r) // 4 + mine.numel()] = every[r].numpy()
+            buf_o[p.o_offset(r) // p.ELEM: p.o_offset(r) // p.ELEM + mine.numel()] = every[r].numpy()
         assert np.array_equal(buf_o[lo: lo + mine.numel()], mine.numpy())
         got = buf_o.reshape(world, batch, d).sum(0)
         ok = np.allclose(got, att @ dq_o.T, rtol=1e-5, atol=1e-6)
         # exchange 2: the down projection over this rank's FFN columns, in padded slices
-        buf_d = np.zeros(p.arena_sizes()["d"] // 4, np.float32)
+        buf_d = np.zeros(p.arena_sizes()["d"] // p.ELEM, np.float32)
         parts, c0 = [], p.f_lo
         for w in p.down_widths:
             xs = np.zeros((batch, p.down_pad), np.float32)
@@ -113,12 +113,12 @@ def _worker(rank, world, port, ret):
         every = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(every, mine)
         for r in range(world):
-            a0 = p.d_offset(r, 0) // 4
+            a0 = p.d_offset(r, 0) // p.ELEM
             buf_d[a0: a0 + mine.numel()] = every[r].numpy()
         got = buf_d.reshape(world * p.down_slices, batch, d).sum(0)
         ok = ok and np.allclose(got, act @ dq_d.T, rtol=1e-5, atol=1e-5)
         # the logits: ragged vocabulary shards packed [batch, rows of rank r] in slot r
-        buf_v = np.zeros(p.arena_sizes()["v"] // 4, np.float32)
+        buf_v = np.zeros(p.arena_sizes()["v"] // p.ELEM, np.float32)
         mine = np.zeros(batch * p.v_max, np.float32)
         mine[: batch * (p.v_hi - p.v_lo)] = (xn @ dq_v[p.v_lo:p.v_hi].T).reshape(-1)
         mine = torch.from_numpy(mine)
@@ -126,9 +126,9 @@ def _worker(rank, world, port, ret):
         dist.all_gather(every, mine)
         logits = np.zeros((batch, vocab), np.float32)
         for r in range(world):
-            buf_v[p.v_offset(r) // 4: p.v_offset(r) // 4 + mine.numel()] = every[r].numpy()
+            buf_v[p.v_offset(r) // p.ELEM: p.v_offset(r) // p.ELEM + mine.numel()] = every[r].numpy()
             lo_r, hi_r = dec.shard_units(vocab, world, r)
-            slot = buf_v[p.v_offset(r) // 4:]
+            slot = buf_v[p.v_offset(r) // p.ELEM:]
             logits[:, lo_r:hi_r] = slot[: batch * (hi_r - lo_r)].reshape(batch, hi_r - lo_r)
         ok = ok and np.allclose(logits, xn @ dq_v.T, rtol=1e-5, atol=1e-6)
         ret[rank] = bool(ok)
