@@ -285,6 +285,37 @@ QB200_API qb200_status qb200_gather_pushed(const void* pushed, uint32_t parts, u
                                            const uint64_t* state_own, float* dst, uint64_t dst_stride, int32_t* status_dev,
                                            void* stream);
 
+/* ---- tensor parallelism over a library collective (no counterpart in the reference) ----
+ * For every shape the fused exchanges above do not take (prefill batches, int8 layers, inputs wider than 4096, GPUs
+ * without peer access): each rank runs its shard's ordinary forward and NCCL moves the outputs.  NCCL is opened at
+ * run time (libnccl.so.2); a failure to load it or an NCCL error is QB200_ERR_NCCL.
+ *   qb200_shard_rows — rows [lo, hi) of rank's block of an `[out, in]` weight: equal blocks of whole scale tiles
+ *     (`gr` rows), trailing ranks short or empty; the codes and scales of the block are contiguous: a pointer offset.
+ *   qb200_shard_cols — columns [lo, hi) for the row-parallel pairing: whole scale tiles (`gc`) and whole packed words.
+ *   qb200_tp_unique_id / qb200_tp_create — rank 0 makes the 128-byte id, the caller hands it to every rank, every
+ *     rank creates its communicator with its own device current.
+ *   qb200_qlinear_forward_tp — QB200_TP_COLUMN: `shard` holds rank's row block (qb200_shard_rows(full_dim, granule)),
+ *     x is the full `[m, in]`, y receives the gathered `[m, full_dim]` on every rank (f32 or bf16).
+ *     QB200_TP_ROW: `shard` holds rank's column block, x is rank's `[m, hi - lo]` slice, y receives the f32 sum of the
+ *     partial outputs on every rank (the order of the sum differs from the unsharded layer's: equal to 1e-4, not bit for
+ *     bit; give the bias to one rank's shard only).  A rank that owns nothing passes shard = NULL.  The gather's staging
+ *     buffer grows on demand: run the largest shape once before capturing calls into a CUDA graph.
+ *   qb200_tp_status — synchronises `stream` and reports the shard's device status word (qb200_qlinear_check). */
+typedef struct qb200_tp qb200_tp;
+enum { QB200_TP_COLUMN = 0, QB200_TP_ROW = 1 };
+QB200_API qb200_status qb200_shard_rows(uint64_t rows, uint64_t gr, uint32_t world, uint32_t rank, uint64_t* lo, uint64_t* hi);
+QB200_API qb200_status qb200_shard_cols(uint64_t cols, uint64_t gc, uint32_t bits, uint32_t world, uint32_t rank, uint64_t* lo,
+                                        uint64_t* hi);
+QB200_API qb200_status qb200_tp_unique_id(uint8_t* id128);
+QB200_API qb200_status qb200_tp_create(uint32_t rank, uint32_t world, const uint8_t* id128, qb200_tp** out);
+QB200_API void qb200_tp_destroy(qb200_tp* tp);
+QB200_API uint32_t qb200_tp_rank(const qb200_tp* tp);
+QB200_API uint32_t qb200_tp_world(const qb200_tp* tp);
+QB200_API qb200_status qb200_qlinear_forward_tp(qb200_tp* tp, qb200_qlinear* shard, int32_t mode, uint64_t full_dim, uint64_t granule,
+                                                const void* x_dev, int32_t x_dtype, uint64_t m, void* y_dev, int32_t y_dtype,
+                                                void* stream);
+QB200_API qb200_status qb200_tp_status(qb200_tp* tp, qb200_qlinear* shard, void* stream);
+
 /* qb200_qlinear_forward_many over HOST buffers: every distinct input pointer is
  * copied to the device once, the forwards run, all outputs are copied back and
  * the call synchronises.  Staging buffers belong to layers[0] and grow on demand.

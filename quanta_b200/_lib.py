@@ -20,6 +20,7 @@ OK, ERR_RANK, ERR_GRANULARITY, ERR_GRID, ERR_FORMAT, ERR_NOT_SUPPORTED, ERR_SCAL
 PER_TENSOR, PER_CHANNEL, GROUP, BLOCK = 0, 1, 2, 3
 IN_OUT, OUT_IN = 0, 1
 F32, BF16, F16 = 0, 1, 2
+TP_COLUMN, TP_ROW = 0, 1
 
 
 class StItem(ctypes.Structure):
@@ -68,6 +69,15 @@ SIGNATURES = {
     "qb200_gather_pushed": (i32, [vp, u32, u64, u32, u64, vp, vp, u64, vp, vp]),
     "qb200_peer_set_spin_limit": (i32, [u32]),
     "qb200_qlinear_check": (i32, [vp, vp]),
+    "qb200_shard_rows": (i32, [u64, u64, u32, u32, P(u64), P(u64)]),
+    "qb200_shard_cols": (i32, [u64, u64, u32, u32, u32, P(u64), P(u64)]),
+    "qb200_tp_unique_id": (i32, [ctypes.c_char_p]),
+    "qb200_tp_create": (i32, [u32, u32, ctypes.c_char_p, P(vp)]),
+    "qb200_tp_destroy": (None, [vp]),
+    "qb200_tp_rank": (u32, [vp]),
+    "qb200_tp_world": (u32, [vp]),
+    "qb200_qlinear_forward_tp": (i32, [vp, vp, i32, u64, u64, vp, i32, u64, vp, i32, vp]),
+    "qb200_tp_status": (i32, [vp, vp, vp]),
     "qb200_gemm_quant": (i32, [i32, u32, u32, u32, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, ctypes.c_float, vp, vp]),
     "qb200_gemm_quant4": (i32, [i32, u32, u32, u32, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, ctypes.c_float, vp, vp]),
     "qb200_gemv_quant": (i32, [i32, u32, u32, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, ctypes.c_float, vp, vp]),

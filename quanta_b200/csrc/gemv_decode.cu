@@ -212,9 +212,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
     if (K / 128 > 2 * REG_WARPS) return QB200_ERR_NOT_SUPPORTED;  // wider inputs run as column slices
     // Row blocks per item: a lone small layer keeps 16-row items (more items to pipeline and to
     // overlap with the neighbouring launches); grouped launches take 32-row items.
-    uint32_t rb = (count > 1 || peers) ? 2 : 1;
-    static const char* exp_rb = getenv("QB200_EXP_RB");  // EXPERIMENT: "1" = 16-row items for batches above 4
-    if (exp_rb && exp_rb[0] == '1' && M > 4) rb = 1;
+    const uint32_t rb = (count > 1 || peers) ? 2 : 1;
     uint64_t all_tiles = 0, all_rows = 0;
     for (uint32_t i = 0; i < count; i++) {
         all_tiles += (f[i].out_dim + 16 * rb - 1) / (16 * rb);

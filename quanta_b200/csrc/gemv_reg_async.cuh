@@ -36,6 +36,7 @@ __host__ __device__ constexpr uint32_t async_threads(int nt, int nserv) { return
 
 // Shared-memory carve-up of the service-warp kernel, identical on host and device.
 // sub_rows: rows folded at a time; red_stride: floats between rows of a slot of partial sums.
+constexpr uint32_t ASYNC_SLOTS = 2;  // slots of partial sums a CTA cycles through
 struct AsyncSmem {
     uint32_t desc, red, scales, codes, total, stage_scales, stage_codes, slot_floats;
 };
@@ -47,7 +48,7 @@ __host__ __device__ inline AsyncSmem async_smem_layout(uint32_t K, uint32_t rb, 
     L.desc = 128;  // barriers at 0: [S <= 8] codes landed, [2] slot parked, [2] slot folded
     L.red = L.desc + up(REG_MAX_ITEMS * (uint32_t)sizeof(RegItem));
     L.slot_floats = REG_WARPS * sub_rows * red_stride;
-    L.scales = L.red + up(2 * L.slot_floats * 4);
+    L.scales = L.red + up(ASYNC_SLOTS * L.slot_floats * 4);
     L.stage_scales = up(rb * 16 * groups * 4);
     L.codes = L.scales + stages * L.stage_scales;
     L.stage_codes = up(rb * 16 * (K / 2));
@@ -101,8 +102,8 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
     const uint32_t RS = a.red_stride;           // floats between rows of a slot
     const AsyncSmem L = async_smem_layout(a.K, RB, SUB_ROWS, RS, S);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [S] codes landed
-    uint64_t* done = bars + 8;                           // [2] all compute warps have parked the sub-item's partial sums
-    uint64_t* vacant = bars + 10;                        // [2] the service warp has folded the slot
+    uint64_t* done = bars + 8;                           // [slots] all compute warps have parked the sub-item's partial sums
+    uint64_t* vacant = bars + 8 + ASYNC_SLOTS;           // [slots] the service warps have folded the slot
     float* s_red = reinterpret_cast<float*>(smem + L.red);
     RegItem* s_desc = reinterpret_cast<RegItem*>(smem + L.desc);     // one per item of this CTA
 
@@ -153,7 +154,7 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
 
     if (tid == 0) {
         for (uint32_t s = 0; s < S; s++) mbar_init(&bars[s], async_scales ? 1 + 32 : 1);
-        for (uint32_t s = 0; s < 2; s++) {
+        for (uint32_t s = 0; s < ASYNC_SLOTS; s++) {
             mbar_init(&done[s], REG_WARPS);
             mbar_init(&vacant[s], NSERV);
         }
@@ -193,8 +194,8 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
             const RegItem& it = s_desc[j];
 #pragma unroll 1
             for (int s = 0; s < SUBS; s++, q++) {
-                const uint32_t slot = q & 1;
-                if (!mbar_wait_bounded(&done[slot], (q >> 1) & 1)) { failed = true; break; }
+                const uint32_t slot = q % ASYNC_SLOTS;
+                if (!mbar_wait_bounded(&done[slot], (q / ASYNC_SLOTS) & 1)) { failed = true; break; }
                 if (sw == 0 && s == SUBS - 1 && j + S < n_my) issue(j + S, st);  // every compute warp has left the stage
                 for (uint32_t u = sw * 32 + lane; u < units; u += NSERV * 32) {
                     const uint32_t row_l = u % SUB_ROWS, b0 = (u / SUB_ROWS) * 4;
@@ -373,12 +374,15 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
                 }
                 if (ood) atomicExch(a.status, QB200_ERR_INVALID_PARAM);  // reported by qb200_qlinear_check
             }
-#pragma unroll 1
+#pragma unroll
             for (int s = 0; s < SUBS; s++, q++) {
-                const uint32_t slot = q & 1, vpar = ((q >> 1) & 1) ^ 1;
-                // the slot's previous sub-item has long been folded: polled here so that its latency overlaps the loads
-                const uint32_t vac = sm0 + 80 + slot * 8;
-                if (q >= 2 && !async_try_wait(vac, vpar) && !async_wait_bounded(vac, vpar)) { failed = true; break; }
+                const uint32_t slot = q % ASYNC_SLOTS, vpar = ((q / ASYNC_SLOTS) & 1) ^ 1;
+                const uint32_t vac = sm0 + 64 + (ASYNC_SLOTS + slot) * 8;
+                // The slot's previous sub-item has long been folded.  With 32-row sub-items the poll sits here, where its
+                // latency overlaps the loads (measured: polling before the stores instead costs a single-row batch a
+                // quarter of its bandwidth); with 16-row sub-items a warp may run one sub-item further ahead of the
+                // fold if it polls only before it parks its sums (+ 7 % for a batch of 16).
+                if (NT == 1 && q >= ASYNC_SLOTS && !async_try_wait(vac, vpar) && !async_wait_bounded(vac, vpar)) { failed = true; break; }
                 // every load of the sub-item first
                 uint4 c[RPS][4];
                 float sc[RPS][4];
@@ -423,6 +427,7 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
                 // park the partial sums in red[slot][warp][row][batch]: (p - 8 * sum x) is the group's sum of q * x in
                 // MMA units (2^-93); 2^93 is applied at the store
                 const uint32_t ra = red0 + slot * (L.slot_floats * 4);
+                if (NT == 2 && q >= ASYNC_SLOTS && !async_try_wait(vac, vpar) && !async_wait_bounded(vac, vpar)) { failed = true; break; }
 #pragma unroll
                 for (int rb = 0; rb < RPS; rb++)
 #pragma unroll

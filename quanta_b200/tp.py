@@ -21,16 +21,15 @@ from .quant import QuantError, QuantizedMatrix, check as _check
 
 
 def shard_range(out_dim: int, world: int, rank: int, multiple: int = 1) -> Tuple[int, int]:
-    """Rows [lo, hi) of rank's shard: equal blocks rounded up to ``multiple`` (the scale tile height,
+    """Rows [lo, hi) of rank's shard (qb200_shard_rows): equal blocks rounded up to ``multiple`` (the scale tile height,
     so no tile straddles a boundary); trailing ranks may get a short or empty block."""
     if world < 1 or not 0 <= rank < world:
         raise QuantError(L.ERR_INVALID_PARAM, f"shard_range: rank {rank} outside world of {world}")
     if multiple < 1:
         raise QuantError(L.ERR_INVALID_PARAM, "shard_range: multiple must be positive")
-    per = -(-out_dim // world)
-    per = -(-per // multiple) * multiple
-    lo = min(out_dim, rank * per)
-    return lo, min(out_dim, lo + per)
+    lo, hi = L.u64(), L.u64()
+    _check(L.load().qb200_shard_rows(out_dim, multiple, world, rank, ctypes.byref(lo), ctypes.byref(hi)))
+    return lo.value, hi.value
 
 
 def shard_matrix(m: QuantizedMatrix, world: int, rank: int) -> QuantizedMatrix:
@@ -69,14 +68,67 @@ def _gather(y_local, m, widths, group):
     return torch.cat([out[r, :, : widths[r]] for r in range(world)], dim=1)
 
 
-class TensorParallelLinear:
-    """A QuantizedLinear whose output features are sharded over the ranks of a process group."""
+class TpComm:
+    """The library's own communicator (qb200_tp_create: NCCL opened at run time), one per rank with its device current.
+    Rank 0's unique id travels to the other ranks through the torch process group that launched them."""
 
-    def __init__(self, local: Optional[QuantizedLinear], out_dim: int, widths: List[int], group=None):
-        self.local, self._out, self._widths, self.group = local, out_dim, widths, group
+    def __init__(self, group=None):
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        lib = L.load()
+        ident = ctypes.create_string_buffer(128)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        err = None
+        if self.rank == 0 and self.world > 1:
+            try:
+                _check(lib.qb200_tp_unique_id(ident))
+            except QuantError as e:
+                err = e
+        if self.world > 1:
+            t = torch.frombuffer(bytearray(ident.raw), dtype=torch.uint8).to(dev)
+            dist.broadcast(t, 0, group=group)
+            ident = ctypes.create_string_buffer(t.cpu().numpy().tobytes(), 128)
+        h = L.vp()
+        if err is None:
+            try:
+                _check(lib.qb200_tp_create(self.rank, self.world, ident if self.world > 1 else None, ctypes.byref(h)))
+            except QuantError as e:
+                err = e
+        ok = torch.tensor([0.0 if err is not None else 1.0], device=dev)
+        if self.world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() == 0:
+            if h.value:
+                lib.qb200_tp_destroy(h)
+            raise QuantError(L.ERR_NCCL, "TpComm: a rank could not create its communicator" + (f" ({err})" if err is not None else ""))
+        self._h = h
+
+    def forward(self, shard: Optional[QuantizedLinear], mode: int, full_dim: int, granule: int, x: torch.Tensor, out: torch.Tensor):
+        """qb200_qlinear_forward_tp: the shard's forward plus the gather (TP_COLUMN) or the sum (TP_ROW) of the outputs."""
+        act = {torch.float32: L.F32, torch.bfloat16: L.BF16}
+        x = x.contiguous()
+        _check(L.load().qb200_qlinear_forward_tp(self._h, shard._h if shard is not None else None, mode, full_dim, granule, x.data_ptr(),
+                                                  act[x.dtype], x.shape[0], out.data_ptr(), act[out.dtype],
+                                                  torch.cuda.current_stream(x.device).cuda_stream))
+        return out
+
+    def close(self):
+        if self._h is not None:
+            torch.cuda.synchronize()
+            L.load().qb200_tp_destroy(self._h)
+            self._h = None
+
+
+class TensorParallelLinear:
+    """A QuantizedLinear whose output features are sharded over the ranks of a process group.  On GPUs with a
+    ``TpComm`` the forward is the library's qb200_qlinear_forward_tp (shard forward + NCCL all-gather behind the C
+    ABI); without one the gather goes through torch.distributed (gloo on CPU ranks, for the host-side tests)."""
+
+    def __init__(self, local: Optional[QuantizedLinear], out_dim: int, widths: List[int], group=None, comm: Optional[TpComm] = None,
+                 granule: int = 1):
+        self.local, self._out, self._widths, self.group, self.comm, self.granule = local, out_dim, widths, group, comm, granule
 
     @classmethod
-    def new(cls, w: QuantizedMatrix, b: Optional[torch.Tensor] = None, group=None) -> "TensorParallelLinear":
+    def new(cls, w: QuantizedMatrix, b: Optional[torch.Tensor] = None, group=None, comm: Optional[TpComm] = None) -> "TensorParallelLinear":
         """Shards an ``[out, in]`` matrix (and its bias) by rows of the scale grid over the group."""
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         rows, _ = w.shape()
@@ -86,7 +138,7 @@ class TensorParallelLinear:
         local = None
         if hi > lo:
             local = QuantizedLinear.new(shard_matrix(w, world, rank), None if b is None else b[lo:hi].contiguous(), L.OUT_IN)
-        return cls(local, rows, [h - l for l, h in ranges], group)
+        return cls(local, rows, [h - l for l, h in ranges], group, comm, gr)
 
     def out_dim(self) -> int:
         return self._out
@@ -94,6 +146,9 @@ class TensorParallelLinear:
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or x.dtype
         rank = dist.get_rank(self.group)
+        if self.comm is not None:
+            out = torch.empty((x.shape[0], self._out), dtype=out_dtype, device=x.device)
+            return self.comm.forward(self.local, L.TP_COLUMN, self._out, self.granule, x, out)
         if self.local is not None:
             y = self.local.forward(x, out_dtype=out_dtype)
         else:
@@ -110,8 +165,9 @@ def shard_columns(m: QuantizedMatrix, world: int, rank: int):
     packed int4 word), so no tile and no word straddles them; the shard's codes and scales are copies."""
     rows, cols = m.shape()
     gr, gc = m.tile()
-    mult = gc if m.dtype().bits() == 8 or gc % 8 == 0 else gc * 8 // math.gcd(gc, 8)
-    lo, hi = shard_range(cols, world, rank, mult)
+    a, b = L.u64(), L.u64()
+    _check(L.load().qb200_shard_cols(cols, gc, m.dtype().bits(), world, rank, ctypes.byref(a), ctypes.byref(b)))
+    lo, hi = a.value, b.value
     if hi <= lo:
         return None, lo, hi
     if m.dtype().bits() == 8:
@@ -128,15 +184,16 @@ class RowParallelLinear:
     column-sharded layer it consumes that layer's local output as is, so a block of two linears needs one
     collective instead of two.  The sum's order differs from the unsharded layer's: equal to 1e-4, not bit for bit."""
 
-    def __init__(self, local: Optional[QuantizedLinear], bias: Optional[torch.Tensor], out_dim: int, lo: int, hi: int, group=None):
-        self.local, self.bias, self._out, self.lo, self.hi, self.group = local, bias, out_dim, lo, hi, group
+    def __init__(self, local: Optional[QuantizedLinear], bias: Optional[torch.Tensor], out_dim: int, lo: int, hi: int, group=None,
+                 comm: Optional[TpComm] = None):
+        self.local, self.bias, self._out, self.lo, self.hi, self.group, self.comm = local, bias, out_dim, lo, hi, group, comm
 
     @classmethod
-    def new(cls, w: QuantizedMatrix, b: Optional[torch.Tensor] = None, group=None) -> "RowParallelLinear":
+    def new(cls, w: QuantizedMatrix, b: Optional[torch.Tensor] = None, group=None, comm: Optional[TpComm] = None) -> "RowParallelLinear":
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         shard, lo, hi = shard_columns(w, world, rank)
         local = None if shard is None else QuantizedLinear.new(shard, None, L.OUT_IN)
-        return cls(local, None if b is None else b.to(torch.float32), w.shape()[0], lo, hi, group)
+        return cls(local, None if b is None else b.to(torch.float32), w.shape()[0], lo, hi, group, comm)
 
     def out_dim(self) -> int:
         return self._out
@@ -144,6 +201,13 @@ class RowParallelLinear:
     def forward(self, x: torch.Tensor, sliced: bool = False) -> torch.Tensor:
         """``x`` is the full ``[m, in]`` activation (this rank's columns are cut out) or, with ``sliced``, already
         this rank's ``[m, hi - lo]`` block.  Returns the f32 ``[m, out]`` on every rank."""
+        if self.comm is not None:  # the shard's forward and the sum behind the C ABI (qb200_qlinear_forward_tp)
+            xs = x if sliced else x[:, self.lo: self.hi].contiguous()
+            y = torch.empty((x.shape[0], self._out), dtype=torch.float32, device=x.device)
+            self.comm.forward(self.local, L.TP_ROW, self._out, 1, xs, y)
+            if self.bias is not None:
+                y = y + self.bias.to(y.device).reshape(1, self._out)
+            return y
         if self.local is not None:
             xs = x if sliced else x[:, self.lo: self.hi].contiguous()
             y = self.local.forward(xs, out_dtype=torch.float32)

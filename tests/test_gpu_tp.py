@@ -28,6 +28,7 @@ def _worker(rank, world, port, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         ok = True
+        comm = tp.TpComm()   # the library's own NCCL communicator behind the C ABI
         for N, K, dt, gran in [(4096, 1024, qb.QuantDtype.Int4, qb.Group(1, 128)), (200, 256, qb.QuantDtype.Int8, qb.Block(32, 32))]:
             gen = torch.Generator(device=dev).manual_seed(5)
             w = torch.randn(N, K, device=dev, generator=gen) * 0.02
@@ -35,12 +36,18 @@ def _worker(rank, world, port, ret):
             qm = qb.QuantizedMatrix.quantize(w, dt, gran)
             full = qb.QuantizedLinear.new(qm, b, qb.OUT_IN)
             tpl = tp.TensorParallelLinear.new(qm, b)
+            tplc = tp.TensorParallelLinear.new(qm, b, comm=comm)   # the same through qb200_qlinear_forward_tp
             for M in (1, 16, 128):
                 x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
                 want = full.forward(x, out_dtype=torch.float32)
                 got = tpl.forward(x, out_dtype=torch.float32)
                 ok = ok and got.shape == want.shape and bool(((got - want).abs() <= 1e-4 * (1 + want.abs())).all())
+                gotc = tplc.forward(x, out_dtype=torch.float32)
+                ok = ok and torch.equal(gotc, got)   # the same shard kernels; the collective only moves bytes
+                gotb = tplc.forward(x, out_dtype=torch.bfloat16)
+                ok = ok and bool(((gotb.float() - want).abs() <= 1e-2 * (1 + want.abs())).all())
             rpl = tp.RowParallelLinear.new(qm, b)  # input features sharded, partial outputs summed
+            rplc = tp.RowParallelLinear.new(qm, b, comm=comm)
             for M in (1, 16, 128):
                 x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
                 want = full.forward(x, out_dtype=torch.float32)
@@ -48,6 +55,9 @@ def _worker(rank, world, port, ret):
                 sliced = rpl.forward(x[:, rpl.lo: rpl.hi].contiguous(), sliced=True)
                 ok = ok and got.shape == want.shape and bool(((got - want).abs() <= 1e-4 * (1 + want.abs())).all())
                 ok = ok and bool(torch.equal(got, sliced))
+                gotc = rplc.forward(x)
+                ok = ok and bool(((gotc - want).abs() <= 1e-4 * (1 + want.abs())).all())
+        comm.close()
         ret[rank] = ok
     finally:
         dist.destroy_process_group()

@@ -27,6 +27,34 @@ def test_shard_range_covers_rows_once():
         tp.shard_range(10, 2, 2)
 
 
+def test_shard_cols_keeps_tiles_and_packed_words_whole():
+    from quanta_b200 import _lib
+    import ctypes
+    lib = _lib.load()
+    for cols, gc, bits, world in [(11008, 128, 4, 8), (4096, 32, 8, 4), (100, 4, 4, 3), (64, 3, 4, 2), (64, 3, 8, 2)]:
+        seen, mult = [], gc if bits == 8 or gc % 8 == 0 else np.lcm(gc, 8)
+        for r in range(world):
+            lo, hi = _lib.u64(), _lib.u64()
+            assert lib.qb200_shard_cols(cols, gc, bits, world, r, ctypes.byref(lo), ctypes.byref(hi)) == 0
+            assert lo.value % mult == 0 or lo.value == cols
+            seen += list(range(lo.value, hi.value))
+        assert seen == list(range(cols))
+    lo, hi = _lib.u64(), _lib.u64()
+    assert lib.qb200_shard_cols(64, 0, 4, 2, 0, ctypes.byref(lo), ctypes.byref(hi)) == _lib.ERR_INVALID_PARAM
+    assert lib.qb200_shard_rows(64, 1, 2, 2, ctypes.byref(lo), ctypes.byref(hi)) == _lib.ERR_INVALID_PARAM
+    assert "outside a world" in _lib.last_error()
+
+
+def test_tp_create_validates_before_touching_a_device():
+    from quanta_b200 import _lib
+    import ctypes
+    lib = _lib.load()
+    h = _lib.vp()
+    assert lib.qb200_tp_create(3, 2, None, ctypes.byref(h)) == _lib.ERR_INVALID_PARAM and not h.value
+    assert lib.qb200_tp_create(0, 2, None, ctypes.byref(h)) == _lib.ERR_INVALID_PARAM and "unique id" in _lib.last_error()
+    assert lib.qb200_qlinear_forward_tp(None, None, 0, 8, 1, None, 0, 1, None, 0, None) == _lib.ERR_INVALID_PARAM
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
