@@ -379,29 +379,36 @@ class PeerArena:
 class PeerGather:
     """The fused all-gather of a group of column-sharded decode layers.
 
-    Every rank owns TWO gather buffers ``[world, count, m, n_local]`` in a PeerArena and alternates between them
-    call by call: a rank that has left the barrier of call s may start call s + 1 and store into its peers'
-    buffers while a slower peer still reads the outputs of call s, so call s + 1 must not touch the buffer of
-    call s; by the time call s + 2 reuses it, the barrier of call s + 1 has shown that every rank is done
-    reading.  ``forward_many`` returns the buffer of this call (valid until the call after the next one).
-    Shapes the kernel does not take raise QuantError(NOT_SUPPORTED); callers fall back to
-    ``TensorParallelLinear``."""
+    Every rank owns TWO receive buffers ``[world, count, m, n_local]`` in a PeerArena and alternates between them
+    call by call: a rank that has finished call s may start call s + 1 and store into its peers' buffers while a
+    slower peer still reads the outputs of call s, so call s + 1 must not touch the buffer of call s; by the time
+    call s + 2 reuses it, call s + 1 has shown that every rank is done reading.  Two mechanisms:
+
+    * ``pushed=False``: the kernel stores plain outputs and runs the arrival barrier in the same launch (or as a
+      one-warp kernel after it, ``fused_barrier=False``); ``forward_many`` returns the receive buffer itself.
+    * ``pushed=True``: the kernel pushes self-validating elements and ends without fence or wait; a second small
+      kernel polls them and writes the dense gathered outputs into a local buffer, which ``forward_many`` returns.
+
+    Shapes the kernel does not take raise QuantError(NOT_SUPPORTED); callers fall back to ``TensorParallelLinear``."""
 
     def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None,
-                 fused_barrier: bool = True):
-        self.fused_barrier = fused_barrier
-        if dtype not in (torch.float32, torch.bfloat16):
-            raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16")
+                 fused_barrier: bool = True, pushed: bool = False):
+        self.fused_barrier, self.pushed = fused_barrier, pushed
+        if dtype not in (torch.float32, torch.bfloat16) or (pushed and dtype != torch.float32):
+            raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16 (pushed: f32)")
         self.count, self.m, self.n_local, self.dtype = count, m, n_local, dtype
-        self.item = 4 if dtype == torch.float32 else 2
+        self.item = 8 if pushed else 4 if dtype == torch.float32 else 2
         world = dist.get_world_size(group)
         self.slot_bytes = count * m * n_local * self.item
         self.arena = PeerArena({"g0": world * self.slot_bytes, "g1": world * self.slot_bytes}, group)
         self.world, self.rank, self.device = self.arena.world, self.arena.rank, self.arena.device
+        self.dense = torch.empty((self.world, count, m, n_local), dtype=torch.float32, device=self.device) if pushed else None
         self.calls = 0
 
     def view(self, parity: Optional[int] = None) -> torch.Tensor:
-        """The gather buffer ``[world, count, m, n_local]`` the last call filled (aliases the allocation)."""
+        """The gathered outputs ``[world, count, m, n_local]`` of the last call (aliases the buffer)."""
+        if self.pushed:
+            return self.dense
         parity = (self.calls - 1) & 1 if parity is None else parity
         return self.arena.tensor("g%d" % parity, (self.world, self.count, self.m, self.n_local), self.dtype)
 
@@ -411,10 +418,15 @@ class PeerGather:
         if len(layers) != self.count or len(xs) != self.count:
             raise QuantError(L.ERR_INVALID_PARAM, f"PeerGather: built for {self.count} layers")
         parity = self.calls & 1 if parity is None else parity
+        name = "g%d" % parity
         per_layer = self.m * self.n_local * self.item
-        own0 = self.arena.address("g%d" % parity, self.rank * self.slot_bytes)
-        self.arena.push(layers, xs, [own0 + i * per_layer for i in range(self.count)], self.m, self.dtype, self.fused_barrier)
+        own = [self.arena.address(name, self.rank * self.slot_bytes + i * per_layer) for i in range(self.count)]
         self.calls += 1
+        if self.pushed:
+            elems = self.count * self.m * self.n_local
+            self.arena.push_pushed(layers, xs, own, self.m)
+            return self.arena.gather_pushed(name, self.world, elems, 1, self.world * elems, self.dense.view(1, -1)).view_as(self.dense)
+        self.arena.push(layers, xs, own, self.m, self.dtype, self.fused_barrier)
         return self.view(parity)
 
     def check(self) -> None:

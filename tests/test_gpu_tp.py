@@ -105,15 +105,16 @@ def _gather_worker(rank, world, port, ret):
                 want = torch.empty(world, count, M, n_local, device=dev)
                 dist.all_gather_into_tensor(want, own)  # the collective the fused path replaces
                 wants.append(want)
-            for fused_barrier in (True, False):  # the barrier inside the launch, or as its own kernel
-                pg = tp.PeerGather(count, M, n_local, torch.float32, fused_barrier=fused_barrier)
+            # the barrier inside the launch, the barrier as its own kernel, or pushed elements and a polling consumer
+            for fused_barrier, pushed in ((True, False), (False, False), (True, True)):
+                pg = tp.PeerGather(count, M, n_local, torch.float32, fused_barrier=fused_barrier, pushed=pushed)
                 # every step's gathered buffer is read while the next step may already be storing into the peers:
                 # the two receive buffers used in turn keep a step's outputs intact until they have been compared
                 gots = []
                 for x in xs:  # the barrier counts steps: repeated use must keep working
                     gots.append(pg.forward_many(layers, [x] * count).clone())
                 pg.check()
-                ok = ok and layers[0].last_kernel() == "gemv_mma_grouped_gather"
+                ok = ok and layers[0].last_kernel() == ("gemv_mma_grouped_push" if pushed else "gemv_mma_grouped_gather")
                 ok = ok and all(torch.equal(g, w) for g, w in zip(gots, wants))
                 pg.close()
         ret[rank] = ok
