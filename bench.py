@@ -40,7 +40,7 @@ NOMINAL_HBM_GBS = 8000.0  # the figure the workload's target is quoted against
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch divided by the layers it processed, from the
 # ncu capture summarised in profiles/gemv_i4_grouped_decode.md (an 8-layer launch; traffic grows in proportion to the
 # layers).  It describes the kernel as captured then; a changed kernel needs a new capture.
-TRAFFIC_PER_LAYER = {1: 72.20e6 / 8}
+TRAFFIC_PER_LAYER = {1: 72.13e6 / 8, 16: 73.43e6 / 8}
 TRAFFIC_SOURCE = "ncu capture of an 8-layer launch (profiles/gemv_i4_grouped_decode.md), scaled by the layers per launch"
 
 

@@ -233,6 +233,20 @@ int main() {
                     for (uint32_t p = 0; p < k4; p++) acc += (float)a4[r * k4 + p] * (float)b4[p * n4 + j];
                     EXPECT(got4[r * n4 + j] == (1.0f * 0.2f * 0.05f) * acc);
                 }
+            {
+                // the reference's own literal cases (crates/sci/quanta-blas/src/reference.rs:1119-1148)
+                auto c8 = DeviceArray<float>::from_slice({0.0f, 0.0f, 0.0f, 0.0f}, {2, 2});
+                gemm_quant(GemmQuantType::Q8Symmetric, 2, 2, 2, 1.0f, 0.5f, 0.25f, DeviceArray<int32_t>::from_slice({2, 4, 6, 8}, {2, 2}),
+                           DeviceArray<int32_t>::from_slice({1, 0, 0, 1}, {2, 2}), 0.0f, c8);
+                gemm_quant_check();
+                EXPECT((c8.to_vec() == std::vector<float>{0.25f, 0.5f, 0.75f, 1.0f}));
+                auto c4b = DeviceArray<float>::from_slice({0.0f, 0.0f, 0.0f, 0.0f}, {2, 2});
+                auto wa = pack({1, 2, 3, -1}), wb = pack({1, 0, 0, 1});
+                gemm_quant4(GemmQuantType::Q4Symmetric, 2, 2, 2, 1.0f, 1.0f, 2.0f, DeviceArray<uint32_t>::from_slice(wa, {wa.size()}),
+                            DeviceArray<uint32_t>::from_slice(wb, {wb.size()}), 0.0f, c4b);
+                gemm_quant_check();
+                EXPECT((c4b.to_vec() == std::vector<float>{2.0f, 4.0f, 6.0f, -2.0f}));
+            }
             bool threw = false;  // gemm_quant.rs:215-238: Q4 through the Q8 entry must error
             try {
                 gemm_quant(GemmQuantType::Q4Symmetric, m, n, k, 1.0f, 0.1f, 0.1f, DeviceArray<int32_t>::from_slice(a, {m, k}),
