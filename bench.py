@@ -496,14 +496,14 @@ def run_ours(args):
     grouped = args.launch == "grouped"
     # N > 1, grouped: the kernel stores the step's outputs into every rank's buffer itself (peer memory) and the
     # arrival barrier runs in the same launch; --gather nccl keeps the library all-gather for comparison
-    fused = world > 1 and grouped and args.gather in ("fused", "pushed") and m <= 16
+    fused = world > 1 and grouped and args.gather in ("fused", "pushed", "pushed+gather") and m <= 16
     pg = None
     if fused:
         # every rank must take the same path: the ranks agree on whether all of them could map the peers' buffers
         from quanta_b200 import tp as _tp
         ok = torch.ones(1, device=dev)
         try:
-            pg = _tp.PeerGather(LAYERS, m, N_OUT, torch.float32, pushed=args.gather == "pushed")
+            pg = _tp.PeerGather(LAYERS, m, N_OUT, torch.float32, mode={"fused": "barrier", "pushed": "pushed", "pushed+gather": "pushed+gather"}[args.gather])
         except Exception as e:  # no peer access between these devices, or IPC refused: the library collective serves
             print(f"bench.py: rank {rank}: fused all-gather unavailable ({type(e).__name__}: {str(e)[:100]}); using NCCL", file=sys.stderr)
             ok.zero_()
@@ -599,7 +599,7 @@ def run_ours(args):
     ms = float(times.median().item())
     timed_region_s = float(times.sum().item()) * 1e-3
     # fused exchange: the arrival barrier runs inside the GEMV launch; pushed exchange: the gathering kernel is a second launch
-    launches = ((1 if grouped else LAYERS) + (1 if fused and args.gather == "pushed" else 0)) * steps * n_blocks
+    launches = ((1 if grouped else LAYERS) + (1 if fused and args.gather == "pushed+gather" else 0)) * steps * n_blocks
     total_bytes = layer_bytes(m) * LAYERS * steps * world
     value = total_bytes / (ms * 1e-3) / 1e9
 
@@ -646,7 +646,7 @@ def run_ours(args):
             xd.copy_(xh, non_blocking=True)
             if fused:
                 got = pg.forward_many(layers, [xd] * LAYERS)
-                yh.view(world, LAYERS, m, N_OUT).copy_(got, non_blocking=True)
+                yh.view(world, LAYERS, m, N_OUT).copy_(got, non_blocking=True)  # (pushed: a strided read of the values)
             else:
                 st = lib.qb200_qlinear_forward_many(hs, LAYERS, xdp, _lib.BF16, m, yp, _lib.F32, cur)
                 if st:
@@ -711,7 +711,9 @@ def run_ours(args):
                                       (", eager" if args.no_graph else ", cuda graph replay of two steps"),
                             "exchange": None if world == 1 else (
                                 ("pushed to every rank's buffer by the kernel as {value, exchange number} elements (peer memory), two receive buffers "
-                                 "used in turn; a second kernel polls them into the dense gathered outputs" if args.gather == "pushed" else
+                                 "used in turn; every CTA polls its twins' rows before the launch ends" if args.gather == "pushed" else
+                                 "pushed to every rank's buffer by the kernel as {value, exchange number} elements (peer memory), two receive buffers "
+                                 "used in turn; a second kernel polls them into the dense gathered outputs" if args.gather == "pushed+gather" else
                                  "stored to every rank's buffer by the kernel (peer memory), two receive buffers used in turn, arrival barrier in the same launch") if fused
                                 else "one NCCL all-gather of the step's outputs" if grouped else "NCCL all-gather per layer")},
             "clocks": clocks.summary(),
@@ -769,10 +771,11 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "per-layer"],
                     help="grouped: the step's layers go through qb200_qlinear_forward_many (one persistent launch); "
                          "per-layer: one qb200_qlinear_forward launch per layer")
-    ap.add_argument("--gather", default="fused", choices=["fused", "pushed", "nccl"],
-                    help="N > 1, grouped launch: pushed = the kernel pushes self-validating elements to every rank and a small kernel "
-                         "polls them into the dense gathered outputs; fused = plain peer stores + arrival barrier in the launch; "
-                         "nccl = all-gather after the kernel")
+    ap.add_argument("--gather", default="pushed", choices=["pushed", "pushed+gather", "fused", "nccl"],
+                    help="N > 1, grouped launch: pushed = the kernel pushes {value, exchange number} elements to every rank and its "
+                         "CTAs poll their twins' rows before the launch ends; pushed+gather = push only, a second kernel polls the "
+                         "elements into dense outputs; fused = plain peer stores + arrival barrier in the launch; nccl = all-gather "
+                         "after the kernel")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
     ap.add_argument("--only", default=None, choices=["prefill", "quantize", "decode_step", "blas_quant"], help="run only a side workload and print its numbers")

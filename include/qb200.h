@@ -274,10 +274,16 @@ QB200_API qb200_status qb200_peer_set_spin_limit(uint32_t polls);
  * buffer) has been consumed in between: a rank cannot finish that one before every rank has read the first.
  * Waits are bounded by qb200_peer_set_spin_limit; a consumer that gives up writes QB200_ERR_TIMEOUT to status_dev
  * (an int32 in device memory, zero-initialised) and uses zeros.  Decode shapes only, all layers in ONE launch
- * (else QB200_ERR_NOT_SUPPORTED).  Exchange numbers are 32 bits wide. */
+ * (else QB200_ERR_NOT_SUPPORTED).  Exchange numbers are 32 bits wide.
+ * slot_stride = 0: the launch only pushes (the consumers above wait for the data).  slot_stride > 0 makes the launch a
+ * complete all-gather: every rank runs the SAME layers shapes into slot `rank` of a buffer whose slots lie slot_stride
+ * bytes apart (slot_own[i] inside slot `rank`), and each CTA, after its own rows, polls the same rows of every other
+ * rank's slot in the own arena — its twin on that rank pushes them at about the same time — so when the launch ends all
+ * ranks' elements are in place (a timeout lands in layers[0]'s status word, qb200_qlinear_check). */
 QB200_API qb200_status qb200_qlinear_forward_many_push(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev,
                                                        int32_t x_dtype, uint64_t m, void* const* slot_own, void* const* arena_bases,
-                                                       uint32_t world, uint32_t rank, uint64_t* state_own, void* stream);
+                                                       uint32_t world, uint32_t rank, uint64_t* state_own, uint64_t slot_stride,
+                                                       void* stream);
 QB200_API qb200_status qb200_add_rmsnorm_pushed(float* h, const void* pushed, uint32_t parts, const uint64_t* state_own,
                                                 const float* gamma, uint64_t n, uint64_t c, float eps, uint16_t* out_bf16,
                                                 int32_t* status_dev, void* stream);

@@ -64,7 +64,7 @@ SIGNATURES = {
     "qb200_peer_free": (i32, [vp]),
     "qb200_qlinear_forward_many_gather": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), i32, P(vp), P(vp), u32, u32, vp]),
     "qb200_peer_signal_wait": (i32, [P(vp), u32, u32, vp, vp]),
-    "qb200_qlinear_forward_many_push": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), P(vp), u32, u32, vp, vp]),
+    "qb200_qlinear_forward_many_push": (i32, [P(vp), u32, P(vp), i32, u64, P(vp), P(vp), u32, u32, vp, u64, vp]),
     "qb200_add_rmsnorm_pushed": (i32, [vp, vp, u32, vp, vp, u64, u64, ctypes.c_float, vp, vp, vp]),
     "qb200_gather_pushed": (i32, [vp, u32, u64, u32, u64, vp, vp, u64, vp, vp]),
     "qb200_peer_set_spin_limit": (i32, [u32]),

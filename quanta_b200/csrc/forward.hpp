@@ -37,6 +37,9 @@ struct PeerSpec {
     // flags[p] is rank p's barrier state (16 u64, zero-initialised) as mapped here
     uint64_t* flags[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint32_t rank = 0;
+    // pushed outputs only: when non-zero, rank p's slot of an arena lies (p - rank) * slot_stride bytes from the own
+    // slot and the launch polls its twins' elements in the own arena before it ends (an all-gather complete at launch end)
+    uint64_t slot_stride = 0;
 };
 // Internal output type of the decode GEMV beside QB200_F32 / QB200_BF16: pushed self-validating elements (8 bytes:
 // f32 bits + exchange number) for every rank; flags[rank] is then this rank's own state array and no barrier runs.

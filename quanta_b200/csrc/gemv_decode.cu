@@ -58,6 +58,7 @@ struct GemvBatch {
     uint64_t* peer_flags[8];  // every rank's barrier state as mapped here (null: the caller runs the barrier itself)
     uint32_t rank;
     uint32_t ll_mode;  // outputs are LLPair elements stamped with the exchange number; no barrier in the launch
+    uint64_t ll_slot_stride;  // pushed all-gather: bytes between the ranks' slots of an arena (0: the launch does not wait for the peers)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -256,6 +257,7 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
         }
         b.rank = peers ? peers->rank : 0;
         b.ll_mode = y_dtype == QB_Y_PUSHED ? 1 : 0;
+        b.ll_slot_stride = b.ll_mode && peers ? peers->slot_stride : 0;
         if (b.ll_mode && (!peers || !peers->flags[peers->rank] || n < count)) return QB200_ERR_NOT_SUPPORTED;  // one launch, one exchange number
         b.peer_spin_limit = peer_spin_limit();
         b.count = n;

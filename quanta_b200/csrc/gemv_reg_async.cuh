@@ -91,6 +91,20 @@ __device__ __forceinline__ bool async_wait_bounded(uint32_t bar, uint32_t parity
     return false;
 }
 
+// Barrier 2 over the CTA's `count` live threads (the warps that left early do not take part) with an OR of a predicate.
+__device__ __forceinline__ uint32_t __syncthreads_or_live(bool pred, uint32_t count) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, 2, %2, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred), "r"(count)
+        : "memory");
+    return r;
+}
+
 template <int NT, int RB, int NSERV, typename YT>
 __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(const __grid_constant__ GemvBatch a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -183,6 +197,7 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
             uint64_t done_count;
             asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(done_count) : "l"(a.peer_flags[a.rank] + 8) : "memory");
             ll_flag = (uint32_t)done_count + 1u;
+            if (sw == 0 && lane == 0) *reinterpret_cast<volatile uint32_t*>(smem + 120) = ll_flag;  // for the validation at the end
         }
         // ---- service warps: refill, fold, store ----
         // A unit of the fold is one row of the sub-item and four batch columns (two when only two are kept): sixteen
@@ -455,6 +470,40 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
                 stage_codes = codes0;
                 stage_scales = scales0;
             }
+        }
+    }
+    if constexpr (sizeof(YT) == 8) {
+        // Pushed all-gather with the arrival checked in the launch: every rank runs the same items, so the rows this CTA
+        // has just pushed are the rows its twin on every peer pushes into this rank's arena at about the same time.
+        // All warps poll those elements (in the peers' slots of the own arena, `ll_slot_stride` bytes apart) until they
+        // carry this exchange's number: when the launch ends, every rank's outputs are here — without a fence, a flag
+        // or a second launch; the wait is one NVLink crossing after the twin's store.
+        if (a.ll_slot_stride && __syncthreads_or_live(failed, REG_THREADS + 32 * NSERV) == 0) {
+            const uint32_t flag = *reinterpret_cast<volatile uint32_t*>(smem + 120), nthreads = REG_THREADS + 32 * NSERV;
+            const uint32_t others = a.n_peers - 1;
+            // one flat index space over (item, peer, batch row, row) so that every thread polls at most a few elements
+            constexpr uint32_t ROWS = RB * 16;
+            const uint32_t per_item = ROWS * a.M * others, total = n_my * per_item;
+            for (uint32_t e = tid; e < total && !failed; e += nthreads) {
+                const uint32_t j = e / per_item, rem = e - j * per_item, pi = rem / (ROWS * a.M), rem2 = rem - pi * (ROWS * a.M);
+                const uint32_t b = rem2 / ROWS, r = rem2 - b * ROWS;
+                const RegItem& it = s_desc[j];
+                if (r >= it.nrows) continue;
+                const int64_t shift = ((int64_t)(pi + (pi >= a.rank ? 1u : 0u)) - (int64_t)a.rank) * (int64_t)a.ll_slot_stride;
+                const uint8_t* p = reinterpret_cast<const uint8_t*>(static_cast<LLPair*>(it.y) + (uint64_t)b * it.N + it.row0 + r) + shift;
+                uint32_t v0, v1, spins = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v0), "=r"(v1) : "l"(p) : "memory");
+                    if (v1 == flag) break;
+                    if (++spins >= a.peer_spin_limit || ((spins & 15u) == 0 && *reinterpret_cast<volatile int32_t*>(a.status) != 0)) {
+                        atomicExch(a.status, QB200_ERR_TIMEOUT);
+                        failed = true;
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            failed = false;  // recorded above; the copies of this launch have all landed
         }
     }
     if (failed) {

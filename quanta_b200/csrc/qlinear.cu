@@ -273,7 +273,7 @@ qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* layers, uin
 
 qb200_status qb200_qlinear_forward_many_push(qb200_qlinear* const* layers, uint32_t count, const void* const* x_dev, int32_t x_dtype,
                                              uint64_t m, void* const* slot_own, void* const* arena_bases, uint32_t world, uint32_t rank,
-                                             uint64_t* state_own, void* stream) {
+                                             uint64_t* state_own, uint64_t slot_stride, void* stream) {
     if (count == 0 || m == 0) return QB200_OK;
     if (!layers || !x_dev || !slot_own || !arena_bases || !state_own || world == 0 || world > 8 || rank >= world)
         return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_push: null argument or bad world / rank");
@@ -295,6 +295,8 @@ qb200_status qb200_qlinear_forward_many_push(qb200_qlinear* const* layers, uint3
         peers.delta[p] = static_cast<int64_t>(reinterpret_cast<intptr_t>(arena_bases[p]) - reinterpret_cast<intptr_t>(arena_bases[rank]));
     }
     peers.flags[rank] = state_own;
+    if (slot_stride & 7u) return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward_many_push: slot_stride must be a multiple of 8 bytes");
+    peers.slot_stride = world > 1 ? slot_stride : 0;
     qb200_status s = qb::gemv_i4_forward_many(args.data(), count, qb::QB_Y_PUSHED, layers[0]->status, static_cast<cudaStream_t>(stream), &peers);
     if (s == QB200_ERR_NOT_SUPPORTED)
         return fail(QB200_ERR_NOT_SUPPORTED, "qb200_qlinear_forward_many_push: the layers do not fit ONE launch of the decode kernel");

@@ -329,16 +329,19 @@ class PeerArena:
         """This rank's 16-word state array (word 8: the exchanges it has launched)."""
         return self._own + self.data_bytes
 
-    def push_pushed(self, layers: List[QuantizedLinear], xs: List[torch.Tensor], own_addresses: List[int], m: int) -> None:
+    def push_pushed(self, layers: List[QuantizedLinear], xs: List[torch.Tensor], own_addresses: List[int], m: int,
+                    slot_stride: int = 0) -> None:
         """layers[i](xs[i]) stored as {f32 bits, exchange number} elements at `own_addresses[i]` of this rank's arena and at
-        the same offset of every peer's; the launch neither fences nor waits — the consumers poll the elements."""
+        the same offset of every peer's; the launch neither fences nor waits — the consumers poll the elements.  With
+        `slot_stride` (bytes between the ranks' slots; every rank runs the same shapes) the launch itself polls its twins'
+        rows before it ends: an all-gather that is complete when the launch is."""
         n = len(layers)
         hs = (L.vp * n)(*[ql._h for ql in layers])
         xp = (L.vp * n)(*[x.data_ptr() for x in xs])
         yp = (L.vp * n)(*own_addresses)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _check(L.load().qb200_qlinear_forward_many_push(hs, n, xp, L.BF16, m, yp, self._bases_c, self.world, self.rank,
-                                                        self.state_address(), stream))
+                                                        self.state_address(), slot_stride, stream))
         self._lead = layers[0]
 
     def add_rmsnorm_pushed(self, h: torch.Tensor, name: str, parts: int, gamma: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
@@ -382,35 +385,43 @@ class PeerGather:
     Every rank owns TWO receive buffers ``[world, count, m, n_local]`` in a PeerArena and alternates between them
     call by call: a rank that has finished call s may start call s + 1 and store into its peers' buffers while a
     slower peer still reads the outputs of call s, so call s + 1 must not touch the buffer of call s; by the time
-    call s + 2 reuses it, call s + 1 has shown that every rank is done reading.  Two mechanisms:
+    call s + 2 reuses it, call s + 1 has shown that every rank is done reading.  Three mechanisms (``mode``):
 
-    * ``pushed=False``: the kernel stores plain outputs and runs the arrival barrier in the same launch (or as a
+    * ``"barrier"``: the kernel stores plain outputs and runs the arrival barrier in the same launch (or as a
       one-warp kernel after it, ``fused_barrier=False``); ``forward_many`` returns the receive buffer itself.
-    * ``pushed=True``: the kernel pushes self-validating elements and ends without fence or wait; a second small
-      kernel polls them and writes the dense gathered outputs into a local buffer, which ``forward_many`` returns.
+    * ``"pushed"``: the kernel pushes self-validating elements, and each of its CTAs then polls the same rows of its
+      twins on the other ranks, so the launch ends when every rank's outputs are here — no fence, no flag, one launch.
+      ``forward_many`` returns a strided f32 view of the receive buffer (the values of its 8-byte elements).
+    * ``"pushed+gather"``: the kernel only pushes; a second small kernel polls the elements and writes the dense
+      gathered outputs into a local buffer, which ``forward_many`` returns.
 
     Shapes the kernel does not take raise QuantError(NOT_SUPPORTED); callers fall back to ``TensorParallelLinear``."""
 
     def __init__(self, count: int, m: int, n_local: int, dtype: torch.dtype = torch.float32, group=None,
-                 fused_barrier: bool = True, pushed: bool = False):
-        self.fused_barrier, self.pushed = fused_barrier, pushed
-        if dtype not in (torch.float32, torch.bfloat16) or (pushed and dtype != torch.float32):
+                 fused_barrier: bool = True, mode: str = "barrier"):
+        if mode not in ("barrier", "pushed", "pushed+gather"):
+            raise QuantError(L.ERR_INVALID_PARAM, f"PeerGather: unknown mode {mode!r}")
+        self.fused_barrier, self.mode, self.pushed = fused_barrier, mode, mode != "barrier"
+        if dtype not in (torch.float32, torch.bfloat16) or (self.pushed and dtype != torch.float32):
             raise QuantError(L.ERR_INVALID_PARAM, "PeerGather: outputs are f32 or bf16 (pushed: f32)")
         self.count, self.m, self.n_local, self.dtype = count, m, n_local, dtype
-        self.item = 8 if pushed else 4 if dtype == torch.float32 else 2
+        self.item = 8 if self.pushed else 4 if dtype == torch.float32 else 2
         world = dist.get_world_size(group)
         self.slot_bytes = count * m * n_local * self.item
         self.arena = PeerArena({"g0": world * self.slot_bytes, "g1": world * self.slot_bytes}, group)
         self.world, self.rank, self.device = self.arena.world, self.arena.rank, self.arena.device
-        self.dense = torch.empty((self.world, count, m, n_local), dtype=torch.float32, device=self.device) if pushed else None
+        self.dense = torch.empty((self.world, count, m, n_local), dtype=torch.float32, device=self.device) if mode == "pushed+gather" else None
         self.calls = 0
 
     def view(self, parity: Optional[int] = None) -> torch.Tensor:
         """The gathered outputs ``[world, count, m, n_local]`` of the last call (aliases the buffer)."""
-        if self.pushed:
+        if self.mode == "pushed+gather":
             return self.dense
         parity = (self.calls - 1) & 1 if parity is None else parity
-        return self.arena.tensor("g%d" % parity, (self.world, self.count, self.m, self.n_local), self.dtype)
+        shape = (self.world, self.count, self.m, self.n_local)
+        if self.mode == "pushed":  # every other 32-bit word of the 8-byte elements
+            return self.arena.tensor("g%d" % parity, shape + (2,), torch.float32)[..., 0]
+        return self.arena.tensor("g%d" % parity, shape, self.dtype)
 
     def forward_many(self, layers: List[QuantizedLinear], xs: List[torch.Tensor], parity: Optional[int] = None) -> torch.Tensor:
         """Runs the call into buffer `parity` (default: alternating).  A caller that captures calls into a CUDA graph
@@ -422,7 +433,10 @@ class PeerGather:
         per_layer = self.m * self.n_local * self.item
         own = [self.arena.address(name, self.rank * self.slot_bytes + i * per_layer) for i in range(self.count)]
         self.calls += 1
-        if self.pushed:
+        if self.mode == "pushed":
+            self.arena.push_pushed(layers, xs, own, self.m, self.slot_bytes)
+            return self.view(parity)
+        if self.mode == "pushed+gather":
             elems = self.count * self.m * self.n_local
             self.arena.push_pushed(layers, xs, own, self.m)
             return self.arena.gather_pushed(name, self.world, elems, 1, self.world * elems, self.dense.view(1, -1)).view_as(self.dense)

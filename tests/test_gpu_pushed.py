@@ -34,13 +34,13 @@ class _Rank:
         self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
 
 
-def _push(lib, ranks, r, layers, xs, offsets, m):
+def _push(lib, ranks, r, layers, xs, offsets, m, slot_stride=0):
     n = len(layers)
     hs = (_lib.vp * n)(*[ql._h for ql in layers])
     xp = (_lib.vp * n)(*[x.data_ptr() for x in xs])
     yp = (_lib.vp * n)(*[ranks[r].arena.data_ptr() + o for o in offsets])
     bases = (_lib.vp * len(ranks))(*[k.arena.data_ptr() for k in ranks])
-    st = lib.qb200_qlinear_forward_many_push(hs, n, xp, _lib.BF16, m, yp, bases, len(ranks), r, ranks[r].state.data_ptr(),
+    st = lib.qb200_qlinear_forward_many_push(hs, n, xp, _lib.BF16, m, yp, bases, len(ranks), r, ranks[r].state.data_ptr(), slot_stride,
                                              torch.cuda.current_stream().cuda_stream)
     assert st == 0, _lib.last_error()
 
@@ -129,6 +129,36 @@ def test_consumer_gives_up_on_a_rank_that_never_pushes():
         assert lib.qb200_peer_set_spin_limit(4 << 20) == 0
 
 
+@pytest.mark.parametrize("M", [1, 5, 16])
+def test_all_gather_checked_inside_the_launch(M):
+    """slot_stride > 0: the launch polls its twins' rows before it ends.  On one GPU the twin cannot run at the same
+    time, so rank 1 pushes first (without waiting) and rank 0's launch then finds rank 1's elements in place; a rank 0
+    whose twin never pushed gives up after a few milliseconds and the handle reports it once."""
+    lib = _lib.load()
+    n_local, K, count, world = 200, 512, 2, 2
+    slot = count * M * n_local * 8
+    ranks = [_Rank(world * slot) for _ in range(world)]
+    shards = [_layers(n_local, K, count, 80 + r) for r in range(world)]
+    x = torch.randn(M, K, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2)).to(torch.bfloat16)
+    offs = lambda r: [r * slot + i * M * n_local * 8 for i in range(count)]
+    _push(lib, ranks, 1, shards[1], [x] * count, offs(1), M)                    # the twin's elements, exchange 1
+    _push(lib, ranks, 0, shards[0], [x] * count, offs(0), M, slot_stride=slot)  # pushes and checks
+    torch.cuda.synchronize()
+    assert lib.qb200_qlinear_check(shards[0][0]._h, None) == 0
+    want = torch.stack([torch.stack(qb.QuantizedLinear.forward_many(shards[r], [x] * count, out_dtype=torch.float32)) for r in range(world)])
+    for k in ranks:   # both arenas hold both ranks' outputs; the values are every other 32-bit word
+        got = k.arena.view(torch.float32).view(world, count, M, n_local, 2)[..., 0]
+        assert torch.equal(got, want)
+    assert lib.qb200_peer_set_spin_limit(3000) == 0
+    try:
+        _push(lib, ranks, 0, shards[0], [x] * count, offs(0), M, slot_stride=slot)  # exchange 2: the twin never pushes it
+        torch.cuda.synchronize()
+        assert lib.qb200_qlinear_check(shards[0][0]._h, None) == _lib.ERR_TIMEOUT
+        assert lib.qb200_qlinear_check(shards[0][0]._h, None) == 0
+    finally:
+        assert lib.qb200_peer_set_spin_limit(4 << 20) == 0
+
+
 def test_push_refuses_what_the_decode_kernel_does_not_take():
     lib = _lib.load()
     ranks = [_Rank(1 << 20)]
@@ -137,7 +167,7 @@ def test_push_refuses_what_the_decode_kernel_does_not_take():
     x = torch.randn(2, 256, device=DEV).to(torch.bfloat16)
     hs, xp = (_lib.vp * 1)(q8._h), (_lib.vp * 1)(x.data_ptr())
     yp, bases = (_lib.vp * 1)(ranks[0].arena.data_ptr()), (_lib.vp * 1)(ranks[0].arena.data_ptr())
-    st = lib.qb200_qlinear_forward_many_push(hs, 1, xp, _lib.BF16, 2, yp, bases, 1, 0, ranks[0].state.data_ptr(), None)
+    st = lib.qb200_qlinear_forward_many_push(hs, 1, xp, _lib.BF16, 2, yp, bases, 1, 0, ranks[0].state.data_ptr(), 0, None)
     assert st == _lib.ERR_NOT_SUPPORTED and "decode kernel" in _lib.last_error()
-    st = lib.qb200_qlinear_forward_many_push(hs, 1, xp, _lib.BF16, 2, yp, bases, 1, 3, ranks[0].state.data_ptr(), None)
+    st = lib.qb200_qlinear_forward_many_push(hs, 1, xp, _lib.BF16, 2, yp, bases, 1, 3, ranks[0].state.data_ptr(), 0, None)
     assert st == _lib.ERR_INVALID_PARAM

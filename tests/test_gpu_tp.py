@@ -105,9 +105,11 @@ def _gather_worker(rank, world, port, ret):
                 want = torch.empty(world, count, M, n_local, device=dev)
                 dist.all_gather_into_tensor(want, own)  # the collective the fused path replaces
                 wants.append(want)
-            # the barrier inside the launch, the barrier as its own kernel, or pushed elements and a polling consumer
-            for fused_barrier, pushed in ((True, False), (False, False), (True, True)):
-                pg = tp.PeerGather(count, M, n_local, torch.float32, fused_barrier=fused_barrier, pushed=pushed)
+            # the barrier inside the launch, the barrier as its own kernel, pushed elements validated by the launch itself,
+            # or pushed elements and a polling consumer kernel
+            for fused_barrier, mode in ((True, "barrier"), (False, "barrier"), (True, "pushed"), (True, "pushed+gather")):
+                pushed = mode != "barrier"
+                pg = tp.PeerGather(count, M, n_local, torch.float32, fused_barrier=fused_barrier, mode=mode)
                 # every step's gathered buffer is read while the next step may already be storing into the peers:
                 # the two receive buffers used in turn keep a step's outputs intact until they have been compared
                 gots = []
