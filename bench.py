@@ -430,6 +430,31 @@ def measure_extras(torch, qb, dev, only=None, small=False, world=1):
         del lys
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
+    # the same decode workload over int8 codes with 32 x 32 blocks (the grid of the quantize-on-load workload's int8 half)
+    try:
+        lys = [qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(torch.randn(4096, 4096, device=dev, generator=gen) * 0.02,
+                                                                   qb.QuantDtype.Int8, qb.Block(32, 32)), None, qb.OUT_IN)
+               for _ in range(32)]
+        from quanta_b200 import _lib
+        lib = _lib.load()
+        hs = (_lib.vp * 32)(*[ql._h for ql in lys])
+        for mm in (1, 8):
+            xm = torch.randn(mm, 4096, device=dev, generator=gen).to(torch.bfloat16)
+            ym = torch.empty(32, mm, 4096, device=dev, dtype=torch.float32)
+            xp = (_lib.vp * 32)(*[xm.data_ptr()] * 32)
+            yp = (_lib.vp * 32)(*[ym[i].data_ptr() for i in range(32)])
+
+            def run8():
+                st = lib.qb200_qlinear_forward_many(hs, 32, xp, _lib.BF16, mm, yp, _lib.F32, torch.cuda.current_stream(dev).cuda_stream)
+                if st:
+                    raise RuntimeError(_lib.last_error())
+            ms = timed(run8, 200)
+            by = 32 * (4096 * 4096 + 128 * 128 * 4 + mm * 4096 * 2 + mm * 4096 * 4)
+            out[f"decode_gemv_int8_32x32_M{mm}"] = {"GB/s": by / ms / 1e6, "ms": ms, "roofline_frac": by / ms / 1e6 / hbm,
+                                                    "kernel": lys[0].last_kernel(), "launch": "grouped, 32 matrices per launch (537 MB of codes)"}
+        del lys
+    except Exception as e:
+        out["decode_gemv_int8"] = {"skipped": str(e)[:80]}
     out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, hbm, 32, 1)
     try:  # the reference's quantize / dequantize are single-threaded host loops: the restatement timed the same way
         out["cpu_quantize_baseline"] = cpu_quantize_baseline()

@@ -54,6 +54,12 @@ qb200_status gemv_i4_forward(const FwdArgs& a, int y_dtype, int32_t* status, cud
 qb200_status gemv_i4_forward_many(const FwdArgs* a, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st,
                                   const PeerSpec* peers = nullptr);
 #endif
+// Decode GEMV over int8 codes (gemv_i8.cuh): OUT_IN, bf16 x, m <= 8, in_dim <= 4096, any grid whose tile width is a multiple of 32.
+bool gemv_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim, uint64_t m,
+                      int x_dtype, const void* codes, const void* x);
+#ifdef __CUDACC__
+qb200_status gemv_i8_forward_many(const FwdArgs* a, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st);
+#endif
 // Prefill GEMM on tcgen05 (gemm_prefill.cu): int4, 1x128 grid, OUT_IN, bf16 x; asked after the decode GEMV.
 bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x);

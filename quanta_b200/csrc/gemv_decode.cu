@@ -147,6 +147,7 @@ constexpr uint32_t X_SCALE_HI = 0x51805180u;  // bf16x2 2^36: pairs with the 16x
 
 #include "gemv_reg.cuh"
 #include "gemv_reg_async.cuh"
+#include "gemv_i8.cuh"
 
 namespace qb {
 
@@ -287,6 +288,97 @@ qb200_status gemv_i4_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
         if (r) return r;
     }
     return QB200_OK;
+}
+
+// ---- int8 ----
+
+bool gemv_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim, uint64_t m,
+                      int x_dtype, const void* codes, const void* x) {
+    if (bits != 8 || layout != QB200_OUT_IN || x_dtype != QB200_BF16 || gr == 0 || gc == 0) return false;
+    if (m == 0 || m > 8 || in_dim % 128 != 0 || in_dim > 128 * 2 * REG_WARPS || out_dim > 0x7FFFFFFF) return false;
+    if (gc % 32 != 0) return false;  // a run of 32 columns shares its scale
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    return al(codes) && al(x);
+}
+
+template <int NSERV, typename YT>
+static qb200_status launch_gemv_i8(const GemvBatchI8& b, uint32_t smem, uint32_t ctas, cudaStream_t st) {
+    auto kern = k_gemv_i8_async<NSERV, YT>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    QB_CUDA_TRY(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        QB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev & 63] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(REG_THREADS + 32 * NSERV);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    QB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, b));
+    return QB200_OK;
+}
+
+// Grouped int8 forward over `count` layers that share K and M (any scale grids).  QB200_ERR_NOT_SUPPORTED (no message)
+// when the shape does not fit the kernel.
+qb200_status gemv_i8_forward_many(const FwdArgs* f, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st) {
+    if (count == 0) return QB200_OK;
+    if (count > (uint32_t)I8_MAX_LAYERS) return QB200_ERR_NOT_SUPPORTED;
+    const uint32_t K = (uint32_t)f[0].in_dim, M = (uint32_t)f[0].m;
+    if (K / 128 > 2 * REG_WARPS || M > 8) return QB200_ERR_NOT_SUPPORTED;
+    uint64_t all_tiles = 0, all_rows = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        all_tiles += (f[i].out_dim + 15) / 16;
+        all_rows += f[i].out_dim;
+    }
+    const uint32_t rpi = gemv_rows_per_item(all_rows, all_tiles, 1, all_tiles >= 8 * 148);
+    GemvBatchI8 b = {};
+    uint32_t items = 0, srows_max = 1, tc_max = 1;
+    for (uint32_t i = 0; i < count; i++) {
+        const FwdArgs& a = f[i];
+        GemvLayerI8& ly = b.layer[i];
+        ly.codes = static_cast<const uint8_t*>(a.codes);
+        ly.scales = a.scales;
+        ly.bias = a.bias;
+        ly.x = static_cast<const uint16_t*>(a.x);
+        ly.y = a.y;
+        ly.N = (uint32_t)a.out_dim;
+        ly.rows_per_item = rpi;
+        ly.item0 = items;
+        ly.gr = (uint32_t)(a.gr > 0xFFFFFFFFull ? 0xFFFFFFFFull : a.gr);
+        ly.gc = (uint32_t)(a.gc > 0xFFFFFFFFull ? 0xFFFFFFFFull : a.gc);
+        ly.tc = (uint32_t)a.tc;
+        ly.ldx = a.x_stride ? (uint32_t)a.x_stride : K;
+        items += (ly.N + rpi - 1) / rpi;
+        // scale rows an item of rpi rows can span, and whether every item's scale rows start on a 16-byte boundary
+        const uint32_t span = ly.gr >= rpi ? 2 : (rpi + ly.gr - 1) / ly.gr + 1;
+        srows_max = span > srows_max ? span : srows_max;
+        tc_max = ly.tc > tc_max ? ly.tc : tc_max;
+        if ((reinterpret_cast<uintptr_t>(ly.scales) & 15u) || (ly.tc & 3u)) b.async_scales = 1;
+    }
+    if ((items + 147) / 148 > REG_MAX_ITEMS) return QB200_ERR_NOT_SUPPORTED;
+    b.status = status;
+    b.count = count;
+    b.total_items = items;
+    b.M = M;
+    b.K = K;
+    b.srows_max = srows_max;
+    b.red_cols = M <= 2 ? 2 : (M + 3) & ~3u;
+    b.red_stride = async_red_stride(b.red_cols);
+    const uint32_t ctas = items < 148 ? items : 148, per_cta = (items + ctas - 1) / ctas;
+    uint32_t stages = per_cta < 2 ? 2 : (per_cta > 4 ? 4 : per_cta);
+    while (stages > 2 && i8_smem_layout(K, b.red_stride, srows_max, tc_max, stages).total > 227u * 1024) stages--;
+    b.stages = stages;
+    const uint32_t smem = i8_smem_layout(K, b.red_stride, srows_max, tc_max, stages).total;
+    if (smem > 227u * 1024) return QB200_ERR_NOT_SUPPORTED;
+    if (M > 4) return y_dtype == QB200_F32 ? launch_gemv_i8<2, float>(b, smem, ctas, st) : launch_gemv_i8<2, uint16_t>(b, smem, ctas, st);
+    return y_dtype == QB200_F32 ? launch_gemv_i8<1, float>(b, smem, ctas, st) : launch_gemv_i8<1, uint16_t>(b, smem, ctas, st);
 }
 
 qb200_status gemv_i4_forward(const FwdArgs& f, int y_dtype, int32_t* status, cudaStream_t st) {

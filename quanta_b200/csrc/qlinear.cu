@@ -68,6 +68,27 @@ qb::FwdArgs fast_args(const qb200_qlinear* q, const void* x, void* y, uint64_t m
     return a;
 }
 
+// The forward's arguments over the stored buffers.
+qb::FwdArgs stored_args(const qb200_qlinear* q, const void* x, void* y, uint64_t m) {
+    qb::FwdArgs a;
+    a.codes = q->codes;
+    a.scales = q->scales;
+    a.bias = q->bias;
+    a.x = x;
+    a.y = y;
+    a.m = m;
+    a.in_dim = q->in_dim;
+    a.out_dim = q->out_dim;
+    a.gr = q->gr;
+    a.gc = q->gc;
+    a.tc = q->tc;
+    return a;
+}
+
+bool decode_i8_eligible(const qb200_qlinear* q, uint64_t m, int x_dtype, const void* x) {
+    return qb::gemv_i8_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes, x);
+}
+
 bool decode_eligible(const qb200_qlinear* q, uint64_t m, int x_dtype, const void* x) {
     return q->fast_view() && qb::gemv_i4_eligible(q->bits, q->fast_gr(), q->fast_gc(), QB200_OUT_IN, q->in_dim, q->out_dim, m,
                                                   x_dtype, q->fast_codes(), q->fast_scales(), x);
@@ -160,6 +181,14 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
             return s;
         }
     }
+    if (decode_i8_eligible(ql, m, x_dtype, x_dev)) {
+        const qb::FwdArgs a8 = stored_args(ql, x_dev, y_dev, m);
+        qb200_status s = qb::gemv_i8_forward_many(&a8, 1, y_dtype, ql->status, st);
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            ql->last_kernel = "gemv_mma_i8";
+            return s;
+        }
+    }
     if (ql->n_slices && m <= 16 && x_dtype == QB200_BF16 && (reinterpret_cast<uintptr_t>(x_dev) & 15u) == 0) {
         qb200_status s = qb::forward_sliced(ql, x_dev, m, y_dev, y_dtype, st);
         if (s != QB200_ERR_NOT_SUPPORTED) {
@@ -180,18 +209,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         ql->last_kernel = "gemm_tcgen05";
         return qb::gemm_i4_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
     }
-    qb::FwdArgs a;
-    a.codes = ql->codes;
-    a.scales = ql->scales;
-    a.bias = ql->bias;
-    a.x = x_dev;
-    a.y = y_dev;
-    a.m = m;
-    a.in_dim = ql->in_dim;
-    a.out_dim = ql->out_dim;
-    a.gr = ql->gr;
-    a.gc = ql->gc;
-    a.tc = ql->tc;
+    const qb::FwdArgs a = stored_args(ql, x_dev, y_dev, m);
     if (ql->layout == QB200_OUT_IN) {
         ql->last_kernel = "generic_rows";
         return qb::forward_generic(a, ql->bits, x_dtype, y_dtype, true, nullptr, 1, st);
@@ -226,6 +244,18 @@ qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t c
                                                   static_cast<cudaStream_t>(stream));
         if (s != QB200_ERR_NOT_SUPPORTED) {
             for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_grouped";
+            return s;
+        }
+    }
+    bool grouped8 = count > 1 && count <= 32 && (y_dtype == QB200_F32 || y_dtype == QB200_BF16);
+    for (uint32_t i = 0; i < count && grouped8; i++)
+        grouped8 = layers[i]->in_dim == layers[0]->in_dim && decode_i8_eligible(layers[i], m, x_dtype, x_dev[i]);
+    if (grouped8) {  // int8 layers that share the input width: one persistent launch as well
+        std::vector<qb::FwdArgs> args(count);
+        for (uint32_t i = 0; i < count; i++) args[i] = stored_args(layers[i], x_dev[i], y_dev[i], m);
+        qb200_status s = qb::gemv_i8_forward_many(args.data(), count, y_dtype, layers[0]->status, static_cast<cudaStream_t>(stream));
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_i8_grouped";
             return s;
         }
     }
@@ -349,7 +379,8 @@ qb200_status qb200_qlinear_forward_many_host(qb200_qlinear* const* layers, uint3
     // tcgen05 GEMM's TMA stores and split-K workspace keep the staging path): the same test the dispatcher applies.
     bool direct = true;
     for (uint32_t i = 0; i < count && direct; i++)
-        direct = decode_eligible(layers[i], m, x_dtype, lead->x_stage) || (layers[i]->n_slices && m <= 16 && x_dtype == QB200_BF16);
+        direct = decode_eligible(layers[i], m, x_dtype, lead->x_stage) || decode_i8_eligible(layers[i], m, x_dtype, lead->x_stage) ||
+                 (layers[i]->n_slices && m <= 16 && x_dtype == QB200_BF16);
     // one query per host allocation: outputs inside the range of an allocation already seen reuse its mapping
     const uint8_t *range_lo = nullptr, *range_hi = nullptr, *range_dev = nullptr;
     for (uint32_t i = 0; i < count && direct; i++) {
@@ -433,7 +464,8 @@ qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, i
     QB_CUDA_TRY(cudaMemcpyAsync(ql->x_stage, x_host, xb, cudaMemcpyHostToDevice, ql->host_stream));
     // a decode-shaped call with its output in pinned, device-mapped memory: the kernel stores there itself
     void* y_direct = nullptr;
-    if (decode_eligible(ql, m, x_dtype, ql->x_stage) || (ql->n_slices && m <= 16 && x_dtype == QB200_BF16)) {
+    if (decode_eligible(ql, m, x_dtype, ql->x_stage) || decode_i8_eligible(ql, m, x_dtype, ql->x_stage) ||
+        (ql->n_slices && m <= 16 && x_dtype == QB200_BF16)) {
         cudaPointerAttributes at;
         void* base = nullptr;
         size_t size = 0;

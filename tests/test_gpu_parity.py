@@ -683,3 +683,84 @@ def test_host_entry_with_unaligned_scales_keeps_the_staging_path():
     close(yh.numpy(), want, 1e-3)
     y2 = np.full((M, N), np.nan, np.float32)
     assert (bits(ql.forward_host(xb, y2)) == bits(yh.numpy())).all()
+
+
+# ---- the int8 decode GEMV on the tensor pipe (any grid whose tile width is a multiple of 32) ------------------
+
+I8_GRIDS = [qb.Block(32, 32), qb.Group(1, 128), qb.PerChannel(0), qb.PerTensor(), qb.Group(1, 32), qb.Block(16, 64), qb.Block(5, 96)]
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1000, 1024), (37, 128), (300, 2560), (16, 256)])
+def test_int8_decode_gemv_shapes(N, K):
+    rng = np.random.default_rng(N * 3 + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    from quanta_b200 import _lib
+    for gran in I8_GRIDS[: (7 if N <= 1000 else 3)]:
+        gr, gc = gran.tile(N, K)
+        if gc % 32 or K % gc and gc < K:
+            continue
+        m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int8, gran)
+        wd = o.dequantize_host(oc, os_, N, K, 8, gr, gc)
+        ql = qb.QuantizedLinear.new(m, t(bias), qb.OUT_IN)
+        for M in (1, 2, 5, 8):
+            xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+            xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+            y = ql.forward(xt, out_dtype=torch.float32)
+            assert ql.last_kernel() == "gemv_mma_i8", (gran, M)
+            want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
+            close(y.cpu().numpy(), want, 1e-4)
+            close(ql.forward(xt).to(torch.float32).cpu().numpy(), want, 1e-2)
+        # one-hot activations read single weights back: 1.0 * (s * q) is exact, every other product is zero
+        ks = sorted({0, 1, 2, 3, 31, 32 % K, 127, K // 2 + 5, K - 1})[:8]
+        y = qb.QuantizedLinear.new(m, None, qb.OUT_IN).forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
+        assert (bits(y.cpu().numpy()) == bits(wd[:, ks].T.copy())).all(), gran
+        xt9 = torch.randn(9, K, device=DEV).to(torch.bfloat16)   # wider batches keep the generic kernel
+        ql.forward(xt9, out_dtype=torch.float32)
+        assert ql.last_kernel() == "generic_rows"
+        assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
+def test_int8_forward_many_and_graph_replay():
+    rng = np.random.default_rng(6)
+    qls = []
+    for N, gran in [(1024, qb.Block(32, 32)), (3000, qb.Group(1, 128)), (37, qb.PerChannel(0)), (2048, qb.Block(32, 32))]:
+        w = torch.from_numpy((rng.standard_normal((N, 1024)) * 0.02).astype(np.float32)).to(DEV)
+        b = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).to(DEV)
+        qls.append(qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, gran), b, qb.OUT_IN))
+    for M in (1, 4, 8):
+        x = torch.randn(M, 1024, device=DEV).to(torch.bfloat16)
+        x2 = torch.randn(M, 1024, device=DEV).to(torch.bfloat16)
+        xs = [x, x, x2, x]
+        want = [ql.forward(xi, out_dtype=torch.float32) for ql, xi in zip(qls, xs)]
+        got = qb.QuantizedLinear.forward_many(qls, xs, out_dtype=torch.float32)
+        assert qls[0].last_kernel() == "gemv_mma_i8_grouped"
+        for a, b_ in zip(got, want):
+            assert torch.equal(a, b_)   # the same arithmetic per output whatever the launch's item partition
+    x = torch.randn(4, 1024, device=DEV).to(torch.bfloat16)
+    eager = [ql.forward(x, out_dtype=torch.float32) for ql in qls]
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            cap = [ql.forward(x, out_dtype=torch.float32) for ql in qls]
+        for _ in range(3):
+            g.replay()
+    torch.cuda.synchronize()
+    for a, b_ in zip(eager, cap):
+        assert torch.equal(a, b_)
+
+
+def test_config1_int8_block32_bf16_activations_take_the_fast_kernel():
+    g = np.random.default_rng(0)
+    w = (g.standard_normal((1024, 1024), dtype=np.float32) * np.float32(0.02))
+    x = g.standard_normal((8, 1024), dtype=np.float32)
+    m, oc, os_ = quantize_both(w, 1024, 1024, qb.QuantDtype.Int8, qb.Block(32, 32))
+    wd = o.dequantize_host(oc, os_, 1024, 1024, 8, 32, 32)
+    ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    xb = o.f32_to_bf16(x)
+    y = ql.forward(torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV), out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemv_mma_i8"
+    close(y.cpu().numpy(), o.linear_forward(o.bf16_to_f32(xb), wd, None, o.OUT_IN, threads=8), 1e-4)
+    assert (bits(ql.forward_host(xb)) == bits(y.cpu().numpy())).all()
