@@ -697,8 +697,9 @@ def test_int8_decode_gemv_shapes(N, K):
     bias = rng.standard_normal(N).astype(np.float32)
     from quanta_b200 import _lib
     for gran in I8_GRIDS[: (7 if N <= 1000 else 3)]:
-        gr, gc = gran.tile(N, K)
-        if gc % 32 or K % gc and gc < K:
+        try:
+            gr, gc = gran.tile(N, K)
+        except qb.QuantError:   # a block larger than this matrix is not a valid spelling
             continue
         m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int8, gran)
         wd = o.dequantize_host(oc, os_, N, K, 8, gr, gc)
