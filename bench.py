@@ -288,6 +288,38 @@ def measure_decode_step(torch, dev, gen, hbm, n_layers, world=1):
         torch.cuda.empty_cache()
 
 
+def measure_int8_decode(torch, qb, dev, gen, timed, hbm, n_layers):
+    """The decode workload over int8 codes with 32 x 32 blocks (the grid of the quantize-on-load workload's int8 half):
+    `n_layers` distinct [4096, 4096] matrices per grouped launch, X bf16 [M, 4096], M = 1 and 8."""
+    out = {}
+    try:
+        lys = [qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(torch.randn(4096, 4096, device=dev, generator=gen) * 0.02,
+                                                                   qb.QuantDtype.Int8, qb.Block(32, 32)), None, qb.OUT_IN)
+               for _ in range(n_layers)]
+        from quanta_b200 import _lib
+        lib = _lib.load()
+        hs = (_lib.vp * n_layers)(*[ql._h for ql in lys])
+        for mm in (1, 8):
+            xm = torch.randn(mm, 4096, device=dev, generator=gen).to(torch.bfloat16)
+            ym = torch.empty(n_layers, mm, 4096, device=dev, dtype=torch.float32)
+            xp = (_lib.vp * n_layers)(*[xm.data_ptr()] * n_layers)
+            yp = (_lib.vp * n_layers)(*[ym[i].data_ptr() for i in range(n_layers)])
+
+            def run8():
+                st = lib.qb200_qlinear_forward_many(hs, n_layers, xp, _lib.BF16, mm, yp, _lib.F32, torch.cuda.current_stream(dev).cuda_stream)
+                if st:
+                    raise RuntimeError(_lib.last_error())
+            ms = timed(run8, 200 if n_layers == 32 else 5)
+            by = n_layers * (4096 * 4096 + 128 * 128 * 4 + mm * 4096 * 2 + mm * 4096 * 4)
+            out[f"decode_gemv_int8_32x32_M{mm}"] = {"GB/s": by / ms / 1e6, "ms": ms, "roofline_frac": by / ms / 1e6 / hbm,
+                                                    "kernel": lys[0].last_kernel(), "bytes": by,
+                                                    "launch": f"grouped, {n_layers} matrices per launch"}
+        del lys
+    except Exception as e:
+        out["decode_gemv_int8"] = {"skipped": str(e)[:80]}
+    return out
+
+
 def measure_extras(torch, qb, dev, only=None, small=False, world=1):
     """Secondary numbers of the same path on one GPU (device-resident inputs, CUDA events):
     the int4 prefill GEMM configuration and quantize-on-load, each with its roofline fraction."""
@@ -339,6 +371,8 @@ def measure_extras(torch, qb, dev, only=None, small=False, world=1):
 
     out = {}
     gen = torch.Generator(device=dev).manual_seed(2)
+    if only == "int8_decode":
+        return measure_int8_decode(torch, qb, dev, gen, timed, hbm, 8 if small else 32)
     if only == "decode_step" or world > 1:  # the one side workload that shards: the whole-model decode step
         return {"decode_step_llama7b_shape": measure_decode_step(torch, dev, gen, hbm, 2 if small else 32, world)}
     M, N, K = (512, 2048, 4096) if small else (2048, 11008, 4096)
@@ -430,31 +464,7 @@ def measure_extras(torch, qb, dev, only=None, small=False, world=1):
         del lys
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
-    # the same decode workload over int8 codes with 32 x 32 blocks (the grid of the quantize-on-load workload's int8 half)
-    try:
-        lys = [qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(torch.randn(4096, 4096, device=dev, generator=gen) * 0.02,
-                                                                   qb.QuantDtype.Int8, qb.Block(32, 32)), None, qb.OUT_IN)
-               for _ in range(32)]
-        from quanta_b200 import _lib
-        lib = _lib.load()
-        hs = (_lib.vp * 32)(*[ql._h for ql in lys])
-        for mm in (1, 8):
-            xm = torch.randn(mm, 4096, device=dev, generator=gen).to(torch.bfloat16)
-            ym = torch.empty(32, mm, 4096, device=dev, dtype=torch.float32)
-            xp = (_lib.vp * 32)(*[xm.data_ptr()] * 32)
-            yp = (_lib.vp * 32)(*[ym[i].data_ptr() for i in range(32)])
-
-            def run8():
-                st = lib.qb200_qlinear_forward_many(hs, 32, xp, _lib.BF16, mm, yp, _lib.F32, torch.cuda.current_stream(dev).cuda_stream)
-                if st:
-                    raise RuntimeError(_lib.last_error())
-            ms = timed(run8, 200)
-            by = 32 * (4096 * 4096 + 128 * 128 * 4 + mm * 4096 * 2 + mm * 4096 * 4)
-            out[f"decode_gemv_int8_32x32_M{mm}"] = {"GB/s": by / ms / 1e6, "ms": ms, "roofline_frac": by / ms / 1e6 / hbm,
-                                                    "kernel": lys[0].last_kernel(), "launch": "grouped, 32 matrices per launch (537 MB of codes)"}
-        del lys
-    except Exception as e:
-        out["decode_gemv_int8"] = {"skipped": str(e)[:80]}
+    out.update(measure_int8_decode(torch, qb, dev, gen, timed, hbm, 32))
     out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, hbm, 32, 1)
     try:  # the reference's quantize / dequantize are single-threaded host loops: the restatement timed the same way
         out["cpu_quantize_baseline"] = cpu_quantize_baseline()
@@ -803,7 +813,7 @@ def main():
                          "after the kernel")
     ap.add_argument("--layers", type=int, default=LAYERS, help="distinct weight matrices per step")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / quantize side measurements")
-    ap.add_argument("--only", default=None, choices=["prefill", "quantize", "decode_step", "blas_quant"], help="run only a side workload and print its numbers")
+    ap.add_argument("--only", default=None, choices=["prefill", "quantize", "decode_step", "blas_quant", "int8_decode"], help="run only a side workload and print its numbers")
     ap.add_argument("--small", action="store_true", help="with --only: a reduced shape, for profiler captures")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()

@@ -199,20 +199,8 @@ __global__ void __launch_bounds__(REG_THREADS + 32 * NSERV, 1) k_gemv_i8_async(c
                 const uint32_t r = u % 16, b0 = (u / 16) * 4;
                 if (r >= it.nrows || b0 >= a.M) continue;
                 const float* red = s_red + slot * L.slot_floats + r * RS + b0;
-                float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if (vec == 4) {
-#pragma unroll 4
-                    for (int w = 0; w < REG_WARPS; w++) {
-                        const float4 p = *reinterpret_cast<const float4*>(red + w * 16 * RS);
-                        v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
-                    }
-                } else {
-#pragma unroll 4
-                    for (int w = 0; w < REG_WARPS; w++) {
-                        const float2 p = *reinterpret_cast<const float2*>(red + w * 16 * RS);
-                        v[0] += p.x; v[1] += p.y;
-                    }
-                }
+                float v[4];
+                fold_sixteen(red, 16 * RS, vec, v);
                 const uint32_t n = it.row0 + r;
                 const float bias = it.bias ? it.bias[n] : 0.0f;
 #pragma unroll

@@ -91,6 +91,25 @@ __device__ __forceinline__ bool async_wait_bounded(uint32_t bar, uint32_t parity
     return false;
 }
 
+// One unit of the service warps' fold: a row of a sub-item and up to four kept batch columns, summed over the sixteen
+// compute warps' partial sums in warp order (`red` points at warp 0's row, the warps lie `warp_stride` floats apart).
+__device__ __forceinline__ void fold_sixteen(const float* red, uint32_t warp_stride, uint32_t vec, float (&v)[4]) {
+    v[0] = v[1] = v[2] = v[3] = 0.0f;
+    if (vec == 4) {
+#pragma unroll 4
+        for (int w = 0; w < REG_WARPS; w++) {
+            const float4 p = *reinterpret_cast<const float4*>(red + w * warp_stride);
+            v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+        }
+    } else {
+#pragma unroll 4
+        for (int w = 0; w < REG_WARPS; w++) {
+            const float2 p = *reinterpret_cast<const float2*>(red + w * warp_stride);
+            v[0] += p.x; v[1] += p.y;
+        }
+    }
+}
+
 // Barrier 2 over the CTA's `count` live threads (the warps that left early do not take part) with an OR of a predicate.
 __device__ __forceinline__ uint32_t __syncthreads_or_live(bool pred, uint32_t count) {
     uint32_t r;
@@ -217,20 +236,8 @@ __global__ void __launch_bounds__(async_threads(NT, NSERV), 1) k_gemv_i4_async(c
                     const uint32_t r = s * SUB_ROWS + row_l;  // row inside the item
                     if (r >= it.nrows || b0 >= a.M) continue;
                     const float* red = s_red + slot * L.slot_floats + row_l * RS + b0;
-                    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (vec == 4) {
-#pragma unroll 4
-                        for (int w = 0; w < REG_WARPS; w++) {
-                            const float4 p = *reinterpret_cast<const float4*>(red + w * SUB_ROWS * RS);
-                            v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
-                        }
-                    } else {
-#pragma unroll 4
-                        for (int w = 0; w < REG_WARPS; w++) {
-                            const float2 p = *reinterpret_cast<const float2*>(red + w * SUB_ROWS * RS);
-                            v[0] += p.x; v[1] += p.y;
-                        }
-                    }
+                    float v[4];
+                    fold_sixteen(red, SUB_ROWS * RS, vec, v);
                     const uint32_t n = it.row0 + r;
                     const float bias = it.bias ? it.bias[n] : 0.0f;
 #pragma unroll

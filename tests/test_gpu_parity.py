@@ -415,7 +415,9 @@ def test_forward_many_matches_per_layer_forward():
     q8 = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w8, qb.QuantDtype.Int8, qb.PerChannel(0)), None, qb.OUT_IN)
     x = torch.randn(2, 1024, device=DEV).to(torch.bfloat16)
     got = qb.QuantizedLinear.forward_many([qls[0], q8], [x, x], out_dtype=torch.float32)
-    assert torch.equal(got[1], q8.forward(x, out_dtype=torch.float32)) and q8.last_kernel() == "generic_rows"
+    # (an int4 and an int8 layer cannot share a launch; each takes its own decode kernel through the per-layer loop)
+    assert torch.equal(got[1], q8.forward(x, out_dtype=torch.float32)) and q8.last_kernel() == "gemv_mma_i8"
+    assert torch.equal(got[0], qls[0].forward(x, out_dtype=torch.float32)) and qls[0].last_kernel() == "gemv_mma"
 
 
 # ---- the prefill GEMM on tcgen05 -------------------------------------------------
