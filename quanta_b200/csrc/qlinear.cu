@@ -188,6 +188,19 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
             ql->last_kernel = "gemv_mma_i8";
             return s;
         }
+    } else if (m > 8 && m <= 16 && decode_i8_eligible(ql, 8, x_dtype, x_dev)) {
+        // the int8 decode kernel keeps eight batch rows in registers: a batch of 9..16 runs as two launches (the second
+        // pass over a layer that fits L2 re-reads it from there)
+        const uint64_t ysz = y_dtype == QB200_F32 ? 4 : 2;
+        qb::FwdArgs lo = stored_args(ql, x_dev, y_dev, 8);
+        qb::FwdArgs hi = stored_args(ql, static_cast<const uint16_t*>(x_dev) + 8 * ql->in_dim,
+                                     static_cast<uint8_t*>(y_dev) + 8 * ql->out_dim * ysz, m - 8);
+        qb200_status s = qb::gemv_i8_forward_many(&lo, 1, y_dtype, ql->status, st);
+        if (s == QB200_OK) s = qb::gemv_i8_forward_many(&hi, 1, y_dtype, ql->status, st);
+        if (s != QB200_ERR_NOT_SUPPORTED) {
+            ql->last_kernel = "gemv_mma_i8_x2";
+            return s;
+        }
     }
     if (ql->n_slices && m <= 16 && x_dtype == QB200_BF16 && (reinterpret_cast<uintptr_t>(x_dev) & 15u) == 0) {
         qb200_status s = qb::forward_sliced(ql, x_dev, m, y_dev, y_dtype, st);

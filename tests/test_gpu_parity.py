@@ -718,8 +718,13 @@ def test_int8_decode_gemv_shapes(N, K):
         ks = sorted({0, 1, 2, 3, 31, 32 % K, 127, K // 2 + 5, K - 1})[:8]
         y = qb.QuantizedLinear.new(m, None, qb.OUT_IN).forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
         assert (bits(y.cpu().numpy()) == bits(wd[:, ks].T.copy())).all(), gran
-        xt9 = torch.randn(9, K, device=DEV).to(torch.bfloat16)   # wider batches keep the generic kernel
-        ql.forward(xt9, out_dtype=torch.float32)
+        for M in (9, 16):   # batches of 9..16: two launches of eight rows at most
+            xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+            xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+            y = ql.forward(xt, out_dtype=torch.float32)
+            assert ql.last_kernel() == "gemv_mma_i8_x2"
+            close(y.cpu().numpy(), o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8), 1e-4)
+        ql.forward(torch.randn(17, K, device=DEV).to(torch.bfloat16), out_dtype=torch.float32)   # prefill batches keep the generic kernel
         assert ql.last_kernel() == "generic_rows"
         assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
 
