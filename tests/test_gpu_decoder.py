@@ -79,6 +79,24 @@ def test_rope_append_and_sdpa_decode():
             close(got[bi, h], want, 1e-2)
 
 
+@pytest.mark.parametrize("b,heads,kv_len", [(16, 16, 200), (8, 40, 3), (2, 4, 1025), (1, 1, 130), (37, 7, 65)])
+def test_sdpa_decode_shapes(b, heads, kv_len):
+    """Many and few (row, head) pairs, one key split and many, a ragged last split: against the restatement."""
+    rng = np.random.default_rng(b * 100 + heads)
+    hd, ctx_max = 128, kv_len + 3
+    q = bf(rng.standard_normal((b, heads, hd)))
+    kc = bf(rng.standard_normal((b, ctx_max, heads, hd)))
+    vc = bf(rng.standard_normal((b, ctx_max, heads, hd)))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.empty(b, heads * hd, dtype=torch.bfloat16, device=DEV)
+    dec.sdpa_decode(t(q.reshape(b, heads * hd)), t(kc), t(vc), kv_len, scale, dec.sdpa_scratch(b, heads, kv_len, DEV), out)
+    got = out.to(torch.float32).cpu().numpy().reshape(b, heads, hd)
+    for bi in range(0, b, max(1, b // 3)):
+        for h in range(0, heads, max(1, heads // 3)):
+            close(got[bi, h], do.sdpa_one_query(q[bi, h], kc[bi, :, h], vc[bi, :, h], scale, kv_len), 1e-2)
+
+
 def test_swiglu_sliced_and_sum():
     rng = np.random.default_rng(3)
     n, h, widths = 5, 1408, [512, 512, 384]
