@@ -146,7 +146,12 @@ typedef struct qb200_qlinear qb200_qlinear;
  * (crates/ml/quanta-nn/src/quant.rs:853-862).  Borrows the caller's device
  * buffers (codes, scales, optional f32 bias of out_dim elements): they must
  * outlive the handle.  bias_len is the bias element count (checked against
- * out_dim like check_bias, quant.rs:838-848); pass bias_dev = NULL for none. */
+ * out_dim like check_bias, quant.rs:838-848); pass bias_dev = NULL for none.
+ * Where the stored layout does not feed the fast int4 kernels as it is, the handle builds an execution copy here (and
+ * synchronises the device once): an `[in, out]` weight with Group{axis: 0, size: 128} is transposed to `[out, in]` with
+ * a 1x128 grid, and a weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode kernel.
+ * Each copy costs 0.5 byte per weight plus its scales (and 16 rows of f32 partial outputs per slice); the caller's
+ * buffers stay the record. */
 QB200_API qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev, uint64_t rows,
                                   uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc,
                                   int32_t layout, const float* bias_dev, uint64_t bias_len,
@@ -160,7 +165,14 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
 /* Layer::apply without the tape — y = x @ deq(w) (+ b), fused: the f32 weight
  * is never materialised (crates/ml/quanta-nn/src/quant.rs:892-918, the
  * "INTEGRATOR SEAM").  x is `[m, in_dim]` of x_dtype, y is `[m, out_dim]` of
- * y_dtype, both device, row-major.  f32 accumulation. */
+ * y_dtype, both device, row-major.  f32 accumulation.
+ * Fast paths (bf16 x): int4 with a 1x128 grid — `[out, in]`, or `[in, out]` with Group{axis: 0, size: 128} through the
+ * transposed execution copy made at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
+ * the tcgen05 GEMM (m > 16); int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on its own
+ * decode GEMV (m <= 16).  Everything else (f32 x, other grids and layouts) runs on the generic kernels.
+ * A call whose scratch is not allocated yet (the GEMM's split-K workspace, the generic column kernel's partial sums)
+ * allocates it; on a stream that is recording a CUDA graph that is refused with QB200_ERR_INVALID_PARAM — run the shape
+ * once before capturing.  The decode GEMVs need finite activations with |x| < 2^87 (see qb200_qlinear_check). */
 QB200_API qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t x_dtype,
                                    uint64_t m, void* y_dev, int32_t y_dtype, void* stream);
 
@@ -345,8 +357,10 @@ QB200_API qb200_status qb200_qlinear_check(qb200_qlinear* ql, void* stream);
 QB200_API qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void* x_host, int32_t x_dtype,
                                         uint64_t m, void* y_host, int32_t y_dtype);
 
-/* Name of the kernel family the last forward on this handle dispatched to
- * ("gemv_mma", "gemv_mma_grouped", "gemm_tcgen05", "generic_rows", "generic_cols"). */
+/* Name of the kernel family the last forward on this handle dispatched to: "gemv_mma" (int4 decode), "gemv_mma_grouped",
+ * "gemv_mma_sliced" (inputs wider than 4096), "gemv_mma_grouped_gather" / "gemv_mma_grouped_push" (fused exchanges),
+ * "gemv_mma_i8", "gemv_mma_i8_grouped", "gemv_mma_i8_x2" (int8 decode), "gemm_tcgen05" (int4 prefill), "generic_rows",
+ * "generic_cols". */
 QB200_API const char* qb200_qlinear_last_kernel(const qb200_qlinear* ql);
 
 /* ---- quantized-safetensors (host bytes in, host bytes out) -------------- */

@@ -40,8 +40,16 @@ bool host_range(const void* p, void** base, size_t* size) {
     return true;
 }
 
-qb200_status grow(void** p, uint64_t* have, uint64_t need) {
+// Grow-only scratch.  Growing frees and allocates, which synchronises the device and is illegal while `capturing` (the
+// stream the forward was given) records a CUDA graph: that case is refused with a message instead of breaking the capture.
+qb200_status grow(void** p, uint64_t* have, uint64_t need, cudaStream_t capturing = nullptr) {
     if (*have >= need) return QB200_OK;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(capturing, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+        return fail(QB200_ERR_INVALID_PARAM, "QuantizedLinear: this forward needs " + std::to_string(need) +
+                                                 " bytes of scratch that are not allocated yet, and its stream is recording a CUDA graph; "
+                                                 "run the same shape once before the capture");
+    cudaGetLastError();
     if (*p) QB_CUDA_TRY(cudaFree(*p));
     *p = nullptr;
     *have = 0;
@@ -215,7 +223,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         const uint64_t need = qb::gemm_i4_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->bias);
         if (need) {
             void* p = ql->scratch;
-            qb200_status s = grow(&p, &ql->scratch_bytes, need);
+            qb200_status s = grow(&p, &ql->scratch_bytes, need, st);
             ql->scratch = static_cast<float*>(p);
             if (s) return s;
         }
@@ -230,7 +238,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     const uint32_t slices = qb::forward_cols_slices(ql->in_dim, ql->out_dim, m);
     if (slices > 1) {
         void* p = ql->scratch;
-        qb200_status s = grow(&p, &ql->scratch_bytes, (uint64_t)slices * m * ql->out_dim * sizeof(float));
+        qb200_status s = grow(&p, &ql->scratch_bytes, (uint64_t)slices * m * ql->out_dim * sizeof(float), st);
         ql->scratch = static_cast<float*>(p);
         if (s) return s;
     }

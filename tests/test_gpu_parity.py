@@ -772,3 +772,32 @@ def test_config1_int8_block32_bf16_activations_take_the_fast_kernel():
     assert ql.last_kernel() == "gemv_mma_i8"
     close(y.cpu().numpy(), o.linear_forward(o.bf16_to_f32(xb), wd, None, o.OUT_IN, threads=8), 1e-4)
     assert (bits(ql.forward_host(xb)) == bits(y.cpu().numpy())).all()
+
+
+def test_scratch_growth_is_refused_while_a_graph_is_recorded():
+    """A forward whose scratch is not allocated yet would free / allocate; on a stream that records a CUDA graph that
+    is refused with a message, the recording survives, and after one call outside a capture the same shape records."""
+    w = torch.randn(4096, 256, device=DEV) * 0.02   # [in, out] int8: the column kernel splits K and needs partial sums
+    ql = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, qb.PerChannel(1)), None, qb.IN_OUT)
+    x = torch.randn(3, 4096, device=DEV)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    caught = None
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            try:
+                ql.forward(x)
+            except qb.QuantError as e:
+                caught = e
+    assert caught is not None and caught.kind == "InvalidParam" and "before the capture" in str(caught)
+    want = ql.forward(x)     # allocates
+    assert ql.last_kernel() == "generic_cols"
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=s):
+            got = ql.forward(x)
+        g2.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
