@@ -52,7 +52,7 @@ def workload_name(m: int) -> str:
 def bench_config(m: int, world: int) -> dict:
     """`config` of the JSON line, the same in both arms."""
     return {"workload": workload_name(m), "layers_per_step": LAYERS,
-            "l2": f"inputs larger than L2 ({LAYERS} distinct weight matrices, {LAYERS * 8.9:.0f} MB)",
+            "l2": f"inputs larger than L2 ({LAYERS} distinct weight matrices, {layer_bytes(m) * LAYERS / 1e6:.0f} MB)",
             "parallelism": "single GPU" if world == 1 else f"column-sharded x{world} (weak scaling: one [{N_OUT},{K_IN}] shard per GPU), outputs all-gathered"}
 
 

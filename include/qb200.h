@@ -264,7 +264,8 @@ QB200_API qb200_status qb200_qlinear_forward_many_gather(qb200_qlinear* const* l
 QB200_API qb200_status qb200_peer_signal_wait(uint64_t* const* flag_arrays, uint32_t world, uint32_t rank,
                                     int32_t* status_dev, void* stream);
 /* Polls (about a quarter of a microsecond each) that an arrival barrier spends on one peer's flag before it
- * gives up with QB200_ERR_TIMEOUT; process-wide, read at launch time, default 4 Mi (about a second). */
+ * gives up with QB200_ERR_TIMEOUT; process-wide, read at launch time.  Default: the environment variable
+ * QB200_SPIN_LIMIT (polls) when set at first use, else 4 Mi (about a second). */
 QB200_API qb200_status qb200_peer_set_spin_limit(uint32_t polls);
 
 /* ---- pushed exchanges for tensor-parallel decode (no counterpart in the reference) ----

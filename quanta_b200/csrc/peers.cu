@@ -8,6 +8,7 @@
 // IPC handles, which the caller exchanges through its own process group.
 #include <atomic>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -16,8 +17,17 @@
 namespace qb {
 
 // polls of ~0.25 us each before a barrier gives up with QB200_ERR_TIMEOUT: about a second by default
-static std::atomic<uint32_t> g_peer_spin_limit{4u << 20};
-uint32_t peer_spin_limit() { return g_peer_spin_limit.load(std::memory_order_relaxed); }
+static std::atomic<uint32_t> g_peer_spin_limit{0};
+uint32_t peer_spin_limit() {
+    uint32_t v = g_peer_spin_limit.load(std::memory_order_relaxed);
+    if (v == 0) {  // first use: the environment may set the limit (QB200_SPIN_LIMIT, in polls), else 4 Mi
+        const char* e = getenv("QB200_SPIN_LIMIT");
+        const unsigned long long n = e ? strtoull(e, nullptr, 10) : 0;
+        v = n >= 1 && n <= 0xFFFFFFFFull ? (uint32_t)n : 4u << 20;
+        g_peer_spin_limit.store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
 
 struct PeerFlags {
     uint64_t* flags[8];  // flags[p]: rank p's array {arrival of rank 0, ..., arrival of rank 7, own step counter}
