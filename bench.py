@@ -777,6 +777,11 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
                                     "sample": f"2 of {LAYERS} layers x {reps} passes ({dt:.1f} s), dequantize + sequential-k "
                                               f"f32 GEMM, {threads} OpenMP threads"}
+            # the same on ONE thread: the reference's host loops are single-threaded, the threaded figure above is the
+            # parallel restatement (its CPU lane spreads workgroups over the host's threads)
+            v1, dt1 = cpu_forward_gbs(m, 1, 1, 3)
+            line["cpu_baseline"]["single_thread"] = {"value": v1, "unit": "GB/s", "cores": 1,
+                                                     "sample": f"1 of {LAYERS} layers x 3 passes ({dt1:.1f} s)"}
         print(json.dumps(line), flush=True)
     if world > 1:
         if gather_checked is False:
