@@ -409,8 +409,17 @@ def measure_extras(torch, qb, dev, only=None, small=False, world=1):
         qm = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int4, qb.Group(1, 128))
         ql = qb.QuantizedLinear.new(qm, None, qb.OUT_IN)
         ms = timed(lambda: ql.forward(x), 3 if small else 10)
-        return {"prefill_int4_gemm": {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
-                                      "peak_TFLOP/s": tf, "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}}
+        res = {"prefill_int4_gemm": {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
+                                     "peak_TFLOP/s": tf, "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}}
+        del ql, qm
+        # the same shape over int8 codes: the 32 x 32 grid closes an accumulator every 32 k, a 1 x 128 grid every 128
+        for name, gran in [("prefill_int8_32x32_gemm", qb.Block(32, 32)), ("prefill_int8_1x128_gemm", qb.Group(1, 128))]:
+            ql = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, gran), None, qb.OUT_IN)
+            ms = timed(lambda: ql.forward(x), 3 if small else 10)
+            res[name] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
+                         "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}
+            del ql
+        return res
     for name, dt, gran, wbytes in [("quantize_int4_1x128", qb.QuantDtype.Int4, qb.Group(1, 128), N * K // 2 + N * (K // 128) * 4),
                                    ("quantize_int8_32x32", qb.QuantDtype.Int8, qb.Block(32, 32), N * K + (N // 32) * (K // 32) * 4)]:
         ms, how = timed_replay(lambda: qb.QuantizedMatrix.quantize(w, dt, gran), 10)

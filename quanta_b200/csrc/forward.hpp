@@ -67,6 +67,14 @@ uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, co
 #ifdef __CUDACC__
 qb200_status gemm_i4_forward(const FwdArgs& a, int y_dtype, void* scratch, int32_t* status, cudaStream_t st);
 #endif
+// The same kernel over int8 codes: OUT_IN, bf16 x, in_dim a multiple of 64, any grid whose tile width is a multiple of
+// 16 that divides in_dim (or covers the row); asked after the int8 decode GEMV.
+bool gemm_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
+                      uint64_t m, int x_dtype, const void* codes, const void* x);
+uint64_t gemm_i8_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, uint64_t gc, const void* bias);
+#ifdef __CUDACC__
+qb200_status gemm_i8_forward(const FwdArgs& a, int y_dtype, void* scratch, int32_t* status, cudaStream_t st);
+#endif
 // K slices the column kernel splits into (1 = no scratch needed).
 uint32_t forward_cols_slices(uint64_t in_dim, uint64_t out_dim, uint64_t m);
 

@@ -186,6 +186,8 @@ struct PrefillArgs {
     uint32_t M, N, K;
     uint32_t ksplit;     // K ranges per output tile (1: the kernel writes Y itself)
     uint32_t tma_store;  // 1 when Y's base and row pitch are multiples of 16 bytes
+    // int8 codes only: the scale grid [ceil(N / gr), tc] and the scale group's length in 16-k MMA steps
+    uint32_t gr, tc, g16;
 };
 
 // One packed word -> eight bf16 values q / 64 in natural k order (four registers).
@@ -216,16 +218,40 @@ __device__ __forceinline__ void pf_unpack_row(uint8_t* dst, uint32_t row_off, co
     }
 }
 
-template <typename YT, bool SPLIT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
-    k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
-                 const __grid_constant__ CUtensorMap ymap, PrefillArgs a) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
+// int8 codes: the 64 bytes of one row and k-step (four 16-byte loads) -> the row's 128-byte line of a swizzled stage.
+// A byte b = q ^ 0x80 = q + 128 in the low byte of a bf16 is worth b * 2^-133 (exponent field 0 or 1), and
+// b * 2^-133 * 2^127 - 2 = q / 64 exactly: one LOP3, two PRMT and two packed FMAs per four codes.
+__device__ __forceinline__ void pf_widen_row(uint8_t* dst, uint32_t row_off, const uint4 (&q)[4]) {
+    const uint32_t up = 0x7F007F00u, off = 0xC000C000u;  // bf16x2: 2^127, -2
+#pragma unroll
+    for (uint32_t c = 0; c < 8; c++) {  // chunk c: codes 8c .. 8c + 7
+        const uint4& v = q[c >> 1];
+        const uint32_t w0 = ((c & 1) ? v.z : v.x) ^ 0x80808080u, w1 = ((c & 1) ? v.w : v.y) ^ 0x80808080u;
+        uint32_t o[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; j++) {
+            uint32_t u;
+            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(u) : "r"(j < 2 ? w0 : w1), "r"(0u), "r"((j & 1) ? 0x4342u : 0x4140u));
+            asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[j]) : "r"(u), "r"(up), "r"(off));
+        }
+        *reinterpret_cast<uint4*>(dst + (row_off ^ (c << 4))) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// The kernel's body for packed int4 codes with a 1x128 grid (BITS = 4) and for int8 codes with any grid whose tile
+// width is a multiple of 16 (BITS = 8).  With int8 a packed-code slot (128 rows x 64 B) is one k-step instead of one
+// k-group, and a scale group is `g16` MMA steps of 16 k: the issuer closes an accumulator every g16 steps.
+template <typename YT, bool SPLIT, uint32_t BITS>
+__device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorMap& xmap, const CUtensorMap& qmap,
+                                              const CUtensorMap& ymap, const PrefillArgs& a) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // a work unit is one output tile over one of `ksplit` equal K ranges (whole scale groups); with ksplit > 1 the
     // units' f32 partial tiles go to a workspace [ksplit, M, N] that a second kernel folds
     const uint32_t ksplit = SPLIT ? a.ksplit : 1u;  // the unsplit instantiation folds every K-range term away
-    const uint32_t row_groups = a.K >> 7, groups = row_groups / ksplit, num_k = 2 * groups;
+    // per unit: num_k k-steps of 64 and `groups` scale groups; a row of the scale grid holds row_groups scales
+    const uint32_t row_groups = BITS == 4 ? a.K >> 7 : a.tc;
+    const uint32_t num_k = BITS == 4 ? 2 * ((a.K >> 7) / ksplit) : (a.K >> 6) / ksplit;
+    const uint32_t groups = BITS == 4 ? num_k >> 1 : num_k * 4 / a.g16;
     uint8_t* sA = smem;                  // [S][128 weight rows][128 B], unpacked bf16
     uint8_t* sX = sA + PF_S * PF_STAGE;  // [S][128 activation rows][128 B]
     uint8_t* sQ = sX + PF_S * PF_STAGE;  // [SQ][128 weight rows][64 B], packed codes
@@ -299,7 +325,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             // from divergent code pays for moving each operand to the uniform registers); one elected
             // lane issues.  The next k-step's barrier is polled before this step's MMAs are issued, so the
             // poll's latency is hidden behind them.
-            if (rank == 0) {
+            if constexpr (BITS == 8) { if (rank == 0) {
+                // scale groups of g16 MMA steps, whatever their position in the k-steps: the accumulator changes
+                // where a group ends, and a k-step's stage is released after its fourth MMA
+                const uint32_t elected = pf_elect();
+                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
+                uint32_t st = 0, par = 0, gcount = 0, in_group = 0, ready = 0;
+                for (uint32_t it = 0; it < total && !failed; it++) {
+                    if (!ready && !pf_wait(&full[st], par)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
+                    ready = it + 1 < total ? pf_test(&full[st1], par1) : 0;
+                    const uint64_t da = pf_desc(pf_smem(sA + st * PF_STAGE)), db = pf_desc(pf_smem(sX + st * PF_STAGE));
+#pragma unroll
+                    for (uint32_t kk = 0; kk < PF_BK / 16; kk++) {
+                        const uint32_t buf = gcount & 1;
+                        if (in_group == 0 && gcount >= 2) {
+                            if (!pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        if (elected) pf_mma_pair(tmem_base + buf * PF_TM, da + 2 * kk, db + 2 * kk, idesc, in_group ? 1u : 0u);
+                        if (++in_group == a.g16) {
+                            if (elected) pf_commit_pair(&dfull[buf]);
+                            in_group = 0;
+                            gcount++;
+                        }
+                    }
+                    if (failed) break;
+                    if (elected) pf_commit_pair(&empty[st]);
+                    st = st1;
+                    par = par1;
+                }
+            } } else if (rank == 0) {
                 const uint32_t elected = pf_elect();
                 // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 256 over the pair
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
@@ -344,13 +401,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             // ---- TMA producer of packed-code tiles, one per k-group; runs ahead of the activation ring ----
             if (lane == 0) {
                 uint32_t sq = 0, pq = 0, qit = 0;
+                // a slot is 64 bytes of each row: one k-group of packed int4 (x in u32 words), one k-step of int8 (x in bytes)
+                const uint32_t slots = BITS == 4 ? groups : num_k, x_step = BITS == 4 ? 16u : 64u;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
-                    const uint32_t tile = t / ksplit, g_first = (t % ksplit) * groups;
+                    const uint32_t tile = t / ksplit, g_first = (t % ksplit) * slots;
                     const int32_t q_row = (int32_t)((tile / m_tiles) * PF_TN + rank * 128);
-                    for (uint32_t g = 0; g < groups; g++, qit++) {
+                    for (uint32_t g = 0; g < slots; g++, qit++) {
                         if (qit >= PF_SQ && !pf_wait(&empty_q[sq], pq ^ 1)) { failed = true; break; }
                         pf_mbar_expect_tx(&full_q[sq], PF_Q_BYTES);
-                        pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)((g_first + g) * 16), q_row, &full_q[sq]);  // x in u32 words
+                        pf_tma_load_2d(sQ + sq * PF_Q_BYTES, &qmap, (int32_t)((g_first + g) * x_step), q_row, &full_q[sq]);
                         if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
                     }
                 }
@@ -365,6 +424,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
         const uint32_t q_row = r * 64, q_sw = ((r >> 1) & 3) << 4;
         const uint32_t remote_full = pf_map_to_cta(pf_smem(&full[0]), 0);
         uint32_t st = 0, par = 0, sq = 0, pq = 0;
+        if constexpr (BITS == 8) {
+            // one k-step (one slot of 64 codes per row) per iteration
+            for (uint32_t it = 0; it < total; it++) {
+                if (!pf_wait(&full_q[sq], pq)) { failed = true; break; }
+                const uint8_t* qs = sQ + sq * PF_Q_BYTES + q_row;
+                uint4 q[4];
+#pragma unroll
+                for (uint32_t c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4*>(qs + ((c << 4) ^ q_sw));
+                if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
+                pf_widen_row(sA + st * PF_STAGE, row_off, q);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    pf_mbar_arrive_cluster(remote_full + st * 8);
+                    pf_mbar_arrive(&empty_q[sq]);
+                }
+                if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
+                if (++st == PF_S) { st = 0; par ^= 1; }
+            }
+        } else
         // one k-group (two k-steps, one packed-code slot) per iteration: one fence and one round of
         // barrier latencies for 16 independent words per thread
         for (uint32_t it = 0; it < total; it += 2) {
@@ -405,7 +484,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
             const uint32_t n_cta = (tile / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
             const uint32_t m0 = (tile % m_tiles) * PF_TM + half * 128;
             const bool n_ok = n < a.N;
-            const float* sp = a.scales + (uint64_t)(n_ok ? n : 0) * row_groups + ks * groups;
+            const float* sp = a.scales + (uint64_t)(BITS == 4 ? (n_ok ? n : 0) : (n_ok ? n : 0) / a.gr) * row_groups + ks * groups;
             float total[128];
 #pragma unroll
             for (uint32_t i = 0; i < 128; i++) total[i] = 0.0f;
@@ -499,6 +578,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
 }
 
+template <typename YT, bool SPLIT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
+    k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
+                 const __grid_constant__ CUtensorMap ymap, const PrefillArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    gemm_codes_tc<YT, SPLIT, 4>(smem_raw, xmap, qmap, ymap, a);
+}
+
+template <typename YT, bool SPLIT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
+    k_gemm_w8_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
+                 const __grid_constant__ CUtensorMap ymap, const PrefillArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    gemm_codes_tc<YT, SPLIT, 8>(smem_raw, xmap, qmap, ymap, a);
+}
+
 // Folds the K ranges' partial tiles: y[m, n] = sum_s ws[s, m, n] (+ bias[n]), four outputs per thread.
 template <typename YT>
 __global__ void __launch_bounds__(256) k_gemm_i4_fold(const float* __restrict__ ws, uint32_t ksplit, uint64_t mn, uint32_t N,
@@ -547,6 +642,34 @@ bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
     return al(codes) && al(x);
 }
 
+// int8 codes: a scale group's length in MMA steps of 16 k (a tile wider than the row is the whole row).
+static uint32_t gemm_i8_g16(uint64_t gc, uint64_t in_dim) { return (uint32_t)((gc >= in_dim ? in_dim : gc) / 16); }
+
+// The same for int8 codes: equal runs of whole k-steps (at least four each) that are also whole scale groups.
+static uint32_t gemm_i8_ksplit(uint64_t m, uint64_t out_dim, uint64_t in_dim, uint64_t gc, const void* bias) {
+    const uint64_t tiles = ((out_dim + PF_TN - 1) / PF_TN) * ((m + PF_TM - 1) / PF_TM), pairs = 74;
+    const uint32_t steps = (uint32_t)(in_dim / PF_BK), g16 = gemm_i8_g16(gc, in_dim);
+    if (tiles * 2 > pairs || out_dim % 4 != 0 || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u))) return 1;
+    uint32_t best = 1;
+    for (uint32_t s = 2; s <= pairs / tiles && s <= steps / 4; s++)
+        if (steps % s == 0 && (steps / s * 4) % g16 == 0) best = s;
+    return best;
+}
+
+bool gemm_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
+                      uint64_t m, int x_dtype, const void* codes, const void* x) {
+    if (bits != 8 || layout != QB200_OUT_IN || x_dtype != QB200_BF16 || gr == 0 || gr > 0x7FFFFFFF) return false;
+    if (m == 0 || m > 0x7FFFFFFF || in_dim % PF_BK != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
+    if (gc < in_dim && (gc % 16 != 0 || in_dim % gc != 0)) return false;  // whole groups of whole MMA steps
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    return al(codes) && al(x);
+}
+
+uint64_t gemm_i8_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, uint64_t gc, const void* bias) {
+    const uint32_t ks = gemm_i8_ksplit(m, out_dim, in_dim, gc, bias);
+    return ks > 1 ? (uint64_t)ks * m * out_dim * 4 : 0;
+}
+
 // Scratch: only the workspace of partial tiles when the K loop is split ([ksplit, m, out] f32).
 uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, const void* bias) {
     const uint32_t ks = gemm_i4_ksplit(m, out_dim, in_dim, bias);
@@ -569,9 +692,23 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
+template <typename YT, bool SPLIT>
+static qb200_status launch_prefill(uint32_t bits, uint32_t grid, const CUtensorMap& xmap, const CUtensorMap& qmap,
+                                   const CUtensorMap& ymap, const PrefillArgs& a, int dev, cudaStream_t st) {
+    static bool attr_set[2][64] = {};
+    if (!attr_set[bits == 8][dev & 63]) {
+        if (bits == 8) QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_w8_tc<YT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+        else QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<YT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+        attr_set[bits == 8][dev & 63] = true;
+    }
+    if (bits == 8) k_gemm_w8_tc<YT, SPLIT><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+    else k_gemm_i4_tc<YT, SPLIT><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+    return QB200_OK;
+}
+
+static qb200_status gemm_tc_forward(const FwdArgs& f, uint32_t bits, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
     const uint32_t M = (uint32_t)f.m, N = (uint32_t)f.out_dim, K = (uint32_t)f.in_dim;
-    const uint32_t ksplit = scratch ? gemm_i4_ksplit(M, N, K, f.bias) : 1;
+    const uint32_t ksplit = !scratch ? 1 : bits == 8 ? gemm_i8_ksplit(M, N, K, f.gc, f.bias) : gemm_i4_ksplit(M, N, K, f.bias);
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled is not available from this driver");
     // activations as a [M, K] bf16 tensor: one box = 128 rows x 64 elements (one 128-byte swizzle row each)
@@ -584,12 +721,13 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled failed with code " + std::to_string((int)cr));
-    // packed codes as a [N, K/8] u32 tensor: one box = 128 rows x 16 words (one k-group), 64-byte swizzle
+    // packed codes as a [N, K/8] u32 tensor: one box = 128 rows x 16 words (one k-group), 64-byte swizzle;
+    // int8 codes as a [N, K] byte tensor: one box = 128 rows x 64 bytes (one k-step)
     CUtensorMap qmap;
-    const cuuint64_t qdims[2] = {K / 8, N};
-    const cuuint64_t qstrides[1] = {(cuuint64_t)K / 2};
-    const cuuint32_t qbox[2] = {16, 128};
-    cr = enc(&qmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(f.codes), qdims, qstrides, qbox, estr,
+    const cuuint64_t qdims[2] = {bits == 8 ? K : K / 8, N};
+    const cuuint64_t qstrides[1] = {bits == 8 ? (cuuint64_t)K : (cuuint64_t)K / 2};
+    const cuuint32_t qbox[2] = {bits == 8 ? 64u : 16u, 128};
+    cr = enc(&qmap, bits == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(f.codes), qdims, qstrides, qbox, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled (codes) failed with code " + std::to_string((int)cr));
@@ -622,6 +760,9 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     a.M = M;
     a.N = N;
     a.K = K;
+    a.gr = (uint32_t)f.gr;
+    a.tc = (uint32_t)f.tc;
+    a.g16 = bits == 8 ? gemm_i8_g16(f.gc, K) : 8;
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
     static int sm_count[64] = {};
@@ -629,29 +770,11 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
     const uint32_t tiles = ((N + PF_TN - 1) / PF_TN) * ((M + PF_TM - 1) / PF_TM) * ksplit;
     const uint32_t max_pairs = (uint32_t)sm_count[dev & 63] / 2;
     const uint32_t grid = 2 * (tiles < max_pairs ? tiles : max_pairs);  // one CTA per SM, in clusters of two
-    static bool attr_set[2][64] = {};
-    if (k_dtype == QB200_F32) {
-        if (!attr_set[0][dev & 63]) {
-            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-            attr_set[0][dev & 63] = true;
-        }
-        if (ksplit > 1) {
-            static bool split_attr[64] = {};
-            if (!split_attr[dev & 63]) {
-                QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-                split_attr[dev & 63] = true;
-            }
-            k_gemm_i4_tc<float, true><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
-        } else {
-            k_gemm_i4_tc<float, false><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
-        }
-    } else {
-        if (!attr_set[1][dev & 63]) {
-            QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-            attr_set[1][dev & 63] = true;
-        }
-        k_gemm_i4_tc<uint16_t, false><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
-    }
+    qb200_status ls;
+    if (k_dtype != QB200_F32) ls = launch_prefill<uint16_t, false>(bits, grid, xmap, qmap, ymap, a, dev, st);
+    else if (ksplit > 1) ls = launch_prefill<float, true>(bits, grid, xmap, qmap, ymap, a, dev, st);
+    else ls = launch_prefill<float, false>(bits, grid, xmap, qmap, ymap, a, dev, st);
+    if (ls) return ls;
     QB_CUDA_TRY(cudaGetLastError());
     if (ksplit > 1) {
         if (!tma_store) return fail(QB200_ERR_CUDA, "prefill GEMM: the split-K workspace is not 16-byte aligned");
@@ -665,6 +788,14 @@ qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32
         QB_CUDA_TRY(cudaGetLastError());
     }
     return QB200_OK;
+}
+
+qb200_status gemm_i4_forward(const FwdArgs& f, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
+    return gemm_tc_forward(f, 4, y_dtype, scratch, status, st);
+}
+
+qb200_status gemm_i8_forward(const FwdArgs& f, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
+    return gemm_tc_forward(f, 8, y_dtype, scratch, status, st);
 }
 
 }  // namespace qb

@@ -230,6 +230,17 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         ql->last_kernel = "gemm_tcgen05";
         return qb::gemm_i4_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
     }
+    if (qb::gemm_i8_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev)) {
+        const uint64_t need = qb::gemm_i8_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->gc, ql->bias);
+        if (need) {
+            void* p = ql->scratch;
+            qb200_status s = grow(&p, &ql->scratch_bytes, need, st);
+            ql->scratch = static_cast<float*>(p);
+            if (s) return s;
+        }
+        ql->last_kernel = "gemm_tcgen05_i8";
+        return qb::gemm_i8_forward(stored_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
+    }
     const qb::FwdArgs a = stored_args(ql, x_dev, y_dev, m);
     if (ql->layout == QB200_OUT_IN) {
         ql->last_kernel = "generic_rows";

@@ -724,9 +724,66 @@ def test_int8_decode_gemv_shapes(N, K):
             y = ql.forward(xt, out_dtype=torch.float32)
             assert ql.last_kernel() == "gemv_mma_i8_x2"
             close(y.cpu().numpy(), o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8), 1e-4)
-        ql.forward(torch.randn(17, K, device=DEV).to(torch.bfloat16), out_dtype=torch.float32)   # prefill batches keep the generic kernel
-        assert ql.last_kernel() == "generic_rows"
+        ql.forward(torch.randn(17, K, device=DEV).to(torch.bfloat16), out_dtype=torch.float32)   # a prefill batch
+        tensor_core = K % 64 == 0 and (gc >= K or (gc % 16 == 0 and K % gc == 0))
+        assert ql.last_kernel() == ("gemm_tcgen05_i8" if tensor_core else "generic_rows"), (gran, K)
         assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
+# ---- the int8 prefill GEMM on tcgen05 (tile widths that are whole 16-k MMA steps) ------------------------------
+
+@pytest.mark.parametrize("M,N,K,gran", [
+    (17, 256, 512, qb.Block(32, 32)), (256, 1024, 1024, qb.Block(32, 32)), (300, 1000, 1024, qb.Block(32, 32)),
+    (64, 130, 2048, qb.Group(1, 128)), (128, 384, 1024, qb.PerChannel(0)), (40, 256, 256, qb.PerTensor()),
+    (200, 300, 512, qb.Block(5, 16)), (96, 257, 192, qb.Group(1, 48)), (333, 128, 4096, qb.Block(16, 64)),
+    (513, 515, 576, qb.Group(1, 192)), (32, 64, 64, qb.Block(32, 32))])
+def test_int8_prefill_gemm_against_oracle(M, N, K, gran):
+    """Codes enter the tensor core as the exact bf16 values q / 64, activations as exact bf16, f32 accumulation per scale
+    group, the f32 scale applied to the group sum.  Checker: f64 accumulation of bf16(x) * (s * q) at the 1e-3 bound;
+    one-hot activations read single weights back bit for bit (1.0 * q / 64 * 64 s rounds once, like s * q)."""
+    rng = np.random.default_rng(M * 31 + N * 7 + K)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    gr, gc = gran.tile(N, K)
+    m, oc, os_ = quantize_both(w, N, K, qb.QuantDtype.Int8, gran)
+    wd = o.dequantize_host(oc, os_, N, K, 8, gr, gc)
+    xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.OUT_IN, threads=8)
+    ql = qb.QuantizedLinear.new(m, t(bias), qb.OUT_IN)
+    y = ql.forward(xt, out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemm_tcgen05_i8"
+    close(y.cpu().numpy(), want, 1e-3)
+    yb = ql.forward(xt)
+    assert yb.dtype == torch.bfloat16
+    close(yb.to(torch.float32).cpu().numpy(), want, 1e-2)
+    ks = sorted(set(int(k) for k in rng.integers(0, K, 40)) | {0, 15, 16, 31, 32, 63, K - 1})[:48]
+    plain = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+    y1 = plain.forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
+    assert plain.last_kernel() == "gemm_tcgen05_i8"
+    assert (bits(y1.cpu().numpy()) == bits(wd[:, ks].T.copy())).all()
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+    assert _lib.load().qb200_qlinear_check(plain._h, None) == 0
+
+
+def test_int8_prefill_full_size_properties():
+    """int8 32x32 prefill at X [2048, 4096], W [11008, 4096]: against an f32 matmul over the bit-exact dequantized
+    weight, and linearity in x; the split-K path ([4096, 4096] at 256 rows) against the same."""
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    for N, M in [(11008, 2048), (4096, 256)]:
+        w = torch.randn(N, 4096, device=DEV, generator=gen) * 0.02
+        x = torch.randn(M, 4096, device=DEV, generator=gen).to(torch.bfloat16)
+        m = qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, qb.Block(32, 32))
+        ql = qb.QuantizedLinear.new(m, None, qb.OUT_IN)
+        y = ql.forward(x, out_dtype=torch.float32)
+        assert ql.last_kernel() == "gemm_tcgen05_i8"
+        ref = x.to(torch.float32) @ m.dequantize().t()
+        assert bool(((y - ref).abs() <= 1e-3 * (1 + ref.abs())).all())
+        y2 = ql.forward((x.to(torch.float32) * 2).to(torch.bfloat16), out_dtype=torch.float32)  # exact doubling in bf16
+        assert bool(((y2 - 2 * y).abs() <= 1e-5 * (1 + y.abs())).all())
+        yb = ql.forward(x)
+        assert bool(((yb.to(torch.float32) - ref).abs() <= 1e-2 * (1 + ref.abs())).all())
 
 
 def test_int8_forward_many_and_graph_replay():
