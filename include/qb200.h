@@ -169,7 +169,8 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * Fast paths (bf16 x): int4 with a 1x128 grid — `[out, in]`, or `[in, out]` with Group{axis: 0, size: 128} through the
  * transposed execution copy made at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
  * the tcgen05 GEMM (m > 16); int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on its own
- * decode GEMV (m <= 16).  Everything else (f32 x, other grids and layouts) runs on the generic kernels.
+ * decode GEMV (m <= 16), and with in_dim a multiple of 64 and tiles of whole 16-column steps that divide in_dim (or span
+ * it) on the same tcgen05 GEMM (m > 16).  Everything else (f32 x, other grids and layouts) runs on the generic kernels.
  * A call whose scratch is not allocated yet (the GEMM's split-K workspace, the generic column kernel's partial sums)
  * allocates it; on a stream that is recording a CUDA graph that is refused with QB200_ERR_INVALID_PARAM — run the shape
  * once before capturing.  The decode GEMVs need finite activations with |x| < 2^87 (see qb200_qlinear_check). */
@@ -360,7 +361,7 @@ QB200_API qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void*
 
 /* Name of the kernel family the last forward on this handle dispatched to: "gemv_mma" (int4 decode), "gemv_mma_grouped",
  * "gemv_mma_sliced" (inputs wider than 4096), "gemv_mma_grouped_gather" / "gemv_mma_grouped_push" (fused exchanges),
- * "gemv_mma_i8", "gemv_mma_i8_grouped", "gemv_mma_i8_x2" (int8 decode), "gemm_tcgen05" (int4 prefill), "generic_rows",
+ * "gemv_mma_i8", "gemv_mma_i8_grouped", "gemv_mma_i8_x2" (int8 decode), "gemm_tcgen05" (int4 prefill), "gemm_tcgen05_i8" (int8 prefill), "generic_rows",
  * "generic_cols". */
 QB200_API const char* qb200_qlinear_last_kernel(const qb200_qlinear* ql);
 

@@ -1,5 +1,6 @@
 // Prefill GEMM (every M the decode kernel does not take: M > 16, or a wider input than it keeps on chip): Y[m, n] = sum_k X[m, k] * s[n, k/128] * q[n, k] over resident
-// packed-int4 codes `[N, K/8]` with a 1x128 f32 scale grid, bf16 activations, f32 accumulation.
+// packed-int4 codes `[N, K/8]` with a 1x128 f32 scale grid, bf16 activations, f32 accumulation; and the same over
+// int8 codes `[N, K]` with any scale grid whose tile width is a whole number of 16-k MMA steps (k_gemm_w8_tc).
 // Tensor-core bound: tcgen05.mma over CTA pairs (cta_group::2) with the accumulator in TMEM.
 //
 // Staging (stated, and mirrored by the checker): the codes enter the tensor core as EXACT
@@ -325,23 +326,30 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
             // from divergent code pays for moving each operand to the uniform registers); one elected
             // lane issues.  The next k-step's barrier is polled before this step's MMAs are issued, so the
             // poll's latency is hidden behind them.
-            if constexpr (BITS == 8) { if (rank == 0) {
+            if constexpr (BITS == 8) {
+              if (rank == 0) {
                 // scale groups of g16 MMA steps, whatever their position in the k-steps: the accumulator changes
                 // where a group ends, and a k-step's stage is released after its fourth MMA
                 const uint32_t elected = pf_elect();
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
                 uint32_t st = 0, par = 0, gcount = 0, in_group = 0, ready = 0;
+                uint32_t dready = 0;  // the accumulator of the next group to start was seen read out by an early poll
                 for (uint32_t it = 0; it < total && !failed; it++) {
                     if (!ready && !pf_wait(&full[st], par)) { failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t st1 = st + 1 == PF_S ? 0 : st + 1, par1 = st + 1 == PF_S ? par ^ 1 : par;
                     ready = it + 1 < total ? pf_test(&full[st1], par1) : 0;
+                    // a group that starts in the next k-step (groups longer than a k-step): its accumulator is polled
+                    // now, behind this k-step's MMAs
+                    const uint32_t gn = gcount + (in_group ? 1u : 0u);
+                    if (!dready && gn >= 2) dready = pf_test(&dempty[gn & 1], ((gn >> 1) & 1) ^ 1);
                     const uint64_t da = pf_desc(pf_smem(sA + st * PF_STAGE)), db = pf_desc(pf_smem(sX + st * PF_STAGE));
 #pragma unroll
                     for (uint32_t kk = 0; kk < PF_BK / 16; kk++) {
                         const uint32_t buf = gcount & 1;
                         if (in_group == 0 && gcount >= 2) {
-                            if (!pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
+                            if (!dready && !pf_wait(&dempty[buf], ((gcount >> 1) & 1) ^ 1)) { failed = true; break; }
+                            dready = 0;
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         }
                         if (elected) pf_mma_pair(tmem_base + buf * PF_TM, da + 2 * kk, db + 2 * kk, idesc, in_group ? 1u : 0u);
@@ -356,7 +364,8 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
                     st = st1;
                     par = par1;
                 }
-            } } else if (rank == 0) {
+              }
+            } else if (rank == 0) {
                 const uint32_t elected = pf_elect();
                 // f32 accumulate, bf16 x bf16, both K-major, N = 256, M = 256 over the pair
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((PF_TM >> 3) << 17) | ((PF_TN >> 4) << 24);
@@ -425,23 +434,52 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
         const uint32_t remote_full = pf_map_to_cta(pf_smem(&full[0]), 0);
         uint32_t st = 0, par = 0, sq = 0, pq = 0;
         if constexpr (BITS == 8) {
-            // one k-step (one slot of 64 codes per row) per iteration
-            for (uint32_t it = 0; it < total; it++) {
+            // a slot of 64 codes per row is one k-step; two per iteration (one fence and one round of barrier
+            // latencies for both), a single one when the count is odd
+            auto ring_next = [](uint32_t& i, uint32_t& p, uint32_t n) { if (++i == n) { i = 0; p ^= 1; } };
+            uint32_t it = 0;
+            for (; it + 1 < total; it += 2) {
+                uint32_t sq1 = sq, pq1 = pq, st1 = st, par1 = par;
+                ring_next(sq1, pq1, PF_SQ);
+                ring_next(st1, par1, PF_S);
+                uint4 q0[4], q1[4];
                 if (!pf_wait(&full_q[sq], pq)) { failed = true; break; }
-                const uint8_t* qs = sQ + sq * PF_Q_BYTES + q_row;
-                uint4 q[4];
 #pragma unroll
-                for (uint32_t c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4*>(qs + ((c << 4) ^ q_sw));
+                for (uint32_t c = 0; c < 4; c++) q0[c] = *reinterpret_cast<const uint4*>(sQ + sq * PF_Q_BYTES + q_row + ((c << 4) ^ q_sw));
+                if (!pf_wait(&full_q[sq1], pq1)) { failed = true; break; }
+#pragma unroll
+                for (uint32_t c = 0; c < 4; c++) q1[c] = *reinterpret_cast<const uint4*>(sQ + sq1 * PF_Q_BYTES + q_row + ((c << 4) ^ q_sw));
                 if (it >= PF_S && !pf_wait(&empty[st], par ^ 1)) { failed = true; break; }
-                pf_widen_row(sA + st * PF_STAGE, row_off, q);
+                if (it + 1 >= PF_S && !pf_wait(&empty[st1], par1 ^ 1)) { failed = true; break; }
+                pf_widen_row(sA + st * PF_STAGE, row_off, q0);
+                pf_widen_row(sA + st1 * PF_STAGE, row_off, q1);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
                     pf_mbar_arrive_cluster(remote_full + st * 8);
+                    pf_mbar_arrive_cluster(remote_full + st1 * 8);
                     pf_mbar_arrive(&empty_q[sq]);
+                    pf_mbar_arrive(&empty_q[sq1]);
                 }
-                if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
-                if (++st == PF_S) { st = 0; par ^= 1; }
+                sq = sq1; pq = pq1; st = st1; par = par1;
+                ring_next(sq, pq, PF_SQ);
+                ring_next(st, par, PF_S);
+            }
+            if (it < total && !failed) {
+                uint4 q[4];
+                if (!pf_wait(&full_q[sq], pq)) failed = true;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4*>(sQ + sq * PF_Q_BYTES + q_row + ((c << 4) ^ q_sw));
+                if (!failed && it >= PF_S && !pf_wait(&empty[st], par ^ 1)) failed = true;
+                if (!failed) {
+                    pf_widen_row(sA + st * PF_STAGE, row_off, q);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        pf_mbar_arrive_cluster(remote_full + st * 8);
+                        pf_mbar_arrive(&empty_q[sq]);
+                    }
+                }
             }
         } else
         // one k-group (two k-steps, one packed-code slot) per iteration: one fence and one round of
