@@ -147,11 +147,12 @@ typedef struct qb200_qlinear qb200_qlinear;
  * buffers (codes, scales, optional f32 bias of out_dim elements): they must
  * outlive the handle.  bias_len is the bias element count (checked against
  * out_dim like check_bias, quant.rs:838-848); pass bias_dev = NULL for none.
- * Where the stored layout does not feed the fast int4 kernels as it is, the handle builds an execution copy here (and
- * synchronises the device once): an `[in, out]` weight with Group{axis: 0, size: 128} is transposed to `[out, in]` with
- * a 1x128 grid, and a weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode kernel.
- * Each copy costs 0.5 byte per weight plus its scales (and 16 rows of f32 partial outputs per slice); the caller's
- * buffers stay the record. */
+ * Where the stored layout does not feed the fast kernels as it is, the handle builds an execution copy here (and
+ * synchronises the device once): an int4 `[in, out]` weight with Group{axis: 0, size: 128} is transposed to `[out, in]`
+ * with a 1x128 grid, an int4 weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode
+ * kernel, and an int8 `[in, out]` weight whose tile height is a multiple of 16 (or the whole input width) is transposed
+ * with its scale grid.  Each copy costs its codes again (0.5 or 1 byte per weight) plus its scales (and 16 rows of f32
+ * partial outputs per slice); the caller's buffers stay the record. */
 QB200_API qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev, uint64_t rows,
                                   uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc,
                                   int32_t layout, const float* bias_dev, uint64_t bias_len,
@@ -170,7 +171,8 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * transposed execution copy made at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
  * the tcgen05 GEMM (m > 16); int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on its own
  * decode GEMV (m <= 16), and with in_dim a multiple of 64 and tiles of whole 16-column steps that divide in_dim (or span
- * it) on the same tcgen05 GEMM (m > 16).  Everything else (f32 x, other grids and layouts) runs on the generic kernels.
+ * it) on the same tcgen05 GEMM (m > 16); int8 `[in, out]` whose tile height is such a number through a transposed copy
+ * of codes and scale grid made at creation.  Everything else (f32 x, other grids and layouts) runs on the generic kernels.
  * A call whose scratch is not allocated yet (the GEMM's split-K workspace, the generic column kernel's partial sums)
  * allocates it; on a stream that is recording a CUDA graph that is refused with QB200_ERR_INVALID_PARAM — run the shape
  * once before capturing.  The decode GEMVs need finite activations with |x| < 2^87 (see qb200_qlinear_check). */

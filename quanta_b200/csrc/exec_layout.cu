@@ -12,6 +12,10 @@
 //     each reads its window of the activations in place — and a fold of their f32 partial outputs.
 // Both are copies (+ 0.5 byte per weight each, + the scales): the stored buffers stay what accessors, writers
 // and the tcgen05 GEMM's tensor maps over `[out, in]` codes see.
+//
+// The int8 kernels read `[out, in]` bytes with a grid whose tile width is a whole number of 16-column steps: an
+// `[in, out]` int8 weight whose tile HEIGHT is such a number (32 x 32 blocks, Group{axis: 0, size: 128}, per-column
+// scales) gets a transposed copy of codes and scale grid as well (+ 1 byte per weight).
 #include <cstdint>
 #include <string>
 
@@ -38,6 +42,18 @@ __global__ void __launch_bounds__(256) k_transpose_i4(const uint32_t* __restrict
         if (k < in_dim) w |= ((src[(uint64_t)k * src_words + (n >> 3)] >> sh) & 0xFu) << (4 * i);
     }
     dst[(uint64_t)n * (in_dim / 8) + kw] = w;
+}
+
+// dst[n][k] = src[k][n] over bytes, through a 64 x 64 tile in shared memory (both sides coalesced).
+__global__ void __launch_bounds__(256) k_transpose_i8(const uint8_t* __restrict__ src, uint32_t in_dim, uint32_t out_dim,
+                                                      uint8_t* __restrict__ dst) {
+    __shared__ uint8_t tile[64][65];
+    const uint32_t n0 = blockIdx.x * 64, k0 = blockIdx.y * 64, tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (uint32_t i = ty; i < 64; i += 4)
+        if (k0 + i < in_dim && n0 + tx < out_dim) tile[i][tx] = src[(uint64_t)(k0 + i) * out_dim + n0 + tx];
+    __syncthreads();
+    for (uint32_t i = ty; i < 64; i += 4)
+        if (n0 + i < out_dim && k0 + tx < in_dim) dst[(uint64_t)(n0 + i) * in_dim + k0 + tx] = tile[tx][i];
 }
 
 // dst[n][g] = src[g][n]
@@ -72,6 +88,26 @@ void free_exec_layout(qb200_qlinear* ql) {
 }
 
 qb200_status build_exec_layout(qb200_qlinear* ql) {
+    if (ql->bits == 8) {
+        if (ql->layout != QB200_IN_OUT || ql->in_dim == 0 || ql->out_dim == 0 || ql->in_dim > 0x7FFFFFFFull || ql->out_dim > 0x7FFFFFFFull)
+            return QB200_OK;
+        if (ql->gr < ql->in_dim && ql->gr % 16 != 0) return QB200_OK;  // the tile height becomes the tile width
+        const uint32_t K = (uint32_t)ql->in_dim, N = (uint32_t)ql->out_dim;
+        const uint64_t tr = (ql->in_dim + ql->gr - 1) / ql->gr;  // the stored grid is [tr, tc]; the copy's [tc, tr]
+        if (tr > 0x7FFFFFFFull || ql->tc > 0x7FFFFFFFull || (K + 63) / 64 > 65535u || tr > 65535u) return QB200_OK;
+        QB_CUDA_TRY(cudaMalloc(&ql->t_codes, (uint64_t)N * K));
+        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, tr * ql->tc * 4));
+        k_transpose_i8<<<dim3((N + 63) / 64, (K + 63) / 64), 256>>>(static_cast<const uint8_t*>(ql->codes), K, N,
+                                                                     static_cast<uint8_t*>(ql->t_codes));
+        QB_CUDA_TRY(cudaGetLastError());
+        k_transpose_f32<<<dim3(((uint32_t)ql->tc + 255) / 256, (uint32_t)tr), 256>>>(ql->scales, (uint32_t)tr, (uint32_t)ql->tc, ql->t_scales);
+        QB_CUDA_TRY(cudaGetLastError());
+        ql->t_gr = ql->gc;
+        ql->t_gc = ql->gr;
+        ql->t_tc = tr;
+        QB_CUDA_TRY(cudaDeviceSynchronize());
+        return QB200_OK;
+    }
     if (ql->bits != 4 || ql->in_dim % 128 != 0 || ql->in_dim == 0 || ql->out_dim == 0 || ql->out_dim > 0x7FFFFFFFull ||
         ql->in_dim > (uint64_t)SLICE_LIMIT * SLICE_MAX)
         return QB200_OK;
@@ -85,6 +121,9 @@ qb200_status build_exec_layout(qb200_qlinear* ql) {
         QB_CUDA_TRY(cudaGetLastError());
         k_transpose_f32<<<dim3((N + 255) / 256, groups), 256>>>(ql->scales, groups, N, ql->t_scales);
         QB_CUDA_TRY(cudaGetLastError());
+        ql->t_gr = 1;
+        ql->t_gc = 128;
+        ql->t_tc = groups;
     } else if (ql->gr != 1 || ql->gc != 128) {
         return QB200_OK;
     }

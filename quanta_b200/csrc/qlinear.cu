@@ -58,7 +58,7 @@ qb200_status grow(void** p, uint64_t* have, uint64_t need, cudaStream_t capturin
     return QB200_OK;
 }
 
-// The forward's arguments over what the fast int4 kernels read (the transposed copy of an [in, out] weight when
+// The forward's arguments over what the fast kernels read (the transposed copy of an [in, out] weight when
 // there is one, else the stored buffers).
 qb::FwdArgs fast_args(const qb200_qlinear* q, const void* x, void* y, uint64_t m) {
     qb::FwdArgs a;
@@ -72,7 +72,7 @@ qb::FwdArgs fast_args(const qb200_qlinear* q, const void* x, void* y, uint64_t m
     a.out_dim = q->out_dim;
     a.gr = q->fast_gr();
     a.gc = q->fast_gc();
-    a.tc = q->t_codes ? q->in_dim / 128 : q->tc;
+    a.tc = q->fast_tc();
     return a;
 }
 
@@ -94,7 +94,8 @@ qb::FwdArgs stored_args(const qb200_qlinear* q, const void* x, void* y, uint64_t
 }
 
 bool decode_i8_eligible(const qb200_qlinear* q, uint64_t m, int x_dtype, const void* x) {
-    return qb::gemv_i8_eligible(q->bits, q->gr, q->gc, q->layout, q->in_dim, q->out_dim, m, x_dtype, q->codes, x);
+    return q->fast_view() && qb::gemv_i8_eligible(q->bits, q->fast_gr(), q->fast_gc(), QB200_OUT_IN, q->in_dim, q->out_dim, m, x_dtype,
+                                                  q->fast_codes(), x);
 }
 
 bool decode_eligible(const qb200_qlinear* q, uint64_t m, int x_dtype, const void* x) {
@@ -190,7 +191,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         }
     }
     if (decode_i8_eligible(ql, m, x_dtype, x_dev)) {
-        const qb::FwdArgs a8 = stored_args(ql, x_dev, y_dev, m);
+        const qb::FwdArgs a8 = fast_args(ql, x_dev, y_dev, m);
         qb200_status s = qb::gemv_i8_forward_many(&a8, 1, y_dtype, ql->status, st);
         if (s != QB200_ERR_NOT_SUPPORTED) {
             ql->last_kernel = "gemv_mma_i8";
@@ -200,8 +201,8 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         // the int8 decode kernel keeps eight batch rows in registers: a batch of 9..16 runs as two launches (the second
         // pass over a layer that fits L2 re-reads it from there)
         const uint64_t ysz = y_dtype == QB200_F32 ? 4 : 2;
-        qb::FwdArgs lo = stored_args(ql, x_dev, y_dev, 8);
-        qb::FwdArgs hi = stored_args(ql, static_cast<const uint16_t*>(x_dev) + 8 * ql->in_dim,
+        qb::FwdArgs lo = fast_args(ql, x_dev, y_dev, 8);
+        qb::FwdArgs hi = fast_args(ql, static_cast<const uint16_t*>(x_dev) + 8 * ql->in_dim,
                                      static_cast<uint8_t*>(y_dev) + 8 * ql->out_dim * ysz, m - 8);
         qb200_status s = qb::gemv_i8_forward_many(&lo, 1, y_dtype, ql->status, st);
         if (s == QB200_OK) s = qb::gemv_i8_forward_many(&hi, 1, y_dtype, ql->status, st);
@@ -230,8 +231,9 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         ql->last_kernel = "gemm_tcgen05";
         return qb::gemm_i4_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
     }
-    if (qb::gemm_i8_eligible(ql->bits, ql->gr, ql->gc, ql->layout, ql->in_dim, ql->out_dim, m, x_dtype, ql->codes, x_dev)) {
-        const uint64_t need = qb::gemm_i8_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->gc, ql->bias);
+    if (ql->fast_view() && qb::gemm_i8_eligible(ql->bits, ql->fast_gr(), ql->fast_gc(), QB200_OUT_IN, ql->in_dim, ql->out_dim, m,
+                                                x_dtype, ql->fast_codes(), x_dev)) {
+        const uint64_t need = qb::gemm_i8_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->fast_gc(), ql->bias);
         if (need) {
             void* p = ql->scratch;
             qb200_status s = grow(&p, &ql->scratch_bytes, need, st);
@@ -239,7 +241,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
             if (s) return s;
         }
         ql->last_kernel = "gemm_tcgen05_i8";
-        return qb::gemm_i8_forward(stored_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
+        return qb::gemm_i8_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, need ? ql->scratch : nullptr, ql->status, st);
     }
     const qb::FwdArgs a = stored_args(ql, x_dev, y_dev, m);
     if (ql->layout == QB200_OUT_IN) {
@@ -284,7 +286,7 @@ qb200_status qb200_qlinear_forward_many(qb200_qlinear* const* layers, uint32_t c
         grouped8 = layers[i]->in_dim == layers[0]->in_dim && decode_i8_eligible(layers[i], m, x_dtype, x_dev[i]);
     if (grouped8) {  // int8 layers that share the input width: one persistent launch as well
         std::vector<qb::FwdArgs> args(count);
-        for (uint32_t i = 0; i < count; i++) args[i] = stored_args(layers[i], x_dev[i], y_dev[i], m);
+        for (uint32_t i = 0; i < count; i++) args[i] = fast_args(layers[i], x_dev[i], y_dev[i], m);
         qb200_status s = qb::gemv_i8_forward_many(args.data(), count, y_dtype, layers[0]->status, static_cast<cudaStream_t>(stream));
         if (s != QB200_ERR_NOT_SUPPORTED) {
             for (uint32_t i = 0; i < count; i++) layers[i]->last_kernel = "gemv_mma_i8_grouped";

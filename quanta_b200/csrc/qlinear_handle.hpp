@@ -23,14 +23,16 @@ struct qb200_qlinear {
     void* y_stage = nullptr;
     uint64_t x_stage_bytes = 0, y_stage_bytes = 0;
     cudaStream_t host_stream = nullptr;
-    // Execution layout, built once at creation where the stored layout does not feed the fast int4 kernels as it is
+    // Execution layout, built once at creation where the stored layout does not feed the fast kernels as it is
     // (copies: the stored codes and scales stay the record that accessors and writers see).
-    //   t_codes / t_scales: an `[in, out]` matrix with Group{axis: 0, size: 128} transposed to `[out, in]` with a
-    //     1 x 128 grid (a permutation of the nibbles and of the scales);
+    //   t_codes / t_scales: an `[in, out]` matrix transposed to `[out, in]` — int4 with Group{axis: 0, size: 128} to a
+    //     1 x 128 grid, int8 with tiles of whole 16-row steps to the transposed grid (t_gr x t_gc tiles, t_tc scales
+    //     per row; a permutation of the codes and of the scales);
     //   slices: inputs wider than the decode kernel keeps in registers (4096) cut into `n_slices` column runs of whole
     //     scale groups, each padded with zero codes and zero scales to `slice_pad` columns, rows contiguous.
     void* t_codes = nullptr;
     float* t_scales = nullptr;
+    uint64_t t_gr = 0, t_gc = 0, t_tc = 0;
     void* slice_codes = nullptr;     // [n_slices][out_dim][slice_pad / 8] u32
     float* slice_scales = nullptr;   // [n_slices][out_dim][slice_pad / 128]
     float* slice_partials = nullptr; // [n_slices][16][out_dim] f32: the slices' partial outputs of one decode call
@@ -39,12 +41,13 @@ struct qb200_qlinear {
     int32_t* status = nullptr;  // device word written by kernels whose bounded waits ran out
     const char* last_kernel = "";
 
-    // what the fast int4 kernels read: the transposed copy when there is one, else the stored buffers
+    // what the fast kernels read: the transposed copy when there is one, else the stored buffers
     bool fast_view() const { return t_codes != nullptr || layout == QB200_OUT_IN; }
     const void* fast_codes() const { return t_codes ? t_codes : codes; }
     const float* fast_scales() const { return t_codes ? t_scales : scales; }
-    uint64_t fast_gr() const { return t_codes ? 1 : gr; }
-    uint64_t fast_gc() const { return t_codes ? 128 : gc; }
+    uint64_t fast_gr() const { return t_codes ? t_gr : gr; }
+    uint64_t fast_gc() const { return t_codes ? t_gc : gc; }
+    uint64_t fast_tc() const { return t_codes ? t_tc : tc; }
 };
 
 namespace qb {

@@ -599,6 +599,39 @@ def test_in_out_int4_takes_the_fast_kernels_and_its_execution_copy_is_a_permutat
     assert _lib.load().qb200_qlinear_check(qlb._h, None) == 0
 
 
+@pytest.mark.parametrize("K,N,gran", [(1024, 520, qb.Block(32, 32)), (512, 264, qb.Group(0, 128)), (256, 136, qb.PerChannel(1)),
+                                      (2048, 300, qb.Block(16, 8)), (192, 72, qb.Group(0, 48)), (320, 100, qb.PerTensor())])
+def test_in_out_int8_takes_the_fast_kernels_through_its_transposed_copy(K, N, gran):
+    """An `[in, out]` int8 weight whose tile height is a whole number of 16-row steps: the handle transposes codes and
+    scale grid once and the int8 decode and prefill kernels serve it.  One-hot activations read single weights back
+    bit for bit against the oracle's dequantize of the ORIGINAL record; random activations against the f64 checker."""
+    rng = np.random.default_rng(K + N)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    gr, gc = gran.tile(K, N)
+    m, oc, os_ = quantize_both(w, K, N, qb.QuantDtype.Int8, gran)
+    wd = o.dequantize_host(oc, os_, K, N, 8, gr, gc)   # [in, out]
+    plain = qb.QuantizedLinear.new(m, None, qb.IN_OUT)
+    ql = qb.QuantizedLinear.new(m, t(bias), qb.IN_OUT)
+    decode = gr % 32 == 0 and K % 128 == 0 and K <= 4096
+    prefill = K % 64 == 0 and (gr >= K or K % gr == 0)
+    ks = sorted(set(int(k) for k in rng.integers(0, K, 40)) | {0, 15, 16, 31, 32, 63, K - 1})
+    for rows, kernel in [(ks[:8], "gemv_mma_i8" if decode else "gemm_tcgen05_i8" if prefill else "generic_cols"),
+                         (ks[:40], "gemm_tcgen05_i8" if prefill else "generic_cols")]:
+        y = plain.forward(_one_hot_rows(rows, K), out_dtype=torch.float32)
+        assert plain.last_kernel() == kernel, (gran, len(rows))
+        assert (bits(y.cpu().numpy()) == bits(wd[rows, :].copy())).all()
+    for M in (3, 8, 12, 50):
+        xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+        want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.IN_OUT, threads=8)
+        close(ql.forward(xt, out_dtype=torch.float32).cpu().numpy(), want, 1e-3)
+        assert not ql.last_kernel().startswith("generic") or not (decode or prefill)
+    assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()   # the record itself is untouched
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
 def test_sliced_decode_of_a_wide_layer_matches_per_slice_sums():
     """A `[4096, 11008]` layer at M <= 16 (a feed-forward down projection called on its own): three column slices in one
     launch plus the fold; with bf16 output; through the host-buffer entry point with pinned outputs."""
