@@ -75,6 +75,13 @@ uint64_t gemm_i8_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, ui
 #ifdef __CUDACC__
 qb200_status gemm_i8_forward(const FwdArgs& a, int y_dtype, void* scratch, int32_t* status, cudaStream_t st);
 #endif
+#ifdef __CUDACC__
+// f32 activations on the bf16 kernels (forward_generic.cu).  split: x [m, k] f32 -> xs [3 m, k] bf16 with
+// x = xs[i] + xs[m + i] + xs[2 m + i] exactly (two truncations and the remainder); fold: y[i] = (ys[i] + ys[m + i]) + ys[2 m + i]
+// (+ bias), ys [3 m, n] f32.
+qb200_status split_f32_activations(const float* x, uint64_t m, uint64_t k, void* xs, cudaStream_t st);
+qb200_status fold_split_outputs(const float* ys, uint64_t m, uint64_t n, const float* bias, void* y, int y_dtype, cudaStream_t st);
+#endif
 // K slices the column kernel splits into (1 = no scratch needed).
 uint32_t forward_cols_slices(uint64_t in_dim, uint64_t out_dim, uint64_t m);
 

@@ -326,6 +326,52 @@ qb200_status forward_generic(const FwdArgs& a, uint32_t bits, int x_dtype, int y
                                 : by_out<8, uint16_t>(a, y_dtype, rows_kernel, scratch, slices, st);
 }
 
+// ---- f32 activations on the bf16 kernels ----------------------------------------------------------------------------
+// An f32 has 24 significant bits: its top 8 (a truncation to bf16), the top 8 of what is left, and the rest are three
+// bf16 values whose sum is the f32 exactly.  The bf16 kernels multiply each part exactly and accumulate in f32, so the
+// three partial outputs added up are the exact-product, f32-accumulated result for the f32 activation.
+
+__global__ void __launch_bounds__(256) k_split_f32(const float* __restrict__ x, uint64_t mk, uint16_t* __restrict__ xs) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < mk; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float v = x[i];
+        const uint32_t b0 = __float_as_uint(v) & 0xFFFF0000u;
+        const float r1 = v - __uint_as_float(b0);  // exact: the low 16 bits of the significand
+        const uint32_t b1 = __float_as_uint(r1) & 0xFFFF0000u;
+        const float r2 = r1 - __uint_as_float(b1);  // exact: at most 8 significant bits
+        xs[i] = (uint16_t)(b0 >> 16);
+        xs[mk + i] = (uint16_t)(b1 >> 16);
+        xs[2 * mk + i] = f32_to_bf16_bits(r2);
+    }
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(256) k_fold_split(const float* __restrict__ ys, uint64_t mn, uint32_t n, const float* __restrict__ bias,
+                                                    YT* __restrict__ y) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < mn; i += (uint64_t)gridDim.x * blockDim.x) {
+        float v = (ys[i] + ys[mn + i]) + ys[2 * mn + i];
+        if (bias) v += bias[i % n];
+        if constexpr (sizeof(YT) == 4) y[i] = v;
+        else y[i] = f32_to_bf16_bits(v);
+    }
+}
+
+qb200_status split_f32_activations(const float* x, uint64_t m, uint64_t k, void* xs, cudaStream_t st) {
+    const uint64_t mk = m * k;
+    const uint32_t blocks = (uint32_t)((mk + 255) / 256 > 1184 ? 1184 : (mk + 255) / 256);
+    k_split_f32<<<blocks, 256, 0, st>>>(x, mk, static_cast<uint16_t*>(xs));
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
+qb200_status fold_split_outputs(const float* ys, uint64_t m, uint64_t n, const float* bias, void* y, int y_dtype, cudaStream_t st) {
+    const uint64_t mn = m * n;
+    const uint32_t blocks = (uint32_t)((mn + 255) / 256 > 1184 ? 1184 : (mn + 255) / 256);
+    if (y_dtype == QB200_F32) k_fold_split<float><<<blocks, 256, 0, st>>>(ys, mn, (uint32_t)n, bias, static_cast<float*>(y));
+    else k_fold_split<uint16_t><<<blocks, 256, 0, st>>>(ys, mn, (uint32_t)n, bias, static_cast<uint16_t*>(y));
+    QB_CUDA_TRY(cudaGetLastError());
+    return QB200_OK;
+}
+
 }  // namespace qb
 
 // ---- forward without any allocation ------------------------------------------------------------

@@ -103,6 +103,17 @@ bool decode_eligible(const qb200_qlinear* q, uint64_t m, int x_dtype, const void
                                                   x_dtype, q->fast_codes(), q->fast_scales(), x);
 }
 
+// Whether a forward of m bf16 rows (at a 16-byte aligned address) would take one of the fast kernels.
+bool bf16_fast(const qb200_qlinear* q, uint64_t m) {
+    const void* aligned = reinterpret_cast<const void*>(uintptr_t(256));  // only its alignment is looked at
+    if (decode_eligible(q, m, QB200_BF16, aligned) || decode_i8_eligible(q, m, QB200_BF16, aligned)) return true;
+    if (m > 8 && m <= 16 && decode_i8_eligible(q, 8, QB200_BF16, aligned)) return true;
+    if (q->n_slices && m <= 16) return true;
+    if (!q->fast_view()) return false;
+    return qb::gemm_i4_eligible(q->bits, q->fast_gr(), q->fast_gc(), QB200_OUT_IN, q->in_dim, q->out_dim, m, QB200_BF16, q->fast_codes(), aligned) ||
+           qb::gemm_i8_eligible(q->bits, q->fast_gr(), q->fast_gc(), QB200_OUT_IN, q->in_dim, q->out_dim, m, QB200_BF16, q->fast_codes(), aligned);
+}
+
 }  // namespace
 
 extern "C" {
@@ -167,6 +178,7 @@ void qb200_qlinear_destroy(qb200_qlinear* ql) {
     if (ql->scratch) cudaFree(ql->scratch);
     if (ql->x_stage) cudaFree(ql->x_stage);
     if (ql->y_stage) cudaFree(ql->y_stage);
+    if (ql->split_stage) cudaFree(ql->split_stage);
     if (ql->host_stream) cudaStreamDestroy(ql->host_stream);
     delete ql;
 }
@@ -183,6 +195,20 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward: activations are f32 or bf16");
     if (m == 0) return QB200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (x_dtype == QB200_F32 && m <= 0x7FFFFFFFull / 3 && bf16_fast(ql, 3 * m)) {
+        // f32 activations (the reference's own dtype) on the bf16 kernels: x is the exact sum of three bf16 parts, the
+        // kernels' products are exact, so three times the rows and one fold give the exact-product result
+        const uint64_t xs_bytes = (3 * m * ql->in_dim * 2 + 255) & ~uint64_t(255);
+        if (qb200_status s = grow(&ql->split_stage, &ql->split_stage_bytes, xs_bytes + 3 * m * ql->out_dim * 4, st)) return s;
+        float* ys = reinterpret_cast<float*>(static_cast<uint8_t*>(ql->split_stage) + xs_bytes);
+        if (qb200_status s = qb::split_f32_activations(static_cast<const float*>(x_dev), m, ql->in_dim, ql->split_stage, st)) return s;
+        const float* bias = ql->bias;
+        ql->bias = nullptr;  // added once, by the fold
+        const qb200_status s = qb200_qlinear_forward(ql, ql->split_stage, QB200_BF16, 3 * m, ys, QB200_F32, stream);
+        ql->bias = bias;
+        if (s) return s;
+        return qb::fold_split_outputs(ys, m, ql->out_dim, bias, y_dev, y_dtype, st);
+    }
     if (decode_eligible(ql, m, x_dtype, x_dev)) {
         qb200_status s = qb::gemv_i4_forward(fast_args(ql, x_dev, y_dev, m), y_dtype, ql->status, st);
         if (s != QB200_ERR_NOT_SUPPORTED) {

@@ -23,6 +23,10 @@ struct qb200_qlinear {
     void* y_stage = nullptr;
     uint64_t x_stage_bytes = 0, y_stage_bytes = 0;
     cudaStream_t host_stream = nullptr;
+    // f32 activations on the bf16 kernels: the three bf16 parts of x, [3 m, in_dim], and their outputs, [3 m, out_dim] f32
+    // (grow-only; apart from `scratch`, which the inner call may grow)
+    void* split_stage = nullptr;
+    uint64_t split_stage_bytes = 0;
     // Execution layout, built once at creation where the stored layout does not feed the fast kernels as it is
     // (copies: the stored codes and scales stay the record that accessors and writers see).
     //   t_codes / t_scales: an `[in, out]` matrix transposed to `[out, in]` — int4 with Group{axis: 0, size: 128} to a

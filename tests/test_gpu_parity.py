@@ -589,10 +589,11 @@ def test_in_out_int4_takes_the_fast_kernels_and_its_execution_copy_is_a_permutat
         if kernel:
             assert qlb.last_kernel() == kernel
         close(got, o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.IN_OUT, threads=8), tol)
-    # f32 activations keep the generic column kernel (the fast kernels take bf16)
-    xf = torch.randn(2, K, device=DEV)
-    qlb.forward(xf)
-    assert qlb.last_kernel() == "generic_cols"
+    # f32 activations (the reference's own dtype) ride the same kernels as three exact bf16 parts
+    xf = rng.standard_normal((2, K)).astype(np.float32)
+    got = qlb.forward(t(xf), out_dtype=torch.float32).cpu().numpy()
+    assert qlb.last_kernel() == ("gemv_mma" if K <= 4096 else "gemv_mma_sliced")
+    close(got, o.linear_forward_f64(xf, wd, bias, o.IN_OUT, threads=8), 1e-5)
     # the record itself is untouched: it still dequantizes to the oracle's matrix
     assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()
     from quanta_b200 import _lib
@@ -864,11 +865,42 @@ def test_config1_int8_block32_bf16_activations_take_the_fast_kernel():
     assert (bits(ql.forward_host(xb)) == bits(y.cpu().numpy())).all()
 
 
+@pytest.mark.parametrize("dtype,gran,layout,shape", [
+    (qb.QuantDtype.Int4, qb.Group(1, 128), qb.OUT_IN, (1000, 1024)), (qb.QuantDtype.Int4, qb.Group(0, 128), qb.IN_OUT, (1024, 520)),
+    (qb.QuantDtype.Int8, qb.Block(32, 32), qb.OUT_IN, (384, 1024)), (qb.QuantDtype.Int8, qb.Block(32, 32), qb.IN_OUT, (512, 200)),
+    (qb.QuantDtype.Int4, qb.Group(1, 128), qb.OUT_IN, (256, 8192))])
+def test_f32_activations_ride_the_bf16_kernels_as_three_exact_parts(dtype, gran, layout, shape):
+    """The reference's activations are f32 (Layer::<f32>::apply, crates/ml/quanta-nn/src/quant.rs:903-918).  An f32 is the
+    exact sum of three bf16 values; the kernels multiply each part exactly and accumulate in f32, so the folded result
+    is the exact-product sum: it meets the f64 checker at 1e-5, tighter than the bf16 tests' bound."""
+    r, c = shape
+    rng = np.random.default_rng(r + c)
+    w = (rng.standard_normal((r, c)) * 0.02).astype(np.float32)
+    in_dim, out_dim = (r, c) if layout == qb.IN_OUT else (c, r)
+    bias = rng.standard_normal(out_dim).astype(np.float32)
+    gr, gc = gran.tile(r, c)
+    m, oc, os_ = quantize_both(w, r, c, dtype, gran)
+    wd = o.dequantize_host(oc, os_, r, c, dtype.bits(), gr, gc)
+    ql = qb.QuantizedLinear.new(m, t(bias), layout)
+    for M in (1, 2, 5, 7, 40):
+        x = (rng.standard_normal((M, in_dim)) * np.exp(rng.uniform(-6, 6, (M, 1)))).astype(np.float32)   # rows of very different size
+        want = o.linear_forward_f64(x, wd, bias, layout, threads=8)
+        y = ql.forward(t(x), out_dtype=torch.float32).cpu().numpy()
+        assert not ql.last_kernel().startswith("generic"), (ql.last_kernel(), M)
+        err = np.abs(y - want) - 1e-5 * (np.abs(x).max(axis=1, keepdims=True) + np.abs(want))
+        assert (err <= 0).all(), (M, ql.last_kernel(), float(err.max()))
+        yb = ql.forward(t(x), out_dtype=torch.bfloat16).to(torch.float32).cpu().numpy()
+        assert (np.abs(yb - want) <= 1e-2 * (np.abs(x).max(axis=1, keepdims=True) + np.abs(want))).all()
+        assert (bits(ql.forward_host(x)) == bits(y)).all()    # host buffers in and out: the same kernels
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
 def test_scratch_growth_is_refused_while_a_graph_is_recorded():
     """A forward whose scratch is not allocated yet would free / allocate; on a stream that records a CUDA graph that
     is refused with a message, the recording survives, and after one call outside a capture the same shape records."""
-    w = torch.randn(4096, 256, device=DEV) * 0.02   # [in, out] int8: the column kernel splits K and needs partial sums
-    ql = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, qb.PerChannel(1)), None, qb.IN_OUT)
+    w = torch.randn(4096, 256, device=DEV) * 0.02   # [in, out] int8, 8 x 8 tiles: the column kernel splits K and needs partial sums
+    ql = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, qb.Block(8, 8)), None, qb.IN_OUT)
     x = torch.randn(3, 4096, device=DEV)
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
