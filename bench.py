@@ -474,6 +474,16 @@ def measure_extras(torch, qb, dev, only=None, small=False, world=1):
     except Exception as e:
         out["decode_gemv_M"] = {"skipped": str(e)[:80]}
     out.update(measure_int8_decode(torch, qb, dev, gen, timed, hbm, 32))
+    try:  # the reference's CPU-runnable configuration as it is: int8 [1024, 1024], 32 x 32 blocks, X f32 [8, 1024], one call
+        w1 = torch.randn(1024, 1024, device=dev, generator=gen) * 0.02
+        x1 = torch.randn(8, 1024, device=dev, generator=gen)
+        ql1 = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w1, qb.QuantDtype.Int8, qb.Block(32, 32)), None, qb.OUT_IN)
+        ms, how = timed_replay(lambda: ql1.forward(x1, out_dtype=torch.float32), 10)
+        out["config1_int8_32x32_f32_x8"] = {"us_per_call": ms * 1e3, "kernel": ql1.last_kernel(), "launch": how,
+                                             "note": "1 MB of codes: launch-bound, not an HBM measurement; f32 activations as three bf16 parts"}
+        del ql1, w1, x1
+    except Exception as e:
+        out["config1_int8_32x32_f32_x8"] = {"skipped": str(e)[:80]}
     out["decode_step_llama7b_shape"] = measure_decode_step(torch, dev, gen, hbm, 32, 1)
     try:  # the reference's quantize / dequantize are single-threaded host loops: the restatement timed the same way
         out["cpu_quantize_baseline"] = cpu_quantize_baseline()
@@ -487,6 +497,15 @@ def measure_extras(torch, qb, dev, only=None, small=False, world=1):
     ms = timed(lambda: ql.forward(x), 10)
     out["prefill_int4_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
                                 "peak_TFLOP/s": tf, "shape": {"M": M, "N": N, "K": K}, "kernel": ql.last_kernel()}
+    del ql
+    try:  # the same shape over int8 codes with 32 x 32 blocks (an accumulator every 32 k)
+        ql8 = qb.QuantizedLinear.new(qb.QuantizedMatrix.quantize(w, qb.QuantDtype.Int8, qb.Block(32, 32)), None, qb.OUT_IN)
+        ms = timed(lambda: ql8.forward(x), 10)
+        out["prefill_int8_32x32_gemm"] = {"TFLOP/s": 2.0 * M * N * K / ms / 1e9, "ms": ms, "roofline_frac": 2.0 * M * N * K / ms / 1e9 / tf,
+                                          "shape": {"M": M, "N": N, "K": K}, "kernel": ql8.last_kernel()}
+        del ql8
+    except Exception as e:
+        out["prefill_int8_32x32_gemm"] = {"skipped": f"{type(e).__name__}: {str(e)[:120]}"}
     return out
 
 
