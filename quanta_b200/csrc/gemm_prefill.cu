@@ -481,7 +481,7 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
                     }
                 }
             }
-        } else
+        } else {
         // one k-group (two k-steps, one packed-code slot) per iteration: one fence and one round of
         // barrier latencies for 16 independent words per thread
         for (uint32_t it = 0; it < total; it += 2) {
@@ -505,6 +505,7 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
             if (++sq == PF_SQ) { sq = 0; pq ^= 1; }
             st = st1 + 1 == PF_S ? 0 : st1 + 1;
             par = st1 + 1 == PF_S ? par1 ^ 1 : par1;
+        }
         }
     } else {
         // ---- epilogue warps: thread = weight row (TMEM lane), warpgroup = 128-column half of the m range ----
