@@ -148,8 +148,8 @@ typedef struct qb200_qlinear qb200_qlinear;
  * outlive the handle.  bias_len is the bias element count (checked against
  * out_dim like check_bias, quant.rs:838-848); pass bias_dev = NULL for none.
  * Where the stored layout does not feed the fast kernels as it is, the handle builds an execution copy here (and
- * synchronises the device once): an int4 `[in, out]` weight with Group{axis: 0, size: 128} is transposed to `[out, in]`
- * with a 1x128 grid, an int4 weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode
+ * synchronises the device once): an int4 `[in, out]` weight with Group{axis: 0, size: 128} (or another multiple of 16 that
+ * divides in_dim) is transposed to `[out, in]` with a 1x128 (1 x size) grid, an int4 weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode
  * kernel, and an int8 `[in, out]` weight whose tile height is a multiple of 16 (or the whole input width) is transposed
  * with its scale grid.  Each copy costs its codes again (0.5 or 1 byte per weight) plus its scales (and 16 rows of f32
  * partial outputs per slice); the caller's buffers stay the record. */
@@ -169,7 +169,9 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * y_dtype, both device, row-major.  f32 accumulation.
  * Fast paths (bf16 x): int4 with a 1x128 grid — `[out, in]`, or `[in, out]` with Group{axis: 0, size: 128} through the
  * transposed execution copy made at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
- * the tcgen05 GEMM (m > 16); int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on its own
+ * the tcgen05 GEMM (m > 16), which also takes the other int4 grids whose tile width along the inputs is a multiple of 16 that
+ * divides in_dim or spans it (Group sizes 32, 64, 256 ..., per-row, per-tensor; `[in, out]` with such groups along axis 0
+ * through the transposed copy); int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on its own
  * decode GEMV (m <= 16), and with in_dim a multiple of 64 and tiles of whole 16-column steps that divide in_dim (or span
  * it) on the same tcgen05 GEMM (m > 16); int8 `[in, out]` whose tile height is such a number through a transposed copy
  * of codes and scale grid made at creation.  f32 activations (the reference's own dtype) whose layer has such a fast path

@@ -113,17 +113,25 @@ qb200_status build_exec_layout(qb200_qlinear* ql) {
         return QB200_OK;
     const uint32_t K = (uint32_t)ql->in_dim, N = (uint32_t)ql->out_dim, groups = K / 128;
     if (ql->layout == QB200_IN_OUT) {
-        if (ql->gr != 128 || ql->gc != 1) return QB200_OK;  // only the documented int4 grid of an [in, out] weight
+        // groups along the inputs, one scale per output column: Group{axis: 0, size: 128} is the documented grid (decode
+        // and prefill kernels); other sizes of whole 16-row steps that divide the inputs reach the prefill kernel
+        if (ql->gc != 1 || ql->gr % 16 != 0 || ql->gr > K || K % ql->gr != 0) return QB200_OK;
+        const uint32_t tr = K / (uint32_t)ql->gr;
+        if (tr > 65535u) return QB200_OK;
         QB_CUDA_TRY(cudaMalloc(&ql->t_codes, (uint64_t)N * (K / 8) * 4));
-        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, (uint64_t)N * groups * 4));
+        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, (uint64_t)N * tr * 4));
         k_transpose_i4<<<dim3((N + 255) / 256, K / 8), 256>>>(static_cast<const uint32_t*>(ql->codes), K, N, (N + 7) / 8,
                                                                static_cast<uint32_t*>(ql->t_codes));
         QB_CUDA_TRY(cudaGetLastError());
-        k_transpose_f32<<<dim3((N + 255) / 256, groups), 256>>>(ql->scales, groups, N, ql->t_scales);
+        k_transpose_f32<<<dim3((N + 255) / 256, tr), 256>>>(ql->scales, tr, N, ql->t_scales);
         QB_CUDA_TRY(cudaGetLastError());
         ql->t_gr = 1;
-        ql->t_gc = 128;
-        ql->t_tc = groups;
+        ql->t_gc = ql->gr;
+        ql->t_tc = tr;
+        if (ql->gr != 128) {
+            QB_CUDA_TRY(cudaDeviceSynchronize());
+            return QB200_OK;
+        }
     } else if (ql->gr != 1 || ql->gc != 128) {
         return QB200_OK;
     }

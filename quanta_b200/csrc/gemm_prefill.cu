@@ -187,7 +187,8 @@ struct PrefillArgs {
     uint32_t M, N, K;
     uint32_t ksplit;     // K ranges per output tile (1: the kernel writes Y itself)
     uint32_t tma_store;  // 1 when Y's base and row pitch are multiples of 16 bytes
-    // int8 codes only: the scale grid [ceil(N / gr), tc] and the scale group's length in 16-k MMA steps
+    // general grids (every int8 launch, int4 grids other than 1x128): the scale grid [ceil(N / gr), tc] and the scale
+    // group's length in 16-k MMA steps
     uint32_t gr, tc, g16;
 };
 
@@ -239,10 +240,12 @@ __device__ __forceinline__ void pf_widen_row(uint8_t* dst, uint32_t row_off, con
     }
 }
 
-// The kernel's body for packed int4 codes with a 1x128 grid (BITS = 4) and for int8 codes with any grid whose tile
-// width is a multiple of 16 (BITS = 8).  With int8 a packed-code slot (128 rows x 64 B) is one k-step instead of one
-// k-group, and a scale group is `g16` MMA steps of 16 k: the issuer closes an accumulator every g16 steps.
-template <typename YT, bool SPLIT, uint32_t BITS>
+// The kernel's body for packed int4 (BITS = 4) and int8 (BITS = 8) codes.  A 64-byte slot of the code ring is one
+// k-group of 128 int4 codes per row or one k-step of 64 int8 codes.  GEN = false is the int4 1x128 grid: a scale
+// group is a slot.  GEN = true is any grid whose tile width is a multiple of 16: a scale group is `g16` MMA steps
+// of 16 k, the issuer closes an accumulator every g16 steps wherever that falls, and the epilogue reads row n / gr
+// of the grid.
+template <typename YT, bool SPLIT, uint32_t BITS, bool GEN>
 __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorMap& xmap, const CUtensorMap& qmap,
                                               const CUtensorMap& ymap, const PrefillArgs& a) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -250,9 +253,10 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
     // units' f32 partial tiles go to a workspace [ksplit, M, N] that a second kernel folds
     const uint32_t ksplit = SPLIT ? a.ksplit : 1u;  // the unsplit instantiation folds every K-range term away
     // per unit: num_k k-steps of 64 and `groups` scale groups; a row of the scale grid holds row_groups scales
-    const uint32_t row_groups = BITS == 4 ? a.K >> 7 : a.tc;
+    static_assert(GEN || BITS == 4, "int8 codes take the general issuer");
+    const uint32_t row_groups = GEN ? a.tc : a.K >> 7;
     const uint32_t num_k = BITS == 4 ? 2 * ((a.K >> 7) / ksplit) : (a.K >> 6) / ksplit;
-    const uint32_t groups = BITS == 4 ? num_k >> 1 : num_k * 4 / a.g16;
+    const uint32_t groups = GEN ? num_k * 4 / a.g16 : num_k >> 1;
     uint8_t* sA = smem;                  // [S][128 weight rows][128 B], unpacked bf16
     uint8_t* sX = sA + PF_S * PF_STAGE;  // [S][128 activation rows][128 B]
     uint8_t* sQ = sX + PF_S * PF_STAGE;  // [SQ][128 weight rows][64 B], packed codes
@@ -326,7 +330,7 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
             // from divergent code pays for moving each operand to the uniform registers); one elected
             // lane issues.  The next k-step's barrier is polled before this step's MMAs are issued, so the
             // poll's latency is hidden behind them.
-            if constexpr (BITS == 8) {
+            if constexpr (GEN) {
               if (rank == 0) {
                 // scale groups of g16 MMA steps, whatever their position in the k-steps: the accumulator changes
                 // where a group ends, and a k-step's stage is released after its fourth MMA
@@ -411,7 +415,7 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
             if (lane == 0) {
                 uint32_t sq = 0, pq = 0, qit = 0;
                 // a slot is 64 bytes of each row: one k-group of packed int4 (x in u32 words), one k-step of int8 (x in bytes)
-                const uint32_t slots = BITS == 4 ? groups : num_k, x_step = BITS == 4 ? 16u : 64u;
+                const uint32_t slots = BITS == 4 ? num_k >> 1 : num_k, x_step = BITS == 4 ? 16u : 64u;
                 for (uint32_t t = pair; t < tiles && !failed; t += pairs) {
                     const uint32_t tile = t / ksplit, g_first = (t % ksplit) * slots;
                     const int32_t q_row = (int32_t)((tile / m_tiles) * PF_TN + rank * 128);
@@ -523,7 +527,7 @@ __device__ __forceinline__ void gemm_codes_tc(uint8_t* smem_raw, const CUtensorM
             const uint32_t n_cta = (tile / m_tiles) * PF_TN + rank * 128, n = n_cta + ml;
             const uint32_t m0 = (tile % m_tiles) * PF_TM + half * 128;
             const bool n_ok = n < a.N;
-            const float* sp = a.scales + (uint64_t)(BITS == 4 ? (n_ok ? n : 0) : (n_ok ? n : 0) / a.gr) * row_groups + ks * groups;
+            const float* sp = a.scales + (uint64_t)(GEN ? (n_ok ? n : 0) / a.gr : (n_ok ? n : 0)) * row_groups + ks * groups;
             float total[128];
 #pragma unroll
             for (uint32_t i = 0; i < 128; i++) total[i] = 0.0f;
@@ -622,7 +626,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     k_gemm_i4_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
                  const __grid_constant__ CUtensorMap ymap, const PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    gemm_codes_tc<YT, SPLIT, 4>(smem_raw, xmap, qmap, ymap, a);
+    gemm_codes_tc<YT, SPLIT, 4, false>(smem_raw, xmap, qmap, ymap, a);
+}
+
+template <typename YT, bool SPLIT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
+    k_gemm_i4g_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
+                  const __grid_constant__ CUtensorMap ymap, const PrefillArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    gemm_codes_tc<YT, SPLIT, 4, true>(smem_raw, xmap, qmap, ymap, a);
 }
 
 template <typename YT, bool SPLIT>
@@ -630,7 +642,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, 1)
     k_gemm_w8_tc(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap qmap,
                  const __grid_constant__ CUtensorMap ymap, const PrefillArgs a) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    gemm_codes_tc<YT, SPLIT, 8>(smem_raw, xmap, qmap, ymap, a);
+    gemm_codes_tc<YT, SPLIT, 8, true>(smem_raw, xmap, qmap, ymap, a);
 }
 
 // Folds the K ranges' partial tiles: y[m, n] = sum_s ws[s, m, n] (+ bias[n]), four outputs per thread.
@@ -660,6 +672,9 @@ __global__ void __launch_bounds__(256) k_gemm_i4_fold(const float* __restrict__ 
 
 // ---- host side ------------------------------------------------------------------------------------
 
+// The int4 grid with a kernel instantiation of its own (a scale group is one 64-byte slot of codes).
+static bool int4_special(uint64_t gr, uint64_t gc) { return gr == 1 && gc == 128; }
+
 // K ranges per output tile: when the output has fewer 256 x 256 tiles than the device has SM pairs, the K loop is cut
 // into equal runs of whole scale groups (at least four each) so that the idle pairs take a share.
 static uint32_t gemm_i4_ksplit(uint64_t m, uint64_t out_dim, uint64_t in_dim, const void* bias) {
@@ -675,23 +690,29 @@ static uint32_t gemm_i4_ksplit(uint64_t m, uint64_t out_dim, uint64_t in_dim, co
 
 bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x) {
-    if (bits != 4 || gr != 1 || gc != 128 || layout != QB200_OUT_IN || x_dtype != QB200_BF16) return false;
+    if (bits != 4 || layout != QB200_OUT_IN || x_dtype != QB200_BF16 || gr == 0 || gr > 0x7FFFFFFF) return false;
     if (m == 0 || m > 0x7FFFFFFF || in_dim % 128 != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
+    if (!int4_special(gr, gc)) {
+        // other grids: tiles of whole 16-k steps that divide the row (or span it); decode batches keep the generic
+        // kernel, which streams the codes once where a 256-row MMA tile would idle on 16 activation rows
+        if (m <= 16 || (gc < in_dim && (gc % 16 != 0 || in_dim % gc != 0))) return false;
+    }
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     return al(codes) && al(x);
 }
 
-// int8 codes: a scale group's length in MMA steps of 16 k (a tile wider than the row is the whole row).
-static uint32_t gemm_i8_g16(uint64_t gc, uint64_t in_dim) { return (uint32_t)((gc >= in_dim ? in_dim : gc) / 16); }
+// General grids: a scale group's length in MMA steps of 16 k (a tile wider than the row is the whole row).
+static uint32_t gemm_gen_g16(uint64_t gc, uint64_t in_dim) { return (uint32_t)((gc >= in_dim ? in_dim : gc) / 16); }
 
-// The same for int8 codes: equal runs of whole k-steps (at least four each) that are also whole scale groups.
-static uint32_t gemm_i8_ksplit(uint64_t m, uint64_t out_dim, uint64_t in_dim, uint64_t gc, const void* bias) {
+// The same for general grids: equal runs of whole k-steps (at least four each; whole 128-k slots for int4 codes) that
+// are also whole scale groups.
+static uint32_t gemm_gen_ksplit(uint32_t bits, uint64_t m, uint64_t out_dim, uint64_t in_dim, uint64_t gc, const void* bias) {
     const uint64_t tiles = ((out_dim + PF_TN - 1) / PF_TN) * ((m + PF_TM - 1) / PF_TM), pairs = 74;
-    const uint32_t steps = (uint32_t)(in_dim / PF_BK), g16 = gemm_i8_g16(gc, in_dim);
+    const uint32_t steps = (uint32_t)(in_dim / PF_BK), g16 = gemm_gen_g16(gc, in_dim);
     if (tiles * 2 > pairs || out_dim % 4 != 0 || (bias && (reinterpret_cast<uintptr_t>(bias) & 15u))) return 1;
     uint32_t best = 1;
     for (uint32_t s = 2; s <= pairs / tiles && s <= steps / 4; s++)
-        if (steps % s == 0 && (steps / s * 4) % g16 == 0) best = s;
+        if (steps % s == 0 && (steps / s * 4) % g16 == 0 && (bits == 8 || (steps / s) % 2 == 0)) best = s;
     return best;
 }
 
@@ -705,13 +726,13 @@ bool gemm_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
 }
 
 uint64_t gemm_i8_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, uint64_t gc, const void* bias) {
-    const uint32_t ks = gemm_i8_ksplit(m, out_dim, in_dim, gc, bias);
+    const uint32_t ks = gemm_gen_ksplit(8, m, out_dim, in_dim, gc, bias);
     return ks > 1 ? (uint64_t)ks * m * out_dim * 4 : 0;
 }
 
 // Scratch: only the workspace of partial tiles when the K loop is split ([ksplit, m, out] f32).
-uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, const void* bias) {
-    const uint32_t ks = gemm_i4_ksplit(m, out_dim, in_dim, bias);
+uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, uint64_t gr, uint64_t gc, const void* bias) {
+    const uint32_t ks = int4_special(gr, gc) ? gemm_i4_ksplit(m, out_dim, in_dim, bias) : gemm_gen_ksplit(4, m, out_dim, in_dim, gc, bias);
     return ks > 1 ? (uint64_t)ks * m * out_dim * 4 : 0;
 }
 
@@ -731,23 +752,24 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// variant: 0 = int4 1x128, 1 = int4 general grid, 2 = int8
 template <typename YT, bool SPLIT>
-static qb200_status launch_prefill(uint32_t bits, uint32_t grid, const CUtensorMap& xmap, const CUtensorMap& qmap,
+static qb200_status launch_prefill(int variant, uint32_t grid, const CUtensorMap& xmap, const CUtensorMap& qmap,
                                    const CUtensorMap& ymap, const PrefillArgs& a, int dev, cudaStream_t st) {
-    static bool attr_set[2][64] = {};
-    if (!attr_set[bits == 8][dev & 63]) {
-        if (bits == 8) QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_w8_tc<YT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-        else QB_CUDA_TRY(cudaFuncSetAttribute(k_gemm_i4_tc<YT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
-        attr_set[bits == 8][dev & 63] = true;
+    static bool attr_set[3][64] = {};
+    auto kern = variant == 2 ? k_gemm_w8_tc<YT, SPLIT> : variant == 1 ? k_gemm_i4g_tc<YT, SPLIT> : k_gemm_i4_tc<YT, SPLIT>;
+    if (!attr_set[variant][dev & 63]) {
+        QB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM));
+        attr_set[variant][dev & 63] = true;
     }
-    if (bits == 8) k_gemm_w8_tc<YT, SPLIT><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
-    else k_gemm_i4_tc<YT, SPLIT><<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
+    kern<<<grid, PF_THREADS, PF_SMEM, st>>>(xmap, qmap, ymap, a);
     return QB200_OK;
 }
 
 static qb200_status gemm_tc_forward(const FwdArgs& f, uint32_t bits, int y_dtype, void* scratch, int32_t* status, cudaStream_t st) {
     const uint32_t M = (uint32_t)f.m, N = (uint32_t)f.out_dim, K = (uint32_t)f.in_dim;
-    const uint32_t ksplit = !scratch ? 1 : bits == 8 ? gemm_i8_ksplit(M, N, K, f.gc, f.bias) : gemm_i4_ksplit(M, N, K, f.bias);
+    const bool gen = bits == 8 || !int4_special(f.gr, f.gc);
+    const uint32_t ksplit = !scratch ? 1 : gen ? gemm_gen_ksplit(bits, M, N, K, f.gc, f.bias) : gemm_i4_ksplit(M, N, K, f.bias);
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(QB200_ERR_CUDA, "prefill GEMM: cuTensorMapEncodeTiled is not available from this driver");
     // activations as a [M, K] bf16 tensor: one box = 128 rows x 64 elements (one 128-byte swizzle row each)
@@ -801,7 +823,7 @@ static qb200_status gemm_tc_forward(const FwdArgs& f, uint32_t bits, int y_dtype
     a.K = K;
     a.gr = (uint32_t)f.gr;
     a.tc = (uint32_t)f.tc;
-    a.g16 = bits == 8 ? gemm_i8_g16(f.gc, K) : 8;
+    a.g16 = gen ? gemm_gen_g16(f.gc, K) : 8;
     int dev = 0;
     QB_CUDA_TRY(cudaGetDevice(&dev));
     static int sm_count[64] = {};
@@ -810,9 +832,10 @@ static qb200_status gemm_tc_forward(const FwdArgs& f, uint32_t bits, int y_dtype
     const uint32_t max_pairs = (uint32_t)sm_count[dev & 63] / 2;
     const uint32_t grid = 2 * (tiles < max_pairs ? tiles : max_pairs);  // one CTA per SM, in clusters of two
     qb200_status ls;
-    if (k_dtype != QB200_F32) ls = launch_prefill<uint16_t, false>(bits, grid, xmap, qmap, ymap, a, dev, st);
-    else if (ksplit > 1) ls = launch_prefill<float, true>(bits, grid, xmap, qmap, ymap, a, dev, st);
-    else ls = launch_prefill<float, false>(bits, grid, xmap, qmap, ymap, a, dev, st);
+    const int variant = bits == 8 ? 2 : gen ? 1 : 0;
+    if (k_dtype != QB200_F32) ls = launch_prefill<uint16_t, false>(variant, grid, xmap, qmap, ymap, a, dev, st);
+    else if (ksplit > 1) ls = launch_prefill<float, true>(variant, grid, xmap, qmap, ymap, a, dev, st);
+    else ls = launch_prefill<float, false>(variant, grid, xmap, qmap, ymap, a, dev, st);
     if (ls) return ls;
     QB_CUDA_TRY(cudaGetLastError());
     if (ksplit > 1) {

@@ -247,7 +247,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     if (ql->fast_view() && qb::gemm_i4_eligible(ql->bits, ql->fast_gr(), ql->fast_gc(), QB200_OUT_IN, ql->in_dim, ql->out_dim, m,
                                                 x_dtype, ql->fast_codes(), x_dev)) {
         // outputs with few tiles split the K loop over the idle SM pairs: partial tiles in the handle's scratch
-        const uint64_t need = qb::gemm_i4_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->bias);
+        const uint64_t need = qb::gemm_i4_scratch_bytes(m, ql->in_dim, ql->out_dim, ql->fast_gr(), ql->fast_gc(), ql->bias);
         if (need) {
             void* p = ql->scratch;
             qb200_status s = grow(&p, &ql->scratch_bytes, need, st);

@@ -446,6 +446,42 @@ def test_prefill_gemm_against_oracle(M, N, K):
     assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
 
 
+@pytest.mark.parametrize("M,N,K,gran,layout", [
+    (17, 256, 512, qb.Group(1, 64), qb.OUT_IN), (256, 1000, 1024, qb.Group(1, 32), qb.OUT_IN), (64, 130, 2048, qb.Group(1, 256), qb.OUT_IN),
+    (128, 384, 1024, qb.PerChannel(0), qb.OUT_IN), (40, 256, 256, qb.PerTensor(), qb.OUT_IN), (200, 300, 512, qb.Block(5, 16), qb.OUT_IN),
+    (96, 257, 384, qb.Group(1, 48), qb.OUT_IN), (300, 264, 1024, qb.Group(0, 64), qb.IN_OUT), (33, 520, 512, qb.Group(0, 256), qb.IN_OUT)])
+def test_int4_prefill_gemm_other_grids(M, N, K, gran, layout):
+    """int4 grids other than 1x128 whose tile width (along the inputs) is a whole number of 16-k MMA steps: the same tcgen05
+    kernel with an accumulator per scale group of that width; `[in, out]` weights through the transposed copy.  f64 checker
+    at 1e-3, one-hot activations bit for bit."""
+    rng = np.random.default_rng(M * 31 + N * 7 + K)
+    r, c = (N, K) if layout == qb.OUT_IN else (K, N)
+    w = (rng.standard_normal((r, c)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    gr, gc = gran.tile(r, c)
+    m, oc, os_ = quantize_both(w, r, c, qb.QuantDtype.Int4, gran)
+    wd = o.dequantize_host(oc, os_, r, c, 4, gr, gc)
+    xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+    xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, layout, threads=8)
+    ql = qb.QuantizedLinear.new(m, t(bias), layout)
+    y = ql.forward(xt, out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemm_tcgen05"
+    close(y.cpu().numpy(), want, 1e-3)
+    close(ql.forward(xt).to(torch.float32).cpu().numpy(), want, 1e-2)
+    ks = sorted(set(int(k) for k in rng.integers(0, K, 40)) | {0, 15, 16, 31, 32, 63, K - 1})[:48]
+    plain = qb.QuantizedLinear.new(m, None, layout)
+    y1 = plain.forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
+    assert plain.last_kernel() == "gemm_tcgen05"
+    ref = wd[:, ks].T.copy() if layout == qb.OUT_IN else wd[ks, :].copy()
+    assert (bits(y1.cpu().numpy()) == bits(ref)).all()
+    # a decode batch on such a grid keeps the generic kernel
+    plain.forward(xt[:4], out_dtype=torch.float32)
+    assert plain.last_kernel().startswith("generic")
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
 def test_prefill_gemm_config3_full_size_properties():
     """int4 prefill at the full workload size (X [2048, 4096], W [11008, 4096]): against an f32 matmul over the
     bit-exact dequantized weight, and linearity in x."""
