@@ -171,9 +171,9 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * transposed execution copy made at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
  * the tcgen05 GEMM (m > 16), which also takes the other int4 grids whose tile width along the inputs is a multiple of 16 that
  * divides in_dim or spans it (Group sizes 32, 64, 256 ..., per-row, per-tensor; `[in, out]` with such groups along axis 0
- * through the transposed copy); int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on its own
- * decode GEMV (m <= 16), and with in_dim a multiple of 64 and tiles of whole 16-column steps that divide in_dim (or span
- * it) on the same tcgen05 GEMM (m > 16); int8 `[in, out]` whose tile height is such a number through a transposed copy
+ * through the transposed copy) from m = 9; int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on
+ * its own decode GEMV (m <= 16, in_dim <= 4096), and with in_dim a multiple of 64 and tiles of whole 16-column steps that
+ * divide in_dim (or span it) on the same tcgen05 GEMM (from m = 5); int8 `[in, out]` whose tile height is such a number through a transposed copy
  * of codes and scale grid made at creation.  f32 activations (the reference's own dtype) whose layer has such a fast path
  * are split into three bf16 parts whose sum is the f32 exactly (x -> [3 m, in_dim], two small kernels and grow-only staging
  * in the handle), run on the bf16 kernel for 3 m rows, and the three partial outputs are added: exact products, f32

@@ -61,7 +61,7 @@ bool gemv_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
 qb200_status gemv_i8_forward_many(const FwdArgs* a, uint32_t count, int y_dtype, int32_t* status, cudaStream_t st);
 #endif
 // Prefill GEMM on tcgen05 (gemm_prefill.cu): int4, OUT_IN, bf16 x; the 1x128 grid at every m (asked after the decode GEMV),
-// other grids whose tile width is a multiple of 16 that divides in_dim (or covers the row) from m = 17.
+// other grids whose tile width is a multiple of 16 that divides in_dim (or covers the row) from m = 9.
 bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x);
 uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, uint64_t gr, uint64_t gc, const void* bias);
@@ -69,7 +69,7 @@ uint64_t gemm_i4_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, ui
 qb200_status gemm_i4_forward(const FwdArgs& a, int y_dtype, void* scratch, int32_t* status, cudaStream_t st);
 #endif
 // The same kernel over int8 codes: OUT_IN, bf16 x, in_dim a multiple of 64, any grid whose tile width is a multiple of
-// 16 that divides in_dim (or covers the row); asked after the int8 decode GEMV.
+// 16 that divides in_dim (or covers the row), from m = 5; asked after the int8 decode GEMV.
 bool gemm_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x);
 uint64_t gemm_i8_scratch_bytes(uint64_t m, uint64_t in_dim, uint64_t out_dim, uint64_t gc, const void* bias);

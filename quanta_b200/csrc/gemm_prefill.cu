@@ -693,9 +693,9 @@ bool gemm_i4_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, u
     if (bits != 4 || layout != QB200_OUT_IN || x_dtype != QB200_BF16 || gr == 0 || gr > 0x7FFFFFFF) return false;
     if (m == 0 || m > 0x7FFFFFFF || in_dim % 128 != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
     if (!int4_special(gr, gc)) {
-        // other grids: tiles of whole 16-k steps that divide the row (or span it); decode batches keep the generic
-        // kernel, which streams the codes once where a 256-row MMA tile would idle on 16 activation rows
-        if (m <= 16 || (gc < in_dim && (gc % 16 != 0 || in_dim % gc != 0))) return false;
+        // other grids: tiles of whole 16-k steps that divide the row (or span it); the smallest batches keep the generic
+        // kernel (one [4096, 4096] layer: 9 us at one row and 2 us more per row, against 18 - 29 us here at any batch)
+        if (m <= 8 || (gc < in_dim && (gc % 16 != 0 || in_dim % gc != 0))) return false;
     }
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     return al(codes) && al(x);
@@ -719,7 +719,8 @@ static uint32_t gemm_gen_ksplit(uint32_t bits, uint64_t m, uint64_t out_dim, uin
 bool gemm_i8_eligible(uint32_t bits, uint64_t gr, uint64_t gc, int32_t layout, uint64_t in_dim, uint64_t out_dim,
                       uint64_t m, int x_dtype, const void* codes, const void* x) {
     if (bits != 8 || layout != QB200_OUT_IN || x_dtype != QB200_BF16 || gr == 0 || gr > 0x7FFFFFFF) return false;
-    if (m == 0 || m > 0x7FFFFFFF || in_dim % PF_BK != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
+    // up to four rows the generic kernel is the faster one (the decode kernel takes what it can before this is asked)
+    if (m <= 4 || m > 0x7FFFFFFF || in_dim % PF_BK != 0 || in_dim > (1u << 20) || out_dim > 0x7FFFFFFF) return false;
     if (gc < in_dim && (gc % 16 != 0 || in_dim % gc != 0)) return false;  // whole groups of whole MMA steps
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     return al(codes) && al(x);

@@ -663,7 +663,7 @@ def test_in_out_int8_takes_the_fast_kernels_through_its_transposed_copy(K, N, gr
         xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
         want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.IN_OUT, threads=8)
         close(ql.forward(xt, out_dtype=torch.float32).cpu().numpy(), want, 1e-3)
-        assert not ql.last_kernel().startswith("generic") or not (decode or prefill)
+        assert not ql.last_kernel().startswith("generic") or not (decode or (prefill and M > 4))
     assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()   # the record itself is untouched
     from quanta_b200 import _lib
     assert _lib.load().qb200_qlinear_check(ql._h, None) == 0

@@ -45,7 +45,7 @@ def _static(ql, x, out_dtype):
 
 def test_static_forward_matches_the_ordinary_forward_twice_in_a_row():
     lib = _lib.load()
-    cases = [(4096, 256, qb.QuantDtype.Int4, qb.Group(0, 64)),    # small out, long K: K is split, scratch in use
+    cases = [(4096, 256, qb.QuantDtype.Int4, qb.Group(0, 40)),    # small out, long K: K is split, scratch in use (groups of 40: no fast kernel)
              (1024, 520, qb.QuantDtype.Int8, qb.Block(8, 8)),         # tiles no fast kernel takes: the ordinary forward is generic too
              (512, 4096, qb.QuantDtype.Int4, qb.Group(0, 8))]     # wide out: one slice, no scratch
     for in_dim, out_dim, dt, gran in cases:
