@@ -150,8 +150,8 @@ typedef struct qb200_qlinear qb200_qlinear;
  * Where the stored layout does not feed the fast kernels as it is, the handle builds an execution copy here (and
  * synchronises the device once): an int4 `[in, out]` weight with Group{axis: 0, size: 128} (or another multiple of 16 that
  * divides in_dim) is transposed to `[out, in]` with a 1x128 (1 x size) grid, an int4 weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode
- * kernel, and an int8 `[in, out]` weight whose tile height is a multiple of 16 (or the whole input width) is transposed
- * with its scale grid.  Each copy costs its codes again (0.5 or 1 byte per weight) plus its scales (and 16 rows of f32
+ * kernel (so is an int8 weight with tiles 32, 64 or 128 columns wide), and an int8 `[in, out]` weight whose tile height is
+ * a multiple of 16 (or the whole input width) is transposed with its scale grid.  Each copy costs its codes again (0.5 or 1 byte per weight) plus its scales (and 16 rows of f32
  * partial outputs per slice); the caller's buffers stay the record. */
 QB200_API qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev, uint64_t rows,
                                   uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc,
@@ -172,7 +172,7 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * the tcgen05 GEMM (m > 16), which also takes the other int4 grids whose tile width along the inputs is a multiple of 16 that
  * divides in_dim or spans it (Group sizes 32, 64, 256 ..., per-row, per-tensor; `[in, out]` with such groups along axis 0
  * through the transposed copy) from m = 9; int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on
- * its own decode GEMV (m <= 16, in_dim <= 4096), and with in_dim a multiple of 64 and tiles of whole 16-column steps that
+ * its own decode GEMV (m <= 16; inputs wider than 4096 as column slices when the tiles are 32, 64 or 128 columns wide), and with in_dim a multiple of 64 and tiles of whole 16-column steps that
  * divide in_dim (or span it) on the same tcgen05 GEMM (from m = 5); int8 `[in, out]` whose tile height is such a number through a transposed copy
  * of codes and scale grid made at creation.  f32 activations (the reference's own dtype) whose layer has such a fast path
  * are split into three bf16 parts whose sum is the f32 exactly (x -> [3 m, in_dim], two small kernels and grow-only staging
@@ -368,7 +368,7 @@ QB200_API qb200_status qb200_qlinear_forward_host(qb200_qlinear* ql, const void*
 
 /* Name of the kernel family the last forward on this handle dispatched to: "gemv_mma" (int4 decode), "gemv_mma_grouped",
  * "gemv_mma_sliced" (inputs wider than 4096), "gemv_mma_grouped_gather" / "gemv_mma_grouped_push" (fused exchanges),
- * "gemv_mma_i8", "gemv_mma_i8_grouped", "gemv_mma_i8_x2" (int8 decode), "gemm_tcgen05" (int4 prefill), "gemm_tcgen05_i8" (int8 prefill), "generic_rows",
+ * "gemv_mma_i8", "gemv_mma_i8_grouped", "gemv_mma_i8_x2", "gemv_mma_i8_sliced" (int8 decode), "gemm_tcgen05" (int4 prefill), "gemm_tcgen05_i8" (int8 prefill), "generic_rows",
  * "generic_cols". */
 QB200_API const char* qb200_qlinear_last_kernel(const qb200_qlinear* ql);
 

@@ -15,7 +15,8 @@
 //
 // The int8 kernels read `[out, in]` bytes with a grid whose tile width is a whole number of 16-column steps: an
 // `[in, out]` int8 weight whose tile HEIGHT is such a number (32 x 32 blocks, Group{axis: 0, size: 128}, per-column
-// scales) gets a transposed copy of codes and scale grid as well (+ 1 byte per weight).
+// scales) gets a transposed copy of codes and scale grid as well (+ 1 byte per weight), and an int8 weight with more
+// than 4096 inputs whose tiles are 32, 64 or 128 columns wide gets column slices like the int4 ones.
 #include <cstdint>
 #include <string>
 
@@ -89,22 +90,54 @@ void free_exec_layout(qb200_qlinear* ql) {
 
 qb200_status build_exec_layout(qb200_qlinear* ql) {
     if (ql->bits == 8) {
-        if (ql->layout != QB200_IN_OUT || ql->in_dim == 0 || ql->out_dim == 0 || ql->in_dim > 0x7FFFFFFFull || ql->out_dim > 0x7FFFFFFFull)
-            return QB200_OK;
-        if (ql->gr < ql->in_dim && ql->gr % 16 != 0) return QB200_OK;  // the tile height becomes the tile width
+        if (ql->in_dim == 0 || ql->out_dim == 0 || ql->in_dim > 0x7FFFFFFFull || ql->out_dim > 0x7FFFFFFFull) return QB200_OK;
         const uint32_t K = (uint32_t)ql->in_dim, N = (uint32_t)ql->out_dim;
-        const uint64_t tr = (ql->in_dim + ql->gr - 1) / ql->gr;  // the stored grid is [tr, tc]; the copy's [tc, tr]
-        if (tr > 0x7FFFFFFFull || ql->tc > 0x7FFFFFFFull || (K + 63) / 64 > 65535u || tr > 65535u) return QB200_OK;
-        QB_CUDA_TRY(cudaMalloc(&ql->t_codes, (uint64_t)N * K));
-        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, tr * ql->tc * 4));
-        k_transpose_i8<<<dim3((N + 63) / 64, (K + 63) / 64), 256>>>(static_cast<const uint8_t*>(ql->codes), K, N,
-                                                                     static_cast<uint8_t*>(ql->t_codes));
-        QB_CUDA_TRY(cudaGetLastError());
-        k_transpose_f32<<<dim3(((uint32_t)ql->tc + 255) / 256, (uint32_t)tr), 256>>>(ql->scales, (uint32_t)tr, (uint32_t)ql->tc, ql->t_scales);
-        QB_CUDA_TRY(cudaGetLastError());
-        ql->t_gr = ql->gc;
-        ql->t_gc = ql->gr;
-        ql->t_tc = tr;
+        if (ql->layout == QB200_IN_OUT) {
+            if (ql->gr < ql->in_dim && ql->gr % 16 != 0) return QB200_OK;  // the tile height becomes the tile width
+            const uint64_t tr = (ql->in_dim + ql->gr - 1) / ql->gr;  // the stored grid is [tr, tc]; the copy's [tc, tr]
+            if (tr > 0x7FFFFFFFull || ql->tc > 0x7FFFFFFFull || (K + 63) / 64 > 65535u || tr > 65535u) return QB200_OK;
+            QB_CUDA_TRY(cudaMalloc(&ql->t_codes, (uint64_t)N * K));
+            QB_CUDA_TRY(cudaMalloc(&ql->t_scales, tr * ql->tc * 4));
+            k_transpose_i8<<<dim3((N + 63) / 64, (K + 63) / 64), 256>>>(static_cast<const uint8_t*>(ql->codes), K, N,
+                                                                         static_cast<uint8_t*>(ql->t_codes));
+            QB_CUDA_TRY(cudaGetLastError());
+            k_transpose_f32<<<dim3(((uint32_t)ql->tc + 255) / 256, (uint32_t)tr), 256>>>(ql->scales, (uint32_t)tr, (uint32_t)ql->tc, ql->t_scales);
+            QB_CUDA_TRY(cudaGetLastError());
+            ql->t_gr = ql->gc;
+            ql->t_gc = ql->gr;
+            ql->t_tc = tr;
+        }
+        // inputs wider than the int8 decode kernel keeps in registers: column slices of whole 128-column runs, like the
+        // int4 ones (+ 1 byte per weight), for grids whose tile width divides 128
+        const uint32_t gc = (uint32_t)(ql->fast_gc() > 0xFFFFFFFFull ? 0 : ql->fast_gc()), gr = (uint32_t)(ql->fast_gr() > 0xFFFFFFFFull ? 0 : ql->fast_gr());
+        if (K > SLICE_LIMIT && K % 128 == 0 && K <= SLICE_LIMIT * SLICE_MAX && gr != 0 && (gc == 32 || gc == 64 || gc == 128)) {
+            const uint32_t groups = K / 128, n = (K + SLICE_LIMIT - 1) / SLICE_LIMIT, base = groups / n, extra = groups % n;
+            const uint32_t tr = (N + gr - 1) / gr, tc = (uint32_t)ql->fast_tc();
+            uint32_t widest = 0, c0 = 0;
+            for (uint32_t s = 0; s < n; s++) {
+                ql->slice_col0[s] = c0;
+                ql->slice_width[s] = (base + (s < extra ? 1u : 0u)) * 128;
+                c0 += ql->slice_width[s];
+                widest = widest > ql->slice_width[s] ? widest : ql->slice_width[s];
+            }
+            const uint32_t pad = (widest + 511) / 512 * 512;  // rows of scales that are whole 16-byte units
+            const uint64_t cbytes = (uint64_t)n * N * pad, sbytes = (uint64_t)n * tr * (pad / gc) * 4;
+            QB_CUDA_TRY(cudaMalloc(&ql->slice_codes, cbytes));
+            QB_CUDA_TRY(cudaMalloc(&ql->slice_scales, sbytes));
+            QB_CUDA_TRY(cudaMalloc(&ql->slice_partials, (uint64_t)n * 16 * N * 4));
+            QB_CUDA_TRY(cudaMemset(ql->slice_codes, 0, cbytes));
+            QB_CUDA_TRY(cudaMemset(ql->slice_scales, 0, sbytes));
+            const uint8_t* codes = static_cast<const uint8_t*>(ql->fast_codes());
+            const float* scales = ql->fast_scales();
+            for (uint32_t s = 0; s < n; s++) {
+                QB_CUDA_TRY(cudaMemcpy2D(static_cast<uint8_t*>(ql->slice_codes) + (uint64_t)s * N * pad, pad, codes + ql->slice_col0[s], K,
+                                         ql->slice_width[s], N, cudaMemcpyDeviceToDevice));
+                QB_CUDA_TRY(cudaMemcpy2D(ql->slice_scales + (uint64_t)s * tr * (pad / gc), (pad / gc) * 4, scales + ql->slice_col0[s] / gc,
+                                         (uint64_t)tc * 4, (ql->slice_width[s] / gc) * 4, tr, cudaMemcpyDeviceToDevice));
+            }
+            ql->n_slices = n;
+            ql->slice_pad = pad;
+        }
         QB_CUDA_TRY(cudaDeviceSynchronize());
         return QB200_OK;
     }
@@ -169,23 +202,31 @@ qb200_status build_exec_layout(qb200_qlinear* ql) {
 
 qb200_status forward_sliced(qb200_qlinear* ql, const void* x, uint64_t m, void* y, int y_dtype, cudaStream_t st) {
     const uint32_t n = ql->n_slices, pad = ql->slice_pad, N = (uint32_t)ql->out_dim;
-    FwdArgs a[SLICE_MAX];
-    for (uint32_t s = 0; s < n; s++) {
-        a[s].codes = static_cast<const uint8_t*>(ql->slice_codes) + (uint64_t)s * N * (pad / 2);
-        a[s].scales = ql->slice_scales + (uint64_t)s * N * (pad / 128);
-        a[s].bias = nullptr;  // added once, by the fold
-        a[s].x = static_cast<const uint16_t*>(x) + ql->slice_col0[s];
-        a[s].y = ql->slice_partials + (uint64_t)s * m * N;
-        a[s].m = m;
-        a[s].in_dim = pad;
-        a[s].out_dim = N;
-        a[s].gr = 1;
-        a[s].gc = 128;
-        a[s].tc = pad / 128;
-        a[s].x_stride = ql->in_dim;
-        a[s].k_valid = ql->slice_width[s];
+    const bool i8 = ql->bits == 8;
+    const uint32_t gr = i8 ? (uint32_t)ql->fast_gr() : 1, gc = i8 ? (uint32_t)ql->fast_gc() : 128, tr = (N + gr - 1) / gr;
+    const uint64_t slice_code_bytes = i8 ? (uint64_t)N * pad : (uint64_t)N * (pad / 2);
+    // the int8 kernel keeps eight batch rows in registers: a batch of 9..16 is two launches over the slices
+    for (uint64_t r0 = 0; r0 < m; r0 += i8 ? 8 : 16) {
+        const uint64_t mr = i8 && m - r0 > 8 ? 8 : m - r0;
+        FwdArgs a[SLICE_MAX];
+        for (uint32_t s = 0; s < n; s++) {
+            a[s].codes = static_cast<const uint8_t*>(ql->slice_codes) + s * slice_code_bytes;
+            a[s].scales = ql->slice_scales + (uint64_t)s * tr * (pad / gc);
+            a[s].bias = nullptr;  // added once, by the fold
+            a[s].x = static_cast<const uint16_t*>(x) + r0 * ql->in_dim + ql->slice_col0[s];
+            a[s].y = ql->slice_partials + ((uint64_t)s * m + r0) * N;
+            a[s].m = mr;
+            a[s].in_dim = pad;
+            a[s].out_dim = N;
+            a[s].gr = gr;
+            a[s].gc = gc;
+            a[s].tc = pad / gc;
+            a[s].x_stride = ql->in_dim;
+            a[s].k_valid = ql->slice_width[s];
+        }
+        const qb200_status r = i8 ? gemv_i8_forward_many(a, n, QB200_F32, ql->status, st) : gemv_i4_forward_many(a, n, QB200_F32, ql->status, st);
+        if (r) return r;
     }
-    if (qb200_status r = gemv_i4_forward_many(a, n, QB200_F32, ql->status, st)) return r;
     const uint64_t mn = m * N;
     const uint32_t blocks = (uint32_t)((mn + 255) / 256 > 592 ? 592 : (mn + 255) / 256);
     if (y_dtype == QB200_F32)

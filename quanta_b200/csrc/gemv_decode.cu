@@ -355,6 +355,7 @@ qb200_status gemv_i8_forward_many(const FwdArgs* f, uint32_t count, int y_dtype,
         ly.gc = (uint32_t)(a.gc > 0xFFFFFFFFull ? 0xFFFFFFFFull : a.gc);
         ly.tc = (uint32_t)a.tc;
         ly.ldx = a.x_stride ? (uint32_t)a.x_stride : K;
+        ly.kvalid = a.k_valid ? (uint32_t)a.k_valid : K;
         items += (ly.N + rpi - 1) / rpi;
         // scale rows an item of rpi rows can span, and whether every item's scale rows start on a 16-byte boundary
         const uint32_t span = ly.gr >= rpi ? 2 : (rpi + ly.gr - 1) / ly.gr + 1;

@@ -29,7 +29,7 @@ struct GemvLayerI8 {
     void* y;                // [M, N] f32 or bf16
     uint32_t N, rows_per_item, item0;
     uint32_t gr, gc, tc;    // scale tile and the row length of the scale grid
-    uint32_t ldx;
+    uint32_t ldx, kvalid;   // x's row stride; columns >= kvalid of x do not exist and read as zero (a multiple of 32)
 };
 constexpr int I8_MAX_LAYERS = 32;
 struct GemvBatchI8 {
@@ -74,14 +74,14 @@ __host__ __device__ inline I8Smem i8_smem_layout(uint32_t K, uint32_t red_stride
 // Activation fragment of one 128-column group for batch row b: this lane's 8 consecutive columns of each of the four
 // 32-column runs, ordered as the two MMAs of a run want them ({k0, k2}, {k1, k3}, {k4, k6}, {k5, k7}), scaled by 2^40;
 // sums[j] receives the plain sum of the lane's 8 activations of run j.
-__device__ __forceinline__ void load_fragment_i8(const uint16_t* __restrict__ x, uint32_t ldx, uint32_t b, uint32_t G, uint32_t t,
-                                                 bool valid, uint4 (&frag)[4], float (&sums)[4], bool& out_of_domain) {
+__device__ __forceinline__ void load_fragment_i8(const uint16_t* __restrict__ x, uint32_t ldx, uint32_t kvalid, uint32_t b, uint32_t G,
+                                                 uint32_t t, bool valid, uint4 (&frag)[4], float (&sums)[4], bool& out_of_domain) {
     uint32_t klo = X_SCALE_LO;
     const __nv_bfloat162 s40 = *reinterpret_cast<const __nv_bfloat162*>(&klo);
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         uint4 v = make_uint4(0, 0, 0, 0);  // 8 consecutive bf16
-        if (valid) v = __ldg(reinterpret_cast<const uint4*>(x + (uint64_t)b * ldx + G * 128 + j * 32 + t * 8));
+        if (valid && G * 128 + j * 32 < kvalid) v = __ldg(reinterpret_cast<const uint4*>(x + (uint64_t)b * ldx + G * 128 + j * 32 + t * 8));
         const uint32_t xr[4] = {v.x, v.y, v.z, v.w};
         float sum = 0.0f;
         uint32_t top = 0;
@@ -236,8 +236,8 @@ __global__ void __launch_bounds__(REG_THREADS + 32 * NSERV, 1) k_gemv_i8_async(c
                 cur_x = it.x;
                 bool ood = false;
                 float sa[4], sb[4];
-                load_fragment_i8(cur_x, ly.ldx, g, Ga, t, v0 && g < a.M, fa, sa, ood);
-                load_fragment_i8(cur_x, ly.ldx, g, Gb, t, v1 && g < a.M, fb, sb, ood);
+                load_fragment_i8(cur_x, ly.ldx, ly.kvalid, g, Ga, t, v0 && g < a.M, fa, sa, ood);
+                load_fragment_i8(cur_x, ly.ldx, ly.kvalid, g, Gb, t, v1 && g < a.M, fb, sb, ood);
 #pragma unroll
                 for (int r = 0; r < 4; r++) {
                     float s0 = sa[r], s1 = sb[r];

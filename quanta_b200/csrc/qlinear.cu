@@ -240,7 +240,7 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
     if (ql->n_slices && m <= 16 && x_dtype == QB200_BF16 && (reinterpret_cast<uintptr_t>(x_dev) & 15u) == 0) {
         qb200_status s = qb::forward_sliced(ql, x_dev, m, y_dev, y_dtype, st);
         if (s != QB200_ERR_NOT_SUPPORTED) {
-            ql->last_kernel = "gemv_mma_sliced";
+            ql->last_kernel = ql->bits == 8 ? "gemv_mma_i8_sliced" : "gemv_mma_sliced";
             return s;
         }
     }

@@ -37,8 +37,8 @@ struct qb200_qlinear {
     void* t_codes = nullptr;
     float* t_scales = nullptr;
     uint64_t t_gr = 0, t_gc = 0, t_tc = 0;
-    void* slice_codes = nullptr;     // [n_slices][out_dim][slice_pad / 8] u32
-    float* slice_scales = nullptr;   // [n_slices][out_dim][slice_pad / 128]
+    void* slice_codes = nullptr;     // [n_slices][out_dim][slice_pad / 8] u32 (int8: [n_slices][out_dim][slice_pad] bytes)
+    float* slice_scales = nullptr;   // [n_slices][out_dim][slice_pad / 128] (int8: [n_slices][ceil(out_dim / gr)][slice_pad / gc])
     float* slice_partials = nullptr; // [n_slices][16][out_dim] f32: the slices' partial outputs of one decode call
     uint32_t n_slices = 0, slice_pad = 0;
     uint32_t slice_col0[8] = {}, slice_width[8] = {};

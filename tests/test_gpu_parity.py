@@ -696,6 +696,40 @@ def test_sliced_decode_of_a_wide_layer_matches_per_slice_sums():
     assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
 
 
+@pytest.mark.parametrize("gran,layout", [(qb.Block(32, 32), qb.OUT_IN), (qb.Group(1, 128), qb.OUT_IN), (qb.Block(32, 32), qb.IN_OUT)])
+def test_int8_sliced_decode_of_a_wide_layer(gran, layout):
+    """An int8 layer with 11008 inputs at M <= 16: three column slices in one launch (two launches for 9..16 rows) plus
+    the fold; one-hot activations at the slices' edges bit for bit; f32 activations as three parts."""
+    rng = np.random.default_rng(13)
+    N, K = 392, 11008
+    r, c = (N, K) if layout == qb.OUT_IN else (K, N)
+    w = (rng.standard_normal((r, c)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    gr, gc = gran.tile(r, c)
+    m, oc, os_ = quantize_both(w, r, c, qb.QuantDtype.Int8, gran)
+    wd = o.dequantize_host(oc, os_, r, c, 8, gr, gc)
+    ql = qb.QuantizedLinear.new(m, t(bias), layout)
+    ks = [0, 3711, 3712, 7423, 7424, 11007, 5000, 1]    # first and last column of every slice
+    y = ql.forward(_one_hot_rows(ks, K), out_dtype=torch.float32)
+    assert ql.last_kernel() == "gemv_mma_i8_sliced"
+    want = (wd[:, ks].T if layout == qb.OUT_IN else wd[ks, :]) + bias[None, :]
+    assert (bits(y.cpu().numpy()) == bits(want.astype(np.float32))).all()
+    for M in (1, 7, 8, 12, 16):
+        xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+        want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, layout, threads=8)
+        yd = ql.forward(xt, out_dtype=torch.float32).cpu().numpy()
+        assert ql.last_kernel() == "gemv_mma_i8_sliced"
+        close(yd, want, 1e-4)
+        close(ql.forward(xt).to(torch.float32).cpu().numpy(), want, 1e-2)
+    xf = rng.standard_normal((2, K)).astype(np.float32)
+    yf = ql.forward(t(xf), out_dtype=torch.float32).cpu().numpy()
+    assert ql.last_kernel() == "gemv_mma_i8_sliced"
+    close(yf, o.linear_forward_f64(xf, wd, bias, layout, threads=8), 1e-5)
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
 def test_decode_domain_limit_is_checked():
     """The decode kernel scales activations by 2^40 inside bf16: |x| < 2^87 is its domain.  Just inside, the result
     matches the oracle; at 2^87 and for non-finite activations the call is flagged and qb200_qlinear_check reports
