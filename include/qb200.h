@@ -177,7 +177,8 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * of codes and scale grid made at creation.  f32 activations (the reference's own dtype) whose layer has such a fast path
  * are split into three bf16 parts whose sum is the f32 exactly (x -> [3 m, in_dim], two small kernels and grow-only staging
  * in the handle), run on the bf16 kernel for 3 m rows, and the three partial outputs are added: exact products, f32
- * accumulation.  Everything else (other grids and layouts) runs on the generic kernels.
+ * accumulation (calls of fewer than 2^24 multiply-adds keep the generic kernel's single launch; QB200_F32_SPLIT=0 in the
+ * environment keeps every f32 call there).  Everything else (other grids and layouts) runs on the generic kernels.
  * A call whose scratch is not allocated yet (the GEMM's split-K workspace, the generic column kernel's partial sums)
  * allocates it; on a stream that is recording a CUDA graph that is refused with QB200_ERR_INVALID_PARAM — run the shape
  * once before capturing.  The decode GEMVs need finite activations with |x| < 2^87 (see qb200_qlinear_check). */

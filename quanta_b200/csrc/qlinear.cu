@@ -3,6 +3,7 @@
 // selection per forward (the body of Layer::apply, quant.rs:903-918).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -195,7 +196,11 @@ qb200_status qb200_qlinear_forward(qb200_qlinear* ql, const void* x_dev, int32_t
         return fail(QB200_ERR_INVALID_PARAM, "qb200_qlinear_forward: activations are f32 or bf16");
     if (m == 0) return QB200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x_dtype == QB200_F32 && m <= 0x7FFFFFFFull / 3 && bf16_fast(ql, 3 * m)) {
+    static const bool split_f32 = [] { const char* e = getenv("QB200_F32_SPLIT"); return !(e && e[0] == '0'); }();
+    // (small layers at small batches stay on the generic kernel: one launch of a few microseconds beats the split's three;
+    // measured, one layer per launch: [1024, 1024] at 8 rows 9 us generic against 15 us split, [4096, 4096] at one row a
+    // tie at 10 us, at 8 rows 58 us against 20 us)
+    if (x_dtype == QB200_F32 && split_f32 && m <= 0x7FFFFFFFull / 3 && m * ql->in_dim * ql->out_dim >= (1ull << 24) && bf16_fast(ql, 3 * m)) {
         // f32 activations (the reference's own dtype) on the bf16 kernels: x is the exact sum of three bf16 parts, the
         // kernels' products are exact, so three times the rows and one fold give the exact-product result
         const uint64_t xs_bytes = (3 * m * ql->in_dim * 2 + 255) & ~uint64_t(255);
