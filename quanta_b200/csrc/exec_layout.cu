@@ -64,6 +64,15 @@ __global__ void __launch_bounds__(256) k_transpose_f32(const float* __restrict__
     if (c < cols) dst[(uint64_t)c * rows + r] = src[(uint64_t)r * cols + c];
 }
 
+// dst[n][g] = src[n / gr][(128 g) / gc]: a grid whose scale is constant over whole 128-column runs, as a 1 x 128 grid.
+__global__ void __launch_bounds__(256) k_expand_scales(const float* __restrict__ src, uint32_t src_tc, uint32_t gr, uint64_t gc, uint32_t N,
+                                                       uint32_t groups, float* __restrict__ dst) {
+    const uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)N * groups) return;
+    const uint32_t n = (uint32_t)(i / groups), g = (uint32_t)(i % groups);
+    dst[i] = src[(uint64_t)(n / gr) * src_tc + (uint32_t)((uint64_t)g * 128 / gc)];
+}
+
 // y[i] = sum_s parts[s][i] (+ bias[i % N]): the slices' partial outputs, summed in slice order.
 template <typename YT>
 __global__ void __launch_bounds__(256) k_fold_slices(const float* __restrict__ parts, uint32_t slices, uint64_t mn, uint32_t N,
@@ -80,6 +89,8 @@ __global__ void __launch_bounds__(256) k_fold_slices(const float* __restrict__ p
 void free_exec_layout(qb200_qlinear* ql) {
     if (ql->t_codes) cudaFree(ql->t_codes);
     if (ql->t_scales) cudaFree(ql->t_scales);
+    if (ql->x_scales) cudaFree(ql->x_scales);
+    ql->x_scales = nullptr;
     if (ql->slice_codes) cudaFree(ql->slice_codes);
     if (ql->slice_scales) cudaFree(ql->slice_scales);
     if (ql->slice_partials) cudaFree(ql->slice_partials);
@@ -146,27 +157,37 @@ qb200_status build_exec_layout(qb200_qlinear* ql) {
         return QB200_OK;
     const uint32_t K = (uint32_t)ql->in_dim, N = (uint32_t)ql->out_dim, groups = K / 128;
     if (ql->layout == QB200_IN_OUT) {
-        // groups along the inputs, one scale per output column: Group{axis: 0, size: 128} is the documented grid (decode
-        // and prefill kernels); other sizes of whole 16-row steps that divide the inputs reach the prefill kernel
-        if (ql->gc != 1 || ql->gr % 16 != 0 || ql->gr > K || K % ql->gr != 0) return QB200_OK;
-        const uint32_t tr = K / (uint32_t)ql->gr;
-        if (tr > 65535u) return QB200_OK;
+        // the transposed copy's tiles are the stored tiles turned: a tile HEIGHT of whole 16-row steps that divides the
+        // inputs (or spans them) becomes a tile width the kernels take.  Group{axis: 0, size: 128} is the documented grid.
+        if (ql->gr < K && (ql->gr % 16 != 0 || K % ql->gr != 0)) return QB200_OK;
+        const uint64_t tr = (K + ql->gr - 1) / ql->gr;
+        if (tr > 65535u || ql->tc > 0x7FFFFFFFull) return QB200_OK;
         QB_CUDA_TRY(cudaMalloc(&ql->t_codes, (uint64_t)N * (K / 8) * 4));
-        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, (uint64_t)N * tr * 4));
+        QB_CUDA_TRY(cudaMalloc(&ql->t_scales, tr * ql->tc * 4));
         k_transpose_i4<<<dim3((N + 255) / 256, K / 8), 256>>>(static_cast<const uint32_t*>(ql->codes), K, N, (N + 7) / 8,
                                                                static_cast<uint32_t*>(ql->t_codes));
         QB_CUDA_TRY(cudaGetLastError());
-        k_transpose_f32<<<dim3((N + 255) / 256, tr), 256>>>(ql->scales, tr, N, ql->t_scales);
+        k_transpose_f32<<<dim3(((uint32_t)ql->tc + 255) / 256, (uint32_t)tr), 256>>>(ql->scales, (uint32_t)tr, (uint32_t)ql->tc, ql->t_scales);
         QB_CUDA_TRY(cudaGetLastError());
-        ql->t_gr = 1;
+        ql->t_gr = ql->gc;
         ql->t_gc = ql->gr;
         ql->t_tc = tr;
-        if (ql->gr != 128) {
+    }
+    if (ql->fast_gr() != 1 || ql->fast_gc() != 128) {
+        // a scale that is constant over whole 128-column runs (tile widths that are multiples of 128, per-row and
+        // per-tensor scales): spelt out per run, the grid is 1 x 128 and every kernel of that grid serves it
+        const uint64_t vgr = ql->fast_gr(), vgc = ql->fast_gc();
+        if (vgr == 0 || vgr > 0x7FFFFFFFull || (vgc < K && vgc % 128 != 0)) {
             QB_CUDA_TRY(cudaDeviceSynchronize());
-            return QB200_OK;
+            return QB200_OK;  // other grids: the prefill kernel's general issuer, the generic kernels
         }
-    } else if (ql->gr != 1 || ql->gc != 128) {
-        return QB200_OK;
+        float* xs = nullptr;
+        QB_CUDA_TRY(cudaMalloc(&xs, (uint64_t)N * groups * 4));
+        const uint64_t total = (uint64_t)N * groups;
+        k_expand_scales<<<(uint32_t)((total + 255) / 256), 256>>>(ql->fast_scales(), (uint32_t)ql->fast_tc(), (uint32_t)vgr, vgc, N, groups, xs);
+        QB_CUDA_TRY(cudaGetLastError());
+        QB_CUDA_TRY(cudaDeviceSynchronize());
+        ql->x_scales = xs;  // from here on the view is 1 x 128
     }
     if (K > SLICE_LIMIT) {
         const uint32_t n = (K + SLICE_LIMIT - 1) / SLICE_LIMIT, base = groups / n, extra = groups % n;

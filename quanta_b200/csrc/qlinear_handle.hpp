@@ -34,9 +34,13 @@ struct qb200_qlinear {
     //     per row; a permutation of the codes and of the scales);
     //   slices: inputs wider than the decode kernel keeps in registers (4096) cut into `n_slices` column runs of whole
     //     scale groups, each padded with zero codes and zero scales to `slice_pad` columns, rows contiguous.
+    //   x_scales: an int4 grid whose scale is constant over whole 128-column runs (tile widths that are multiples of 128,
+    //     per-row and per-tensor scales) spelt out as a 1 x 128 grid `[out_dim][in_dim / 128]`, so that the 1 x 128
+    //     kernels serve it: the same scale multiplies the same codes.
     void* t_codes = nullptr;
     float* t_scales = nullptr;
     uint64_t t_gr = 0, t_gc = 0, t_tc = 0;
+    float* x_scales = nullptr;
     void* slice_codes = nullptr;     // [n_slices][out_dim][slice_pad / 8] u32 (int8: [n_slices][out_dim][slice_pad] bytes)
     float* slice_scales = nullptr;   // [n_slices][out_dim][slice_pad / 128] (int8: [n_slices][ceil(out_dim / gr)][slice_pad / gc])
     float* slice_partials = nullptr; // [n_slices][16][out_dim] f32: the slices' partial outputs of one decode call
@@ -48,10 +52,10 @@ struct qb200_qlinear {
     // what the fast kernels read: the transposed copy when there is one, else the stored buffers
     bool fast_view() const { return t_codes != nullptr || layout == QB200_OUT_IN; }
     const void* fast_codes() const { return t_codes ? t_codes : codes; }
-    const float* fast_scales() const { return t_codes ? t_scales : scales; }
-    uint64_t fast_gr() const { return t_codes ? t_gr : gr; }
-    uint64_t fast_gc() const { return t_codes ? t_gc : gc; }
-    uint64_t fast_tc() const { return t_codes ? t_tc : tc; }
+    const float* fast_scales() const { return x_scales ? x_scales : t_codes ? t_scales : scales; }
+    uint64_t fast_gr() const { return x_scales ? 1 : t_codes ? t_gr : gr; }
+    uint64_t fast_gc() const { return x_scales ? 128 : t_codes ? t_gc : gc; }
+    uint64_t fast_tc() const { return x_scales ? in_dim / 128 : t_codes ? t_tc : tc; }
 };
 
 namespace qb {

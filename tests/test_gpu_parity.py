@@ -475,9 +475,15 @@ def test_int4_prefill_gemm_other_grids(M, N, K, gran, layout):
     assert plain.last_kernel() == "gemm_tcgen05"
     ref = wd[:, ks].T.copy() if layout == qb.OUT_IN else wd[ks, :].copy()
     assert (bits(y1.cpu().numpy()) == bits(ref)).all()
-    # a decode batch on such a grid keeps the generic kernel
-    plain.forward(xt[:4], out_dtype=torch.float32)
-    assert plain.last_kernel().startswith("generic")
+    # a decode batch: grids whose scale is constant over whole 128-column runs are served as 1 x 128 (the decode kernel),
+    # the others keep the generic kernel
+    vgc = gc if layout == qb.OUT_IN else gr      # tile width along the inputs
+    y4 = plain.forward(xt[:4], out_dtype=torch.float32)
+    if vgc % 128 == 0 or vgc >= K:
+        assert plain.last_kernel() == "gemv_mma", gran
+    else:
+        assert plain.last_kernel().startswith("generic"), gran
+    close(y4.cpu().numpy(), want[:4] - bias[None, :], 1e-4)
     from quanta_b200 import _lib
     assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
 
@@ -665,6 +671,41 @@ def test_in_out_int8_takes_the_fast_kernels_through_its_transposed_copy(K, N, gr
         want = o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, o.IN_OUT, threads=8)
         close(ql.forward(xt, out_dtype=torch.float32).cpu().numpy(), want, 1e-3)
         assert not ql.last_kernel().startswith("generic") or not (decode or (prefill and M > 4))
+    assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()   # the record itself is untouched
+    from quanta_b200 import _lib
+    assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
+
+
+@pytest.mark.parametrize("N,K,gran,layout", [
+    (1000, 1024, qb.PerChannel(0), qb.OUT_IN), (264, 2048, qb.PerTensor(), qb.OUT_IN), (130, 1024, qb.Group(1, 256), qb.OUT_IN),
+    (300, 512, qb.Block(4, 128), qb.OUT_IN), (520, 1024, qb.PerChannel(1), qb.IN_OUT), (136, 512, qb.PerTensor(), qb.IN_OUT),
+    (72, 11008, qb.PerChannel(0), qb.OUT_IN), (264, 1024, qb.Group(0, 512), qb.IN_OUT)])
+def test_int4_grids_constant_over_128_column_runs_take_the_1x128_kernels(N, K, gran, layout):
+    """Per-row, per-tensor and wide-tile int4 grids: the handle spells the scales out per 128-column run (the same scale
+    on the same codes), after which the decode kernel, its sliced form and the prefill kernel of the 1 x 128 grid serve the
+    layer.  One-hot activations read single weights back bit for bit against the oracle's dequantize of the stored record."""
+    rng = np.random.default_rng(N + K)
+    r, c = (N, K) if layout == qb.OUT_IN else (K, N)
+    w = (rng.standard_normal((r, c)) * 0.02).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    gr, gc = gran.tile(r, c)
+    m, oc, os_ = quantize_both(w, r, c, qb.QuantDtype.Int4, gran)
+    wd = o.dequantize_host(oc, os_, r, c, 4, gr, gc)
+    ql = qb.QuantizedLinear.new(m, t(bias), layout)
+    plain = qb.QuantizedLinear.new(m, None, layout)
+    decode = "gemv_mma" if K <= 4096 else "gemv_mma_sliced"
+    ks = sorted(set(int(k) for k in rng.integers(0, K, 40)) | {0, 127, 128, K - 1})
+    for rows, kernel in [(ks[:8], decode), (ks[:40], "gemm_tcgen05")]:
+        y = plain.forward(_one_hot_rows(rows, K), out_dtype=torch.float32)
+        assert plain.last_kernel() == kernel, (gran, len(rows))
+        ref = wd[:, rows].T.copy() if layout == qb.OUT_IN else wd[rows, :].copy()
+        assert (bits(y.cpu().numpy()) == bits(ref)).all()
+    for M, kernel, tol in [(1, decode, 1e-4), (16, decode, 1e-4), (50, "gemm_tcgen05", 1e-3)]:
+        xb = o.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
+        xt = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).to(DEV)
+        y = ql.forward(xt, out_dtype=torch.float32)
+        assert ql.last_kernel() == kernel, (gran, M)
+        close(y.cpu().numpy(), o.linear_forward_f64(o.bf16_to_f32(xb), wd, bias, layout, threads=8), tol)
     assert (bits(m.dequantize().cpu().numpy()) == bits(wd)).all()   # the record itself is untouched
     from quanta_b200 import _lib
     assert _lib.load().qb200_qlinear_check(ql._h, None) == 0
