@@ -148,11 +148,16 @@ typedef struct qb200_qlinear qb200_qlinear;
  * outlive the handle.  bias_len is the bias element count (checked against
  * out_dim like check_bias, quant.rs:838-848); pass bias_dev = NULL for none.
  * Where the stored layout does not feed the fast kernels as it is, the handle builds an execution copy here (and
- * synchronises the device once): an int4 `[in, out]` weight with Group{axis: 0, size: 128} (or another multiple of 16 that
- * divides in_dim) is transposed to `[out, in]` with a 1x128 (1 x size) grid, an int4 weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode
- * kernel (so is an int8 weight with tiles 32, 64 or 128 columns wide), and an int8 `[in, out]` weight whose tile height is
- * a multiple of 16 (or the whole input width) is transposed with its scale grid.  Each copy costs its codes again (0.5 or 1 byte per weight) plus its scales (and 16 rows of f32
- * partial outputs per slice); the caller's buffers stay the record. */
+ * synchronises the device once):
+ *   - an `[in, out]` weight whose tile height is a multiple of 16 that divides in_dim, or spans it (int4
+ *     Group{axis: 0, size: 128}, the reference's own orientation; int8 32 x 32 blocks; per-column scales ...) is transposed
+ *     to `[out, in]` together with its scale grid;
+ *   - an int4 grid whose scale is constant over whole 128-column runs (tile widths that are multiples of 128, per-row and
+ *     per-tensor scales) gets its scales spelt out per run, `[out][in / 128]` f32, and is a 1x128 layer from then on;
+ *   - a weight with more than 4096 inputs (up to 32768) is cut into column slices for the decode kernels (int4 1x128;
+ *     int8 with tiles 32, 64 or 128 columns wide).
+ * A copy of codes costs them again (0.5 or 1 byte per weight) plus its scales (and 16 rows of f32 partial outputs per
+ * slice); the caller's buffers stay the record. */
 QB200_API qb200_status qb200_qlinear_create(const void* codes_dev, const float* scales_dev, uint64_t rows,
                                   uint64_t cols, uint32_t bits, uint64_t gr, uint64_t gc,
                                   int32_t layout, const float* bias_dev, uint64_t bias_len,
@@ -168,7 +173,8 @@ QB200_API uint64_t qb200_qlinear_out_dim(const qb200_qlinear* ql);
  * "INTEGRATOR SEAM").  x is `[m, in_dim]` of x_dtype, y is `[m, out_dim]` of
  * y_dtype, both device, row-major.  f32 accumulation.
  * Fast paths (bf16 x): int4 with a 1x128 grid — `[out, in]`, or `[in, out]` with Group{axis: 0, size: 128} through the
- * transposed execution copy made at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
+ * transposed execution copy made at creation; also every int4 grid whose scale is constant over whole 128-column runs
+ * (tile widths that are multiples of 128, per-row and per-tensor scales), spelt out as 1x128 at creation — on the decode GEMV (m <= 16; inputs wider than 4096 as column slices) and
  * the tcgen05 GEMM (m > 16), which also takes the other int4 grids whose tile width along the inputs is a multiple of 16 that
  * divides in_dim or spans it (Group sizes 32, 64, 256 ..., per-row, per-tensor; `[in, out]` with such groups along axis 0
  * through the transposed copy) from m = 9; int8 `[out, in]` with any grid whose tiles are a multiple of 32 columns wide on
