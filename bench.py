@@ -699,23 +699,56 @@ def run_ours(args):
     xh.copy_(x.cpu())
     xd = torch.empty_like(x)
     xdp = (_lib.vp * LAYERS)(*[xd.data_ptr()] * LAYERS)
-    yh = torch.empty(world * LAYERS, m, N_OUT, dtype=torch.float32).pin_memory()
+    # on one GPU every layer's output goes to the host; on N the host reads every output ONCE across the job: each rank
+    # copies out the rows another rank computed (its neighbour's), as they arrived in its own gathered buffer
+    yh = torch.empty(LAYERS, m, N_OUT, dtype=torch.float32).pin_memory()
+    peer = (rank + 1) % world
     xhp = (_lib.vp * LAYERS)(*[xh.data_ptr()] * LAYERS)
     yhp = (_lib.vp * LAYERS)(*[yh[i].data_ptr() for i in range(LAYERS)])
 
+    # the fused step at N > 1 as two CUDA graphs (the exchange alternates between two receive buffers): copy in, forward
+    # with its exchange, copy out — one graph launch and one synchronize per step, the Python wrappers out of the way
+    e2e_graphs = []
+    if world > 1 and fused and not args.no_graph:
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for parity in (0, 1):
+                    xd.copy_(xh, non_blocking=True)
+                    yh.copy_(pg.forward_many(layers, [xd] * LAYERS, parity=parity)[peer], non_blocking=True)
+                torch.cuda.synchronize(dev)
+                for parity in (0, 1):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        xd.copy_(xh, non_blocking=True)
+                        yh.copy_(pg.forward_many(layers, [xd] * LAYERS, parity=parity)[peer], non_blocking=True)
+                    e2e_graphs.append(g)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize(dev)
+        except Exception:
+            e2e_graphs = []
+            torch.cuda.synchronize(dev)
+    e2e_calls = [0]
+
     def step_host():
-        if world > 1:  # copy in, the forward with its exchange, copy the gathered outputs out
+        if world > 1:  # copy in, the forward with its exchange, copy the neighbour's rows of the gathered outputs out
+            if e2e_graphs:
+                e2e_graphs[e2e_calls[0] & 1].replay()
+                e2e_calls[0] += 1
+                torch.cuda.synchronize(dev)
+                return
             cur = torch.cuda.current_stream(dev).cuda_stream
             xd.copy_(xh, non_blocking=True)
             if fused:
                 got = pg.forward_many(layers, [xd] * LAYERS)
-                yh.view(world, LAYERS, m, N_OUT).copy_(got, non_blocking=True)  # (pushed: a strided read of the values)
+                yh.copy_(got[peer], non_blocking=True)  # (pushed: a strided read of the values)
             else:
                 st = lib.qb200_qlinear_forward_many(hs, LAYERS, xdp, _lib.BF16, m, yp, _lib.F32, cur)
                 if st:
                     raise RuntimeError(_lib.last_error())
                 dist.all_gather_into_tensor(y_cat_all, y_cat)
-                yh.copy_(y_cat_all, non_blocking=True)
+                yh.copy_(y_cat_all.view(world, LAYERS, m, N_OUT)[peer], non_blocking=True)
             torch.cuda.synchronize(dev)
             return
         if grouped:  # one call: x copied once, one persistent launch, every layer's y copied back
@@ -781,8 +814,10 @@ def run_ours(args):
                                 else "one NCCL all-gather of the step's outputs" if grouped else "NCCL all-gather per layer")},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": (1 if grouped or world > 1 else LAYERS) * m * K_IN * 2,
-                    "d2h_bytes_per_step": world * LAYERS * m * N_OUT * 4, "steps": e2e_steps,
-                    "call": ("copy in + fused forward / exchange + copy out of the gathered outputs" if world > 1 else
+                    "d2h_bytes_per_step": LAYERS * m * N_OUT * 4, "steps": e2e_steps,
+                    "call": ("per rank: copy in + fused forward / exchange + copy out of the rows its neighbour computed, from its own gathered "
+                             "buffer (the job reads every output once)" + (", one CUDA graph launch and one synchronize per step" if e2e_graphs else "")
+                             if world > 1 else
                              "qb200_qlinear_forward_many_host" if grouped else "qb200_qlinear_forward_host")},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
