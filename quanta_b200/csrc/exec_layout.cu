@@ -1,7 +1,7 @@
 // Execution layouts of a QuantizedLinear handle, built once at creation.
 //
 // The fast int4 kernels read K-contiguous rows: codes `[out, in / 8]` with a 1 x 128 scale grid, at most 4096
-// inputs per launch.  Two stored layouts do not have that shape as they are:
+// inputs per launch.  These stored layouts do not have that shape as they are:
 //   - the reference's own `[in, out]` weight with Group{axis: 0, size: 128} (QuantizedLinear::new takes
 //     `w: [in, out]`, crates/ml/quanta-nn/src/quant.rs:853-862): the nibbles run along `out`.  A transposed copy
 //     of codes and scales is a pure permutation — every dequantized weight s * q keeps its bits;
@@ -12,6 +12,9 @@
 //     each reads its window of the activations in place — and a fold of their f32 partial outputs.
 // Both are copies (+ 0.5 byte per weight each, + the scales): the stored buffers stay what accessors, writers
 // and the tcgen05 GEMM's tensor maps over `[out, in]` codes see.
+//   - a third int4 copy is scales only: a grid whose scale is constant over whole 128-column runs (tile widths that
+//     are multiples of 128, per-row and per-tensor scales, after the transposition where there is one) is spelt out
+//     per run as `[out][in / 128]`, after which the layer IS a 1 x 128 layer for every kernel.
 //
 // The int8 kernels read `[out, in]` bytes with a grid whose tile width is a whole number of 16-column steps: an
 // `[in, out]` int8 weight whose tile HEIGHT is such a number (32 x 32 blocks, Group{axis: 0, size: 128}, per-column
